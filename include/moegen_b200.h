@@ -1,0 +1,225 @@
+/*
+ * moegen_b200 — C ABI of the B200 (sm_100a) MoE-layer library.
+ *
+ * This is the boundary that replaces, for the MoE layer only, what the
+ * reference reaches through its op_builder-compiled pybind module
+ * (core/MoE_Gen_Binding.cpp:44-87: get_weights / free_weights_buffer /
+ * clear_expert_buffer) plus the PyTorch arithmetic of
+ * moe_gen/models/deepseek/deepseekv2/modeling_deepseek_v2.py (MoEGate,
+ * DeepseekV2MoE) and .../deepseekv3/modeling_deepseek_v3.py (MoEGate,
+ * DeepseekV3MoE) and of transformers' MixtralSparseMoeBlock.
+ *
+ * Conventions
+ *  - plain C symbols, no torch / pybind types; every pointer named d_* is a
+ *    raw DEVICE address on the device the handle was created on, `stream` is a
+ *    cudaStream_t passed as void*;
+ *  - every call returns an int: 0 = OK, negative = argument / shape / state
+ *    error detected on the host before any launch, positive = CUDA runtime or
+ *    driver error (cudaError_t value).  Nothing throws, exits or traps.
+ *    mg_last_error() returns a text for the last non-zero return on the calling
+ *    thread.  Problems found on the device (a bounded wait that ran out) are
+ *    written to a status word that mg_device_status() reads after the caller
+ *    has synchronised the stream;
+ *  - calls are asynchronous on `stream`; the caller owns all memory (inputs,
+ *    outputs, workspace, packed weights).  The library owns only the handle;
+ *  - one handle is bound to one device and used by one thread at a time.
+ */
+#ifndef MOEGEN_B200_H
+#define MOEGEN_B200_H
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+/* gating modes */
+#define MG_GATE_SOFTMAX_GREEDY      0  /* modeling_deepseek_v2.py:493-504  */
+#define MG_GATE_SOFTMAX_GROUP_MAX   1  /* modeling_deepseek_v2.py:505-526  */
+#define MG_GATE_SIGMOID_NOAUX_TC    2  /* modeling_deepseek_v3.py:509-547  */
+#define MG_GATE_SOFTMAX_TOPK_RENORM 3  /* MixtralSparseMoeBlock router     */
+
+/* combine modes */
+#define MG_COMBINE_FP32       0  /* modeling_deepseek_v3.py:702-710: fp32 products, fp32 sum */
+#define MG_COMBINE_BF16_PROD  1  /* modeling_deepseek_v2.py:744-757: bf16 weight, bf16 products */
+#define MG_COMBINE_BF16_SEQ   2  /* Mixtral: bf16 products added one by one, experts ascending */
+
+/* expert weight formats */
+#define MG_WEIGHT_BF16          0
+#define MG_WEIGHT_FP8_BLOCK128  1  /* e4m3 + fp32 scale per 128x128 block (Wrapper.py:109-138) */
+
+/* error codes (negative: host-side argument/state errors) */
+#define MG_OK                 0
+#define MG_ERR_NULL          -1
+#define MG_ERR_SHAPE         -2  /* unsupported or inconsistent shape */
+#define MG_ERR_CONFIG        -3  /* unsupported combination in mg_layer_desc */
+#define MG_ERR_WORKSPACE     -4  /* workspace too small */
+#define MG_ERR_STATE         -5  /* handle not usable (wrong device, destroyed) */
+#define MG_ERR_DRIVER        -6  /* CUDA driver entry point unavailable */
+#define MG_ERR_LIMIT         -7  /* size beyond a documented maximum */
+
+/* device status word values (mg_device_status) */
+#define MG_DEV_OK             0
+#define MG_DEV_WAIT_TIMEOUT   1  /* a bounded mbarrier wait ran out; results invalid */
+
+typedef struct mg_layer_desc {
+  int32_t struct_bytes;    /* = sizeof(mg_layer_desc), for versioning */
+  int32_t hidden;          /* H:  config.hidden_size */
+  int32_t inter;           /* I:  config.moe_intermediate_size (Mixtral: intermediate_size) */
+  int32_t inter_shared;    /* I_s = n_shared_experts * I, 0 = no shared expert */
+  int32_t n_experts;       /* E:  config.n_routed_experts (global) */
+  int32_t top_k;           /* k:  config.num_experts_per_tok */
+  int32_t n_group;         /* config.n_group   (1 when ungrouped) */
+  int32_t topk_group;      /* config.topk_group */
+  int32_t gating;          /* MG_GATE_* */
+  int32_t norm_topk_prob;  /* config.norm_topk_prob */
+  float   routed_scale;    /* config.routed_scaling_factor */
+  int32_t weight_format;   /* MG_WEIGHT_* */
+  int32_t combine_mode;    /* MG_COMBINE_* */
+  int32_t ep_rank;         /* this rank owns experts [ep_rank*E/ep_size, (ep_rank+1)*E/ep_size) */
+  int32_t ep_size;         /* (modeling_deepseek_v3.py:586-587) */
+} mg_layer_desc;
+
+typedef struct mg_handle_s* mg_handle;
+
+/* ---- handle ------------------------------------------------------------- */
+
+/* Validates the description and binds a handle to the current CUDA device.
+ * Replaces: the config reads of DeepseekV3MoE.__init__ / MoEGate.__init__
+ * (modeling_deepseek_v3.py:470-492,564-611). */
+int mg_create(const mg_layer_desc* desc, mg_handle* out);
+int mg_destroy(mg_handle h);
+
+/* Text of the last error returned on this thread ("" if none). */
+const char* mg_last_error(void);
+
+/* Reads (and clears) the device status word; the caller must have synchronised
+ * the streams it used.  *code gets MG_DEV_*; *detail a kernel-specific value. */
+int mg_device_status(mg_handle h, int32_t* code, int32_t* detail);
+
+/* ---- sizes -------------------------------------------------------------- */
+
+/* Bytes of the packed weight buffer for the experts this rank owns (+ shared
+ * expert).  Replaces the per-expert slots of GPU_Weight_Buffer
+ * (core/GPU_Weight_Buffer/GPU_Weight_Buffer.cpp:64-101). */
+int mg_packed_weight_bytes(mg_handle h, size_t* bytes);
+
+/* Bytes of workspace mg_moe_forward needs for up to max_tokens local tokens and
+ * up to max_rows rows routed to this rank's experts (max_rows = 0 means
+ * max_tokens * top_k, the single-GPU bound). */
+int mg_workspace_bytes(mg_handle h, int64_t max_tokens, int64_t max_rows, size_t* bytes);
+
+/* Rows of the expert-sorted buffers for n_rows routed rows: every expert's
+ * segment starts on a 128-row boundary, so up to 127 pad rows per expert. */
+int mg_padded_rows(mg_handle h, int64_t n_rows, int64_t* padded);
+
+/* ---- weights ------------------------------------------------------------ */
+
+/* Copies one expert's three matrices ([I,H] gate_proj, [I,H] up_proj, [H,I]
+ * down_proj, row-major, as nn.Linear stores them: modeling_deepseek_v3.py:439-467;
+ * Mixtral: w1, w3, w2) into the packed buffer.  local_expert in [0, E/ep_size),
+ * or -1 for the shared expert ([I_s,H],[I_s,H],[H,I_s]).  For
+ * MG_WEIGHT_FP8_BLOCK128 the matrices are e4m3 bytes and d_*_scale are the fp32
+ * [ceil(rows/128), ceil(cols/128)] weight_scale_inv tensors; for MG_WEIGHT_BF16
+ * the scale pointers are ignored.  The shared expert is always bf16.
+ * Replaces HtoD copy into a slot + Expert_Wrapper's per-call parameter binding
+ * (moe_gen/models/Wrapper.py:470-491). */
+int mg_pack_expert(mg_handle h, int32_t local_expert,
+                   const void* d_gate, const void* d_up, const void* d_down,
+                   const float* d_gate_scale, const float* d_up_scale, const float* d_down_scale,
+                   void* d_packed, void* stream);
+
+/* De-quantises an e4m3 [rows,cols] matrix with 128x128 block scales to bf16:
+ * bf16(float(q) * scale[r/128][c/128]).  Replaces deepseek_v3_dequantization
+ * (moe_gen/models/Wrapper.py:109-138). */
+int mg_dequant_fp8_block128(const void* d_q, const float* d_scale_inv, int64_t rows, int64_t cols,
+                            void* d_out_bf16, void* stream);
+
+/* ---- stages ------------------------------------------------------------- */
+
+/* logits[T,E] (fp32) = x[T,H] (bf16) . gate_w[E,H]^T (bf16), fp32 accumulation
+ * on the tensor cores.  For MG_GATE_SOFTMAX_TOPK_RENORM the logits are rounded to
+ * bf16 (the Mixtral router is a bf16 nn.Linear) and stored widened to fp32.
+ * Replaces F.linear(x.float(), W.float()) (modeling_deepseek_v3.py:503-508). */
+int mg_gate_logits(mg_handle h, const void* d_x, const void* d_gate_w, int64_t n_tokens,
+                   float* d_logits, void* stream);
+
+/* Scoring + top-k from fp32 logits: topk_idx[T,k] (int32, global expert ids,
+ * slot order = selection score descending, equal scores -> lower id) and
+ * topk_w[T,k] (fp32).  d_bias[E] (fp32) only for MG_GATE_SIGMOID_NOAUX_TC.
+ * Replaces MoEGate.forward after the logits (modeling_deepseek_v2.py:493-533,
+ * modeling_deepseek_v3.py:509-561). */
+int mg_route_topk(mg_handle h, const float* d_logits, const float* d_bias, int64_t n_tokens,
+                  int32_t* d_topk_idx, float* d_topk_w, void* stream);
+
+/* Histogram + prefix sums + stable placement over experts [expert_lo,
+ * expert_lo + n_plan_experts): picks outside that range are skipped (dst_row=-1).
+ *   counts[n]        rows per expert
+ *   offsets[n+1]     exclusive scan of counts (the reference's row order)
+ *   pad_offsets[n+1] the same with every expert starting on a 128-row boundary
+ *   dst_row[T*k]     row of (token, slot) in the padded expert-sorted buffers;
+ *                    tokens ascend inside an expert (stable sort)
+ * d_plan_ws: scratch of mg_plan_ws_bytes() bytes.
+ * Replaces cnts.scatter_/sum, argsort (modeling_deepseek_v3.py:630-635). */
+int mg_plan_ws_bytes(mg_handle h, int64_t n_tokens, size_t* bytes);
+int mg_permute_plan(mg_handle h, const int32_t* d_topk_idx, int64_t n_tokens,
+                    int32_t expert_lo, int32_t n_plan_experts,
+                    int32_t* d_counts, int32_t* d_offsets, int32_t* d_pad_offsets,
+                    int32_t* d_dst_row, void* d_plan_ws, void* stream);
+
+/* perm_x[dst_row[t*k+j], :] = x[t, :] for every pick with dst_row >= 0.
+ * Replaces sorted_tokens = x[idxs // k] (modeling_deepseek_v3.py:634). */
+int mg_permute_rows(mg_handle h, const void* d_x, const int32_t* d_dst_row, int64_t n_tokens,
+                    void* d_perm_x, void* stream);
+
+/* Grouped SwiGLU experts over the padded expert-sorted rows:
+ *   h_buf[r, :]   = silu(perm_x[r] . Wg_e^T) * (perm_x[r] . Wu_e^T)   (bf16)
+ *   out_rows[r,:] = h_buf[r] . Wd_e^T                                  (bf16)
+ * for r in [pad_offsets[e], pad_offsets[e]+counts[e]).  n_rows_padded bounds the
+ * buffers (rows of perm_x / h_buf / out_rows).  For FP8 layers d_dequant_ws is a
+ * bf16 scratch of mg_dequant_ws_bytes() bytes.
+ * Replaces the expert loop (modeling_deepseek_v3.py:675-691) and
+ * DeepseekV3MLP.forward (modeling_deepseek_v3.py:463-467). */
+int mg_dequant_ws_bytes(mg_handle h, size_t* bytes);
+int mg_expert_ffn(mg_handle h, const void* d_perm_x, const int32_t* d_pad_offsets,
+                  const int32_t* d_counts, int64_t n_rows_padded, const void* d_packed,
+                  void* d_h_buf, void* d_out_rows, void* d_dequant_ws, void* stream);
+
+/* Shared expert on the un-permuted tokens: shared_out = MLP_shared(x).
+ * hs_buf: [T, I_s] bf16 scratch.  Replaces self.shared_experts(identity)
+ * (modeling_deepseek_v3.py:624-625). */
+int mg_shared_ffn(mg_handle h, const void* d_x, int64_t n_tokens, const void* d_packed,
+                  void* d_hs_buf, void* d_shared_out, void* stream);
+
+/* y[t] = sum_j topk_w[t,j] * out_rows[dst_row[t*k+j]]  (+ shared_out[t] when
+ * d_shared_out != NULL), arithmetic per combine_mode.  Picks with dst_row < 0
+ * contribute nothing.  Replaces new_x[idxs] = outs and the weighted sum
+ * (modeling_deepseek_v3.py:702-711) and y + shared (…:624-625). */
+int mg_combine(mg_handle h, const void* d_out_rows, const int32_t* d_dst_row,
+               const int32_t* d_topk_idx, const float* d_topk_w, const void* d_shared_out,
+               int64_t n_tokens, void* d_y, void* stream);
+
+/* ---- whole layer on one GPU (ep_size == 1) ------------------------------- */
+
+/* y[T,H] = MoE(x[T,H]); bf16 in and out.  d_bias may be NULL unless the gating
+ * needs it.  No host synchronisation.  Replaces DeepseekV3MoE.forward /
+ * DeepseekV2MoE.forward / MixtralSparseMoeBlock.forward
+ * (modeling_deepseek_v3.py:614-626, modeling_deepseek_v2.py:642-668). */
+int mg_moe_forward(mg_handle h, const void* d_x, int64_t n_tokens,
+                   const void* d_gate_w, const float* d_bias, const void* d_packed,
+                   void* d_workspace, size_t workspace_bytes, void* d_y, void* stream);
+
+/* Pointers into a workspace laid out by mg_moe_forward, for tests and tools:
+ * which = 0 logits, 1 topk_idx, 2 topk_w, 3 counts, 4 offsets, 5 pad_offsets,
+ * 6 dst_row, 7 perm_x, 8 h_buf, 9 out_rows. */
+int mg_workspace_ptr(mg_handle h, void* d_workspace, int64_t max_tokens, int64_t max_rows,
+                     int32_t which, void** ptr);
+
+/* Number of kernel launches the last mg_moe_forward on this handle issued. */
+int mg_last_launch_count(mg_handle h, int32_t* launches);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* MOEGEN_B200_H */

@@ -1,0 +1,396 @@
+// extern "C" surface: handle, sizes, stage entry points and the whole-layer forward.
+#include <stdarg.h>
+#include <string.h>
+
+#include <new>
+
+#include "common.cuh"
+
+namespace mg {
+
+static thread_local char g_err[512] = "";
+
+void set_error(const char* fmt, ...) {
+  va_list ap;
+  va_start(ap, fmt);
+  vsnprintf(g_err, sizeof(g_err), fmt, ap);
+  va_end(ap);
+}
+
+int cuda_fail(cudaError_t e, const char* what) {
+  set_error("CUDA error %d (%s) in %s", static_cast<int>(e), cudaGetErrorString(e), what);
+  return static_cast<int>(e);
+}
+
+static Handle* check(mg_handle hh) {
+  Handle* h = reinterpret_cast<Handle*>(hh);
+  if (h == nullptr || h->magic != kMagic) { set_error("invalid handle"); return nullptr; }
+  return h;
+}
+
+static int64_t padded_rows(const Handle* h, int64_t rows) {
+  return ((rows + kTileM - 1) / kTileM + h->e_local) * kTileM;
+}
+
+// workspace carving ---------------------------------------------------------------------
+enum { WS_LOGITS, WS_IDX, WS_W, WS_COUNTS, WS_OFFSETS, WS_PAD, WS_DST, WS_PERM, WS_H, WS_OUT, WS_PLAN,
+       WS_HS, WS_SHARED, WS_DEQ, WS_N };
+struct WsLayout { size_t off[WS_N]; size_t total; };
+
+static size_t dequant_ws(const Handle* h) {
+  if (h->d.weight_format != MG_WEIGHT_FP8_BLOCK128) return 0;
+  return static_cast<size_t>(h->e_local) * 3 * h->d.inter * h->d.hidden * 2;
+}
+
+static WsLayout ws_layout(const Handle* h, int64_t T, int64_t R) {
+  const mg_layer_desc& d = h->d;
+  if (R <= 0) R = T * d.top_k;
+  const size_t Rp = static_cast<size_t>(padded_rows(h, R));
+  WsLayout L;
+  size_t off = 0;
+  auto take = [&](int which, size_t bytes) { L.off[which] = off; off += (bytes + 255) / 256 * 256; };
+  take(WS_LOGITS, static_cast<size_t>(T) * d.n_experts * 4);
+  take(WS_IDX, static_cast<size_t>(T) * d.top_k * 4);
+  take(WS_W, static_cast<size_t>(T) * d.top_k * 4);
+  take(WS_COUNTS, static_cast<size_t>(d.n_experts) * 4);
+  take(WS_OFFSETS, static_cast<size_t>(d.n_experts + 1) * 4);
+  take(WS_PAD, static_cast<size_t>(d.n_experts + 1) * 4);
+  take(WS_DST, static_cast<size_t>(T) * d.top_k * 4);
+  take(WS_PERM, Rp * d.hidden * 2);
+  take(WS_H, Rp * d.inter * 2);
+  take(WS_OUT, Rp * d.hidden * 2);
+  take(WS_PLAN, plan_ws_bytes(h, T));
+  take(WS_HS, static_cast<size_t>(T) * d.inter_shared * 2);
+  take(WS_SHARED, d.inter_shared ? static_cast<size_t>(T) * d.hidden * 2 : 0);
+  take(WS_DEQ, dequant_ws(h));
+  L.total = off;
+  return L;
+}
+
+}  // namespace mg
+
+using namespace mg;
+
+extern "C" {
+
+const char* mg_last_error(void) { return g_err; }
+
+int mg_create(const mg_layer_desc* desc, mg_handle* out) {
+  MG_REQUIRE(desc && out, MG_ERR_NULL, "mg_create: null argument");
+  MG_REQUIRE(desc->struct_bytes == static_cast<int32_t>(sizeof(mg_layer_desc)), MG_ERR_CONFIG,
+             "mg_layer_desc.struct_bytes=%d, library expects %d", desc->struct_bytes,
+             static_cast<int>(sizeof(mg_layer_desc)));
+  const mg_layer_desc& d = *desc;
+  MG_REQUIRE(d.hidden > 0 && d.hidden % 256 == 0, MG_ERR_SHAPE, "hidden=%d must be a positive multiple of 256", d.hidden);
+  MG_REQUIRE(d.inter > 0 && d.inter % 128 == 0, MG_ERR_SHAPE, "inter=%d must be a positive multiple of 128", d.inter);
+  MG_REQUIRE(d.inter_shared >= 0 && d.inter_shared % 128 == 0, MG_ERR_SHAPE,
+             "inter_shared=%d must be a multiple of 128", d.inter_shared);
+  MG_REQUIRE(d.n_experts >= 1 && d.n_experts <= kMaxExperts && d.n_experts % 4 == 0, MG_ERR_SHAPE,
+             "n_experts=%d must be a multiple of 4 in [4,%d]", d.n_experts, kMaxExperts);
+  MG_REQUIRE(d.top_k >= 1 && d.top_k <= kMaxTopK && d.top_k <= d.n_experts, MG_ERR_SHAPE,
+             "top_k=%d must be in [1,min(%d,n_experts)]", d.top_k, kMaxTopK);
+  MG_REQUIRE(d.gating >= 0 && d.gating <= 3, MG_ERR_CONFIG, "unknown gating mode %d", d.gating);
+  MG_REQUIRE(d.combine_mode >= 0 && d.combine_mode <= 2, MG_ERR_CONFIG, "unknown combine mode %d", d.combine_mode);
+  MG_REQUIRE(d.weight_format == MG_WEIGHT_BF16 || d.weight_format == MG_WEIGHT_FP8_BLOCK128, MG_ERR_CONFIG,
+             "unknown weight format %d", d.weight_format);
+  if (d.gating == MG_GATE_SOFTMAX_GROUP_MAX || d.gating == MG_GATE_SIGMOID_NOAUX_TC) {
+    MG_REQUIRE(d.n_group >= 1 && d.n_group <= 32 && d.n_experts % d.n_group == 0, MG_ERR_CONFIG,
+               "n_group=%d must divide n_experts and be <= 32", d.n_group);
+    MG_REQUIRE(d.topk_group >= 1 && d.topk_group <= d.n_group, MG_ERR_CONFIG, "topk_group=%d must be in [1,n_group]",
+               d.topk_group);
+    MG_REQUIRE(d.n_experts / d.n_group >= (d.gating == MG_GATE_SIGMOID_NOAUX_TC ? 2 : 1), MG_ERR_CONFIG,
+               "groups too small for the group score");
+  }
+  MG_REQUIRE(d.ep_size >= 1 && d.ep_rank >= 0 && d.ep_rank < d.ep_size && d.n_experts % d.ep_size == 0, MG_ERR_CONFIG,
+             "ep_rank=%d / ep_size=%d invalid for %d experts", d.ep_rank, d.ep_size, d.n_experts);
+  Handle* h = new (std::nothrow) Handle();
+  MG_REQUIRE(h != nullptr, MG_ERR_STATE, "out of host memory");
+  h->magic = kMagic;
+  h->d = d;
+  h->e_local = d.n_experts / d.ep_size;
+  h->last_launches = 0;
+  cudaError_t e = cudaGetDevice(&h->device);
+  if (e == cudaSuccess) e = cudaDeviceGetAttribute(&h->sm_count, cudaDevAttrMultiProcessorCount, h->device);
+  int major = 0;
+  if (e == cudaSuccess) e = cudaDeviceGetAttribute(&major, cudaDevAttrComputeCapabilityMajor, h->device);
+  if (e == cudaSuccess && major != 10) {
+    delete h;
+    set_error("device compute capability %d.x: this library contains sm_100a code only", major);
+    return MG_ERR_STATE;
+  }
+  if (e == cudaSuccess) e = cudaMalloc(&h->d_status, 2 * sizeof(int32_t));
+  if (e == cudaSuccess) e = cudaMemset(h->d_status, 0, 2 * sizeof(int32_t));
+  if (e != cudaSuccess) { delete h; return cuda_fail(e, "mg_create"); }
+  *out = reinterpret_cast<mg_handle>(h);
+  return MG_OK;
+}
+
+int mg_destroy(mg_handle hh) {
+  Handle* h = check(hh);
+  if (!h) return MG_ERR_STATE;
+  cudaFree(h->d_status);
+  h->magic = 0;
+  delete h;
+  return MG_OK;
+}
+
+int mg_device_status(mg_handle hh, int32_t* code, int32_t* detail) {
+  Handle* h = check(hh);
+  if (!h) return MG_ERR_STATE;
+  int32_t v[2] = {0, 0};
+  MG_CUDA(cudaMemcpy(v, h->d_status, sizeof(v), cudaMemcpyDeviceToHost));
+  if (v[0] != 0) MG_CUDA(cudaMemset(h->d_status, 0, sizeof(v)));
+  if (code) *code = v[0];
+  if (detail) *detail = v[1];
+  return MG_OK;
+}
+
+int mg_packed_weight_bytes(mg_handle hh, size_t* bytes) {
+  Handle* h = check(hh);
+  if (!h) return MG_ERR_STATE;
+  MG_REQUIRE(bytes, MG_ERR_NULL, "null argument");
+  *bytes = packed_layout(h).total;
+  return MG_OK;
+}
+
+int mg_workspace_bytes(mg_handle hh, int64_t max_tokens, int64_t max_rows, size_t* bytes) {
+  Handle* h = check(hh);
+  if (!h) return MG_ERR_STATE;
+  MG_REQUIRE(bytes, MG_ERR_NULL, "null argument");
+  MG_REQUIRE(max_tokens >= 0 && max_rows >= 0, MG_ERR_SHAPE, "negative size");
+  MG_REQUIRE(max_tokens * h->d.top_k < (1ll << 31) - 65536, MG_ERR_LIMIT, "tokens*top_k exceeds 32-bit row indices");
+  *bytes = ws_layout(h, max_tokens, max_rows).total;
+  return MG_OK;
+}
+
+int mg_padded_rows(mg_handle hh, int64_t n_rows, int64_t* padded) {
+  Handle* h = check(hh);
+  if (!h) return MG_ERR_STATE;
+  MG_REQUIRE(padded, MG_ERR_NULL, "null argument");
+  *padded = padded_rows(h, n_rows);
+  return MG_OK;
+}
+
+int mg_pack_expert(mg_handle hh, int32_t local_expert, const void* d_gate, const void* d_up, const void* d_down,
+                   const float* gs, const float* us, const float* ds, void* d_packed, void* stream) {
+  Handle* h = check(hh);
+  if (!h) return MG_ERR_STATE;
+  MG_REQUIRE(d_gate && d_up && d_down && d_packed, MG_ERR_NULL, "mg_pack_expert: null pointer");
+  return launch_pack_expert(h, local_expert, d_gate, d_up, d_down, gs, us, ds, d_packed,
+                            static_cast<cudaStream_t>(stream));
+}
+
+int mg_dequant_fp8_block128(const void* d_q, const float* d_scale_inv, int64_t rows, int64_t cols, void* d_out,
+                            void* stream) {
+  MG_REQUIRE(d_q && d_scale_inv && d_out, MG_ERR_NULL, "mg_dequant_fp8_block128: null pointer");
+  MG_REQUIRE(rows >= 0 && cols >= 0, MG_ERR_SHAPE, "negative size");
+  return launch_dequant(d_q, d_scale_inv, rows, cols, d_out, static_cast<cudaStream_t>(stream));
+}
+
+int mg_gate_logits(mg_handle hh, const void* d_x, const void* d_gate_w, int64_t T, float* d_logits, void* stream) {
+  Handle* h = check(hh);
+  if (!h) return MG_ERR_STATE;
+  MG_REQUIRE(d_x && d_gate_w && d_logits, MG_ERR_NULL, "mg_gate_logits: null pointer");
+  MG_REQUIRE(T >= 0, MG_ERR_SHAPE, "negative token count");
+  MG_REQUIRE(h->d.n_experts <= 256, MG_ERR_SHAPE, "router GEMM supports at most 256 experts");
+  GemmProblem p{};
+  p.a = d_x; p.a_rows = T; p.b = d_gate_w; p.n_groups = 1; p.n_per_group = h->d.n_experts; p.K = h->d.hidden;
+  p.pad_offsets = nullptr; p.counts = nullptr; p.dense_rows = T; p.out = d_logits; p.ldo = h->d.n_experts;
+  p.epilogue = h->d.gating == MG_GATE_SOFTMAX_TOPK_RENORM ? EPI_ROUND_BF16_F32 : EPI_PLAIN_F32;
+  return launch_grouped_gemm(h, p, static_cast<cudaStream_t>(stream));
+}
+
+int mg_route_topk(mg_handle hh, const float* d_logits, const float* d_bias, int64_t T, int32_t* d_idx, float* d_w,
+                  void* stream) {
+  Handle* h = check(hh);
+  if (!h) return MG_ERR_STATE;
+  MG_REQUIRE(d_logits && d_idx && d_w, MG_ERR_NULL, "mg_route_topk: null pointer");
+  MG_REQUIRE(h->d.gating != MG_GATE_SIGMOID_NOAUX_TC || d_bias != nullptr, MG_ERR_NULL,
+             "noaux_tc gating needs e_score_correction_bias");
+  MG_REQUIRE(T >= 0, MG_ERR_SHAPE, "negative token count");
+  return launch_route_topk(h, d_logits, d_bias, T, d_idx, d_w, static_cast<cudaStream_t>(stream));
+}
+
+int mg_plan_ws_bytes(mg_handle hh, int64_t T, size_t* bytes) {
+  Handle* h = check(hh);
+  if (!h) return MG_ERR_STATE;
+  MG_REQUIRE(bytes, MG_ERR_NULL, "null argument");
+  *bytes = plan_ws_bytes(h, T);
+  return MG_OK;
+}
+
+int mg_permute_plan(mg_handle hh, const int32_t* d_idx, int64_t T, int32_t expert_lo, int32_t n_plan,
+                    int32_t* d_counts, int32_t* d_offsets, int32_t* d_pad, int32_t* d_dst, void* d_ws, void* stream) {
+  Handle* h = check(hh);
+  if (!h) return MG_ERR_STATE;
+  MG_REQUIRE(d_idx && d_counts && d_offsets && d_pad && d_dst && d_ws, MG_ERR_NULL, "mg_permute_plan: null pointer");
+  MG_REQUIRE(T >= 0 && expert_lo >= 0 && n_plan >= 1 && expert_lo + n_plan <= h->d.n_experts, MG_ERR_SHAPE,
+             "expert range [%d,%d) outside [0,%d)", expert_lo, expert_lo + n_plan, h->d.n_experts);
+  return launch_permute_plan(h, d_idx, T, expert_lo, n_plan, d_counts, d_offsets, d_pad, d_dst, d_ws,
+                             static_cast<cudaStream_t>(stream), nullptr);
+}
+
+int mg_permute_rows(mg_handle hh, const void* d_x, const int32_t* d_dst, int64_t T, void* d_perm, void* stream) {
+  Handle* h = check(hh);
+  if (!h) return MG_ERR_STATE;
+  MG_REQUIRE(d_x && d_dst && d_perm, MG_ERR_NULL, "mg_permute_rows: null pointer");
+  MG_REQUIRE(T >= 0, MG_ERR_SHAPE, "negative token count");
+  return launch_permute_rows(h, d_x, d_dst, T, d_perm, static_cast<cudaStream_t>(stream));
+}
+
+int mg_dequant_ws_bytes(mg_handle hh, size_t* bytes) {
+  Handle* h = check(hh);
+  if (!h) return MG_ERR_STATE;
+  MG_REQUIRE(bytes, MG_ERR_NULL, "null argument");
+  *bytes = dequant_ws(h);
+  return MG_OK;
+}
+
+static int expert_ffn(Handle* h, const void* perm_x, const int32_t* pad, const int32_t* counts, int64_t rows_padded,
+                      const void* packed, void* h_buf, void* out_rows, void* deq, cudaStream_t st, int* launches) {
+  const mg_layer_desc& d = h->d;
+  const PackedLayout L = packed_layout(h);
+  const uint8_t* base = static_cast<const uint8_t*>(packed);
+  const void* w13 = base + L.w13;
+  const void* w2 = base + L.w2;
+  if (d.weight_format == MG_WEIGHT_FP8_BLOCK128) {
+    MG_REQUIRE(deq != nullptr, MG_ERR_NULL, "FP8 layer needs the de-quantisation scratch");
+    int rc = launch_dequant_packed(h, packed, deq, st);
+    if (rc != MG_OK) return rc;
+    w13 = deq;
+    w2 = static_cast<const __nv_bfloat16*>(deq) + static_cast<size_t>(h->e_local) * 2 * d.inter * d.hidden;
+    if (launches) *launches += 2;
+  }
+  GemmProblem p{};
+  p.a = perm_x; p.a_rows = rows_padded; p.b = w13; p.n_groups = h->e_local; p.n_per_group = 2 * d.inter;
+  p.K = d.hidden; p.pad_offsets = pad; p.counts = counts; p.out = h_buf; p.ldo = d.inter;
+  p.epilogue = EPI_SWIGLU_BF16;
+  int rc = launch_grouped_gemm(h, p, st);
+  if (rc != MG_OK) return rc;
+  p.a = h_buf; p.b = w2; p.n_per_group = d.hidden; p.K = d.inter; p.out = out_rows; p.ldo = d.hidden;
+  p.epilogue = EPI_PLAIN_BF16;
+  rc = launch_grouped_gemm(h, p, st);
+  if (launches) *launches += 2;
+  return rc;
+}
+
+int mg_expert_ffn(mg_handle hh, const void* d_perm_x, const int32_t* d_pad, const int32_t* d_counts,
+                  int64_t n_rows_padded, const void* d_packed, void* d_h_buf, void* d_out_rows, void* d_deq,
+                  void* stream) {
+  Handle* h = check(hh);
+  if (!h) return MG_ERR_STATE;
+  MG_REQUIRE(d_perm_x && d_pad && d_counts && d_packed && d_h_buf && d_out_rows, MG_ERR_NULL,
+             "mg_expert_ffn: null pointer");
+  MG_REQUIRE(n_rows_padded >= 0 && n_rows_padded % kTileM == 0, MG_ERR_SHAPE,
+             "n_rows_padded=%lld must be a multiple of %d", static_cast<long long>(n_rows_padded), kTileM);
+  return expert_ffn(h, d_perm_x, d_pad, d_counts, n_rows_padded, d_packed, d_h_buf, d_out_rows, d_deq,
+                    static_cast<cudaStream_t>(stream), nullptr);
+}
+
+static int shared_ffn(Handle* h, const void* x, int64_t T, const void* packed, void* hs, void* out, cudaStream_t st) {
+  const mg_layer_desc& d = h->d;
+  MG_REQUIRE(d.inter_shared > 0, MG_ERR_CONFIG, "layer has no shared expert");
+  const PackedLayout L = packed_layout(h);
+  const uint8_t* base = static_cast<const uint8_t*>(packed);
+  GemmProblem p{};
+  p.a = x; p.a_rows = T; p.b = base + L.sh13; p.n_groups = 1; p.n_per_group = 2 * d.inter_shared; p.K = d.hidden;
+  p.dense_rows = T; p.out = hs; p.ldo = d.inter_shared; p.epilogue = EPI_SWIGLU_BF16;
+  int rc = launch_grouped_gemm(h, p, st);
+  if (rc != MG_OK) return rc;
+  p.a = hs; p.b = base + L.sh2; p.n_per_group = d.hidden; p.K = d.inter_shared; p.out = out; p.ldo = d.hidden;
+  p.epilogue = EPI_PLAIN_BF16;
+  return launch_grouped_gemm(h, p, st);
+}
+
+int mg_shared_ffn(mg_handle hh, const void* d_x, int64_t T, const void* d_packed, void* d_hs, void* d_out,
+                  void* stream) {
+  Handle* h = check(hh);
+  if (!h) return MG_ERR_STATE;
+  MG_REQUIRE(d_x && d_packed && d_hs && d_out, MG_ERR_NULL, "mg_shared_ffn: null pointer");
+  MG_REQUIRE(T >= 0, MG_ERR_SHAPE, "negative token count");
+  return shared_ffn(h, d_x, T, d_packed, d_hs, d_out, static_cast<cudaStream_t>(stream));
+}
+
+int mg_combine(mg_handle hh, const void* d_out_rows, const int32_t* d_dst, const int32_t* d_idx, const float* d_w,
+               const void* d_shared, int64_t T, void* d_y, void* stream) {
+  Handle* h = check(hh);
+  if (!h) return MG_ERR_STATE;
+  MG_REQUIRE(d_out_rows && d_dst && d_idx && d_w && d_y, MG_ERR_NULL, "mg_combine: null pointer");
+  MG_REQUIRE(T >= 0, MG_ERR_SHAPE, "negative token count");
+  return launch_combine(h, d_out_rows, d_dst, d_idx, d_w, d_shared, T, d_y, static_cast<cudaStream_t>(stream));
+}
+
+int mg_workspace_ptr(mg_handle hh, void* d_ws, int64_t max_tokens, int64_t max_rows, int32_t which, void** ptr) {
+  Handle* h = check(hh);
+  if (!h) return MG_ERR_STATE;
+  MG_REQUIRE(d_ws && ptr, MG_ERR_NULL, "null argument");
+  MG_REQUIRE(which >= 0 && which < WS_N, MG_ERR_SHAPE, "which=%d out of range", which);
+  *ptr = static_cast<uint8_t*>(d_ws) + ws_layout(h, max_tokens, max_rows).off[which];
+  return MG_OK;
+}
+
+int mg_moe_forward(mg_handle hh, const void* d_x, int64_t T, const void* d_gate_w, const float* d_bias,
+                   const void* d_packed, void* d_ws, size_t ws_bytes, void* d_y, void* stream) {
+  Handle* h = check(hh);
+  if (!h) return MG_ERR_STATE;
+  MG_REQUIRE(d_x && d_gate_w && d_packed && d_ws && d_y, MG_ERR_NULL, "mg_moe_forward: null pointer");
+  MG_REQUIRE(T >= 0, MG_ERR_SHAPE, "negative token count");
+  MG_REQUIRE(h->d.ep_size == 1, MG_ERR_CONFIG, "mg_moe_forward is the single-GPU path (ep_size == 1)");
+  MG_REQUIRE(h->d.gating != MG_GATE_SIGMOID_NOAUX_TC || d_bias != nullptr, MG_ERR_NULL,
+             "noaux_tc gating needs e_score_correction_bias");
+  const mg_layer_desc& d = h->d;
+  const WsLayout L = ws_layout(h, T, 0);
+  MG_REQUIRE(ws_bytes >= L.total, MG_ERR_WORKSPACE, "workspace %zu bytes < %zu needed for %lld tokens", ws_bytes,
+             L.total, static_cast<long long>(T));
+  h->last_launches = 0;
+  if (T == 0) return MG_OK;
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  uint8_t* ws = static_cast<uint8_t*>(d_ws);
+  float* logits = reinterpret_cast<float*>(ws + L.off[WS_LOGITS]);
+  int32_t* idx = reinterpret_cast<int32_t*>(ws + L.off[WS_IDX]);
+  float* w = reinterpret_cast<float*>(ws + L.off[WS_W]);
+  int32_t* counts = reinterpret_cast<int32_t*>(ws + L.off[WS_COUNTS]);
+  int32_t* offsets = reinterpret_cast<int32_t*>(ws + L.off[WS_OFFSETS]);
+  int32_t* pad = reinterpret_cast<int32_t*>(ws + L.off[WS_PAD]);
+  int32_t* dst = reinterpret_cast<int32_t*>(ws + L.off[WS_DST]);
+  void* perm = ws + L.off[WS_PERM];
+  void* hbuf = ws + L.off[WS_H];
+  void* orow = ws + L.off[WS_OUT];
+  void* plan = ws + L.off[WS_PLAN];
+  void* hs = ws + L.off[WS_HS];
+  void* sh = d.inter_shared ? ws + L.off[WS_SHARED] : nullptr;
+  void* deq = d.weight_format == MG_WEIGHT_FP8_BLOCK128 ? ws + L.off[WS_DEQ] : nullptr;
+  int launches = 0;
+  int rc = mg_gate_logits(hh, d_x, d_gate_w, T, logits, stream);
+  if (rc != MG_OK) return rc;
+  rc = launch_route_topk(h, logits, d_bias, T, idx, w, st);
+  if (rc != MG_OK) return rc;
+  launches += 2;
+  rc = launch_permute_plan(h, idx, T, 0, d.n_experts, counts, offsets, pad, dst, plan, st, &launches);
+  if (rc != MG_OK) return rc;
+  rc = launch_permute_rows(h, d_x, dst, T, perm, st);
+  if (rc != MG_OK) return rc;
+  launches += 1;
+  rc = expert_ffn(h, perm, pad, counts, padded_rows(h, T * d.top_k), d_packed, hbuf, orow, deq, st, &launches);
+  if (rc != MG_OK) return rc;
+  if (d.inter_shared) {
+    rc = shared_ffn(h, d_x, T, d_packed, hs, sh, st);
+    if (rc != MG_OK) return rc;
+    launches += 2;
+  }
+  rc = launch_combine(h, orow, dst, idx, w, sh, T, d_y, st);
+  if (rc != MG_OK) return rc;
+  launches += 1;
+  h->last_launches = launches;
+  return MG_OK;
+}
+
+int mg_last_launch_count(mg_handle hh, int32_t* launches) {
+  Handle* h = check(hh);
+  if (!h) return MG_ERR_STATE;
+  MG_REQUIRE(launches, MG_ERR_NULL, "null argument");
+  *launches = h->last_launches;
+  return MG_OK;
+}
+
+}  // extern "C"

@@ -1,0 +1,94 @@
+// Internal declarations shared by the translation units of libmoegen_b200.so.
+#pragma once
+#include <cuda.h>
+#include <cuda_bf16.h>
+#include <cuda_runtime.h>
+#include <stdint.h>
+#include <stdio.h>
+
+#include "../../include/moegen_b200.h"
+
+namespace mg {
+
+constexpr int kTileM = 128;          // rows per GEMM tile == expert segment alignment
+constexpr int kMaxExperts = 512;     // plan and top-k kernels keep per-expert state on chip
+constexpr int kMaxTopK = 16;
+
+// thread-local error text -------------------------------------------------------------
+void set_error(const char* fmt, ...);
+int cuda_fail(cudaError_t e, const char* what);   // records text, returns (int)e
+
+#define MG_CUDA(call)                                                    \
+  do {                                                                   \
+    cudaError_t _e = (call);                                             \
+    if (_e != cudaSuccess) return ::mg::cuda_fail(_e, #call);            \
+  } while (0)
+
+#define MG_REQUIRE(cond, code, ...)                                      \
+  do {                                                                   \
+    if (!(cond)) { ::mg::set_error(__VA_ARGS__); return (code); }        \
+  } while (0)
+
+struct Handle {
+  uint32_t magic;
+  mg_layer_desc d;
+  int device;
+  int sm_count;
+  int e_local;            // experts owned by this rank
+  int32_t* d_status;      // [2]: code, detail
+  int last_launches;
+};
+constexpr uint32_t kMagic = 0x4d474232u;  // "MGB2"
+
+static inline int64_t round_up(int64_t a, int64_t b) { return (a + b - 1) / b * b; }
+
+// packed weight buffer offsets (bytes) ------------------------------------------------
+struct PackedLayout {
+  size_t w13, w2, s13, s2, sh13, sh2, total;
+  size_t w_elem;          // bytes per routed weight element
+};
+PackedLayout packed_layout(const Handle* h);
+
+// routing / permute / combine launchers (route.cu) -------------------------------------
+int launch_route_topk(const Handle* h, const float* logits, const float* bias, int64_t T,
+                      int32_t* idx, float* w, cudaStream_t st);
+size_t plan_ws_bytes(const Handle* h, int64_t T);
+int launch_permute_plan(const Handle* h, const int32_t* idx, int64_t T, int expert_lo, int n_exp,
+                        int32_t* counts, int32_t* offsets, int32_t* pad_offsets, int32_t* dst_row,
+                        void* ws, cudaStream_t st, int* launches);
+int launch_permute_rows(const Handle* h, const void* x, const int32_t* dst_row, int64_t T,
+                        void* perm_x, cudaStream_t st);
+int launch_combine(const Handle* h, const void* out_rows, const int32_t* dst_row,
+                   const int32_t* idx, const float* w, const void* shared, int64_t T, void* y,
+                   cudaStream_t st);
+
+// weights (pack.cu) --------------------------------------------------------------------
+int launch_pack_expert(const Handle* h, int local_expert, const void* g, const void* u,
+                       const void* dn, const float* gs, const float* us, const float* ds,
+                       void* packed, cudaStream_t st);
+int launch_dequant(const void* q, const float* s, int64_t rows, int64_t cols, void* out,
+                   cudaStream_t st);
+// de-quantise every routed expert of a packed FP8 buffer into a bf16 buffer of the same
+// layout (w13 then w2)
+int launch_dequant_packed(const Handle* h, const void* packed, void* bf16_out, cudaStream_t st);
+
+// grouped GEMM (gemm.cu) ---------------------------------------------------------------
+enum GemmEpilogue { EPI_SWIGLU_BF16 = 0, EPI_PLAIN_BF16 = 1, EPI_PLAIN_F32 = 2, EPI_ROUND_BF16_F32 = 3 };
+
+struct GemmProblem {
+  const void* a;          // [a_rows, K] bf16 row-major
+  int64_t a_rows;
+  const void* b;          // [n_groups * n_per_group, K] bf16 row-major ("N x K, K-major")
+  int n_groups;
+  int n_per_group;        // rows of B per group (2I for SwiGLU, H for down, E for the gate)
+  int K;
+  const int32_t* pad_offsets;  // [n_groups+1] device, or nullptr = dense (one group, rows = dense_rows)
+  const int32_t* counts;       // [n_groups] device
+  int64_t dense_rows;
+  void* out;              // bf16 or fp32
+  int64_t ldo;            // elements between output rows
+  int epilogue;
+};
+int launch_grouped_gemm(const Handle* h, const GemmProblem& p, cudaStream_t st);
+
+}  // namespace mg

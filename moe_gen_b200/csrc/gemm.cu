@@ -1,0 +1,479 @@
+// Grouped GEMM for sm_100a: C[rows, N] = A[rows, K] . B_e[N, K]^T per expert segment,
+// bf16 operands, fp32 accumulation in tensor memory.
+//
+//   * persistent kernel, one CTA per SM, 6 warps: warp 0 = TMA producer, warp 1 = MMA
+//     issuer + TMEM owner, warps 2-5 = epilogue (one TMEM lane quarter each);
+//   * operands arrive by TMA (cp.async.bulk.tensor, no multicast) into a 4-stage ring of
+//     128B-swizzled K-major tiles (A 128x64, B 256x64) guarded by mbarriers;
+//   * tcgen05.mma cta_group::1 kind::f16, M=128, N<=256, K=16 per instruction, accumulating
+//     into one of two 256-column TMEM buffers so the epilogue of tile i overlaps the MMAs of
+//     tile i+1;
+//   * epilogue reads TMEM with tcgen05.ld (one row per thread) and applies SiLU(gate)*up,
+//     or stores plain bf16 / fp32;
+//   * the tile list is derived on the device from the padded expert offsets (every expert
+//     starts on a 128-row boundary, so a tile never straddles two experts) — no host sync;
+//   * every mbarrier wait is bounded; on expiry the kernel records MG_DEV_WAIT_TIMEOUT, all
+//     roles leave their loops, TMEM is freed and the kernel returns.
+#include "common.cuh"
+
+namespace mg {
+
+constexpr int BM = 128;
+constexpr int BK = 64;                       // 64 bf16 = 128 bytes = one swizzle row
+constexpr int BN_MAX = 256;
+constexpr int STAGES = 4;
+constexpr int A_BYTES = BM * BK * 2;         // 16 KiB
+constexpr int B_BYTES = BN_MAX * BK * 2;     // 32 KiB
+constexpr int STAGE_BYTES = A_BYTES + B_BYTES;
+constexpr int GEMM_THREADS = 192;
+constexpr int TMEM_COLS = 512;
+constexpr int ACC_COLS = 256;
+constexpr unsigned long long WAIT_LIMIT_NS = 2000000000ull;
+
+struct GemmArgs {
+  const int32_t* pad_offsets;   // nullptr => dense
+  const int32_t* counts;
+  int n_groups;
+  int dense_rows;
+  int n_tiles;                  // tiles along N per group
+  int bn;                       // UMMA N
+  int n_per_group;              // rows of B per group
+  int k_blocks;
+  int group_m;
+  uint32_t idesc;
+  void* out;
+  long long ldo;
+  int32_t* status;
+};
+
+constexpr size_t SMEM_CTRL_BYTES = 8 * (2 * STAGES + 4) + 16 + 4 * (2 * kMaxExperts + 2);
+constexpr size_t GEMM_SMEM_BYTES = 1024 + STAGES * STAGE_BYTES + SMEM_CTRL_BYTES;
+
+// ---- PTX wrappers ---------------------------------------------------------------------
+__device__ __forceinline__ uint32_t smem_u32(const void* p) {
+  return static_cast<uint32_t>(__cvta_generic_to_shared(p));
+}
+__device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count) {
+  asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(count));
+}
+__device__ __forceinline__ void mbar_expect_tx(uint32_t bar, uint32_t bytes) {
+  asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes)
+               : "memory");
+}
+__device__ __forceinline__ void mbar_arrive(uint32_t bar) {
+  asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar) : "memory");
+}
+__device__ __forceinline__ uint32_t mbar_try_wait(uint32_t bar, uint32_t parity) {
+  uint32_t ok;
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+      "selp.u32 %0, 1, 0, p;\n\t}"
+      : "=r"(ok)
+      : "r"(bar), "r"(parity)
+      : "memory");
+  return ok;
+}
+__device__ __forceinline__ unsigned long long global_timer() {
+  unsigned long long t;
+  asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
+  return t;
+}
+// Bounded wait.  Returns false if the wait ran out or another role already gave up.
+__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile int* abort_flag,
+                                          int32_t* status, int where) {
+  if (mbar_try_wait(bar, parity)) return true;
+  const unsigned long long t0 = global_timer();
+  uint32_t spins = 0;
+  while (true) {
+    if (mbar_try_wait(bar, parity)) return true;
+    if ((++spins & 63u) == 0u) {
+      if (*abort_flag) return false;
+      if (global_timer() - t0 > WAIT_LIMIT_NS) {
+        *abort_flag = 1;
+        if (atomicCAS(status, MG_DEV_OK, MG_DEV_WAIT_TIMEOUT) == MG_DEV_OK) status[1] = where;
+        return false;
+      }
+    }
+  }
+}
+__device__ __forceinline__ void tma_load_2d(uint32_t dst, const CUtensorMap* map, int c0, int c1,
+                                            uint32_t bar) {
+  asm volatile(
+      "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];"
+      ::"r"(dst), "l"(map), "r"(bar), "r"(c0), "r"(c1)
+      : "memory");
+}
+__device__ __forceinline__ void tc_fence_before() {
+  asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+}
+__device__ __forceinline__ void tc_fence_after() {
+  asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+}
+__device__ __forceinline__ void tc_commit(uint32_t bar) {
+  asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar)
+               : "memory");
+}
+__device__ __forceinline__ void tc_mma_bf16(uint32_t d_tmem, uint64_t a_desc, uint64_t b_desc,
+                                            uint32_t idesc, uint32_t accumulate) {
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "setp.ne.b32 p, %4, 0;\n\t"
+      "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}"
+      ::"r"(d_tmem), "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate)
+      : "memory");
+}
+__device__ __forceinline__ void tc_ld32(uint32_t taddr, uint32_t* r) {
+  asm volatile(
+      "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
+      "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "
+      "%16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31}, [%32];"
+      : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]),
+        "=r"(r[7]), "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]),
+        "=r"(r[14]), "=r"(r[15]), "=r"(r[16]), "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]),
+        "=r"(r[21]), "=r"(r[22]), "=r"(r[23]), "=r"(r[24]), "=r"(r[25]), "=r"(r[26]), "=r"(r[27]),
+        "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
+      : "r"(taddr));
+}
+__device__ __forceinline__ void tc_ld_wait() {
+  asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+}
+
+// K-major, 128B-swizzled operand tile: rows of 128 bytes, 8-row groups 1024 bytes apart.
+__device__ __forceinline__ uint64_t make_smem_desc(uint32_t saddr) {
+  uint64_t d = 0;
+  d |= static_cast<uint64_t>((saddr & 0x3FFFFu) >> 4);        // start address, 16-byte units
+  d |= static_cast<uint64_t>(1) << 16;                        // leading byte offset (unused here)
+  d |= static_cast<uint64_t>(1024 >> 4) << 32;                // stride byte offset between 8-row groups
+  d |= static_cast<uint64_t>(1) << 46;                        // descriptor version (Blackwell)
+  d |= static_cast<uint64_t>(2) << 61;                        // SWIZZLE_128B
+  return d;
+}
+
+// ---- tile scheduler -------------------------------------------------------------------
+struct Tile {
+  int row0;        // first row of A / C
+  int valid_rows;  // rows of the tile that belong to the expert
+  int b_row;       // first row of B
+  int n_idx;       // tile index along N
+};
+
+__device__ __forceinline__ Tile locate_tile(int tile, const int* s_pad, const int* s_cnt,
+                                            int n_groups, int n_tiles, int n_per_group, int bn,
+                                            int group_m) {
+  // greatest e with prefix(e) <= tile, prefix(e) = s_pad[e]/BM*n_tiles
+  int lo = 0, hi = n_groups;  // answer in [lo, hi)
+  while (hi - lo > 1) {
+    int mid = (lo + hi) >> 1;
+    if ((s_pad[mid] / BM) * n_tiles <= tile) lo = mid; else hi = mid;
+  }
+  const int e = lo;
+  const int local = tile - (s_pad[e] / BM) * n_tiles;
+  const int m_e = (s_pad[e + 1] - s_pad[e]) / BM;
+  const int per_group = group_m * n_tiles;
+  const int grp = local / per_group;
+  const int rem = local - grp * per_group;
+  const int gm = min(group_m, m_e - grp * group_m);
+  const int n = rem / gm;
+  const int m = grp * group_m + (rem - n * gm);
+  Tile t;
+  t.row0 = s_pad[e] + m * BM;
+  t.valid_rows = min(BM, s_cnt[e] - m * BM);
+  t.b_row = e * n_per_group + n * bn;
+  t.n_idx = n;
+  return t;
+}
+
+__device__ __forceinline__ float silu_f(float g) { return __fdividef(g, 1.0f + __expf(-g)); }
+
+template <int EPI>
+__global__ void __launch_bounds__(GEMM_THREADS, 1)
+grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
+                    const GemmArgs g) {
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  uint64_t* bars = reinterpret_cast<uint64_t*>(smem + STAGES * STAGE_BYTES);
+  uint64_t* full = bars;
+  uint64_t* empty = bars + STAGES;
+  uint64_t* tfull = bars + 2 * STAGES;
+  uint64_t* tempty = bars + 2 * STAGES + 2;
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 2 * STAGES + 4);
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
+  int* s_pad = reinterpret_cast<int*>(tmem_slot + 4);
+  int* s_cnt = s_pad + kMaxExperts + 1;
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < STAGES; ++s) { mbar_init(smem_u32(&full[s]), 1); mbar_init(smem_u32(&empty[s]), 1); }
+    for (int a = 0; a < 2; ++a) { mbar_init(smem_u32(&tfull[a]), 1); mbar_init(smem_u32(&tempty[a]), 4); }
+    *abort_flag = 0;
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+  }
+  if (g.pad_offsets != nullptr) {
+    for (int i = threadIdx.x; i <= g.n_groups; i += blockDim.x) s_pad[i] = g.pad_offsets[i];
+    for (int i = threadIdx.x; i < g.n_groups; i += blockDim.x) s_cnt[i] = g.counts[i];
+  } else if (threadIdx.x == 0) {
+    s_pad[0] = 0;
+    s_pad[1] = (g.dense_rows + BM - 1) / BM * BM;
+    s_cnt[0] = g.dense_rows;
+  }
+  if (warp == 1) {
+    __syncwarp();
+    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(tmem_slot)),
+                 "r"(TMEM_COLS)
+                 : "memory");
+    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = *tmem_slot;
+  const int total_tiles = (s_pad[g.n_groups] / BM) * g.n_tiles;
+  const uint32_t smem_base = smem_u32(smem);
+
+  if (warp == 0) {
+    // ---------------- TMA producer ----------------
+    if (lane == 0) {
+      uint32_t it = 0;
+      const uint32_t tx_bytes = A_BYTES + static_cast<uint32_t>(g.bn) * BK * 2;
+      for (int tile = blockIdx.x; tile < total_tiles && !*abort_flag; tile += gridDim.x) {
+        const Tile t = locate_tile(tile, s_pad, s_cnt, g.n_groups, g.n_tiles, g.n_per_group, g.bn, g.group_m);
+        for (int kb = 0; kb < g.k_blocks; ++kb, ++it) {
+          const uint32_t s = it % STAGES, ph = (it / STAGES) & 1u;
+          if (!mbar_wait(smem_u32(&empty[s]), ph ^ 1u, abort_flag, g.status, 1)) break;
+          const uint32_t fb = smem_u32(&full[s]);
+          mbar_expect_tx(fb, tx_bytes);
+          const uint32_t sa = smem_base + s * STAGE_BYTES;
+          tma_load_2d(sa, &tmA, kb * BK, t.row0, fb);
+          tma_load_2d(sa + A_BYTES, &tmB, kb * BK, t.b_row, fb);
+        }
+      }
+    }
+  } else if (warp == 1) {
+    // ---------------- MMA issuer ----------------
+    if (lane == 0) {
+      uint32_t it = 0, tcount = 0;
+      for (int tile = blockIdx.x; tile < total_tiles && !*abort_flag; tile += gridDim.x, ++tcount) {
+        const uint32_t acc = tcount & 1u, acc_ph = (tcount >> 1) & 1u;
+        if (!mbar_wait(smem_u32(&tempty[acc]), acc_ph ^ 1u, abort_flag, g.status, 2)) break;
+        tc_fence_after();
+        const uint32_t d_tmem = tmem_base + acc * ACC_COLS;
+        bool ok = true;
+        for (int kb = 0; kb < g.k_blocks; ++kb, ++it) {
+          const uint32_t s = it % STAGES, ph = (it / STAGES) & 1u;
+          if (!mbar_wait(smem_u32(&full[s]), ph, abort_flag, g.status, 3)) { ok = false; break; }
+          tc_fence_after();
+          const uint32_t sa = smem_base + s * STAGE_BYTES;
+          const uint64_t da = make_smem_desc(sa), db = make_smem_desc(sa + A_BYTES);
+#pragma unroll
+          for (int k = 0; k < BK / 16; ++k) {
+            // 16 bf16 = 32 bytes = 2 sixteen-byte units further along K inside the swizzle row
+            tc_mma_bf16(d_tmem, da + 2 * k, db + 2 * k, g.idesc, (kb | k) != 0 ? 1u : 0u);
+          }
+          tc_commit(smem_u32(&empty[s]));   // frees the stage once these MMAs have read it
+        }
+        if (!ok) break;
+        tc_commit(smem_u32(&tfull[acc]));   // accumulator complete
+      }
+    }
+  } else {
+    // ---------------- epilogue ----------------
+    const int quarter = warp & 3;             // TMEM lanes [32*quarter, 32*quarter+32)
+    const int row_in_tile = quarter * 32 + lane;
+    uint32_t tcount = 0;
+    for (int tile = blockIdx.x; tile < total_tiles && !*abort_flag; tile += gridDim.x, ++tcount) {
+      const Tile t = locate_tile(tile, s_pad, s_cnt, g.n_groups, g.n_tiles, g.n_per_group, g.bn, g.group_m);
+      const uint32_t acc = tcount & 1u, acc_ph = (tcount >> 1) & 1u;
+      if (!mbar_wait(smem_u32(&tfull[acc]), acc_ph, abort_flag, g.status, 4)) break;
+      tc_fence_after();
+      const uint32_t taddr = tmem_base + acc * ACC_COLS + (static_cast<uint32_t>(quarter * 32) << 16);
+      const bool live = row_in_tile < t.valid_rows;
+      const long long row = static_cast<long long>(t.row0) + row_in_tile;
+      if (EPI == EPI_SWIGLU_BF16) {
+        const int half = g.bn >> 1;
+        __nv_bfloat16* orow = static_cast<__nv_bfloat16*>(g.out) + row * g.ldo + static_cast<long long>(t.n_idx) * half;
+        for (int c = 0; c < half; c += 32) {
+          uint32_t gr[32], ur[32];
+          tc_ld32(taddr + c, gr);
+          tc_ld32(taddr + half + c, ur);
+          tc_ld_wait();
+          if (live) {
+            uint32_t packed[16];
+#pragma unroll
+            for (int i = 0; i < 16; ++i) {
+              float h0 = silu_f(__uint_as_float(gr[2 * i])) * __uint_as_float(ur[2 * i]);
+              float h1 = silu_f(__uint_as_float(gr[2 * i + 1])) * __uint_as_float(ur[2 * i + 1]);
+              __nv_bfloat162 b = __floats2bfloat162_rn(h0, h1);
+              packed[i] = *reinterpret_cast<uint32_t*>(&b);
+            }
+            uint4* dst = reinterpret_cast<uint4*>(orow + c);
+#pragma unroll
+            for (int i = 0; i < 4; ++i) dst[i] = make_uint4(packed[4 * i], packed[4 * i + 1], packed[4 * i + 2], packed[4 * i + 3]);
+          }
+        }
+      } else if (EPI == EPI_PLAIN_BF16) {
+        __nv_bfloat16* orow = static_cast<__nv_bfloat16*>(g.out) + row * g.ldo + static_cast<long long>(t.n_idx) * g.bn;
+        for (int c = 0; c < g.bn; c += 32) {
+          uint32_t r[32];
+          tc_ld32(taddr + c, r);
+          tc_ld_wait();
+          if (live) {
+            uint32_t packed[16];
+#pragma unroll
+            for (int i = 0; i < 16; ++i) {
+              __nv_bfloat162 b = __floats2bfloat162_rn(__uint_as_float(r[2 * i]), __uint_as_float(r[2 * i + 1]));
+              packed[i] = *reinterpret_cast<uint32_t*>(&b);
+            }
+            uint4* dst = reinterpret_cast<uint4*>(orow + c);
+#pragma unroll
+            for (int i = 0; i < 4; ++i) dst[i] = make_uint4(packed[4 * i], packed[4 * i + 1], packed[4 * i + 2], packed[4 * i + 3]);
+          }
+        }
+      } else {
+        // fp32 output, N = n_per_group columns in one tile (the router logits)
+        float* orow = static_cast<float*>(g.out) + row * g.ldo;
+        for (int c = 0; c < g.n_per_group; c += 32) {
+          uint32_t r[32];
+          tc_ld32(taddr + c, r);
+          tc_ld_wait();
+          if (live) {
+#pragma unroll
+            for (int i = 0; i < 32; i += 4) {
+              if (c + i < g.n_per_group) {
+                float4 v;
+                v.x = __uint_as_float(r[i]); v.y = __uint_as_float(r[i + 1]);
+                v.z = __uint_as_float(r[i + 2]); v.w = __uint_as_float(r[i + 3]);
+                if (EPI == EPI_ROUND_BF16_F32) {
+                  v.x = __bfloat162float(__float2bfloat16_rn(v.x)); v.y = __bfloat162float(__float2bfloat16_rn(v.y));
+                  v.z = __bfloat162float(__float2bfloat16_rn(v.z)); v.w = __bfloat162float(__float2bfloat16_rn(v.w));
+                }
+                *reinterpret_cast<float4*>(orow + c + i) = v;
+              }
+            }
+          }
+        }
+      }
+      // hand the accumulator back to the MMA warp
+      tc_fence_before();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(smem_u32(&tempty[acc]));
+    }
+  }
+
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 1) {
+    __syncwarp();
+    tc_fence_after();
+    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(TMEM_COLS)
+                 : "memory");
+  }
+}
+
+// ---- host side ------------------------------------------------------------------------
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
+                                  const cuuint64_t*, const cuuint32_t*, const cuuint32_t*,
+                                  CUtensorMapInterleave, CUtensorMapSwizzle, CUtensorMapL2promotion,
+                                  CUtensorMapFloatOOBfill);
+
+static EncodeTiledFn get_encode_fn() {
+  static EncodeTiledFn fn = nullptr;
+  static bool tried = false;
+  if (!tried) {
+    tried = true;
+    void* p = nullptr;
+    cudaDriverEntryPointQueryResult q;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &q) == cudaSuccess &&
+        q == cudaDriverEntryPointSuccess)
+      fn = reinterpret_cast<EncodeTiledFn>(p);
+  }
+  return fn;
+}
+
+static int encode_2d(CUtensorMap* map, const void* base, uint64_t rows, uint64_t cols, uint32_t box_rows) {
+  EncodeTiledFn fn = get_encode_fn();
+  MG_REQUIRE(fn != nullptr, MG_ERR_DRIVER, "cuTensorMapEncodeTiled not available from the driver");
+  cuuint64_t dims[2] = {cols, rows};
+  cuuint64_t strides[1] = {cols * 2};
+  cuuint32_t box[2] = {static_cast<cuuint32_t>(BK), box_rows};
+  cuuint32_t estr[2] = {1, 1};
+  CUresult r = fn(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(base), dims, strides, box, estr,
+                  CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                  CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  MG_REQUIRE(r == CUDA_SUCCESS, MG_ERR_DRIVER, "cuTensorMapEncodeTiled failed (%d) rows=%llu cols=%llu box=%u",
+             static_cast<int>(r), static_cast<unsigned long long>(rows), static_cast<unsigned long long>(cols),
+             box_rows);
+  return MG_OK;
+}
+
+template <int EPI>
+static int launch_epi(const Handle* h, const CUtensorMap& ta, const CUtensorMap& tb, const GemmArgs& args,
+                      int grid, cudaStream_t st) {
+  // per device, and cheap: set on every launch rather than tracking which devices have it
+  MG_CUDA(cudaFuncSetAttribute(grouped_gemm_kernel<EPI>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                               static_cast<int>(GEMM_SMEM_BYTES)));
+  grouped_gemm_kernel<EPI><<<grid, GEMM_THREADS, GEMM_SMEM_BYTES, st>>>(ta, tb, args);
+  MG_CUDA(cudaGetLastError());
+  return MG_OK;
+}
+
+int launch_grouped_gemm(const Handle* h, const GemmProblem& p, cudaStream_t st) {
+  const bool dense = p.pad_offsets == nullptr;
+  if (p.a_rows <= 0 || (dense && p.dense_rows <= 0)) return MG_OK;
+  MG_REQUIRE(p.K % BK == 0, MG_ERR_SHAPE, "GEMM K=%d must be a multiple of %d", p.K, BK);
+  MG_REQUIRE(p.n_groups >= 1 && p.n_groups <= kMaxExperts, MG_ERR_SHAPE, "n_groups=%d out of range", p.n_groups);
+  int bn;
+  const bool f32_out = p.epilogue == EPI_PLAIN_F32 || p.epilogue == EPI_ROUND_BF16_F32;
+  if (f32_out) {
+    bn = static_cast<int>(round_up(p.n_per_group, 16));
+    MG_REQUIRE(bn <= BN_MAX && p.n_groups == 1 && p.n_per_group % 4 == 0, MG_ERR_SHAPE,
+               "fp32-output GEMM needs one group of <=256 columns (multiple of 4), got %d", p.n_per_group);
+  } else {
+    bn = BN_MAX;
+    MG_REQUIRE(p.n_per_group % BN_MAX == 0, MG_ERR_SHAPE, "GEMM N per expert (%d) must be a multiple of %d",
+               p.n_per_group, BN_MAX);
+  }
+  CUtensorMap ta, tb;
+  int rc = encode_2d(&ta, p.a, static_cast<uint64_t>(p.a_rows), static_cast<uint64_t>(p.K), BM);
+  if (rc != MG_OK) return rc;
+  rc = encode_2d(&tb, p.b, static_cast<uint64_t>(p.n_groups) * p.n_per_group, static_cast<uint64_t>(p.K), bn);
+  if (rc != MG_OK) return rc;
+
+  GemmArgs a;
+  a.pad_offsets = p.pad_offsets;
+  a.counts = p.counts;
+  a.n_groups = p.n_groups;
+  a.dense_rows = static_cast<int>(p.dense_rows);
+  a.n_tiles = f32_out ? 1 : p.n_per_group / bn;
+  a.bn = bn;
+  a.n_per_group = p.n_per_group;
+  a.k_blocks = p.K / BK;
+  a.group_m = 16;
+  // kind::f16: D fp32 (bit 4), A bf16 (bit 7), B bf16 (bit 10), both K-major, N>>3 at 17, M>>4 at 24
+  a.idesc = (1u << 4) | (1u << 7) | (1u << 10) | (static_cast<uint32_t>(bn >> 3) << 17) |
+            (static_cast<uint32_t>(BM >> 4) << 24);
+  a.out = p.out;
+  a.ldo = p.ldo;
+  a.status = h->d_status;
+
+  int grid = h->sm_count;
+  if (dense) {
+    long long tiles = (p.dense_rows + BM - 1) / BM * a.n_tiles;
+    if (tiles < grid) grid = static_cast<int>(tiles);
+  } else {
+    long long max_tiles = (p.a_rows / BM) * a.n_tiles;
+    if (max_tiles < grid) grid = static_cast<int>(max_tiles);
+  }
+  if (grid < 1) return MG_OK;
+  switch (p.epilogue) {
+    case EPI_SWIGLU_BF16: return launch_epi<EPI_SWIGLU_BF16>(h, ta, tb, a, grid, st);
+    case EPI_PLAIN_BF16: return launch_epi<EPI_PLAIN_BF16>(h, ta, tb, a, grid, st);
+    case EPI_PLAIN_F32: return launch_epi<EPI_PLAIN_F32>(h, ta, tb, a, grid, st);
+    case EPI_ROUND_BF16_F32: return launch_epi<EPI_ROUND_BF16_F32>(h, ta, tb, a, grid, st);
+  }
+  set_error("bad epilogue");
+  return MG_ERR_CONFIG;
+}
+
+}  // namespace mg

@@ -1,0 +1,476 @@
+// Routing (scoring + top-k), permute plan (histogram, prefix sums, stable placement),
+// row scatter and weighted combine.  All HBM-bound index/byte work: one warp per token,
+// 128-bit vector accesses on rows.
+#include "common.cuh"
+
+namespace mg {
+
+// ---------------------------------------------------------------------------------------
+// scoring + top-k: one warp per token, lane l owns experts [l*P, l*P+P)
+// ---------------------------------------------------------------------------------------
+__device__ __forceinline__ uint32_t ordered_bits(float v) {
+  v = v + 0.0f;  // -0.0 -> +0.0 so that equal values have equal keys
+  uint32_t u = __float_as_uint(v);
+  return (u & 0x80000000u) ? ~u : (u | 0x80000000u);
+}
+// larger key = better pick: score descending, then index ascending
+__device__ __forceinline__ unsigned long long make_key(float v, uint32_t index) {
+  return (static_cast<unsigned long long>(ordered_bits(v)) << 32) | (0xFFFFFFFFu - index);
+}
+__device__ __forceinline__ unsigned long long warp_max_u64(unsigned long long k) {
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) {
+    unsigned long long other = __shfl_xor_sync(0xFFFFFFFFu, k, o);
+    k = other > k ? other : k;
+  }
+  return k;
+}
+__device__ __forceinline__ float warp_max_f(float v) {
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) v = fmaxf(v, __shfl_xor_sync(0xFFFFFFFFu, v, o));
+  return v;
+}
+// fixed-order sum: the same pairing on every launch, so results are reproducible
+__device__ __forceinline__ float warp_sum_f(float v) {
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) v = __fadd_rn(v, __shfl_xor_sync(0xFFFFFFFFu, v, o));
+  return v;
+}
+
+struct RouteParams {
+  int E, k, n_group, topk_group, gating, norm;
+  float scale;
+};
+
+template <int P>
+__global__ void __launch_bounds__(256) route_topk_kernel(const float* __restrict__ logits,
+                                                         const float* __restrict__ bias,
+                                                         int64_t T, RouteParams rp,
+                                                         int32_t* __restrict__ out_idx,
+                                                         float* __restrict__ out_w) {
+  const int lane = threadIdx.x & 31;
+  const int64_t t = static_cast<int64_t>(blockIdx.x) * (blockDim.x >> 5) + (threadIdx.x >> 5);
+  if (t >= T) return;
+  const int E = rp.E;
+  const float NEG_INF = __int_as_float(0xff800000);
+
+  float lg[P];   // logits
+  float s[P];    // scores (softmax or sigmoid)
+  float c[P];    // selection values
+  const float* row = logits + t * E;
+#pragma unroll
+  for (int i = 0; i < P; ++i) {
+    int e = lane * P + i;
+    lg[i] = e < E ? row[e] : NEG_INF;
+  }
+  if (rp.gating == MG_GATE_SIGMOID_NOAUX_TC) {
+#pragma unroll
+    for (int i = 0; i < P; ++i) {
+      int e = lane * P + i;
+      s[i] = 1.0f / (1.0f + expf(-lg[i]));
+      c[i] = e < E ? __fadd_rn(s[i], bias[e]) : NEG_INF;
+    }
+  } else {
+    float m = NEG_INF;
+#pragma unroll
+    for (int i = 0; i < P; ++i) m = fmaxf(m, lg[i]);
+    m = warp_max_f(m);
+    float sum = 0.f;
+#pragma unroll
+    for (int i = 0; i < P; ++i) {
+      s[i] = (lane * P + i) < E ? expf(lg[i] - m) : 0.f;
+      sum = __fadd_rn(sum, s[i]);
+    }
+    sum = warp_sum_f(sum);
+#pragma unroll
+    for (int i = 0; i < P; ++i) {
+      s[i] = __fdiv_rn(s[i], sum);
+      c[i] = (lane * P + i) < E ? s[i] : NEG_INF;
+    }
+  }
+
+  // group-limited selection: keep topk_group groups, others compete with value 0.0
+  if (rp.gating == MG_GATE_SOFTMAX_GROUP_MAX || rp.gating == MG_GATE_SIGMOID_NOAUX_TC) {
+    const int G = rp.n_group, gsz = E / G;
+    float my_gs = NEG_INF;  // lane g holds the score of group g
+    for (int g = 0; g < G; ++g) {
+      float b1 = NEG_INF, b2 = NEG_INF;  // two largest values of group g seen by this lane
+#pragma unroll
+      for (int i = 0; i < P; ++i) {
+        int e = lane * P + i;
+        if (e < E && e / gsz == g) {
+          float v = c[i];
+          if (v > b1) { b2 = b1; b1 = v; } else if (v > b2) { b2 = v; }
+        }
+      }
+#pragma unroll
+      for (int o = 16; o > 0; o >>= 1) {
+        float o1 = __shfl_xor_sync(0xFFFFFFFFu, b1, o);
+        float o2 = __shfl_xor_sync(0xFFFFFFFFu, b2, o);
+        float hi = fmaxf(b1, o1), lo = fminf(b1, o1);
+        b2 = fmaxf(lo, fmaxf(b2, o2));
+        b1 = hi;
+      }
+      float gscore = rp.gating == MG_GATE_SIGMOID_NOAUX_TC ? __fadd_rn(b1, b2) : b1;
+      if (lane == g) my_gs = gscore;
+    }
+    uint32_t gmask = 0;
+    bool taken = lane >= G;
+    for (int r = 0; r < rp.topk_group; ++r) {
+      unsigned long long key = taken ? 0ull : make_key(my_gs, lane);
+      key = warp_max_u64(key);
+      int win = static_cast<int>(0xFFFFFFFFu - static_cast<uint32_t>(key));
+      gmask |= 1u << win;
+      if (lane == win) taken = true;
+    }
+#pragma unroll
+    for (int i = 0; i < P; ++i) {
+      int e = lane * P + i;
+      if (e < E && !((gmask >> (e / gsz)) & 1u)) c[i] = 0.0f;
+    }
+  }
+
+  // k rounds of warp arg-max
+  uint32_t taken = 0;
+  int my_idx = 0;
+  float my_w = 0.f;
+  for (int r = 0; r < rp.k; ++r) {
+    unsigned long long best = 0ull;
+#pragma unroll
+    for (int i = 0; i < P; ++i) {
+      int e = lane * P + i;
+      if (e < E && !((taken >> i) & 1u)) {
+        unsigned long long key = make_key(c[i], e);
+        best = key > best ? key : best;
+      }
+    }
+    best = warp_max_u64(best);
+    int e_win = static_cast<int>(0xFFFFFFFFu - static_cast<uint32_t>(best));
+    int owner = e_win / P, slot = e_win - owner * P;
+    float wv = 0.f;
+#pragma unroll
+    for (int i = 0; i < P; ++i) {
+      if (i == slot) wv = rp.gating == MG_GATE_SIGMOID_NOAUX_TC ? s[i] : c[i];
+    }
+    if (lane == owner) taken |= 1u << slot;
+    wv = __shfl_sync(0xFFFFFFFFu, wv, owner);
+    if (lane == r) { my_idx = e_win; my_w = wv; }
+  }
+
+  // normalise / scale
+  float denom = 0.f;
+  for (int r = 0; r < rp.k; ++r) denom = __fadd_rn(denom, __shfl_sync(0xFFFFFFFFu, my_w, r));
+  if (rp.gating == MG_GATE_SOFTMAX_TOPK_RENORM) {
+    my_w = __fdiv_rn(my_w, denom);
+  } else if (rp.gating == MG_GATE_SIGMOID_NOAUX_TC) {
+    if (rp.k > 1 && rp.norm) my_w = __fdiv_rn(my_w, __fadd_rn(denom, 1e-20f));
+    my_w = __fmul_rn(my_w, rp.scale);
+  } else {
+    if (rp.k > 1 && rp.norm) my_w = __fdiv_rn(my_w, __fadd_rn(denom, 1e-20f));
+    else my_w = __fmul_rn(my_w, rp.scale);
+  }
+  if (lane < rp.k) {
+    out_idx[t * rp.k + lane] = my_idx;
+    out_w[t * rp.k + lane] = my_w;
+  }
+}
+
+int launch_route_topk(const Handle* h, const float* logits, const float* bias, int64_t T,
+                      int32_t* idx, float* w, cudaStream_t st) {
+  if (T == 0) return MG_OK;
+  const mg_layer_desc& d = h->d;
+  RouteParams rp{d.n_experts, d.top_k, d.n_group, d.topk_group, d.gating, d.norm_topk_prob,
+                 d.routed_scale};
+  const int warps = 8;
+  dim3 grid(static_cast<unsigned>((T + warps - 1) / warps)), block(warps * 32);
+  const int P = (d.n_experts + 31) / 32;
+#define MG_ROUTE_CASE(PP)                                                             \
+  route_topk_kernel<PP><<<grid, block, 0, st>>>(logits, bias, T, rp, idx, w)
+  if (P <= 1) MG_ROUTE_CASE(1);
+  else if (P <= 2) MG_ROUTE_CASE(2);
+  else if (P <= 4) MG_ROUTE_CASE(4);
+  else if (P <= 5) MG_ROUTE_CASE(5);
+  else if (P <= 8) MG_ROUTE_CASE(8);
+  else if (P <= 16) MG_ROUTE_CASE(16);
+  else { set_error("n_experts %d > 512 unsupported by the top-k kernel", d.n_experts); return MG_ERR_SHAPE; }
+#undef MG_ROUTE_CASE
+  MG_CUDA(cudaGetLastError());
+  return MG_OK;
+}
+
+// ---------------------------------------------------------------------------------------
+// permute plan
+// ---------------------------------------------------------------------------------------
+constexpr int kPlanTokens = 256;  // tokens per block (one per thread)
+
+__global__ void __launch_bounds__(kPlanTokens) plan_count_kernel(const int32_t* __restrict__ idx,
+                                                                 int64_t T, int k, int lo, int n,
+                                                                 int32_t* __restrict__ block_counts) {
+  extern __shared__ int32_t hist[];
+  for (int e = threadIdx.x; e < n; e += blockDim.x) hist[e] = 0;
+  __syncthreads();
+  int64_t t = static_cast<int64_t>(blockIdx.x) * kPlanTokens + threadIdx.x;
+  if (t < T) {
+    for (int j = 0; j < k; ++j) {
+      int e = idx[t * k + j] - lo;
+      if (e >= 0 && e < n) atomicAdd(&hist[e], 1);
+    }
+  }
+  __syncthreads();
+  for (int e = threadIdx.x; e < n; e += blockDim.x)
+    block_counts[static_cast<int64_t>(blockIdx.x) * n + e] = hist[e];
+}
+
+// one block: per expert, turn block_counts[:,e] into an exclusive prefix over blocks and
+// produce counts / offsets / pad_offsets
+__global__ void __launch_bounds__(1024) plan_scan_kernel(int32_t* __restrict__ block_counts,
+                                                         int nblk, int n,
+                                                         int32_t* __restrict__ counts,
+                                                         int32_t* __restrict__ offsets,
+                                                         int32_t* __restrict__ pad_offsets) {
+  __shared__ int32_t tot[kMaxExperts];
+  for (int e = threadIdx.x; e < n; e += blockDim.x) {
+    int32_t run = 0;
+    for (int b = 0; b < nblk; ++b) {
+      int32_t c = block_counts[static_cast<int64_t>(b) * n + e];
+      block_counts[static_cast<int64_t>(b) * n + e] = run;
+      run += c;
+    }
+    tot[e] = run;
+    counts[e] = run;
+  }
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    int32_t o = 0, p = 0;
+    for (int e = 0; e < n; ++e) {
+      offsets[e] = o;
+      pad_offsets[e] = p;
+      o += tot[e];
+      p += (tot[e] + kTileM - 1) / kTileM * kTileM;
+    }
+    offsets[n] = o;
+    pad_offsets[n] = p;
+  }
+}
+
+__global__ void __launch_bounds__(kPlanTokens) plan_place_kernel(const int32_t* __restrict__ idx,
+                                                                 int64_t T, int k, int lo, int n,
+                                                                 const int32_t* __restrict__ block_base,
+                                                                 const int32_t* __restrict__ pad_offsets,
+                                                                 int32_t* __restrict__ dst_row) {
+  extern __shared__ int32_t sm[];
+  constexpr int W = kPlanTokens / 32;
+  uint32_t* bm = reinterpret_cast<uint32_t*>(sm);  // [W][n] lanes of warp w that picked e
+  int32_t* wbase = sm + W * n;                     // [W][n] first row for warp w, expert e
+  for (int i = threadIdx.x; i < W * n; i += blockDim.x) bm[i] = 0u;
+  __syncthreads();
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  int64_t t = static_cast<int64_t>(blockIdx.x) * kPlanTokens + threadIdx.x;
+  if (t < T) {
+    for (int j = 0; j < k; ++j) {
+      int e = idx[t * k + j] - lo;
+      if (e >= 0 && e < n) atomicOr(&bm[warp * n + e], 1u << lane);
+    }
+  }
+  __syncthreads();
+  for (int e = threadIdx.x; e < n; e += blockDim.x) {
+    int32_t run = pad_offsets[e] + block_base[static_cast<int64_t>(blockIdx.x) * n + e];
+    for (int w = 0; w < W; ++w) {
+      wbase[w * n + e] = run;
+      run += __popc(bm[w * n + e]);
+    }
+  }
+  __syncthreads();
+  if (t < T) {
+    const uint32_t lt = (1u << lane) - 1u;
+    for (int j = 0; j < k; ++j) {
+      int e = idx[t * k + j] - lo;
+      int32_t dst = -1;
+      if (e >= 0 && e < n) dst = wbase[warp * n + e] + __popc(bm[warp * n + e] & lt);
+      dst_row[t * k + j] = dst;
+    }
+  }
+}
+
+size_t plan_ws_bytes(const Handle* h, int64_t T) {
+  int64_t nblk = (T + kPlanTokens - 1) / kPlanTokens;
+  if (nblk < 1) nblk = 1;
+  return static_cast<size_t>(nblk) * h->d.n_experts * sizeof(int32_t);
+}
+
+int launch_permute_plan(const Handle* h, const int32_t* idx, int64_t T, int expert_lo, int n_exp,
+                        int32_t* counts, int32_t* offsets, int32_t* pad_offsets, int32_t* dst_row,
+                        void* ws, cudaStream_t st, int* launches) {
+  const int k = h->d.top_k;
+  int nblk = static_cast<int>((T + kPlanTokens - 1) / kPlanTokens);
+  int32_t* bc = static_cast<int32_t*>(ws);
+  if (nblk > 0) {
+    plan_count_kernel<<<nblk, kPlanTokens, n_exp * sizeof(int32_t), st>>>(idx, T, k, expert_lo,
+                                                                          n_exp, bc);
+    MG_CUDA(cudaGetLastError());
+  }
+  plan_scan_kernel<<<1, 1024, 0, st>>>(bc, nblk, n_exp, counts, offsets, pad_offsets);
+  MG_CUDA(cudaGetLastError());
+  if (nblk > 0) {
+    size_t smem = static_cast<size_t>(2) * (kPlanTokens / 32) * n_exp * sizeof(int32_t);
+    plan_place_kernel<<<nblk, kPlanTokens, smem, st>>>(idx, T, k, expert_lo, n_exp, bc,
+                                                       pad_offsets, dst_row);
+    MG_CUDA(cudaGetLastError());
+  }
+  if (launches) *launches += nblk > 0 ? 3 : 1;
+  return MG_OK;
+}
+
+// ---------------------------------------------------------------------------------------
+// row scatter: one warp per token, x row read once, written to each destination row
+// ---------------------------------------------------------------------------------------
+__global__ void __launch_bounds__(256) permute_rows_kernel(const uint4* __restrict__ x,
+                                                           const int32_t* __restrict__ dst_row,
+                                                           int64_t T, int k, int vec_per_row,
+                                                           uint4* __restrict__ perm_x) {
+  const int lane = threadIdx.x & 31;
+  const int64_t t = static_cast<int64_t>(blockIdx.x) * (blockDim.x >> 5) + (threadIdx.x >> 5);
+  if (t >= T) return;
+  int32_t my_dst = lane < k ? dst_row[t * k + lane] : -1;
+  const uint4* src = x + t * vec_per_row;
+  for (int v0 = 0; v0 < vec_per_row; v0 += 128) {
+    uint4 val[4];
+#pragma unroll
+    for (int u = 0; u < 4; ++u) {
+      int v = v0 + u * 32 + lane;
+      if (v < vec_per_row) val[u] = __ldg(src + v);
+    }
+    for (int j = 0; j < k; ++j) {
+      int32_t d = __shfl_sync(0xFFFFFFFFu, my_dst, j);
+      if (d < 0) continue;
+      uint4* dst = perm_x + static_cast<int64_t>(d) * vec_per_row;
+#pragma unroll
+      for (int u = 0; u < 4; ++u) {
+        int v = v0 + u * 32 + lane;
+        if (v < vec_per_row) dst[v] = val[u];
+      }
+    }
+  }
+}
+
+int launch_permute_rows(const Handle* h, const void* x, const int32_t* dst_row, int64_t T,
+                        void* perm_x, cudaStream_t st) {
+  if (T == 0) return MG_OK;
+  const int warps = 8;
+  dim3 grid(static_cast<unsigned>((T + warps - 1) / warps)), block(warps * 32);
+  permute_rows_kernel<<<grid, block, 0, st>>>(static_cast<const uint4*>(x), dst_row, T,
+                                              h->d.top_k, h->d.hidden / 8,
+                                              static_cast<uint4*>(perm_x));
+  MG_CUDA(cudaGetLastError());
+  return MG_OK;
+}
+
+// ---------------------------------------------------------------------------------------
+// combine: y[t] = sum_j w[t,j] * out_rows[dst_row[t,j]] (+ shared[t])
+// ---------------------------------------------------------------------------------------
+__device__ __forceinline__ void unpack8(const uint4& v, float* f) {
+  const __nv_bfloat162* p = reinterpret_cast<const __nv_bfloat162*>(&v);
+#pragma unroll
+  for (int i = 0; i < 4; ++i) {
+    float2 t = __bfloat1622float2(p[i]);
+    f[2 * i] = t.x;
+    f[2 * i + 1] = t.y;
+  }
+}
+__device__ __forceinline__ uint4 pack8(const float* f) {
+  uint4 v;
+  __nv_bfloat162* p = reinterpret_cast<__nv_bfloat162*>(&v);
+#pragma unroll
+  for (int i = 0; i < 4; ++i) p[i] = __floats2bfloat162_rn(f[2 * i], f[2 * i + 1]);
+  return v;
+}
+__device__ __forceinline__ float round_bf16(float f) {
+  return __bfloat162float(__float2bfloat16_rn(f));
+}
+
+template <int MODE>
+__global__ void __launch_bounds__(256) combine_kernel(const uint4* __restrict__ rows,
+                                                      const int32_t* __restrict__ dst_row,
+                                                      const int32_t* __restrict__ topk_idx,
+                                                      const float* __restrict__ topk_w,
+                                                      const uint4* __restrict__ shared,
+                                                      int64_t T, int k, int vec_per_row,
+                                                      uint4* __restrict__ y) {
+  const int lane = threadIdx.x & 31;
+  const int64_t t = static_cast<int64_t>(blockIdx.x) * (blockDim.x >> 5) + (threadIdx.x >> 5);
+  if (t >= T) return;
+  int32_t my_dst = -1, my_e = 0x7fffffff;
+  float my_w = 0.f;
+  if (lane < k) {
+    my_dst = dst_row[t * k + lane];
+    my_w = topk_w[t * k + lane];
+    if (MODE == MG_COMBINE_BF16_SEQ) my_e = topk_idx[t * k + lane];
+    if (MODE != MG_COMBINE_FP32) my_w = round_bf16(my_w);
+  }
+  // BF16_SEQ adds in ascending expert order: rank of my slot among the k picks
+  int order_src = lane;  // slot visited at step `lane`
+  if (MODE == MG_COMBINE_BF16_SEQ) {
+    int rank = 0;
+    for (int j = 0; j < k; ++j) {
+      int32_t ej = __shfl_sync(0xFFFFFFFFu, my_e, j);
+      if (lane < k && (ej < my_e || (ej == my_e && j < lane))) ++rank;
+    }
+    // step r visits the slot whose rank is r
+    order_src = 0;
+    for (int j = 0; j < k; ++j) {
+      int rj = __shfl_sync(0xFFFFFFFFu, rank, j);
+      if (rj == lane) order_src = j;
+    }
+  }
+  for (int v = lane; v < vec_per_row; v += 32) {
+    float acc[8];
+#pragma unroll
+    for (int i = 0; i < 8; ++i) acc[i] = 0.f;
+    for (int step = 0; step < k; ++step) {
+      int j = MODE == MG_COMBINE_BF16_SEQ ? __shfl_sync(0xFFFFFFFFu, order_src, step) : step;
+      int32_t d = __shfl_sync(0xFFFFFFFFu, my_dst, j);
+      float w = __shfl_sync(0xFFFFFFFFu, my_w, j);
+      if (d < 0) continue;
+      float f[8];
+      unpack8(__ldg(rows + static_cast<int64_t>(d) * vec_per_row + v), f);
+#pragma unroll
+      for (int i = 0; i < 8; ++i) {
+        float p = __fmul_rn(f[i], w);
+        if (MODE == MG_COMBINE_FP32) acc[i] = __fadd_rn(acc[i], p);
+        else if (MODE == MG_COMBINE_BF16_PROD) acc[i] = __fadd_rn(acc[i], round_bf16(p));
+        else acc[i] = round_bf16(__fadd_rn(acc[i], round_bf16(p)));
+      }
+    }
+    if (shared != nullptr) {
+      float f[8];
+      unpack8(__ldg(shared + t * vec_per_row + v), f);
+#pragma unroll
+      for (int i = 0; i < 8; ++i) acc[i] = __fadd_rn(round_bf16(acc[i]), f[i]);
+    }
+    y[t * vec_per_row + v] = pack8(acc);
+  }
+}
+
+int launch_combine(const Handle* h, const void* out_rows, const int32_t* dst_row,
+                   const int32_t* idx, const float* w, const void* shared, int64_t T, void* y,
+                   cudaStream_t st) {
+  if (T == 0) return MG_OK;
+  const int warps = 8;
+  dim3 grid(static_cast<unsigned>((T + warps - 1) / warps)), block(warps * 32);
+  const int k = h->d.top_k, vpr = h->d.hidden / 8;
+#define MG_COMBINE_CASE(M)                                                                  \
+  combine_kernel<M><<<grid, block, 0, st>>>(static_cast<const uint4*>(out_rows), dst_row,   \
+                                            idx, w, static_cast<const uint4*>(shared), T, k, \
+                                            vpr, static_cast<uint4*>(y))
+  switch (h->d.combine_mode) {
+    case MG_COMBINE_FP32: MG_COMBINE_CASE(MG_COMBINE_FP32); break;
+    case MG_COMBINE_BF16_PROD: MG_COMBINE_CASE(MG_COMBINE_BF16_PROD); break;
+    case MG_COMBINE_BF16_SEQ: MG_COMBINE_CASE(MG_COMBINE_BF16_SEQ); break;
+    default: set_error("bad combine_mode"); return MG_ERR_CONFIG;
+  }
+#undef MG_COMBINE_CASE
+  MG_CUDA(cudaGetLastError());
+  return MG_OK;
+}
+
+}  // namespace mg

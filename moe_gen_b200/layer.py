@@ -1,0 +1,281 @@
+"""Host-side MoE layer object: owns the native handle, the packed weight buffer and
+the workspace (all torch CUDA tensors — torch is used for device memory and streams
+only), and calls the C ABI for every computation.
+
+The staged methods mirror the steps of the reference's layer
+(moe_gen/models/deepseek/deepseekv3/modeling_deepseek_v3.py: MoEGate.forward
+:500-561, DeepseekV3MoE.moe_infer :628-711) so tests can compare stage by stage.
+"""
+from __future__ import annotations
+
+import ctypes as C
+from typing import Optional, Tuple
+
+import torch
+
+from . import lib as L
+
+
+def _ptr(t: Optional[torch.Tensor]) -> Optional[int]:
+    return None if t is None else t.data_ptr()
+
+
+class MoELayer:
+    def __init__(self, *, hidden: int, inter: int, n_experts: int, top_k: int, inter_shared: int = 0,
+                 n_group: int = 1, topk_group: int = 1, gating: int = L.GATE_SOFTMAX_GREEDY,
+                 norm_topk_prob: bool = False, routed_scale: float = 1.0,
+                 weight_format: int = L.WEIGHT_BF16, combine_mode: int = L.COMBINE_FP32,
+                 ep_rank: int = 0, ep_size: int = 1, device=None):
+        if not torch.cuda.is_available():
+            raise RuntimeError("moe_gen_b200 needs a CUDA device (sm_100a); there is no CPU path")
+        self.lib = L.load()
+        self.device = torch.device("cuda", torch.cuda.current_device()) if device is None else torch.device(device)
+        self.desc = L.LayerDesc(C.sizeof(L.LayerDesc), hidden, inter, inter_shared, n_experts, top_k, n_group,
+                                topk_group, gating, int(bool(norm_topk_prob)), float(routed_scale),
+                                weight_format, combine_mode, ep_rank, ep_size)
+        self.H, self.I, self.Is, self.E, self.k = hidden, inter, inter_shared, n_experts, top_k
+        self.e_local = n_experts // ep_size
+        self.expert_lo = ep_rank * self.e_local
+        self._h = C.c_void_p()
+        with torch.cuda.device(self.device):
+            L.check(self.lib.mg_create(C.byref(self.desc), C.byref(self._h)))
+            n = C.c_size_t()
+            L.check(self.lib.mg_packed_weight_bytes(self._h, C.byref(n)))
+            self.packed = torch.empty(n.value, dtype=torch.uint8, device=self.device)
+        self.gate_w: Optional[torch.Tensor] = None
+        self.bias: Optional[torch.Tensor] = None
+        self._ws: Optional[torch.Tensor] = None
+        self._ws_tokens = -1
+
+    # ------------------------------------------------------------------ lifetime
+    def close(self):
+        if getattr(self, "_h", None) is not None and self._h.value:
+            self.lib.mg_destroy(self._h)
+            self._h = C.c_void_p()
+
+    def __del__(self):
+        try:
+            self.close()
+        except Exception:
+            pass
+
+    @staticmethod
+    def _stream() -> int:
+        return torch.cuda.current_stream().cuda_stream
+
+    def _check_in(self, t: torch.Tensor, dtype, what: str):
+        if t.device != self.device or t.dtype != dtype or not t.is_contiguous():
+            raise ValueError(f"{what}: expected contiguous {dtype} tensor on {self.device}, got "
+                             f"{t.dtype} on {t.device} contiguous={t.is_contiguous()}")
+
+    # ------------------------------------------------------------------ weights
+    def set_router(self, gate_weight: torch.Tensor, bias: Optional[torch.Tensor] = None):
+        """gate.weight [E,H] (kept as bf16) and, for noaux_tc, e_score_correction_bias [E] (fp32)."""
+        self.gate_w = gate_weight.detach().to(self.device, torch.bfloat16).contiguous()
+        assert self.gate_w.shape == (self.E, self.H)
+        self.bias = None if bias is None else bias.detach().to(self.device, torch.float32).contiguous()
+
+    def load_expert(self, local_expert: int, gate: torch.Tensor, up: torch.Tensor, down: torch.Tensor,
+                    scales: Optional[Tuple[torch.Tensor, torch.Tensor, torch.Tensor]] = None):
+        """Packs one expert ([I,H], [I,H], [H,I] as nn.Linear stores them).  local_expert = -1 is
+        the shared expert.  FP8 layers pass float8_e4m3fn matrices plus their fp32 scales."""
+        fp8 = self.desc.weight_format == L.WEIGHT_FP8_BLOCK128 and local_expert >= 0
+        dt = torch.float8_e4m3fn if fp8 else torch.bfloat16
+        mats = [m.detach().to(self.device).contiguous() for m in (gate, up, down)]
+        I = self.Is if local_expert < 0 else self.I
+        for m, shp in zip(mats, ((I, self.H), (I, self.H), (self.H, I))):
+            if m.dtype != dt or tuple(m.shape) != shp:
+                raise ValueError(f"expert matrix {tuple(m.shape)} {m.dtype}, expected {shp} {dt}")
+        sc = [None, None, None]
+        if fp8:
+            if scales is None:
+                raise ValueError("FP8 layer: scales=(gate_scale, up_scale, down_scale) required")
+            sc = [s.detach().to(self.device, torch.float32).contiguous() for s in scales]
+        with torch.cuda.device(self.device):
+            L.check(self.lib.mg_pack_expert(self._h, local_expert, mats[0].data_ptr(), mats[1].data_ptr(),
+                                            mats[2].data_ptr(), _ptr(sc[0]), _ptr(sc[1]), _ptr(sc[2]),
+                                            self.packed.data_ptr(), self._stream()))
+            torch.cuda.current_stream().synchronize()   # sources may be temporaries
+
+    def load_shared(self, gate, up, down):
+        self.load_expert(-1, gate, up, down)
+
+    # ------------------------------------------------------------------ sizes
+    def padded_rows(self, n_rows: int) -> int:
+        out = C.c_int64()
+        L.check(self.lib.mg_padded_rows(self._h, n_rows, C.byref(out)))
+        return out.value
+
+    def _workspace(self, T: int) -> torch.Tensor:
+        if self._ws is None or T > self._ws_tokens:
+            n = C.c_size_t()
+            L.check(self.lib.mg_workspace_bytes(self._h, T, 0, C.byref(n)))
+            self._ws = None
+            self._ws = torch.empty(max(n.value, 256), dtype=torch.uint8, device=self.device)
+            self._ws_tokens = T
+        return self._ws
+
+    def workspace_view(self, which: int, T: int) -> int:
+        p = C.c_void_p()
+        L.check(self.lib.mg_workspace_ptr(self._h, self._ws.data_ptr(), self._ws_tokens, 0, which, C.byref(p)))
+        return p.value
+
+    def device_status(self) -> Tuple[int, int]:
+        code, detail = C.c_int32(), C.c_int32()
+        L.check(self.lib.mg_device_status(self._h, C.byref(code), C.byref(detail)))
+        return code.value, detail.value
+
+    def last_launch_count(self) -> int:
+        n = C.c_int32()
+        L.check(self.lib.mg_last_launch_count(self._h, C.byref(n)))
+        return n.value
+
+    # ------------------------------------------------------------------ whole layer
+    def forward(self, x: torch.Tensor, out: Optional[torch.Tensor] = None) -> torch.Tensor:
+        """x: [..., H] bf16 on the layer's device -> same shape.  Asynchronous on the current stream."""
+        shape = x.shape
+        x2 = x.reshape(-1, self.H)
+        self._check_in(x2, torch.bfloat16, "hidden_states")
+        T = x2.shape[0]
+        ws = self._workspace(T)
+        y = torch.empty_like(x2) if out is None else out
+        with torch.cuda.device(self.device):
+            L.check(self.lib.mg_moe_forward(self._h, x2.data_ptr(), T, self.gate_w.data_ptr(), _ptr(self.bias),
+                                            self.packed.data_ptr(), ws.data_ptr(), ws.numel(), y.data_ptr(),
+                                            self._stream()))
+        return y.view(shape)
+
+    __call__ = forward
+
+    def forward_host(self, x_host: torch.Tensor, y_host: Optional[torch.Tensor] = None,
+                     chunk_tokens: int = 8192) -> torch.Tensor:
+        """Host-buffer entry: x_host [T,H] bf16 in (preferably pinned) host memory -> y_host.
+        Tokens are independent, so chunks are copied in, computed and copied out on three
+        streams; returns after the last copy has finished."""
+        T = x_host.shape[0]
+        if y_host is None:
+            y_host = torch.empty_like(x_host, pin_memory=x_host.is_pinned())
+        cs = min(chunk_tokens, max(T, 1))
+        with torch.cuda.device(self.device):
+            if getattr(self, "_hb", None) is None or self._hb[0].shape[0] < cs:
+                self._hb = [torch.empty(cs, self.H, dtype=torch.bfloat16, device=self.device) for _ in range(4)]
+                self._hs = [torch.cuda.Stream(), torch.cuda.Stream()]
+            xin, yout = self._hb[:2], self._hb[2:]
+            s_in, s_out = self._hs
+            comp = torch.cuda.current_stream()
+            ev_in = [torch.cuda.Event() for _ in range(2)]
+            ev_done = [torch.cuda.Event() for _ in range(2)]
+            ev_out = [torch.cuda.Event() for _ in range(2)]
+            s_in.wait_stream(comp)
+            s_out.wait_stream(comp)
+            self._workspace(cs)
+            for c, t0 in enumerate(range(0, T, cs)):
+                b, n = c & 1, min(cs, T - t0)
+                if c >= 2:
+                    s_in.wait_event(ev_done[b])
+                with torch.cuda.stream(s_in):
+                    xin[b][:n].copy_(x_host[t0:t0 + n], non_blocking=True)
+                    ev_in[b].record(s_in)
+                comp.wait_event(ev_in[b])
+                if c >= 2:
+                    comp.wait_event(ev_out[b])
+                self.forward(xin[b][:n], out=yout[b][:n])
+                ev_done[b].record(comp)
+                s_out.wait_event(ev_done[b])
+                with torch.cuda.stream(s_out):
+                    y_host[t0:t0 + n].copy_(yout[b][:n], non_blocking=True)
+                    ev_out[b].record(s_out)
+            s_out.synchronize()
+        return y_host
+
+    # ------------------------------------------------------------------ stages
+    def gate_logits(self, x: torch.Tensor) -> torch.Tensor:
+        self._check_in(x, torch.bfloat16, "hidden_states")
+        T = x.shape[0]
+        logits = torch.empty(T, self.E, dtype=torch.float32, device=self.device)
+        with torch.cuda.device(self.device):
+            L.check(self.lib.mg_gate_logits(self._h, x.data_ptr(), self.gate_w.data_ptr(), T, logits.data_ptr(),
+                                            self._stream()))
+        return logits
+
+    def route_topk(self, logits: torch.Tensor) -> Tuple[torch.Tensor, torch.Tensor]:
+        self._check_in(logits, torch.float32, "logits")
+        T = logits.shape[0]
+        idx = torch.empty(T, self.k, dtype=torch.int32, device=self.device)
+        w = torch.empty(T, self.k, dtype=torch.float32, device=self.device)
+        with torch.cuda.device(self.device):
+            L.check(self.lib.mg_route_topk(self._h, logits.data_ptr(), _ptr(self.bias), T, idx.data_ptr(),
+                                           w.data_ptr(), self._stream()))
+        return idx, w
+
+    def permute_plan(self, topk_idx: torch.Tensor, expert_lo: int = 0, n_plan: Optional[int] = None):
+        """-> counts [n], offsets [n+1], pad_offsets [n+1], dst_row [T,k] (all int32)."""
+        self._check_in(topk_idx, torch.int32, "topk_idx")
+        n = self.E if n_plan is None else n_plan
+        T = topk_idx.shape[0]
+        dev = self.device
+        counts = torch.empty(n, dtype=torch.int32, device=dev)
+        offsets = torch.empty(n + 1, dtype=torch.int32, device=dev)
+        pad = torch.empty(n + 1, dtype=torch.int32, device=dev)
+        dst = torch.empty(T, self.k, dtype=torch.int32, device=dev)
+        nb = C.c_size_t()
+        L.check(self.lib.mg_plan_ws_bytes(self._h, T, C.byref(nb)))
+        ws = torch.empty(max(nb.value, 4), dtype=torch.uint8, device=dev)
+        with torch.cuda.device(dev):
+            L.check(self.lib.mg_permute_plan(self._h, topk_idx.data_ptr(), T, expert_lo, n, counts.data_ptr(),
+                                             offsets.data_ptr(), pad.data_ptr(), dst.data_ptr(), ws.data_ptr(),
+                                             self._stream()))
+        return counts, offsets, pad, dst
+
+    def permute_rows(self, x: torch.Tensor, dst_row: torch.Tensor, rows_padded: int) -> torch.Tensor:
+        self._check_in(x, torch.bfloat16, "hidden_states")
+        perm = torch.zeros(rows_padded, self.H, dtype=torch.bfloat16, device=self.device)
+        with torch.cuda.device(self.device):
+            L.check(self.lib.mg_permute_rows(self._h, x.data_ptr(), dst_row.data_ptr(), x.shape[0],
+                                             perm.data_ptr(), self._stream()))
+        return perm
+
+    def expert_ffn(self, perm_x: torch.Tensor, pad_offsets: torch.Tensor, counts: torch.Tensor):
+        """-> (h_buf [rows,I], out_rows [rows,H]) over the padded expert-sorted rows."""
+        rows = perm_x.shape[0]
+        hbuf = torch.zeros(rows, self.I, dtype=torch.bfloat16, device=self.device)
+        out = torch.zeros(rows, self.H, dtype=torch.bfloat16, device=self.device)
+        nb = C.c_size_t()
+        L.check(self.lib.mg_dequant_ws_bytes(self._h, C.byref(nb)))
+        deq = torch.empty(nb.value, dtype=torch.uint8, device=self.device) if nb.value else None
+        with torch.cuda.device(self.device):
+            L.check(self.lib.mg_expert_ffn(self._h, perm_x.data_ptr(), pad_offsets.data_ptr(), counts.data_ptr(),
+                                           rows, self.packed.data_ptr(), hbuf.data_ptr(), out.data_ptr(),
+                                           _ptr(deq), self._stream()))
+            if deq is not None:
+                torch.cuda.current_stream().synchronize()
+        return hbuf, out
+
+    def shared_ffn(self, x: torch.Tensor) -> torch.Tensor:
+        self._check_in(x, torch.bfloat16, "hidden_states")
+        T = x.shape[0]
+        hs = torch.empty(T, self.Is, dtype=torch.bfloat16, device=self.device)
+        out = torch.empty(T, self.H, dtype=torch.bfloat16, device=self.device)
+        with torch.cuda.device(self.device):
+            L.check(self.lib.mg_shared_ffn(self._h, x.data_ptr(), T, self.packed.data_ptr(), hs.data_ptr(),
+                                           out.data_ptr(), self._stream()))
+        return out
+
+    def combine(self, out_rows: torch.Tensor, dst_row: torch.Tensor, topk_idx: torch.Tensor,
+                topk_w: torch.Tensor, shared_out: Optional[torch.Tensor] = None) -> torch.Tensor:
+        T = topk_idx.shape[0]
+        y = torch.empty(T, self.H, dtype=torch.bfloat16, device=self.device)
+        with torch.cuda.device(self.device):
+            L.check(self.lib.mg_combine(self._h, out_rows.data_ptr(), dst_row.data_ptr(), topk_idx.data_ptr(),
+                                        topk_w.data_ptr(), _ptr(shared_out), T, y.data_ptr(), self._stream()))
+        return y
+
+    def dequant_fp8(self, q: torch.Tensor, scale_inv: torch.Tensor) -> torch.Tensor:
+        """bf16(float(q) * scale[r/128][c/128]) (moe_gen/models/Wrapper.py:109-138)."""
+        q = q.to(self.device).contiguous()
+        s = scale_inv.to(self.device, torch.float32).contiguous()
+        out = torch.empty(q.shape, dtype=torch.bfloat16, device=self.device)
+        with torch.cuda.device(self.device):
+            L.check(self.lib.mg_dequant_fp8_block128(q.data_ptr(), s.data_ptr(), q.shape[0], q.shape[1],
+                                                     out.data_ptr(), self._stream()))
+        return out

@@ -1,0 +1,69 @@
+"""CPU: the C-ABI library builds, loads, exports every symbol the header declares, and
+rejects bad arguments on the host without touching a GPU."""
+import ctypes as C
+import os
+import re
+
+import pytest
+
+from moe_gen_b200 import lib as L
+
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+
+
+def _header_functions():
+    src = open(os.path.join(ROOT, "include", "moegen_b200.h")).read()
+    src = re.sub(r"/\*.*?\*/", "", src, flags=re.S)
+    return sorted(set(re.findall(r"\b(mg_[a-z0-9_]+)\s*\(", src)))
+
+
+def test_every_declared_symbol_is_exported(built_lib):
+    lib = C.CDLL(built_lib)
+    names = _header_functions()
+    assert len(names) >= 20
+    for n in names:
+        assert hasattr(lib, n), f"{n} declared in include/moegen_b200.h but not exported"
+
+
+def test_binding_covers_the_header(built_lib):
+    declared = set(_header_functions()) - {"mg_last_error"}
+    assert declared == set(L.SIGNATURES), declared ^ set(L.SIGNATURES)
+
+
+def test_layer_desc_matches_header():
+    src = open(os.path.join(ROOT, "include", "moegen_b200.h")).read()
+    body = re.search(r"typedef struct mg_layer_desc \{(.*?)\} mg_layer_desc;", src, re.S).group(1)
+    body = re.sub(r"/\*.*?\*/", "", body, flags=re.S)
+    fields = re.findall(r"\b(?:int32_t|float)\s+([a-z_0-9]+)\s*;", body)
+    assert fields == [f[0] for f in L.LayerDesc._fields_]
+    assert C.sizeof(L.LayerDesc) == 4 * len(fields)
+
+
+@pytest.mark.parametrize("field,value,code", [
+    ("hidden", 250, -2), ("inter", 100, -2), ("top_k", 0, -2), ("top_k", 65, -2),
+    ("gating", 9, -3), ("weight_format", 7, -3), ("ep_size", 3, -3), ("struct_bytes", 8, -3),
+])
+def test_create_rejects_bad_descriptions_on_the_host(built_lib, field, value, code):
+    lib = L.load()
+    d = L.LayerDesc(C.sizeof(L.LayerDesc), 256, 128, 0, 64, 6, 1, 1, 0, 0, 1.0, 0, 0, 0, 1)
+    setattr(d, field, value)
+    h = C.c_void_p()
+    assert lib.mg_create(C.byref(d), C.byref(h)) == code
+    assert lib.mg_last_error() != b""
+    assert not h.value
+
+
+def test_null_arguments_are_errors_not_crashes(built_lib):
+    lib = L.load()
+    assert lib.mg_create(None, None) == -1
+    assert lib.mg_destroy(None) == -5
+    n = C.c_size_t()
+    assert lib.mg_packed_weight_bytes(None, C.byref(n)) == -5
+    assert lib.mg_dequant_fp8_block128(None, None, 1, 16, None, None) == -1
+
+
+def test_missing_library_fails_loudly(monkeypatch, tmp_path):
+    monkeypatch.setattr(L, "_lib", None)
+    monkeypatch.setattr(L, "LIB_PATH", str(tmp_path / "nope.so"))
+    with pytest.raises(RuntimeError, match="no CPU or PyTorch fallback"):
+        L.load()
