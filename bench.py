@@ -1,0 +1,418 @@
+#!/usr/bin/env python
+"""Benchmark of the MoE-layer hot path.
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl reference]
+                    [--workload v3|v2_236b|mixtral8x7b|v2lite] [--tokens T] [--zipf A]
+
+One step = one forward of one MoE layer over T tokens of synthetic hidden states.
+Default workload: DeepSeek-V3/R1 layer shape, W8A16 (FP8-e4m3 expert weights with 128x128
+block scales), T = 65536 tokens, seed 3.  Rank 0 prints ONE JSON line.
+
+  value     tokens/s with inputs resident in HBM (CUDA events, max over ranks)
+  e2e       tokens/s through MoELayer.forward_host: pinned host input -> device -> layer ->
+            host output, copies inside the timed region
+  roofline  the dominant kernel (routed gate/up grouped GEMM with the SiLU*mul epilogue):
+            algorithmic FLOPs per launch / mean device time of that stage, against the measured
+            sustained bf16 GEMM throughput of this pool
+  cpu_baseline  the CPU restatement of the reference layer (oracle/moe_oracle.py, torch CPU ops,
+            all host threads) on a bounded token sample of the same layer
+
+--impl reference times that CPU restatement alone (the reference ships no device code for
+this path; its layer is PyTorch arithmetic, which the oracle restates and which cannot be
+imported on the benchmark machine).
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import subprocess
+import sys
+import threading
+import time
+
+import torch
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+if ROOT not in sys.path:
+    sys.path.insert(0, ROOT)
+
+WORKLOADS = {
+    # name: (hidden, inter, n_experts, top_k, inter_shared, n_group, topk_group, gating, norm, scale, wfmt, combine, T, seed)
+    "v3": (7168, 2048, 256, 8, 2048, 8, 4, 2, True, 2.5, 1, 0, 65536, 3),
+    "v2_236b": (5120, 1536, 160, 6, 3072, 8, 3, 1, False, 16.0, 0, 1, 32768, 2),
+    "mixtral8x7b": (4096, 14336, 8, 2, 0, 1, 1, 3, True, 1.0, 0, 2, 16384, 1),
+    "v2lite": (2048, 1408, 64, 6, 2816, 1, 1, 0, False, 1.0, 0, 1, 2048, 0),
+    # the V3 layer with 32 experts and 4096 tokens: same kernels, same rows per expert per tile wave,
+    # a few GB on the device -- the case profiler captures are taken on
+    "v3_small": (7168, 2048, 32, 8, 2048, 8, 4, 2, True, 2.5, 1, 0, 4096, 3),
+}
+WORKLOAD_TEXT = {
+    "v3": "DeepSeek-V3/R1 MoE layer W8A16: H=7168 E=256 k=8 I=2048 shared I=2048, sigmoid+bias noaux_tc G=8 keep 4",
+    "v2_236b": "DeepSeek-V2-236B MoE layer bf16: H=5120 E=160 k=6 I=1536 shared I=3072, softmax group-limited G=8 keep 3",
+    "mixtral8x7b": "Mixtral-8x7B MoE layer bf16: H=4096 E=8 k=2 I=14336, softmax top-2 renormalised",
+    "v2lite": "DeepSeek-V2-Lite MoE layer bf16: H=2048 E=64 k=6 I=1408 shared I=2816, softmax greedy",
+    "v3_small": "DeepSeek-V3 layer shape cut to 32 experts (profiling case): H=7168 E=32 k=8 I=2048 shared I=2048",
+}
+FALLBACK_PEAKS = {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0, "bf16_tflops_sustained": 1400.0}
+
+
+def measured_peaks():
+    p = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.exists(p):
+        try:
+            return json.load(open(p)), "measured"
+        except Exception:
+            pass
+    return dict(FALLBACK_PEAKS), "fallback"
+
+
+# --------------------------------------------------------------------------------------
+# synthetic layer on the device
+# --------------------------------------------------------------------------------------
+def quantize_fp8_block128_gpu(w: torch.Tensor):
+    """Per-128x128-block e4m3 quantisation with scale = amax/448 (the DeepSeek-V3 checkpoint
+    format: moe_gen/models/deepseek/deepseekv3/deepseekv3_initializer.py:191-205)."""
+    m, n = w.shape
+    v = w.view(m // 128, 128, n // 128, 128)
+    amax = v.abs().float().amax(dim=(1, 3), keepdim=True).clamp(1e-4)
+    q = (v * (448.0 / amax)).to(torch.float8_e4m3fn)
+    return q.view(m, n).contiguous(), (amax / 448.0).view(m // 128, n // 128).contiguous()
+
+
+def build_layer(name: str, device, ep_rank=0, ep_size=1, zipf=0.0):
+    from moe_gen_b200 import MoELayer
+    H, I, E, k, Is, G, keep, gating, norm, scale, wfmt, comb, _, seed = WORKLOADS[name]
+    layer = MoELayer(hidden=H, inter=I, n_experts=E, top_k=k, inter_shared=Is, n_group=G, topk_group=keep,
+                     gating=gating, norm_topk_prob=norm, routed_scale=scale, weight_format=wfmt,
+                     combine_mode=comb, ep_rank=ep_rank, ep_size=ep_size, device=device)
+    g = torch.Generator(device=device).manual_seed(seed)           # same on every rank
+    gate_w = (torch.randn(E, H, generator=g, device=device) * 0.02).to(torch.bfloat16)
+    bias = torch.randn(E, generator=g, device=device) * 0.01 if gating == 2 else None
+    if zipf > 0:
+        # per-expert logit offset through hidden column 0 (set to 1.0 in the inputs)
+        perm = torch.randperm(E, generator=g, device=device)
+        pmf = 1.0 / torch.arange(1, E + 1, dtype=torch.float64, device=device) ** zipf
+        b = (pmf / pmf.sum()).log()
+        col = torch.empty(E, device=device)
+        col[perm] = (b - b.mean()).float()
+        gate_w[:, 0] = col.to(torch.bfloat16)
+    layer.set_router(gate_w, bias)
+    ge = torch.Generator(device=device)
+    for i in range(layer.e_local):
+        ge.manual_seed(seed * 100003 + layer.expert_lo + i)        # per global expert id
+        mats = [(torch.randn(r, c, generator=ge, device=device) * 0.02).to(torch.bfloat16)
+                for r, c in ((I, H), (I, H), (H, I))]
+        if wfmt == 1:
+            qs = [quantize_fp8_block128_gpu(m) for m in mats]
+            layer.load_expert(i, qs[0][0], qs[1][0], qs[2][0], (qs[0][1], qs[1][1], qs[2][1]))
+        else:
+            layer.load_expert(i, *mats)
+    if Is:
+        ge.manual_seed(seed * 100003 + 99991)
+        layer.load_shared(*[(torch.randn(r, c, generator=ge, device=device) * 0.02).to(torch.bfloat16)
+                            for r, c in ((Is, H), (Is, H), (H, Is))])
+    return layer
+
+
+def make_tokens(name: str, T: int, device, rank=0, zipf=0.0):
+    H = WORKLOADS[name][0]
+    seed = WORKLOADS[name][13]
+    g = torch.Generator(device=device).manual_seed(seed * 7919 + 17 + rank)
+    x = torch.randn(T, H, generator=g, device=device).to(torch.bfloat16)
+    if zipf > 0:
+        x[:, 0] = 1.0
+    return x
+
+
+# --------------------------------------------------------------------------------------
+# clocks
+# --------------------------------------------------------------------------------------
+class ClockSampler:
+    FIELDS = ("clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.hw_slowdown,"
+              "clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,"
+              "clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, index: int):
+        self.index, self.proc, self.lines = index, None, []
+
+    def start(self):
+        try:
+            self.proc = subprocess.Popen(["nvidia-smi", "-i", str(self.index), f"--query-gpu={self.FIELDS}",
+                                          "--format=csv,noheader,nounits", "-lms", "100"],
+                                         stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+            self.thread = threading.Thread(target=self._read, daemon=True)
+            self.thread.start()
+        except Exception:
+            self.proc = None
+
+    def _read(self):
+        for line in self.proc.stdout:
+            self.lines.append(line.strip())
+
+    def stop(self):
+        if self.proc is None:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
+        self.proc.terminate()
+        try:
+            self.proc.wait(timeout=5)
+        except Exception:
+            self.proc.kill()
+        sm, mx, pw, reasons = [], [], [], set()
+        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
+        for ln in self.lines:
+            f = [s.strip() for s in ln.split(",")]
+            if len(f) < 7:
+                continue
+            try:
+                sm.append(float(f[0])); mx.append(float(f[1])); pw.append(float(f[2]))
+            except ValueError:
+                continue
+            for n, v in zip(names, f[3:7]):
+                if v.lower().startswith("active"):
+                    reasons.add(n)
+        sm.sort()
+        return {"sm_mhz": sm[len(sm) // 2] if sm else None, "sm_max_mhz": max(mx) if mx else None,
+                "power_w_max": max(pw) if pw else None, "samples": len(sm), "reasons": sorted(reasons)}
+
+
+# --------------------------------------------------------------------------------------
+# CPU restatement of the reference layer (baseline leg and --impl reference)
+# --------------------------------------------------------------------------------------
+def cpu_reference(name: str, t_sample: int, steps: int, warmup: int, zipf=0.0):
+    """Times oracle.layer_forward (bf16, as the reference modules run on CPU) on t_sample tokens.
+    Expert weights: N(0,0.02) bf16 drawn once for min(E,16) distinct experts and reused cyclically
+    (each expert's matrices are far larger than the host caches, so reuse 16 experts apart does not
+    change the memory behaviour; it only bounds set-up time and host memory)."""
+    from oracle import moe_oracle as O
+    H, I, E, k, Is, G, keep, gating, norm, scale, wfmt, comb = WORKLOADS[name][:12]
+    spec = O.LayerSpec(H, I, E, k, Is, G, keep, gating, norm, scale, wfmt, comb, name)
+    threads = os.cpu_count() or 1
+    torch.set_num_threads(threads)
+    g = torch.Generator().manual_seed(WORKLOADS[name][13])
+    H, I, E = spec.hidden, spec.inter, spec.n_experts
+    x = torch.randn(t_sample, H, generator=g).to(torch.bfloat16)
+    gate_w = (torch.randn(E, H, generator=g) * 0.02).to(torch.bfloat16)
+    bias = torch.randn(E, generator=g) * 0.01 if spec.gating == O.GATE_SIGMOID_NOAUX_TC else None
+    W = O.LayerWeights(gate_w, bias)
+    distinct = min(E, 16)
+    base = [[(torch.randn(r, c, generator=g) * 0.02).to(torch.bfloat16) for r, c in ((I, H), (I, H), (H, I))]
+            for _ in range(distinct)]
+    for e in range(E):
+        m = base[e % distinct]
+        W.w_gate.append(m[0]); W.w_up.append(m[1]); W.w_down.append(m[2])
+    if spec.inter_shared:
+        Is = spec.inter_shared
+        W.shared = tuple((torch.randn(r, c, generator=g) * 0.02).to(torch.bfloat16)
+                         for r, c in ((Is, H), (Is, H), (H, Is)))
+    if zipf > 0:
+        x[:, 0] = 1.0
+    with torch.no_grad():
+        for _ in range(warmup):
+            O.layer_forward(spec, x, W)
+        t0 = time.perf_counter()
+        for _ in range(steps):
+            O.layer_forward(spec, x, W)
+        dt = (time.perf_counter() - t0) / max(steps, 1)
+    return {"tokens_per_s": t_sample / dt, "ms_per_step": dt * 1e3, "cores": threads,
+            "sample": f"{t_sample} tokens of the {name} layer per step, full expert count, "
+                      f"{distinct} distinct expert weight sets reused cyclically, torch CPU bf16, "
+                      f"{steps} timed steps after {warmup} warm-up"}
+
+
+# --------------------------------------------------------------------------------------
+def algorithmic(name: str, T: int):
+    H, I, E, k, Is = WORKLOADS[name][:5]
+    R = T * k
+    return {
+        "gemm1_flops": 4.0 * R * H * I, "gemm2_flops": 2.0 * R * H * I,
+        "shared_flops": 6.0 * T * H * Is, "gate_flops": 2.0 * T * H * E,
+        "permute_bytes": T * H * 2 + R * H * 2 + R * 4 + (E + 1) * 4,
+        "combine_bytes": R * H * 2 + R * 4 + T * H * 2 + (T * H * 2 if Is else 0),
+        "gate_bytes": T * H * 2 + E * H * 2 + T * E * 4,
+        "topk_bytes": T * E * 4 + T * k * 8,
+    }
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=10)
+    ap.add_argument("--warmup", type=int, default=3)
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--workload", default="v3", choices=sorted(WORKLOADS))
+    ap.add_argument("--tokens", type=int, default=0)
+    ap.add_argument("--zipf", type=float, default=0.0)
+    ap.add_argument("--cpu-sample-tokens", type=int, default=4096)
+    ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--no-e2e", action="store_true")
+    ap.add_argument("--chunk-tokens", type=int, default=16384)
+    args = ap.parse_args()
+
+    rank = int(os.environ.get("RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+    name = args.workload
+    T = args.tokens or WORKLOADS[name][12]
+    H, I, E, k, Is = WORKLOADS[name][:5]
+    warmup = max(args.warmup, 3) if args.impl == "ours" else args.warmup
+    config = {"workload": WORKLOAD_TEXT[name], "tokens": T, "seed": WORKLOADS[name][13],
+              "zipf_alpha": args.zipf, "l2": "inputs exceed L2 (x, routed rows and weights are each >126 MB)"
+              if T * H * 2 > 126e6 else "L2 flushed between steps by writing a 256 MB buffer"}
+
+    # ------------------------------------------------------------------ reference arm (CPU)
+    if args.impl == "reference":
+        if rank != 0:
+            return
+        r = cpu_reference(name, min(args.cpu_sample_tokens, T), max(args.steps, 1), args.warmup, args.zipf)
+        out = {"impl": "reference", "metric": "MoE-layer tokens/s", "value": r["tokens_per_s"], "unit": "tokens/s",
+               "n_gpus": args.gpus, "steps": args.steps, "warmup": args.warmup, "ms_per_step": r["ms_per_step"],
+               "higher_is_better": True, "scaling": "strong", "vs_baseline": None, "dtype": "bf16",
+               "data": "synthetic", "config": config,
+               "cpu_baseline": {"value": r["tokens_per_s"], "unit": "tokens/s", "cores": r["cores"],
+                                "kind": "port", "sample": r["sample"]},
+               "e2e": {"value": r["tokens_per_s"], "unit": "tokens/s", "h2d_bytes_per_step": 0,
+                       "d2h_bytes_per_step": 0}, "gpu_launches": 0}
+        print(json.dumps(out), flush=True)
+        return
+
+    # ------------------------------------------------------------------ our arm
+    if not torch.cuda.is_available():
+        raise SystemExit("bench.py needs a CUDA device: the library has no CPU path")
+    import torch.distributed as dist
+    torch.cuda.set_device(local_rank)
+    device = torch.device("cuda", local_rank)
+    if world > 1:
+        dist.init_process_group("nccl", device_id=device)
+    peaks, peak_kind = measured_peaks()
+
+    if world == 1:
+        layer = build_layer(name, device, zipf=args.zipf)
+        x = make_tokens(name, T, device, 0, args.zipf)
+        step = lambda: layer.forward(x)                                   # noqa: E731
+        T_total = T
+    else:
+        from moe_gen_b200.ep import EPMoELayer
+        assert T % world == 0
+        layer = EPMoELayer(build_layer(name, device, rank, world, args.zipf))
+        x = make_tokens(name, T // world, device, rank, args.zipf)
+        step = lambda: layer.forward(x)                                   # noqa: E731
+        T_total = T
+    flush = None if T * H * 2 > 126e6 else torch.empty(256 << 20, dtype=torch.uint8, device=device)
+
+    def run_step():
+        if flush is not None:
+            flush.zero_()
+        return step()
+
+    base = layer.layer if world > 1 else layer
+    for _ in range(warmup):
+        y = run_step()
+    torch.cuda.synchronize()
+    code, detail = base.device_status()
+    if code != 0:
+        raise SystemExit(f"device status {code} (detail {detail}) after warm-up")
+    base.set_stage_timing(True)
+    sampler = ClockSampler(local_rank)
+    if rank == 0:
+        sampler.start()
+    if world > 1:
+        dist.barrier()
+    torch.cuda.synchronize()
+    ev0, ev1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    ev0.record()
+    for _ in range(args.steps):
+        y = run_step()
+    ev1.record()
+    torch.cuda.synchronize()
+    if world > 1:
+        dist.barrier()
+    ms = ev0.elapsed_time(ev1)
+    clocks = sampler.stop() if rank == 0 else None
+    if world > 1:
+        t = torch.tensor([ms], device=device)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        ms = float(t.item())
+    stage_ms = base.stage_times()
+    base.set_stage_timing(False)
+    launches = base.last_launch_count() + (1 if flush is not None else 0)
+    code, detail = base.device_status()
+    if code != 0:
+        raise SystemExit(f"device status {code} (detail {detail}) in the timed region")
+    ms_per_step = ms / args.steps
+    value = T_total / (ms_per_step * 1e-3)
+
+    # ------------------------------------------------------------------ e2e: host buffers in and out
+    e2e = None
+    if not args.no_e2e and world == 1:
+        xh = x.cpu().pin_memory()
+        yh = torch.empty_like(xh).pin_memory()
+        for _ in range(2):
+            layer.forward_host(xh, yh, chunk_tokens=args.chunk_tokens)
+        torch.cuda.synchronize()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        for _ in range(args.steps):
+            layer.forward_host(xh, yh, chunk_tokens=args.chunk_tokens)
+        e1.record()
+        torch.cuda.synchronize()
+        e_ms = e0.elapsed_time(e1) / args.steps
+        same = torch.equal(yh.view(torch.int16), y.cpu().view(torch.int16))
+        e2e = {"value": T / (e_ms * 1e-3), "unit": "tokens/s", "ms_per_step": e_ms,
+               "h2d_bytes_per_step": xh.numel() * 2, "d2h_bytes_per_step": yh.numel() * 2,
+               "equals_device_path": bool(same), "chunk_tokens": args.chunk_tokens}
+    elif not args.no_e2e:
+        e2e = layer.bench_e2e(x, args.steps) if hasattr(layer, "bench_e2e") else None
+
+    if rank != 0:
+        if world > 1:
+            dist.destroy_process_group()
+        return
+
+    alg = algorithmic(name, T_total)
+    t_g1 = stage_ms["expert_gemm1"] * 1e-3
+    tf = alg["gemm1_flops"] / world / t_g1 / 1e12 if t_g1 > 0 else 0.0
+    peak_tf = peaks.get("bf16_tflops_sustained", FALLBACK_PEAKS["bf16_tflops_sustained"])
+    roofline = {"kernel": "grouped_gemm_kernel<SWIGLU> (routed gate/up projections + SiLU*mul)",
+                "bound": "tensor", "achieved": tf, "peak": peak_tf, "unit": "TFLOP/s", "frac": tf / peak_tf,
+                "peak_kind": f"of {peak_kind} sustained bf16 GEMM", "frac_of_burst": tf / peaks.get("bf16_tflops", 1590.0),
+                "traffic": None}
+    hbm = peaks.get("hbm_gbs", FALLBACK_PEAKS["hbm_gbs"])
+    Tl = T_total // world
+    algl = algorithmic(name, Tl)
+    stages = {}
+    for st, num, unit in (("permute_rows", algl["permute_bytes"], "GB/s"), ("combine", algl["combine_bytes"], "GB/s"),
+                          ("route_topk", algl["topk_bytes"], "GB/s"), ("gate_logits", algl["gate_bytes"], "GB/s"),
+                          ("expert_gemm1", alg["gemm1_flops"] / world, "TFLOP/s"),
+                          ("expert_gemm2", alg["gemm2_flops"] / world, "TFLOP/s"),
+                          ("shared_gemm1", algl["shared_flops"] * 2 / 3, "TFLOP/s"),
+                          ("shared_gemm2", algl["shared_flops"] / 3, "TFLOP/s")):
+        t = stage_ms.get(st, 0.0) * 1e-3
+        if t > 0 and num > 0:
+            rate = num / t / (1e9 if unit == "GB/s" else 1e12)
+            stages[st] = {"ms": round(t * 1e3, 4), "achieved": round(rate, 1), "unit": unit,
+                          "frac": round(rate / (hbm if unit == "GB/s" else peak_tf), 3)}
+    for st in ("permute_plan", "dequant"):
+        if stage_ms.get(st, 0.0) > 0:
+            stages[st] = {"ms": round(stage_ms[st], 4)}
+
+    cpu = None
+    if not args.no_cpu_baseline:
+        r = cpu_reference(name, min(args.cpu_sample_tokens, T), 2, 1, args.zipf)
+        cpu = {"value": r["tokens_per_s"], "unit": "tokens/s", "cores": r["cores"], "kind": "port",
+               "sample": r["sample"]}
+
+    out = {"metric": "MoE-layer tokens/s", "value": value, "unit": "tokens/s", "n_gpus": world, "steps": args.steps,
+           "warmup": warmup, "ms_per_step": ms_per_step, "higher_is_better": True, "scaling": "strong",
+           "vs_baseline": None, "dtype": "bf16", "data": "synthetic", "config": config, "clocks": clocks,
+           "e2e": e2e, "gpu_launches": launches * args.steps, "roofline": roofline, "cpu_baseline": cpu,
+           "stages": stages,
+           "layer_tflops": (alg["gemm1_flops"] + alg["gemm2_flops"] + alg["shared_flops"] + alg["gate_flops"])
+           / (ms_per_step * 1e-3) / 1e12 / world}
+    print(json.dumps(out), flush=True)
+    if world > 1:
+        dist.destroy_process_group()
+
+
+if __name__ == "__main__":
+    main()

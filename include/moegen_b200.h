@@ -63,6 +63,19 @@ extern "C" {
 #define MG_DEV_OK             0
 #define MG_DEV_WAIT_TIMEOUT   1  /* a bounded mbarrier wait ran out; results invalid */
 
+/* stages of mg_moe_forward, in launch order (mg_stage_times) */
+#define MG_STAGE_GATE_LOGITS   0
+#define MG_STAGE_ROUTE_TOPK    1
+#define MG_STAGE_PERMUTE_PLAN  2
+#define MG_STAGE_PERMUTE_ROWS  3
+#define MG_STAGE_DEQUANT       4
+#define MG_STAGE_EXPERT_GEMM1  5  /* gate/up projections + SiLU*mul */
+#define MG_STAGE_EXPERT_GEMM2  6  /* down projection */
+#define MG_STAGE_SHARED_GEMM1  7
+#define MG_STAGE_SHARED_GEMM2  8
+#define MG_STAGE_COMBINE       9
+#define MG_STAGE_COUNT        10
+
 typedef struct mg_layer_desc {
   int32_t struct_bytes;    /* = sizeof(mg_layer_desc), for versioning */
   int32_t hidden;          /* H:  config.hidden_size */
@@ -218,6 +231,15 @@ int mg_workspace_ptr(mg_handle h, void* d_workspace, int64_t max_tokens, int64_t
 
 /* Number of kernel launches the last mg_moe_forward on this handle issued. */
 int mg_last_launch_count(mg_handle h, int32_t* launches);
+
+/* Per-stage device times of mg_moe_forward (no counterpart in the reference, whose
+ * timers are commented out: moe_gen/models/Wrapper.py:112-137).  When enabled, the
+ * forward records a CUDA event on `stream` after every stage; after the caller has
+ * synchronised, mg_stage_times() returns the milliseconds per MG_STAGE_* (0 for stages
+ * the layer does not have), averaged over the forwards since timing was enabled (the
+ * last 32 if there were more). */
+int mg_set_stage_timing(mg_handle h, int32_t enable);
+int mg_stage_times(mg_handle h, float* ms, int32_t n);
 
 #ifdef __cplusplus
 }

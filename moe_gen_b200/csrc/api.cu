@@ -109,6 +109,10 @@ int mg_create(const mg_layer_desc* desc, mg_handle* out) {
   h->d = d;
   h->e_local = d.n_experts / d.ep_size;
   h->last_launches = 0;
+  h->stage_timing = false;
+  h->stage_calls = 0;
+  for (int s = 0; s < kStageSlots; ++s)
+    for (int i = 0; i <= MG_STAGE_COUNT; ++i) h->stage_ev[s][i] = nullptr;
   cudaError_t e = cudaGetDevice(&h->device);
   if (e == cudaSuccess) e = cudaDeviceGetAttribute(&h->sm_count, cudaDevAttrMultiProcessorCount, h->device);
   int major = 0;
@@ -129,6 +133,9 @@ int mg_destroy(mg_handle hh) {
   Handle* h = check(hh);
   if (!h) return MG_ERR_STATE;
   cudaFree(h->d_status);
+  for (int s = 0; s < kStageSlots; ++s)
+    for (int i = 0; i <= MG_STAGE_COUNT; ++i)
+      if (h->stage_ev[s][i]) cudaEventDestroy(h->stage_ev[s][i]);
   h->magic = 0;
   delete h;
   return MG_OK;
@@ -246,8 +253,14 @@ int mg_dequant_ws_bytes(mg_handle hh, size_t* bytes) {
   return MG_OK;
 }
 
+// records the event that ends `stage` (and every skipped stage before it) when timing is on
+static void mark(Handle* h, int stage, cudaStream_t st) {
+  if (h->stage_timing) cudaEventRecord(h->stage_ev[h->stage_calls % kStageSlots][stage + 1], st);
+}
+
 static int expert_ffn(Handle* h, const void* perm_x, const int32_t* pad, const int32_t* counts, int64_t rows_padded,
-                      const void* packed, void* h_buf, void* out_rows, void* deq, cudaStream_t st, int* launches) {
+                      const void* packed, void* h_buf, void* out_rows, void* deq, cudaStream_t st, int* launches,
+                      bool timed = false) {
   const mg_layer_desc& d = h->d;
   const PackedLayout L = packed_layout(h);
   const uint8_t* base = static_cast<const uint8_t*>(packed);
@@ -261,15 +274,18 @@ static int expert_ffn(Handle* h, const void* perm_x, const int32_t* pad, const i
     w2 = static_cast<const __nv_bfloat16*>(deq) + static_cast<size_t>(h->e_local) * 2 * d.inter * d.hidden;
     if (launches) *launches += 2;
   }
+  if (timed) mark(h, MG_STAGE_DEQUANT, st);
   GemmProblem p{};
   p.a = perm_x; p.a_rows = rows_padded; p.b = w13; p.n_groups = h->e_local; p.n_per_group = 2 * d.inter;
   p.K = d.hidden; p.pad_offsets = pad; p.counts = counts; p.out = h_buf; p.ldo = d.inter;
   p.epilogue = EPI_SWIGLU_BF16;
   int rc = launch_grouped_gemm(h, p, st);
   if (rc != MG_OK) return rc;
+  if (timed) mark(h, MG_STAGE_EXPERT_GEMM1, st);
   p.a = h_buf; p.b = w2; p.n_per_group = d.hidden; p.K = d.inter; p.out = out_rows; p.ldo = d.hidden;
   p.epilogue = EPI_PLAIN_BF16;
   rc = launch_grouped_gemm(h, p, st);
+  if (timed) mark(h, MG_STAGE_EXPERT_GEMM2, st);
   if (launches) *launches += 2;
   return rc;
 }
@@ -287,7 +303,8 @@ int mg_expert_ffn(mg_handle hh, const void* d_perm_x, const int32_t* d_pad, cons
                     static_cast<cudaStream_t>(stream), nullptr);
 }
 
-static int shared_ffn(Handle* h, const void* x, int64_t T, const void* packed, void* hs, void* out, cudaStream_t st) {
+static int shared_ffn(Handle* h, const void* x, int64_t T, const void* packed, void* hs, void* out, cudaStream_t st,
+                      bool timed = false) {
   const mg_layer_desc& d = h->d;
   MG_REQUIRE(d.inter_shared > 0, MG_ERR_CONFIG, "layer has no shared expert");
   const PackedLayout L = packed_layout(h);
@@ -297,6 +314,7 @@ static int shared_ffn(Handle* h, const void* x, int64_t T, const void* packed, v
   p.dense_rows = T; p.out = hs; p.ldo = d.inter_shared; p.epilogue = EPI_SWIGLU_BF16;
   int rc = launch_grouped_gemm(h, p, st);
   if (rc != MG_OK) return rc;
+  if (timed) mark(h, MG_STAGE_SHARED_GEMM1, st);
   p.a = hs; p.b = base + L.sh2; p.n_per_group = d.hidden; p.K = d.inter_shared; p.out = out; p.ldo = d.hidden;
   p.epilogue = EPI_PLAIN_BF16;
   return launch_grouped_gemm(h, p, st);
@@ -333,8 +351,9 @@ int mg_moe_forward(mg_handle hh, const void* d_x, int64_t T, const void* d_gate_
                    const void* d_packed, void* d_ws, size_t ws_bytes, void* d_y, void* stream) {
   Handle* h = check(hh);
   if (!h) return MG_ERR_STATE;
-  MG_REQUIRE(d_x && d_gate_w && d_packed && d_ws && d_y, MG_ERR_NULL, "mg_moe_forward: null pointer");
   MG_REQUIRE(T >= 0, MG_ERR_SHAPE, "negative token count");
+  if (T == 0) { h->last_launches = 0; return MG_OK; }   // empty batch: nothing to read or write
+  MG_REQUIRE(d_x && d_gate_w && d_packed && d_ws && d_y, MG_ERR_NULL, "mg_moe_forward: null pointer");
   MG_REQUIRE(h->d.ep_size == 1, MG_ERR_CONFIG, "mg_moe_forward is the single-GPU path (ep_size == 1)");
   MG_REQUIRE(h->d.gating != MG_GATE_SIGMOID_NOAUX_TC || d_bias != nullptr, MG_ERR_NULL,
              "noaux_tc gating needs e_score_correction_bias");
@@ -361,27 +380,67 @@ int mg_moe_forward(mg_handle hh, const void* d_x, int64_t T, const void* d_gate_
   void* sh = d.inter_shared ? ws + L.off[WS_SHARED] : nullptr;
   void* deq = d.weight_format == MG_WEIGHT_FP8_BLOCK128 ? ws + L.off[WS_DEQ] : nullptr;
   int launches = 0;
+  if (h->stage_timing) MG_CUDA(cudaEventRecord(h->stage_ev[h->stage_calls % kStageSlots][0], st));
   int rc = mg_gate_logits(hh, d_x, d_gate_w, T, logits, stream);
   if (rc != MG_OK) return rc;
+  mark(h, MG_STAGE_GATE_LOGITS, st);
   rc = launch_route_topk(h, logits, d_bias, T, idx, w, st);
   if (rc != MG_OK) return rc;
+  mark(h, MG_STAGE_ROUTE_TOPK, st);
   launches += 2;
   rc = launch_permute_plan(h, idx, T, 0, d.n_experts, counts, offsets, pad, dst, plan, st, &launches);
   if (rc != MG_OK) return rc;
+  mark(h, MG_STAGE_PERMUTE_PLAN, st);
   rc = launch_permute_rows(h, d_x, dst, T, perm, st);
   if (rc != MG_OK) return rc;
+  mark(h, MG_STAGE_PERMUTE_ROWS, st);
   launches += 1;
-  rc = expert_ffn(h, perm, pad, counts, padded_rows(h, T * d.top_k), d_packed, hbuf, orow, deq, st, &launches);
+  rc = expert_ffn(h, perm, pad, counts, padded_rows(h, T * d.top_k), d_packed, hbuf, orow, deq, st, &launches, true);
   if (rc != MG_OK) return rc;
   if (d.inter_shared) {
-    rc = shared_ffn(h, d_x, T, d_packed, hs, sh, st);
+    rc = shared_ffn(h, d_x, T, d_packed, hs, sh, st, true);
     if (rc != MG_OK) return rc;
     launches += 2;
+  } else {
+    mark(h, MG_STAGE_SHARED_GEMM1, st);
   }
+  mark(h, MG_STAGE_SHARED_GEMM2, st);
   rc = launch_combine(h, orow, dst, idx, w, sh, T, d_y, st);
   if (rc != MG_OK) return rc;
+  mark(h, MG_STAGE_COMBINE, st);
   launches += 1;
   h->last_launches = launches;
+  if (h->stage_timing) ++h->stage_calls;
+  return MG_OK;
+}
+
+int mg_set_stage_timing(mg_handle hh, int32_t enable) {
+  Handle* h = check(hh);
+  if (!h) return MG_ERR_STATE;
+  if (enable) {
+    for (int s = 0; s < kStageSlots; ++s)
+      for (int i = 0; i <= MG_STAGE_COUNT; ++i)
+        if (!h->stage_ev[s][i]) MG_CUDA(cudaEventCreate(&h->stage_ev[s][i]));
+    h->stage_calls = 0;
+  }
+  h->stage_timing = enable != 0;
+  return MG_OK;
+}
+
+int mg_stage_times(mg_handle hh, float* ms, int32_t n) {
+  Handle* h = check(hh);
+  if (!h) return MG_ERR_STATE;
+  MG_REQUIRE(ms && n >= MG_STAGE_COUNT, MG_ERR_NULL, "mg_stage_times: need room for %d values", MG_STAGE_COUNT);
+  MG_REQUIRE(h->stage_calls > 0, MG_ERR_STATE, "no timed forward has completed on this handle");
+  const int n_sets = h->stage_calls < kStageSlots ? h->stage_calls : kStageSlots;
+  for (int i = 0; i < MG_STAGE_COUNT; ++i) ms[i] = 0.f;
+  for (int s = 0; s < n_sets; ++s) {
+    for (int i = 0; i < MG_STAGE_COUNT; ++i) {
+      float t = 0.f;
+      MG_CUDA(cudaEventElapsedTime(&t, h->stage_ev[s][i], h->stage_ev[s][i + 1]));
+      ms[i] += t / n_sets;
+    }
+  }
   return MG_OK;
 }
 

@@ -13,6 +13,7 @@ namespace mg {
 constexpr int kTileM = 128;          // rows per GEMM tile == expert segment alignment
 constexpr int kMaxExperts = 512;     // plan and top-k kernels keep per-expert state on chip
 constexpr int kMaxTopK = 16;
+constexpr int kStageSlots = 32;      // forwards whose per-stage times are kept for averaging
 
 // thread-local error text -------------------------------------------------------------
 void set_error(const char* fmt, ...);
@@ -37,6 +38,9 @@ struct Handle {
   int e_local;            // experts owned by this rank
   int32_t* d_status;      // [2]: code, detail
   int last_launches;
+  bool stage_timing;      // record an event after every stage of mg_moe_forward
+  int stage_calls;        // forwards recorded since timing was enabled
+  cudaEvent_t stage_ev[kStageSlots][MG_STAGE_COUNT + 1];   // ring of event sets, one per forward
 };
 constexpr uint32_t kMagic = 0x4d474232u;  // "MGB2"
 

@@ -125,6 +125,15 @@ class MoELayer:
         L.check(self.lib.mg_device_status(self._h, C.byref(code), C.byref(detail)))
         return code.value, detail.value
 
+    def set_stage_timing(self, enable: bool):
+        L.check(self.lib.mg_set_stage_timing(self._h, int(enable)))
+
+    def stage_times(self) -> dict:
+        """Milliseconds per stage of the last forward (call after synchronising)."""
+        ms = (C.c_float * len(L.STAGES))()
+        L.check(self.lib.mg_stage_times(self._h, ms, len(L.STAGES)))
+        return dict(zip(L.STAGES, [float(v) for v in ms]))
+
     def last_launch_count(self) -> int:
         n = C.c_int32()
         L.check(self.lib.mg_last_launch_count(self._h, C.byref(n)))

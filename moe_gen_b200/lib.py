@@ -52,7 +52,12 @@ SIGNATURES = {
     "mg_moe_forward": [_vp, _vp, _i64, _vp, _vp, _vp, _vp, _sz, _vp, _vp],
     "mg_workspace_ptr": [_vp, _vp, _i64, _i64, _i32, _P(_vp)],
     "mg_last_launch_count": [_vp, _P(_i32)],
+    "mg_set_stage_timing": [_vp, _i32],
+    "mg_stage_times": [_vp, _P(C.c_float), _i32],
 }
+
+STAGES = ["gate_logits", "route_topk", "permute_plan", "permute_rows", "dequant", "expert_gemm1",
+          "expert_gemm2", "shared_gemm1", "shared_gemm2", "combine"]
 
 _lib = None
 

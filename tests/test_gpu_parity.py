@@ -1,0 +1,350 @@
+"""GPU parity tests: every stage and the whole layer, through the C ABI, against the CPU
+oracle on identical seeded inputs and against the fixtures recorded from the reference.
+
+Bars: routing indices, histogram and permutation bit-exact (tokens whose k-th / (k+1)-th
+selection scores are closer than the fp32 noise of the logits are exempt, counted and
+bounded); routing weights <= 1e-6 relative; de-quantisation and row copies bit-exact;
+layer output <= 1e-2 relative L2 of the fp32-accumulated reference output."""
+import numpy as np
+import pytest
+import torch
+
+from oracle import moe_oracle as O
+from tests.golden.make_golden import CASES, GATE_CASES
+from tests.util import bf16_from_bits, load_golden, make_layer
+
+pytestmark = pytest.mark.gpu
+
+DEV = "cuda:0"
+TOL_LAYER = 1e-2          # relative L2 vs the fp32-accumulated reference output
+TOL_WEIGHT = 1e-6         # routing weights, relative, on identical logits
+TOL_WEIGHT_FUSED = 1e-4   # same, when the logits come from the tensor-core router product, whose
+                          # fp32 accumulation differs from a scalar fp32 sum by up to ~1e-5 absolute
+NEAR_TIE = 1e-4           # relative gap below which that difference may decide a pick
+
+
+def _status_ok(layer):
+    torch.cuda.synchronize()
+    assert layer.device_status() == (0, 0)
+
+
+def _route_equal(spec, idx_gpu, w_gpu, idx_ref, w_ref, logits_ref, bias, exact_logits):
+    """Compares per-token sets; returns number of exempted near-tie tokens."""
+    gi, gw = O.canonical_sets(idx_gpu.cpu().long(), w_gpu.cpu())
+    ri, rw = O.canonical_sets(idx_ref.long(), w_ref)
+    same = (gi == ri).all(dim=1)
+    if exact_logits:
+        assert bool(same.all()), f"{int((~same).sum())} tokens differ on identical logits"
+    else:
+        gap = O.kth_gap(spec, logits_ref, bias)
+        bad = ~same
+        assert bool((gap[bad] < NEAR_TIE).all()), "a token with a clear score gap was routed differently"
+        assert int(bad.sum()) <= max(2, idx_ref.shape[0] // 500), f"{int(bad.sum())} near-tie flips"
+    rel = ((gw - rw).abs() / rw.abs().clamp_min(1e-12))[same]
+    if rel.numel():
+        assert float(rel.max()) <= (TOL_WEIGHT if exact_logits else TOL_WEIGHT_FUSED), float(rel.max())
+    return int((~same).sum())
+
+
+# --------------------------------------------------------------------------- routing
+@pytest.mark.parametrize("name", sorted(GATE_CASES))
+def test_topk_on_identical_logits_is_exact_at_full_gate_shapes(built_lib, name):
+    cfg, T, seed = GATE_CASES[name]
+    spec = O.named_spec(cfg)
+    gen = torch.Generator().manual_seed(seed)
+    x = torch.randn(T, spec.hidden, generator=gen).to(torch.bfloat16)
+    gw = (torch.randn(spec.n_experts, spec.hidden, generator=gen) * 0.02).to(torch.bfloat16)
+    bias = torch.randn(spec.n_experts, generator=gen) * 0.01 if spec.gating == O.GATE_SIGMOID_NOAUX_TC else None
+    W = O.LayerWeights(gw, bias)
+    layer = make_layer(O.LayerSpec(**{**spec.__dict__, "inter_shared": 0, "weight_format": 0}), W, DEV, 0, spec.n_experts)
+    logits = O.gate_logits(x, gw)
+    idx, w = layer.route_topk(logits.to(DEV))
+    ridx, rw = O.route(spec, logits, bias)
+    # slot order too: score descending, ties to the lower id
+    assert torch.equal(idx.cpu().long(), ridx)
+    _route_equal(spec, idx, w, ridx, rw, logits, bias, exact_logits=True)
+    # and against what the reference's own gate produced (recorded fixture)
+    g = load_golden(name)
+    gi, gwt = O.canonical_sets(idx.cpu().long(), w.cpu())
+    assert np.array_equal(gi.numpy().astype(np.int16), g["topk_idx"])
+    assert np.abs(gwt.numpy() - g["topk_w"]).max() <= 2e-6 * max(1.0, spec.routed_scale)
+    # fused path: logits from the tensor-core router GEMM
+    idx2, w2 = layer.route_topk(layer.gate_logits(x.to(DEV)))
+    _route_equal(spec, idx2, w2, ridx, rw, logits, bias, exact_logits=False)
+    _status_ok(layer)
+
+
+def test_ties_break_toward_lower_expert_id(built_lib):
+    spec = O.LayerSpec(256, 128, 16, 4, gating=O.GATE_SOFTMAX_GREEDY)
+    W = O.LayerWeights(torch.zeros(16, 256, dtype=torch.bfloat16), None)
+    layer = make_layer(spec, W, DEV, 0, 16)
+    logits = torch.zeros(3, 16)
+    logits[1, 5] = 1.0
+    logits[2, 8:] = 2.0
+    idx, w = layer.route_topk(logits.to(DEV))
+    assert idx.cpu().tolist() == [[0, 1, 2, 3], [5, 0, 1, 2], [8, 9, 10, 11]]
+    ridx, rw = O.route(spec, logits)
+    assert torch.allclose(w.cpu(), rw, rtol=1e-6, atol=0)
+
+
+def test_masked_groups_compete_as_zero(built_lib):
+    spec = O.LayerSpec(256, 128, 8, 3, n_group=4, topk_group=1, gating=O.GATE_SIGMOID_NOAUX_TC,
+                       norm_topk_prob=True, routed_scale=1.0)
+    bias = torch.full((8,), -0.5)
+    bias[2:4] = -0.1
+    W = O.LayerWeights(torch.zeros(8, 256, dtype=torch.bfloat16), bias)
+    layer = make_layer(spec, W, DEV, 0, 8)
+    logits = torch.full((1, 8), -20.0)
+    idx, w = layer.route_topk(logits.to(DEV))
+    ridx, rw = O.route(spec, logits, bias)
+    assert idx.cpu().tolist() == ridx.tolist() == [[0, 1, 4]]
+    assert torch.allclose(w.cpu(), rw, rtol=1e-5, atol=1e-12)
+
+
+@pytest.mark.parametrize("E,k,G,keep,gating", [
+    (8, 2, 1, 1, O.GATE_SOFTMAX_TOPK_RENORM), (64, 6, 1, 1, O.GATE_SOFTMAX_GREEDY),
+    (160, 6, 8, 3, O.GATE_SOFTMAX_GROUP_MAX), (256, 8, 8, 4, O.GATE_SIGMOID_NOAUX_TC),
+    (32, 1, 4, 2, O.GATE_SIGMOID_NOAUX_TC), (128, 8, 16, 5, O.GATE_SOFTMAX_GROUP_MAX),
+    (384, 8, 8, 4, O.GATE_SIGMOID_NOAUX_TC),
+])
+@pytest.mark.parametrize("T", [1, 2, 3, 127, 128, 129, 1000])
+def test_topk_exhaustive_small_shapes(built_lib, E, k, G, keep, gating, T):
+    spec = O.LayerSpec(256, 128, E, k, n_group=G, topk_group=keep, gating=gating, norm_topk_prob=(E % 3 == 0),
+                       routed_scale=2.5)
+    gen = torch.Generator().manual_seed(E * 1000 + T)
+    bias = torch.randn(E, generator=gen) * 0.01 if gating == O.GATE_SIGMOID_NOAUX_TC else None
+    W = O.LayerWeights(torch.zeros(E, 256, dtype=torch.bfloat16), bias)
+    layer = make_layer(spec, W, DEV, 0, E)
+    logits = torch.randn(T, E, generator=gen) * 1.7
+    idx, w = layer.route_topk(logits.to(DEV))
+    ridx, rw = O.route(spec, logits, bias)
+    _route_equal(spec, idx, w, ridx, rw, logits, bias, exact_logits=True)
+
+
+# --------------------------------------------------------------------------- permute
+@pytest.mark.parametrize("T,E,k", [(1, 8, 2), (3, 64, 6), (127, 64, 6), (128, 160, 6), (129, 256, 8), (5000, 256, 8),
+                                   (4096, 8, 2)])
+def test_permute_plan_and_rows_are_exact(built_lib, T, E, k):
+    spec = O.LayerSpec(512, 128, E, k)
+    W = O.LayerWeights(torch.zeros(E, 512, dtype=torch.bfloat16), None)
+    layer = make_layer(spec, W, DEV)
+    gen = torch.Generator().manual_seed(T + E)
+    # distinct experts per token, skewed so that some experts stay empty
+    scores = torch.rand(T, E, generator=gen)
+    scores[:, E // 2:] *= 0.2
+    scores[:, 1] = -1.0                      # expert 1 never chosen
+    idx = scores.topk(k, dim=-1).indices.to(torch.int32)
+    counts, offsets, pad, dst = layer.permute_plan(idx.to(DEV))
+    rc, roff, order, src = O.permute_plan(idx.long(), E)
+    assert torch.equal(counts.cpu().long(), rc)
+    assert torch.equal(offsets.cpu().long(), roff)
+    padc = pad.cpu().long()
+    assert torch.equal(padc[1:] - padc[:-1], (rc + 127) // 128 * 128)
+    # stable placement: the r-th row of expert e is the r-th pick of e in flattened order
+    flat_dst = dst.cpu().long().view(-1)
+    expert_of_sorted = torch.repeat_interleave(torch.arange(E), rc)
+    rank = torch.arange(order.numel()) - roff[expert_of_sorted]
+    assert torch.equal(flat_dst[order], padc[expert_of_sorted] + rank)
+    x = torch.randn(T, 512, generator=gen).to(torch.bfloat16)
+    rows = layer.padded_rows(T * k)
+    assert int(padc[-1]) <= rows
+    perm = layer.permute_rows(x.to(DEV), dst, rows).cpu()
+    assert torch.equal(perm[flat_dst].view(torch.int16), x[torch.arange(T * k) // k].view(torch.int16))
+    _status_ok(layer)
+
+
+def test_permute_plan_expert_range_skips_foreign_picks(built_lib):
+    spec = O.LayerSpec(256, 128, 64, 6)
+    W = O.LayerWeights(torch.zeros(64, 256, dtype=torch.bfloat16), None)
+    layer = make_layer(spec, W, DEV, 0, 64)
+    gen = torch.Generator().manual_seed(5)
+    idx = torch.rand(777, 64, generator=gen).topk(6, dim=-1).indices.to(torch.int32)
+    counts, offsets, pad, dst = layer.permute_plan(idx.to(DEV), expert_lo=16, n_plan=16)
+    local = (idx >= 16) & (idx < 32)
+    assert torch.equal(counts.cpu().long(), torch.bincount(idx[local].long() - 16, minlength=16))
+    assert bool((dst.cpu()[~local] == -1).all()) and bool((dst.cpu()[local] >= 0).all())
+
+
+# --------------------------------------------------------------------------- de-quantisation
+def test_fp8_dequant_is_bit_exact(built_lib):
+    spec = O.LayerSpec(256, 128, 8, 2)
+    layer = make_layer(spec, O.LayerWeights(torch.zeros(8, 256, dtype=torch.bfloat16), None), DEV, 0, 8)
+    gen = torch.Generator().manual_seed(3)
+    for shape in [(128, 256), (384, 512), (2048, 7168)]:
+        w = (torch.randn(*shape, generator=gen) * 0.02).to(torch.bfloat16)
+        q, s = O.quantize_fp8_block128(w)
+        out = layer.dequant_fp8(q, s).cpu()
+        assert torch.equal(out.view(torch.int16), O.dequantize_fp8_block128(q, s).view(torch.int16))
+
+
+# --------------------------------------------------------------------------- experts
+def _check_expert_rows(spec, W, x, layer, idx):
+    counts, offsets, pad, dst = layer.permute_plan(idx)
+    rows = layer.padded_rows(x.shape[0] * spec.top_k)
+    perm = layer.permute_rows(x, dst, rows)
+    hbuf, out = layer.expert_ffn(perm, pad, counts)
+    _status_ok(layer)
+    padc, cc, permc, outc = pad.cpu().long(), counts.cpu().long(), perm.cpu(), out.cpu()
+    worst = 0.0
+    for e in range(spec.n_experts):
+        n, r0 = int(cc[e]), int(padc[e])
+        if n == 0:
+            continue
+        ref = O.swiglu_mlp(permc[r0:r0 + n].float(), W.w_gate[e].float(), W.w_up[e].float(), W.w_down[e].float())
+        worst = max(worst, O.rel_l2(outc[r0:r0 + n].float(), ref))
+    return worst, (counts, offsets, pad, dst, out)
+
+
+@pytest.mark.parametrize("T", [1, 5, 128, 700])
+def test_grouped_swiglu_matches_fp32_oracle_with_ragged_and_empty_experts(built_lib, T):
+    spec = O.LayerSpec(512, 256, 16, 4, combine_mode=O.COMBINE_FP32)
+    x, W = O.make_inputs(spec, T, 40 + T)
+    layer = make_layer(spec, W, DEV)
+    gen = torch.Generator().manual_seed(T)
+    scores = torch.rand(T, 16, generator=gen)
+    scores[:, 3] = -1.0                       # empty expert
+    scores[:, 7] += 0.6                       # heavy expert
+    idx = scores.topk(4, dim=-1).indices.to(torch.int32).to(DEV)
+    worst, _ = _check_expert_rows(spec, W, x.to(DEV), layer, idx)
+    assert worst < 5e-3, worst
+
+
+def test_all_tokens_to_one_expert(built_lib):
+    spec = O.LayerSpec(256, 128, 8, 1, combine_mode=O.COMBINE_FP32)
+    x, W = O.make_inputs(spec, 1000, 77)
+    layer = make_layer(spec, W, DEV)
+    idx = torch.full((1000, 1), 5, dtype=torch.int32, device=DEV)
+    worst, (counts, *_rest) = _check_expert_rows(spec, W, x.to(DEV), layer, idx)
+    assert counts.cpu().tolist() == [0, 0, 0, 0, 0, 1000, 0, 0]
+    assert worst < 5e-3
+
+
+# --------------------------------------------------------------------------- combine
+@pytest.mark.parametrize("mode", [O.COMBINE_FP32, O.COMBINE_BF16_PROD, O.COMBINE_BF16_SEQ])
+@pytest.mark.parametrize("with_shared", [False, True])
+def test_combine_matches_oracle(built_lib, mode, with_shared):
+    T, E, k, H = 300, 32, 4, 512
+    spec = O.LayerSpec(H, 128, E, k, combine_mode=mode)
+    layer = make_layer(spec, O.LayerWeights(torch.zeros(E, H, dtype=torch.bfloat16), None), DEV)
+    gen = torch.Generator().manual_seed(mode * 2 + with_shared)
+    idx = torch.rand(T, E, generator=gen).topk(k, dim=-1).indices.to(torch.int32)
+    w = torch.rand(T, k, generator=gen) * 2.5
+    counts, offsets, pad, dst = layer.permute_plan(idx.to(DEV))
+    rows = layer.padded_rows(T * k)
+    out_rows = torch.randn(rows, H, generator=gen).to(torch.bfloat16)
+    shared = torch.randn(T, H, generator=gen).to(torch.bfloat16) if with_shared else None
+    y = layer.combine(out_rows.to(DEV), dst, idx.to(DEV), w.to(DEV), None if shared is None else shared.to(DEV))
+    by_slot = out_rows[dst.cpu().long().view(-1)].view(T, k, H)
+    ref = O.combine(spec, by_slot, idx.long(), w)
+    if shared is not None:
+        ref = ref + shared
+    diff = (y.cpu().float() - ref.float()).abs()
+    # same arithmetic, same rounding points: at most a last-place difference from the order of
+    # the k fp32 additions on a handful of elements
+    assert float((diff > 0).float().mean()) < 2e-3
+    assert O.rel_l2(y.cpu().float(), ref.float()) < 2e-4
+
+
+# --------------------------------------------------------------------------- whole layer
+@pytest.mark.parametrize("name", sorted(CASES))
+def test_layer_against_reference_fixture(built_lib, name):
+    spec, T, seed = CASES[name]
+    g = load_golden(name)
+    x, W = O.make_inputs(spec, T, seed)
+    layer = make_layer(spec, W, DEV)
+    xd = x.to(DEV)
+    y = layer.forward(xd)
+    _status_ok(layer)
+    # routing as the layer computed it (read back from its workspace through the staged calls)
+    logits = O.gate_logits(x, W.gate_w)
+    idx, w = layer.route_topk(layer.gate_logits(xd))
+    ridx = torch.from_numpy(g["topk_idx"].astype(np.int64))
+    rw = torch.from_numpy(g["topk_w"])
+    flips = _route_equal(spec, idx, w, ridx, rw, logits, W.bias, exact_logits=False)
+    counts, *_ = layer.permute_plan(idx)
+    if flips == 0:
+        assert np.array_equal(counts.cpu().numpy(), g["counts"])
+    y_gold = torch.from_numpy(g["y_gold_fp32"])
+    err = O.rel_l2(y.cpu().float(), y_gold)
+    assert err <= TOL_LAYER, err
+    # for information: distance to the reference's own bf16 output is of the same size as the
+    # reference's bf16-vs-fp32 distance
+    assert O.rel_l2(y.cpu().float(), bf16_from_bits(g["y_ref_bf16"]).float()) < 1.5e-2
+
+
+@pytest.mark.parametrize("T", [0, 1, 127, 129])
+def test_layer_edge_token_counts(built_lib, T):
+    spec = O.LayerSpec(256, 128, 64, 6, 256, 1, 1, O.GATE_SOFTMAX_GREEDY, False, 1.0, O.WEIGHT_BF16,
+                       O.COMBINE_BF16_PROD)
+    x, W = O.make_inputs(spec, max(T, 1), 90 + T)
+    x = x[:T]
+    layer = make_layer(spec, W, DEV)
+    y = layer.forward(x.to(DEV))
+    _status_ok(layer)
+    assert y.shape == (T, 256)
+    if T:
+        gold = O.layer_forward(spec, x, W, gold_fp32=True)
+        assert O.rel_l2(y.cpu().float(), gold["y"]) <= TOL_LAYER
+
+
+def test_mixtral_layer(built_lib):
+    spec = O.LayerSpec(512, 1024, 8, 2, gating=O.GATE_SOFTMAX_TOPK_RENORM, norm_topk_prob=True,
+                       combine_mode=O.COMBINE_BF16_SEQ)
+    x, W = O.make_inputs(spec, 900, 17)
+    layer = make_layer(spec, W, DEV)
+    y = layer.forward(x.to(DEV))
+    _status_ok(layer)
+    gold = O.layer_forward(spec, x, W, gold_fp32=True)
+    ref = O.layer_forward(spec, x, W)
+    # the bf16 router output makes exact ties common; both sides resolve them to the lower id,
+    # but a logit that rounds differently can still flip a token: compare only agreeing tokens
+    idx, w = layer.route_topk(layer.gate_logits(x.to(DEV)))
+    same = (O.canonical_sets(idx.cpu().long(), w.cpu())[0] == O.canonical_sets(ref["topk_idx"], ref["topk_w"])[0]).all(1)
+    assert float(same.float().mean()) > 0.995
+    assert O.rel_l2(y.cpu().float()[same], gold["y"][same]) <= TOL_LAYER
+
+
+def test_forward_host_equals_forward(built_lib):
+    spec = O.LayerSpec(256, 128, 64, 6, 256, 1, 1, O.GATE_SOFTMAX_GREEDY, False, 1.0, O.WEIGHT_BF16,
+                       O.COMBINE_BF16_PROD)
+    x, W = O.make_inputs(spec, 1000, 33)
+    layer = make_layer(spec, W, DEV)
+    y = layer.forward(x.to(DEV)).cpu()
+    yh = layer.forward_host(x.pin_memory(), chunk_tokens=256)
+    assert torch.equal(y.view(torch.int16), yh.view(torch.int16))
+
+
+def test_patched_reference_style_module(built_lib):
+    """The patcher reads the attributes the reference modules expose (config, gate,
+    experts[i].{gate,up,down}_proj, shared_experts) and serves forward([B,S,H])."""
+    import types
+    import torch.nn as nn
+    from moe_gen_b200 import patch_moe_module
+    spec = O.LayerSpec(256, 128, 32, 4, 128, 4, 2, O.GATE_SIGMOID_NOAUX_TC, True, 2.5, O.WEIGHT_BF16, O.COMBINE_FP32)
+    x, W = O.make_inputs(spec, 64, 3)
+
+    def mlp(g, u, d):
+        m = nn.Module()
+        for n, w in (("gate_proj", g), ("up_proj", u), ("down_proj", d)):
+            lin = nn.Linear(w.shape[1], w.shape[0], bias=False, dtype=torch.bfloat16)
+            lin.weight.data = w.clone()
+            setattr(m, n, lin)
+        return m
+
+    class DeepseekV3MoE(nn.Module):
+        pass
+    mod = DeepseekV3MoE().eval()
+    mod.config = types.SimpleNamespace(hidden_size=256, moe_intermediate_size=128, n_routed_experts=32,
+                                       num_experts_per_tok=4, n_shared_experts=1, n_group=4, topk_group=2,
+                                       topk_method="noaux_tc", scoring_func="sigmoid", norm_topk_prob=True,
+                                       routed_scaling_factor=2.5)
+    mod.gate = nn.Module()
+    mod.gate.weight = nn.Parameter(W.gate_w.clone())
+    mod.gate.e_score_correction_bias = nn.Parameter(W.bias.clone())
+    mod.experts = nn.ModuleList([mlp(W.w_gate[e], W.w_up[e], W.w_down[e]) for e in range(32)])
+    mod.shared_experts = mlp(*W.shared)
+    patch_moe_module(mod, device=DEV)
+    y = mod(x.view(2, 32, 256).to(DEV))
+    assert y.shape == (2, 32, 256)
+    gold = O.layer_forward(spec, x, W, gold_fp32=True)
+    assert O.rel_l2(y.view(64, 256).cpu().float(), gold["y"]) <= TOL_LAYER

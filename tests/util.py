@@ -18,7 +18,7 @@ def make_layer(spec: O.LayerSpec, W: O.LayerWeights, device="cuda:0", ep_rank=0,
                      ep_rank=ep_rank, ep_size=ep_size, device=device)
     layer.set_router(W.gate_w, W.bias)
     fp8 = spec.weight_format == O.WEIGHT_FP8_BLOCK128
-    for i in range(layer.e_local):
+    for i in range(layer.e_local if W.w_gate else 0):   # router-only tests carry no expert weights
         e = layer.expert_lo + i
         if fp8:
             (g, gs), (u, us), (d, ds) = W.q_gate[e], W.q_up[e], W.q_down[e]
