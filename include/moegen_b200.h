@@ -62,6 +62,7 @@ extern "C" {
 /* device status word values (mg_device_status) */
 #define MG_DEV_OK             0
 #define MG_DEV_WAIT_TIMEOUT   1  /* a bounded mbarrier wait ran out; results invalid */
+#define MG_DEV_CAPACITY       2  /* expert-parallel receive buffer too small; detail = rank */
 
 /* stages of mg_moe_forward, in launch order (mg_stage_times) */
 #define MG_STAGE_GATE_LOGITS   0
@@ -190,8 +191,9 @@ int mg_permute_rows(mg_handle h, const void* d_x, const int32_t* d_dst_row, int6
  *   h_buf[r, :]   = silu(perm_x[r] . Wg_e^T) * (perm_x[r] . Wu_e^T)   (bf16)
  *   out_rows[r,:] = h_buf[r] . Wd_e^T                                  (bf16)
  * for r in [pad_offsets[e], pad_offsets[e]+counts[e]).  n_rows_padded bounds the
- * buffers (rows of perm_x / h_buf / out_rows).  For FP8 layers d_dequant_ws is a
- * bf16 scratch of mg_dequant_ws_bytes() bytes.
+ * buffers (rows of perm_x / h_buf / out_rows).  For FP8 layers d_dequant_ws may be NULL
+ * (the kernels convert weight tiles on the fly) or a bf16 scratch of mg_dequant_ws_bytes()
+ * bytes (weights are de-quantised into it first); results are identical.
  * Replaces the expert loop (modeling_deepseek_v3.py:675-691) and
  * DeepseekV3MLP.forward (modeling_deepseek_v3.py:463-467). */
 int mg_dequant_ws_bytes(mg_handle h, size_t* bytes);
@@ -223,6 +225,56 @@ int mg_moe_forward(mg_handle h, const void* d_x, int64_t n_tokens,
                    const void* d_gate_w, const float* d_bias, const void* d_packed,
                    void* d_workspace, size_t workspace_bytes, void* d_y, void* stream);
 
+/* ---- expert parallelism (ep_size > 1): one process per GPU ------------------- */
+/* The reference's expert-parallel branch (modeling_deepseek_v3.py:636-672,692-700) exchanges
+ * counts with all_to_all_single, rows with two all_to_all calls and regroups on the host.
+ * Here every rank owns two buffers that all ranks map (CUDA IPC over NVLink):
+ *   recv_x   [cap_rows, H]  rows routed to this rank's experts, expert-sorted and 128-padded
+ *   out_rows [cap_rows, H]  the experts' outputs for those rows
+ * A rank writes its tokens straight into the owners' recv_x (dispatch = the permute scatter
+ * with peer destinations) and later reads the owners' out_rows (return = the combine gather
+ * with peer sources).  Between the steps the ranks need a barrier (any stream-ordered
+ * collective, e.g. a one-element NCCL all-reduce): after dispatch before the experts run, and
+ * after the experts before combine.  Sequence per forward on each rank:
+ *   mg_gate_logits, mg_route_topk, mg_ep_count -> all-gather counts -> mg_ep_place,
+ *   mg_ep_dispatch, [mg_shared_ffn], barrier, mg_expert_ffn, barrier, mg_ep_combine. */
+
+/* Device memory that can be shared with the other ranks / its 64-byte IPC handle / mapping
+ * a peer's handle / unmapping.  The importing process must run on a GPU with peer access. */
+int mg_ep_alloc(size_t bytes, void** d_ptr);
+int mg_ep_free(void* d_ptr);
+int mg_ep_export(void* d_ptr, void* handle64);
+int mg_ep_import(const void* handle64, void** d_ptr);
+int mg_ep_unimport(void* d_ptr);
+
+/* counts[E]: picks per global expert among this rank's n_tokens tokens.  d_plan_ws
+ * (mg_plan_ws_bytes) must stay untouched until mg_ep_place.  Replaces the histogram of
+ * modeling_deepseek_v3.py:630-632. */
+int mg_ep_count(mg_handle h, const int32_t* d_topk_idx, int64_t n_tokens, int32_t* d_counts,
+                void* d_plan_ws, void* stream);
+
+/* From the all-gathered counts [ep_size][E] (row s = rank s): recv_counts[E/ep_size] and
+ * recv_pad[E/ep_size+1] of this rank's experts (inputs of mg_expert_ffn), and dst[T*k] =
+ * owner_rank << 24 | row in the owner's buffers.  Inside an expert's segment the rows of rank
+ * 0 come first, then rank 1, ..., tokens ascending.  If a rank would receive more than
+ * cap_rows rows, picks sent to it are dropped (dst < 0) and the device status becomes
+ * MG_DEV_CAPACITY.  Replaces all_to_all_single + host split computation + numpy argsort
+ * (modeling_deepseek_v3.py:636-671). */
+int mg_ep_place(mg_handle h, const int32_t* d_topk_idx, int64_t n_tokens, const int32_t* d_counts_all,
+                int64_t cap_rows, void* d_plan_ws, int32_t* d_recv_counts, int32_t* d_recv_pad,
+                int32_t* d_dst, void* stream);
+
+/* peer_recv[ep_size]: every rank's recv_x as mapped in this process (own buffer at own rank).
+ * Replaces dist.all_to_all of the sorted rows (modeling_deepseek_v3.py:656-659). */
+int mg_ep_dispatch(mg_handle h, const void* d_x, const int32_t* d_dst, int64_t n_tokens,
+                   void* const* peer_recv, void* stream);
+
+/* peer_out[ep_size]: every rank's out_rows.  Replaces the return all_to_all and the
+ * weighted sum (modeling_deepseek_v3.py:692-710). */
+int mg_ep_combine(mg_handle h, void* const* peer_out, const int32_t* d_dst, const int32_t* d_topk_idx,
+                  const float* d_topk_w, const void* d_shared_out, int64_t n_tokens, void* d_y,
+                  void* stream);
+
 /* Pointers into a workspace laid out by mg_moe_forward, for tests and tools:
  * which = 0 logits, 1 topk_idx, 2 topk_w, 3 counts, 4 offsets, 5 pad_offsets,
  * 6 dst_row, 7 perm_x, 8 h_buf, 9 out_rows. */
@@ -231,6 +283,21 @@ int mg_workspace_ptr(mg_handle h, void* d_workspace, int64_t max_tokens, int64_t
 
 /* Number of kernel launches the last mg_moe_forward on this handle issued. */
 int mg_last_launch_count(mg_handle h, int32_t* launches);
+
+/* Options (no counterpart in the reference).
+ * MG_OPT_FP8_MODE, for MG_WEIGHT_FP8_BLOCK128 layers in mg_moe_forward:
+ *   MG_FP8_PREDEQUANT  de-quantise the expert weights into workspace scratch, one chunk of
+ *                      experts ahead of the bf16 grouped GEMMs, on a side stream (the reference
+ *                      de-quantises per expert call, moe_gen/models/Wrapper.py:481-491);
+ *   MG_FP8_IN_KERNEL   the grouped GEMMs convert FP8 weight tiles to bf16 in shared memory;
+ *   MG_FP8_AUTO        (default) in-kernel while an expert sees at most 256 rows on average
+ *                      (the layer is then bound by streaming the FP8 bytes), else pre-dequantise.
+ * All give bit-identical results.  Set before asking mg_workspace_bytes. */
+#define MG_OPT_FP8_MODE    1
+#define MG_FP8_AUTO        0
+#define MG_FP8_PREDEQUANT  1
+#define MG_FP8_IN_KERNEL   2
+int mg_set_option(mg_handle h, int32_t option, int32_t value);
 
 /* Per-stage device times of mg_moe_forward (no counterpart in the reference, whose
  * timers are commented out: moe_gen/models/Wrapper.py:112-137).  When enabled, the

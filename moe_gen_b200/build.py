@@ -11,7 +11,7 @@ PKG = os.path.dirname(os.path.abspath(__file__))
 ROOT = os.path.dirname(PKG)
 CSRC = os.path.join(PKG, "csrc")
 LIB = os.path.join(PKG, "libmoegen_b200.so")
-SOURCES = ["api.cu", "route.cu", "pack.cu", "gemm.cu"]
+SOURCES = ["api.cu", "route.cu", "pack.cu", "gemm.cu", "ep.cu"]
 NVCC_FLAGS = ["-std=c++17", "-O3", "-lineinfo", "-gencode", "arch=compute_100a,code=sm_100a",
               "-Xcompiler", "-fPIC", "-shared", "-cudart", "static"]
 

@@ -28,6 +28,8 @@ static Handle* check(mg_handle hh) {
   return h;
 }
 
+Handle* check_handle(mg_handle hh) { return check(hh); }
+
 static int64_t padded_rows(const Handle* h, int64_t rows) {
   return ((rows + kTileM - 1) / kTileM + h->e_local) * kTileM;
 }
@@ -40,6 +42,16 @@ struct WsLayout { size_t off[WS_N]; size_t total; };
 static size_t dequant_ws(const Handle* h) {
   if (h->d.weight_format != MG_WEIGHT_FP8_BLOCK128) return 0;
   return static_cast<size_t>(h->e_local) * 3 * h->d.inter * h->d.hidden * 2;
+}
+
+// FP8 layers: de-quantise ahead of the GEMMs (true) or convert tiles inside them (false).
+// Converting in the kernel re-does the work for every 128-row tile of an expert, so it pays
+// only while an expert sees few rows (then the layer is bound by streaming the FP8 bytes).
+static bool fp8_predequant(const Handle* h, int64_t T) {
+  if (h->d.weight_format != MG_WEIGHT_FP8_BLOCK128) return false;
+  if (h->opt_fp8_mode == MG_FP8_PREDEQUANT) return true;
+  if (h->opt_fp8_mode == MG_FP8_IN_KERNEL) return false;
+  return T * h->d.top_k > static_cast<int64_t>(256) * h->d.n_experts;
 }
 
 static WsLayout ws_layout(const Handle* h, int64_t T, int64_t R) {
@@ -62,7 +74,7 @@ static WsLayout ws_layout(const Handle* h, int64_t T, int64_t R) {
   take(WS_PLAN, plan_ws_bytes(h, T));
   take(WS_HS, static_cast<size_t>(T) * d.inter_shared * 2);
   take(WS_SHARED, d.inter_shared ? static_cast<size_t>(T) * d.hidden * 2 : 0);
-  take(WS_DEQ, dequant_ws(h));
+  take(WS_DEQ, fp8_predequant(h, T) ? dequant_ws(h) : 0);
   L.total = off;
   return L;
 }
@@ -110,6 +122,10 @@ int mg_create(const mg_layer_desc* desc, mg_handle* out) {
   h->e_local = d.n_experts / d.ep_size;
   h->last_launches = 0;
   h->stage_timing = false;
+  h->opt_fp8_mode = MG_FP8_AUTO;
+  h->side = nullptr;
+  h->ev_entry = nullptr;
+  for (int i = 0; i < kDequantChunks; ++i) h->ev_w13[i] = h->ev_w2[i] = nullptr;
   h->stage_calls = 0;
   for (int s = 0; s < kStageSlots; ++s)
     for (int i = 0; i <= MG_STAGE_COUNT; ++i) h->stage_ev[s][i] = nullptr;
@@ -136,6 +152,12 @@ int mg_destroy(mg_handle hh) {
   for (int s = 0; s < kStageSlots; ++s)
     for (int i = 0; i <= MG_STAGE_COUNT; ++i)
       if (h->stage_ev[s][i]) cudaEventDestroy(h->stage_ev[s][i]);
+  if (h->side) cudaStreamDestroy(h->side);
+  if (h->ev_entry) cudaEventDestroy(h->ev_entry);
+  for (int i = 0; i < kDequantChunks; ++i) {
+    if (h->ev_w13[i]) cudaEventDestroy(h->ev_w13[i]);
+    if (h->ev_w2[i]) cudaEventDestroy(h->ev_w2[i]);
+  }
   h->magic = 0;
   delete h;
   return MG_OK;
@@ -258,36 +280,85 @@ static void mark(Handle* h, int stage, cudaStream_t st) {
   if (h->stage_timing) cudaEventRecord(h->stage_ev[h->stage_calls % kStageSlots][stage + 1], st);
 }
 
+static int ensure_side_stream(Handle* h) {
+  if (h->side) return MG_OK;
+  MG_CUDA(cudaStreamCreateWithFlags(&h->side, cudaStreamNonBlocking));
+  MG_CUDA(cudaEventCreateWithFlags(&h->ev_entry, cudaEventDisableTiming));
+  for (int i = 0; i < kDequantChunks; ++i) {
+    MG_CUDA(cudaEventCreateWithFlags(&h->ev_w13[i], cudaEventDisableTiming));
+    MG_CUDA(cudaEventCreateWithFlags(&h->ev_w2[i], cudaEventDisableTiming));
+  }
+  return MG_OK;
+}
+
 static int expert_ffn(Handle* h, const void* perm_x, const int32_t* pad, const int32_t* counts, int64_t rows_padded,
                       const void* packed, void* h_buf, void* out_rows, void* deq, cudaStream_t st, int* launches,
                       bool timed = false) {
   const mg_layer_desc& d = h->d;
   const PackedLayout L = packed_layout(h);
   const uint8_t* base = static_cast<const uint8_t*>(packed);
-  const void* w13 = base + L.w13;
-  const void* w2 = base + L.w2;
-  if (d.weight_format == MG_WEIGHT_FP8_BLOCK128) {
-    MG_REQUIRE(deq != nullptr, MG_ERR_NULL, "FP8 layer needs the de-quantisation scratch");
-    int rc = launch_dequant_packed(h, packed, deq, st);
+  const bool fp8 = d.weight_format == MG_WEIGHT_FP8_BLOCK128;
+  const int E = h->e_local;
+  GemmProblem p{};
+  p.a_rows = rows_padded;
+  if (!fp8 || deq == nullptr) {
+    // bf16 weights, or FP8 tiles converted inside the GEMM kernels: two launches over all experts
+    if (timed) mark(h, MG_STAGE_DEQUANT, st);
+    p.a = perm_x; p.b = base + L.w13; p.n_groups = E; p.n_per_group = 2 * d.inter; p.K = d.hidden;
+    p.pad_offsets = pad; p.counts = counts; p.out = h_buf; p.ldo = d.inter; p.epilogue = EPI_SWIGLU_BF16;
+    p.b_fp8 = fp8;
+    p.scales = fp8 ? reinterpret_cast<const float*>(base + L.s13) : nullptr;
+    int rc = launch_grouped_gemm(h, p, st);
     if (rc != MG_OK) return rc;
-    w13 = deq;
-    w2 = static_cast<const __nv_bfloat16*>(deq) + static_cast<size_t>(h->e_local) * 2 * d.inter * d.hidden;
+    if (timed) mark(h, MG_STAGE_EXPERT_GEMM1, st);
+    p.a = h_buf; p.b = base + L.w2; p.n_per_group = d.hidden; p.K = d.inter; p.out = out_rows; p.ldo = d.hidden;
+    p.epilogue = EPI_PLAIN_BF16;
+    p.scales = fp8 ? reinterpret_cast<const float*>(base + L.s2) : nullptr;
+    rc = launch_grouped_gemm(h, p, st);
+    if (timed) mark(h, MG_STAGE_EXPERT_GEMM2, st);
     if (launches) *launches += 2;
+    return rc;
+  }
+  // FP8 weights de-quantised into `deq` one chunk of experts ahead of the bf16 GEMMs: the
+  // conversion is HBM-bound and runs on a side stream while the tensor cores work on the
+  // previous chunk, so only the first chunk is exposed
+  int rc = ensure_side_stream(h);
+  if (rc != MG_OK) return rc;
+  const int n_chunks = E < kDequantChunks ? E : kDequantChunks;
+  const int per = (E + n_chunks - 1) / n_chunks;
+  MG_CUDA(cudaEventRecord(h->ev_entry, st));
+  MG_CUDA(cudaStreamWaitEvent(h->side, h->ev_entry, 0));
+  for (int which = 0; which < 2; ++which) {
+    for (int c = 0; c < n_chunks; ++c) {
+      const int lo = c * per, n = (lo + per <= E ? per : E - lo);
+      rc = launch_dequant_packed(h, packed, deq, which, lo, n, h->side);
+      if (rc != MG_OK) return rc;
+      MG_CUDA(cudaEventRecord(which == 0 ? h->ev_w13[c] : h->ev_w2[c], h->side));
+    }
   }
   if (timed) mark(h, MG_STAGE_DEQUANT, st);
-  GemmProblem p{};
-  p.a = perm_x; p.a_rows = rows_padded; p.b = w13; p.n_groups = h->e_local; p.n_per_group = 2 * d.inter;
-  p.K = d.hidden; p.pad_offsets = pad; p.counts = counts; p.out = h_buf; p.ldo = d.inter;
-  p.epilogue = EPI_SWIGLU_BF16;
-  int rc = launch_grouped_gemm(h, p, st);
-  if (rc != MG_OK) return rc;
-  if (timed) mark(h, MG_STAGE_EXPERT_GEMM1, st);
-  p.a = h_buf; p.b = w2; p.n_per_group = d.hidden; p.K = d.inter; p.out = out_rows; p.ldo = d.hidden;
-  p.epilogue = EPI_PLAIN_BF16;
-  rc = launch_grouped_gemm(h, p, st);
-  if (timed) mark(h, MG_STAGE_EXPERT_GEMM2, st);
-  if (launches) *launches += 2;
-  return rc;
+  const __nv_bfloat16* w13 = static_cast<const __nv_bfloat16*>(deq);
+  const __nv_bfloat16* w2 = w13 + static_cast<size_t>(E) * 2 * d.inter * d.hidden;
+  for (int which = 0; which < 2; ++which) {
+    for (int c = 0; c < n_chunks; ++c) {
+      const int lo = c * per, n = (lo + per <= E ? per : E - lo);
+      if (n <= 0) continue;
+      MG_CUDA(cudaStreamWaitEvent(st, which == 0 ? h->ev_w13[c] : h->ev_w2[c], 0));
+      p.n_groups = n; p.pad_offsets = pad + lo; p.counts = counts + lo; p.b_fp8 = false; p.scales = nullptr;
+      if (which == 0) {
+        p.a = perm_x; p.b = w13 + static_cast<size_t>(lo) * 2 * d.inter * d.hidden; p.n_per_group = 2 * d.inter;
+        p.K = d.hidden; p.out = h_buf; p.ldo = d.inter; p.epilogue = EPI_SWIGLU_BF16;
+      } else {
+        p.a = h_buf; p.b = w2 + static_cast<size_t>(lo) * d.hidden * d.inter; p.n_per_group = d.hidden;
+        p.K = d.inter; p.out = out_rows; p.ldo = d.hidden; p.epilogue = EPI_PLAIN_BF16;
+      }
+      rc = launch_grouped_gemm(h, p, st);
+      if (rc != MG_OK) return rc;
+    }
+    if (timed) mark(h, which == 0 ? MG_STAGE_EXPERT_GEMM1 : MG_STAGE_EXPERT_GEMM2, st);
+  }
+  if (launches) *launches += 4 * n_chunks;
+  return MG_OK;
 }
 
 int mg_expert_ffn(mg_handle hh, const void* d_perm_x, const int32_t* d_pad, const int32_t* d_counts,
@@ -378,7 +449,7 @@ int mg_moe_forward(mg_handle hh, const void* d_x, int64_t T, const void* d_gate_
   void* plan = ws + L.off[WS_PLAN];
   void* hs = ws + L.off[WS_HS];
   void* sh = d.inter_shared ? ws + L.off[WS_SHARED] : nullptr;
-  void* deq = d.weight_format == MG_WEIGHT_FP8_BLOCK128 ? ws + L.off[WS_DEQ] : nullptr;
+  void* deq = fp8_predequant(h, T) ? ws + L.off[WS_DEQ] : nullptr;
   int launches = 0;
   if (h->stage_timing) MG_CUDA(cudaEventRecord(h->stage_ev[h->stage_calls % kStageSlots][0], st));
   int rc = mg_gate_logits(hh, d_x, d_gate_w, T, logits, stream);
@@ -412,6 +483,18 @@ int mg_moe_forward(mg_handle hh, const void* d_x, int64_t T, const void* d_gate_
   h->last_launches = launches;
   if (h->stage_timing) ++h->stage_calls;
   return MG_OK;
+}
+
+int mg_set_option(mg_handle hh, int32_t option, int32_t value) {
+  Handle* h = check(hh);
+  if (!h) return MG_ERR_STATE;
+  switch (option) {
+    case MG_OPT_FP8_MODE:
+      MG_REQUIRE(value >= MG_FP8_AUTO && value <= MG_FP8_IN_KERNEL, MG_ERR_CONFIG, "bad FP8 mode %d", value);
+      h->opt_fp8_mode = value;
+      return MG_OK;
+    default: set_error("unknown option %d", option); return MG_ERR_CONFIG;
+  }
 }
 
 int mg_set_stage_timing(mg_handle hh, int32_t enable) {

@@ -13,6 +13,11 @@ namespace mg {
 constexpr int kTileM = 128;          // rows per GEMM tile == expert segment alignment
 constexpr int kMaxExperts = 512;     // plan and top-k kernels keep per-expert state on chip
 constexpr int kMaxTopK = 16;
+constexpr int kMaxPeers = 8;         // ranks of one NVSwitch domain
+constexpr int kPeerShift = 24;       // expert-parallel destinations: rank << 24 | row
+constexpr int kPeerRowMask = (1 << kPeerShift) - 1;
+constexpr int kSkipRow = -(1 << 30); // stays negative after the in-segment rank is added
+constexpr int kDequantChunks = 8;    // expert chunks of the overlapped FP8 de-quantisation
 constexpr int kStageSlots = 32;      // forwards whose per-stage times are kept for averaging
 
 // thread-local error text -------------------------------------------------------------
@@ -38,6 +43,9 @@ struct Handle {
   int e_local;            // experts owned by this rank
   int32_t* d_status;      // [2]: code, detail
   int last_launches;
+  int opt_fp8_mode;       // MG_FP8_AUTO / MG_FP8_PREDEQUANT / MG_FP8_IN_KERNEL
+  cudaStream_t side;      // de-quantisation runs here, one chunk of experts ahead of the GEMMs
+  cudaEvent_t ev_entry, ev_w13[kDequantChunks], ev_w2[kDequantChunks];
   bool stage_timing;      // record an event after every stage of mg_moe_forward
   int stage_calls;        // forwards recorded since timing was enabled
   cudaEvent_t stage_ev[kStageSlots][MG_STAGE_COUNT + 1];   // ring of event sets, one per forward
@@ -66,6 +74,18 @@ int launch_combine(const Handle* h, const void* out_rows, const int32_t* dst_row
                    const int32_t* idx, const float* w, const void* shared, int64_t T, void* y,
                    cudaStream_t st);
 
+struct PeerPtrs { void* p[kMaxPeers]; };
+int launch_dispatch_rows(const Handle* h, const void* x, const int32_t* dst, int64_t T,
+                         const PeerPtrs& peers, cudaStream_t st);
+int launch_combine_peers(const Handle* h, const PeerPtrs& peers, const int32_t* dst,
+                         const int32_t* idx, const float* w, const void* shared, int64_t T, void* y,
+                         cudaStream_t st);
+int launch_ep_count(const Handle* h, const int32_t* idx, int64_t T, int32_t* counts, void* ws,
+                    cudaStream_t st);
+int launch_ep_place(const Handle* h, const int32_t* idx, int64_t T, const int32_t* counts_all,
+                    int cap_rows, void* ws, int32_t* recv_counts, int32_t* recv_pad, int32_t* dst,
+                    cudaStream_t st);
+
 // weights (pack.cu) --------------------------------------------------------------------
 int launch_pack_expert(const Handle* h, int local_expert, const void* g, const void* u,
                        const void* dn, const float* gs, const float* us, const float* ds,
@@ -74,7 +94,8 @@ int launch_dequant(const void* q, const float* s, int64_t rows, int64_t cols, vo
                    cudaStream_t st);
 // de-quantise every routed expert of a packed FP8 buffer into a bf16 buffer of the same
 // layout (w13 then w2)
-int launch_dequant_packed(const Handle* h, const void* packed, void* bf16_out, cudaStream_t st);
+int launch_dequant_packed(const Handle* h, const void* packed, void* bf16_out, int which, int e_lo, int e_n,
+                          cudaStream_t st);
 
 // grouped GEMM (gemm.cu) ---------------------------------------------------------------
 enum GemmEpilogue { EPI_SWIGLU_BF16 = 0, EPI_PLAIN_BF16 = 1, EPI_PLAIN_F32 = 2, EPI_ROUND_BF16_F32 = 3 };
@@ -82,7 +103,9 @@ enum GemmEpilogue { EPI_SWIGLU_BF16 = 0, EPI_PLAIN_BF16 = 1, EPI_PLAIN_F32 = 2, 
 struct GemmProblem {
   const void* a;          // [a_rows, K] bf16 row-major
   int64_t a_rows;
-  const void* b;          // [n_groups * n_per_group, K] bf16 row-major ("N x K, K-major")
+  const void* b;          // [n_groups * n_per_group, K] row-major ("N x K, K-major"), bf16 or FP8 e4m3
+  bool b_fp8;             // B holds e4m3 bytes; `scales` holds fp32 [rows/128][K/128]
+  const float* scales;
   int n_groups;
   int n_per_group;        // rows of B per group (2I for SwiGLU, H for down, E for the gate)
   int K;

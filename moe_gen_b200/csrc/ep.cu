@@ -1,0 +1,111 @@
+// Expert-parallel entry points: symmetric device buffers shared between the ranks of one
+// NVSwitch domain (CUDA IPC), and the dispatch / return steps that move rows with plain
+// stores and loads through the peer mappings.  No TMA and no multicast touches peer memory.
+#include <string.h>
+
+#include "common.cuh"
+
+using namespace mg;
+
+namespace mg {
+Handle* check_handle(mg_handle hh);
+}
+
+extern "C" {
+
+int mg_ep_alloc(size_t bytes, void** d_ptr) {
+  MG_REQUIRE(d_ptr && bytes > 0, MG_ERR_NULL, "mg_ep_alloc: null argument or zero size");
+  MG_CUDA(cudaMalloc(d_ptr, bytes));
+  return MG_OK;
+}
+
+int mg_ep_free(void* d_ptr) {
+  if (d_ptr) MG_CUDA(cudaFree(d_ptr));
+  return MG_OK;
+}
+
+int mg_ep_export(void* d_ptr, void* handle64) {
+  MG_REQUIRE(d_ptr && handle64, MG_ERR_NULL, "mg_ep_export: null argument");
+  static_assert(sizeof(cudaIpcMemHandle_t) == 64, "IPC handle size");
+  cudaIpcMemHandle_t hd;
+  MG_CUDA(cudaIpcGetMemHandle(&hd, d_ptr));
+  memcpy(handle64, &hd, 64);
+  return MG_OK;
+}
+
+int mg_ep_import(const void* handle64, void** d_ptr) {
+  MG_REQUIRE(handle64 && d_ptr, MG_ERR_NULL, "mg_ep_import: null argument");
+  cudaIpcMemHandle_t hd;
+  memcpy(&hd, handle64, 64);
+  MG_CUDA(cudaIpcOpenMemHandle(d_ptr, hd, cudaIpcMemLazyEnablePeerAccess));
+  return MG_OK;
+}
+
+int mg_ep_unimport(void* d_ptr) {
+  if (d_ptr) MG_CUDA(cudaIpcCloseMemHandle(d_ptr));
+  return MG_OK;
+}
+
+int mg_ep_count(mg_handle hh, const int32_t* d_topk_idx, int64_t T, int32_t* d_counts, void* d_plan_ws,
+                void* stream) {
+  Handle* h = check_handle(hh);
+  if (!h) return MG_ERR_STATE;
+  MG_REQUIRE(d_counts && d_plan_ws && (T == 0 || d_topk_idx), MG_ERR_NULL, "mg_ep_count: null pointer");
+  MG_REQUIRE(T >= 0, MG_ERR_SHAPE, "negative token count");
+  return launch_ep_count(h, d_topk_idx, T, d_counts, d_plan_ws, static_cast<cudaStream_t>(stream));
+}
+
+int mg_ep_place(mg_handle hh, const int32_t* d_topk_idx, int64_t T, const int32_t* d_counts_all, int64_t cap_rows,
+                void* d_plan_ws, int32_t* d_recv_counts, int32_t* d_recv_pad, int32_t* d_dst, void* stream) {
+  Handle* h = check_handle(hh);
+  if (!h) return MG_ERR_STATE;
+  MG_REQUIRE(d_counts_all && d_plan_ws && d_recv_counts && d_recv_pad && (T == 0 || (d_topk_idx && d_dst)),
+             MG_ERR_NULL, "mg_ep_place: null pointer");
+  MG_REQUIRE(T >= 0, MG_ERR_SHAPE, "negative token count");
+  MG_REQUIRE(h->d.ep_size <= kMaxPeers, MG_ERR_LIMIT, "ep_size %d > %d", h->d.ep_size, kMaxPeers);
+  MG_REQUIRE(cap_rows > 0 && cap_rows % kTileM == 0 && cap_rows <= kPeerRowMask, MG_ERR_LIMIT,
+             "cap_rows=%lld must be a positive multiple of %d below 2^%d", static_cast<long long>(cap_rows), kTileM,
+             kPeerShift);
+  return launch_ep_place(h, d_topk_idx, T, d_counts_all, static_cast<int>(cap_rows), d_plan_ws, d_recv_counts,
+                         d_recv_pad, d_dst, static_cast<cudaStream_t>(stream));
+}
+
+static int gather_peers(const Handle* h, void* const* ptrs, PeerPtrs* out) {
+  MG_REQUIRE(ptrs != nullptr, MG_ERR_NULL, "null peer pointer table");
+  MG_REQUIRE(h->d.ep_size <= kMaxPeers, MG_ERR_LIMIT, "ep_size %d > %d", h->d.ep_size, kMaxPeers);
+  for (int i = 0; i < kMaxPeers; ++i) out->p[i] = nullptr;
+  for (int i = 0; i < h->d.ep_size; ++i) {
+    MG_REQUIRE(ptrs[i] != nullptr, MG_ERR_NULL, "peer pointer %d is null", i);
+    out->p[i] = ptrs[i];
+  }
+  return MG_OK;
+}
+
+int mg_ep_dispatch(mg_handle hh, const void* d_x, const int32_t* d_dst, int64_t T, void* const* peer_recv,
+                   void* stream) {
+  Handle* h = check_handle(hh);
+  if (!h) return MG_ERR_STATE;
+  MG_REQUIRE(T >= 0, MG_ERR_SHAPE, "negative token count");
+  if (T == 0) return MG_OK;
+  MG_REQUIRE(d_x && d_dst, MG_ERR_NULL, "mg_ep_dispatch: null pointer");
+  PeerPtrs peers;
+  int rc = gather_peers(h, peer_recv, &peers);
+  if (rc != MG_OK) return rc;
+  return launch_dispatch_rows(h, d_x, d_dst, T, peers, static_cast<cudaStream_t>(stream));
+}
+
+int mg_ep_combine(mg_handle hh, void* const* peer_out, const int32_t* d_dst, const int32_t* d_topk_idx,
+                  const float* d_topk_w, const void* d_shared_out, int64_t T, void* d_y, void* stream) {
+  Handle* h = check_handle(hh);
+  if (!h) return MG_ERR_STATE;
+  MG_REQUIRE(T >= 0, MG_ERR_SHAPE, "negative token count");
+  if (T == 0) return MG_OK;
+  MG_REQUIRE(d_dst && d_topk_idx && d_topk_w && d_y, MG_ERR_NULL, "mg_ep_combine: null pointer");
+  PeerPtrs peers;
+  int rc = gather_peers(h, peer_out, &peers);
+  if (rc != MG_OK) return rc;
+  return launch_combine_peers(h, peers, d_dst, d_topk_idx, d_topk_w, d_shared_out, T, d_y,
+                              static_cast<cudaStream_t>(stream));
+}
+
+}  // extern "C"

@@ -12,8 +12,14 @@
 //     or stores plain bf16 / fp32;
 //   * the tile list is derived on the device from the padded expert offsets (every expert
 //     starts on a 128-row boundary, so a tile never straddles two experts) — no host sync;
+//   * W8A16 variant (F8B): the B tile arrives as FP8 e4m3 bytes; eight converter warps turn it
+//     into the bf16 operand tile in shared memory, bf16(float(q) * scale[row/128][k/128]) —
+//     bit-identical to de-quantising the whole matrix first — in the same 128B-swizzled
+//     layout TMA would have produced, then hand it to the MMA warp through an mbarrier;
 //   * every mbarrier wait is bounded; on expiry the kernel records MG_DEV_WAIT_TIMEOUT, all
 //     roles leave their loops, TMEM is freed and the kernel returns.
+#include <cuda_fp8.h>
+
 #include "common.cuh"
 
 namespace mg {
@@ -24,8 +30,18 @@ constexpr int BN_MAX = 256;
 constexpr int STAGES = 4;
 constexpr int A_BYTES = BM * BK * 2;         // 16 KiB
 constexpr int B_BYTES = BN_MAX * BK * 2;     // 32 KiB
-constexpr int STAGE_BYTES = A_BYTES + B_BYTES;
+constexpr int B8_BYTES = BN_MAX * BK;         // 16 KiB: the same tile as FP8 bytes
+constexpr int B_SLOTS = 2;                   // converted bf16 B tiles in flight (W8A16 variant)
 constexpr int GEMM_THREADS = 192;
+constexpr int CONVERT_THREADS = 256;
+constexpr int NUM_BARS = 2 * STAGES + 4 + 2 * B_SLOTS;
+
+template <bool F8B>
+struct Cfg {
+  static constexpr int STAGE_BYTES = A_BYTES + (F8B ? B8_BYTES : B_BYTES);
+  static constexpr int RING_BYTES = STAGES * STAGE_BYTES + (F8B ? B_SLOTS * B_BYTES : 0);
+  static constexpr int THREADS = GEMM_THREADS + (F8B ? CONVERT_THREADS : 0);
+};
 constexpr int TMEM_COLS = 512;
 constexpr int ACC_COLS = 256;
 constexpr unsigned long long WAIT_LIMIT_NS = 2000000000ull;
@@ -41,13 +57,16 @@ struct GemmArgs {
   int k_blocks;
   int group_m;
   uint32_t idesc;
+  const float* scales;          // W8A16: [rows of B / 128][K / 128] fp32
+  int scale_cols;               // K / 128
   void* out;
   long long ldo;
   int32_t* status;
 };
 
-constexpr size_t SMEM_CTRL_BYTES = 8 * (2 * STAGES + 4) + 16 + 4 * (2 * kMaxExperts + 2);
-constexpr size_t GEMM_SMEM_BYTES = 1024 + STAGES * STAGE_BYTES + SMEM_CTRL_BYTES;
+constexpr size_t SMEM_CTRL_BYTES = 8 * NUM_BARS + 16 + 4 * (2 * kMaxExperts + 2);
+template <bool F8B>
+constexpr size_t gemm_smem_bytes() { return 1024 + Cfg<F8B>::RING_BYTES + SMEM_CTRL_BYTES; }
 
 // ---- PTX wrappers ---------------------------------------------------------------------
 __device__ __forceinline__ uint32_t smem_u32(const void* p) {
@@ -161,14 +180,16 @@ struct Tile {
 __device__ __forceinline__ Tile locate_tile(int tile, const int* s_pad, const int* s_cnt,
                                             int n_groups, int n_tiles, int n_per_group, int bn,
                                             int group_m) {
-  // greatest e with prefix(e) <= tile, prefix(e) = s_pad[e]/BM*n_tiles
+  // greatest e with prefix(e) <= tile, prefix(e) = (s_pad[e]-s_pad[0])/BM*n_tiles (the offsets
+  // may be a slice of a longer table, so they need not start at 0)
+  const int base0 = s_pad[0];
   int lo = 0, hi = n_groups;  // answer in [lo, hi)
   while (hi - lo > 1) {
     int mid = (lo + hi) >> 1;
-    if ((s_pad[mid] / BM) * n_tiles <= tile) lo = mid; else hi = mid;
+    if (((s_pad[mid] - base0) / BM) * n_tiles <= tile) lo = mid; else hi = mid;
   }
   const int e = lo;
-  const int local = tile - (s_pad[e] / BM) * n_tiles;
+  const int local = tile - ((s_pad[e] - base0) / BM) * n_tiles;
   const int m_e = (s_pad[e + 1] - s_pad[e]) / BM;
   const int per_group = group_m * n_tiles;
   const int grp = local / per_group;
@@ -186,18 +207,36 @@ __device__ __forceinline__ Tile locate_tile(int tile, const int* s_pad, const in
 
 __device__ __forceinline__ float silu_f(float g) { return __fdividef(g, 1.0f + __expf(-g)); }
 
-template <int EPI>
-__global__ void __launch_bounds__(GEMM_THREADS, 1)
+// 16 FP8 values -> 16 bf16 (two 16-byte chunks), each bf16(float(q) * s)
+__device__ __forceinline__ void convert16(const uint4& q, float s, uint4& lo, uint4& hi) {
+  const __nv_fp8x2_storage_t* p = reinterpret_cast<const __nv_fp8x2_storage_t*>(&q);
+  uint32_t o[8];
+#pragma unroll
+  for (int i = 0; i < 8; ++i) {
+    __half2_raw hr = __nv_cvt_fp8x2_to_halfraw2(p[i], __NV_E4M3);
+    float2 f = __half22float2(*reinterpret_cast<__half2*>(&hr));
+    __nv_bfloat162 b = __floats2bfloat162_rn(__fmul_rn(f.x, s), __fmul_rn(f.y, s));
+    o[i] = *reinterpret_cast<uint32_t*>(&b);
+  }
+  lo = make_uint4(o[0], o[1], o[2], o[3]);
+  hi = make_uint4(o[4], o[5], o[6], o[7]);
+}
+
+template <int EPI, bool F8B>
+__global__ void __launch_bounds__(Cfg<F8B>::THREADS, 1)
 grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
                     const GemmArgs g) {
+  constexpr int STAGE_BYTES = Cfg<F8B>::STAGE_BYTES;
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
-  uint64_t* bars = reinterpret_cast<uint64_t*>(smem + STAGES * STAGE_BYTES);
+  uint64_t* bars = reinterpret_cast<uint64_t*>(smem + Cfg<F8B>::RING_BYTES);
   uint64_t* full = bars;
   uint64_t* empty = bars + STAGES;
   uint64_t* tfull = bars + 2 * STAGES;
   uint64_t* tempty = bars + 2 * STAGES + 2;
-  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 2 * STAGES + 4);
+  uint64_t* bready = bars + 2 * STAGES + 4;            // converted B tile ready (W8A16)
+  uint64_t* bfree = bars + 2 * STAGES + 4 + B_SLOTS;   // converted B tile consumed
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + NUM_BARS);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
   int* s_pad = reinterpret_cast<int*>(tmem_slot + 4);
   int* s_cnt = s_pad + kMaxExperts + 1;
@@ -207,6 +246,7 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
   if (threadIdx.x == 0) {
     for (int s = 0; s < STAGES; ++s) { mbar_init(smem_u32(&full[s]), 1); mbar_init(smem_u32(&empty[s]), 1); }
     for (int a = 0; a < 2; ++a) { mbar_init(smem_u32(&tfull[a]), 1); mbar_init(smem_u32(&tempty[a]), 4); }
+    for (int j = 0; j < B_SLOTS; ++j) { mbar_init(smem_u32(&bready[j]), CONVERT_THREADS / 32); mbar_init(smem_u32(&bfree[j]), 1); }
     *abort_flag = 0;
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
   }
@@ -229,14 +269,15 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
   __syncthreads();
   tc_fence_after();
   const uint32_t tmem_base = *tmem_slot;
-  const int total_tiles = (s_pad[g.n_groups] / BM) * g.n_tiles;
+  const int total_tiles = ((s_pad[g.n_groups] - s_pad[0]) / BM) * g.n_tiles;
   const uint32_t smem_base = smem_u32(smem);
+  const uint32_t bslot_base = smem_base + STAGES * STAGE_BYTES;   // W8A16: converted B tiles
 
   if (warp == 0) {
     // ---------------- TMA producer ----------------
     if (lane == 0) {
       uint32_t it = 0;
-      const uint32_t tx_bytes = A_BYTES + static_cast<uint32_t>(g.bn) * BK * 2;
+      const uint32_t tx_bytes = A_BYTES + static_cast<uint32_t>(g.bn) * BK * (F8B ? 1 : 2);
       for (int tile = blockIdx.x; tile < total_tiles && !*abort_flag; tile += gridDim.x) {
         const Tile t = locate_tile(tile, s_pad, s_cnt, g.n_groups, g.n_tiles, g.n_per_group, g.bn, g.group_m);
         for (int kb = 0; kb < g.k_blocks; ++kb, ++it) {
@@ -263,21 +304,62 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
         for (int kb = 0; kb < g.k_blocks; ++kb, ++it) {
           const uint32_t s = it % STAGES, ph = (it / STAGES) & 1u;
           if (!mbar_wait(smem_u32(&full[s]), ph, abort_flag, g.status, 3)) { ok = false; break; }
+          const uint32_t j = it % B_SLOTS, jph = (it / B_SLOTS) & 1u;
+          if (F8B && !mbar_wait(smem_u32(&bready[j]), jph, abort_flag, g.status, 5)) { ok = false; break; }
           tc_fence_after();
           const uint32_t sa = smem_base + s * STAGE_BYTES;
-          const uint64_t da = make_smem_desc(sa), db = make_smem_desc(sa + A_BYTES);
+          const uint64_t da = make_smem_desc(sa);
+          const uint64_t db = make_smem_desc(F8B ? bslot_base + j * B_BYTES : sa + A_BYTES);
 #pragma unroll
           for (int k = 0; k < BK / 16; ++k) {
             // 16 bf16 = 32 bytes = 2 sixteen-byte units further along K inside the swizzle row
             tc_mma_bf16(d_tmem, da + 2 * k, db + 2 * k, g.idesc, (kb | k) != 0 ? 1u : 0u);
           }
           tc_commit(smem_u32(&empty[s]));   // frees the stage once these MMAs have read it
+          if (F8B) tc_commit(smem_u32(&bfree[j]));
         }
         if (!ok) break;
         tc_commit(smem_u32(&tfull[acc]));   // accumulator complete
       }
     }
-  } else {
+  } else if (F8B && warp >= 6) {
+    // ---------------- FP8 -> bf16 converter (W8A16) ----------------
+    const int ct = threadIdx.x - GEMM_THREADS;          // 0..CONVERT_THREADS-1
+    const int units = g.bn * (BK / 16);                   // 16-byte units of the FP8 tile
+    uint32_t it = 0;
+    for (int tile = blockIdx.x; tile < total_tiles && !*abort_flag; tile += gridDim.x) {
+      const Tile t = locate_tile(tile, s_pad, s_cnt, g.n_groups, g.n_tiles, g.n_per_group, g.bn, g.group_m);
+      const float* srow = g.scales + static_cast<long long>(t.b_row >> 7) * g.scale_cols;
+      bool ok = true;
+      for (int kb = 0; kb < g.k_blocks; ++kb, ++it) {
+        const uint32_t s = it % STAGES, ph = (it / STAGES) & 1u;
+        const uint32_t j = it % B_SLOTS, jph = (it / B_SLOTS) & 1u;
+        // one scale per 128 rows x 128 columns: rows [0,128) and [128,256) of the tile
+        const float s0 = __ldg(srow + (kb >> 1));
+        const float s1 = g.bn > 128 ? __ldg(srow + g.scale_cols + (kb >> 1)) : s0;
+        if (!mbar_wait(smem_u32(&full[s]), ph, abort_flag, g.status, 6)) { ok = false; break; }
+        if (!mbar_wait(smem_u32(&bfree[j]), jph ^ 1u, abort_flag, g.status, 7)) { ok = false; break; }
+        const uint8_t* src = smem + s * STAGE_BYTES + A_BYTES;
+        uint8_t* dst = smem + STAGES * STAGE_BYTES + j * B_BYTES;
+#pragma unroll
+        for (int u = ct; u < units; u += CONVERT_THREADS) {
+          const int r = u >> 2, c = u & 3;                // row of the tile, 16-byte chunk of its 64 bytes
+          const uint4 q = *reinterpret_cast<const uint4*>(src + u * 16);
+          uint4 lo, hi;
+          convert16(q, r < 128 ? s0 : s1, lo, hi);
+          // 128-byte bf16 row, 16-byte chunks XOR-swizzled by (row mod 8), as TMA SWIZZLE_128B lays them out
+          uint8_t* drow = dst + r * 128;
+          *reinterpret_cast<uint4*>(drow + (((2 * c) ^ (r & 7)) << 4)) = lo;
+          *reinterpret_cast<uint4*>(drow + (((2 * c + 1) ^ (r & 7)) << 4)) = hi;
+        }
+        // make the generic-proxy writes visible to the tensor core's shared-memory reads
+        asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+        __syncwarp();
+        if (lane == 0) mbar_arrive(smem_u32(&bready[j]));
+      }
+      if (!ok) break;
+    }
+  } else if (warp >= 2 && warp < 6) {
     // ---------------- epilogue ----------------
     const int quarter = warp & 3;             // TMEM lanes [32*quarter, 32*quarter+32)
     const int row_in_tile = quarter * 32 + lane;
@@ -391,15 +473,19 @@ static EncodeTiledFn get_encode_fn() {
   return fn;
 }
 
-static int encode_2d(CUtensorMap* map, const void* base, uint64_t rows, uint64_t cols, uint32_t box_rows) {
+// bf16 operands land 128B-swizzled (what the UMMA descriptor expects); FP8 bytes land as plain
+// rows of 64 bytes for the converter warps
+static int encode_2d(CUtensorMap* map, const void* base, uint64_t rows, uint64_t cols, uint32_t box_rows,
+                     bool fp8 = false) {
   EncodeTiledFn fn = get_encode_fn();
   MG_REQUIRE(fn != nullptr, MG_ERR_DRIVER, "cuTensorMapEncodeTiled not available from the driver");
   cuuint64_t dims[2] = {cols, rows};
-  cuuint64_t strides[1] = {cols * 2};
+  cuuint64_t strides[1] = {cols * (fp8 ? 1 : 2)};
   cuuint32_t box[2] = {static_cast<cuuint32_t>(BK), box_rows};
   cuuint32_t estr[2] = {1, 1};
-  CUresult r = fn(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(base), dims, strides, box, estr,
-                  CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+  CUresult r = fn(map, fp8 ? CU_TENSOR_MAP_DATA_TYPE_UINT8 : CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2,
+                  const_cast<void*>(base), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                  fp8 ? CU_TENSOR_MAP_SWIZZLE_NONE : CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
                   CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
   MG_REQUIRE(r == CUDA_SUCCESS, MG_ERR_DRIVER, "cuTensorMapEncodeTiled failed (%d) rows=%llu cols=%llu box=%u",
              static_cast<int>(r), static_cast<unsigned long long>(rows), static_cast<unsigned long long>(cols),
@@ -407,13 +493,14 @@ static int encode_2d(CUtensorMap* map, const void* base, uint64_t rows, uint64_t
   return MG_OK;
 }
 
-template <int EPI>
+template <int EPI, bool F8B>
 static int launch_epi(const Handle* h, const CUtensorMap& ta, const CUtensorMap& tb, const GemmArgs& args,
                       int grid, cudaStream_t st) {
   // per device, and cheap: set on every launch rather than tracking which devices have it
-  MG_CUDA(cudaFuncSetAttribute(grouped_gemm_kernel<EPI>, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                               static_cast<int>(GEMM_SMEM_BYTES)));
-  grouped_gemm_kernel<EPI><<<grid, GEMM_THREADS, GEMM_SMEM_BYTES, st>>>(ta, tb, args);
+  constexpr size_t smem = gemm_smem_bytes<F8B>();
+  MG_CUDA(cudaFuncSetAttribute(grouped_gemm_kernel<EPI, F8B>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                               static_cast<int>(smem)));
+  grouped_gemm_kernel<EPI, F8B><<<grid, Cfg<F8B>::THREADS, smem, st>>>(ta, tb, args);
   MG_CUDA(cudaGetLastError());
   return MG_OK;
 }
@@ -437,8 +524,13 @@ int launch_grouped_gemm(const Handle* h, const GemmProblem& p, cudaStream_t st) 
   CUtensorMap ta, tb;
   int rc = encode_2d(&ta, p.a, static_cast<uint64_t>(p.a_rows), static_cast<uint64_t>(p.K), BM);
   if (rc != MG_OK) return rc;
-  rc = encode_2d(&tb, p.b, static_cast<uint64_t>(p.n_groups) * p.n_per_group, static_cast<uint64_t>(p.K), bn);
+  rc = encode_2d(&tb, p.b, static_cast<uint64_t>(p.n_groups) * p.n_per_group, static_cast<uint64_t>(p.K), bn,
+                 p.b_fp8);
   if (rc != MG_OK) return rc;
+  if (p.b_fp8) {
+    MG_REQUIRE(!f32_out && p.scales != nullptr && p.K % 128 == 0, MG_ERR_SHAPE,
+               "FP8 weights need scales, K a multiple of 128 and a bf16 epilogue");
+  }
 
   GemmArgs a;
   a.pad_offsets = p.pad_offsets;
@@ -453,6 +545,8 @@ int launch_grouped_gemm(const Handle* h, const GemmProblem& p, cudaStream_t st) 
   // kind::f16: D fp32 (bit 4), A bf16 (bit 7), B bf16 (bit 10), both K-major, N>>3 at 17, M>>4 at 24
   a.idesc = (1u << 4) | (1u << 7) | (1u << 10) | (static_cast<uint32_t>(bn >> 3) << 17) |
             (static_cast<uint32_t>(BM >> 4) << 24);
+  a.scales = p.scales;
+  a.scale_cols = p.K / 128;
   a.out = p.out;
   a.ldo = p.ldo;
   a.status = h->d_status;
@@ -466,11 +560,18 @@ int launch_grouped_gemm(const Handle* h, const GemmProblem& p, cudaStream_t st) 
     if (max_tiles < grid) grid = static_cast<int>(max_tiles);
   }
   if (grid < 1) return MG_OK;
-  switch (p.epilogue) {
-    case EPI_SWIGLU_BF16: return launch_epi<EPI_SWIGLU_BF16>(h, ta, tb, a, grid, st);
-    case EPI_PLAIN_BF16: return launch_epi<EPI_PLAIN_BF16>(h, ta, tb, a, grid, st);
-    case EPI_PLAIN_F32: return launch_epi<EPI_PLAIN_F32>(h, ta, tb, a, grid, st);
-    case EPI_ROUND_BF16_F32: return launch_epi<EPI_ROUND_BF16_F32>(h, ta, tb, a, grid, st);
+  if (p.b_fp8) {
+    switch (p.epilogue) {
+      case EPI_SWIGLU_BF16: return launch_epi<EPI_SWIGLU_BF16, true>(h, ta, tb, a, grid, st);
+      case EPI_PLAIN_BF16: return launch_epi<EPI_PLAIN_BF16, true>(h, ta, tb, a, grid, st);
+    }
+  } else {
+    switch (p.epilogue) {
+      case EPI_SWIGLU_BF16: return launch_epi<EPI_SWIGLU_BF16, false>(h, ta, tb, a, grid, st);
+      case EPI_PLAIN_BF16: return launch_epi<EPI_PLAIN_BF16, false>(h, ta, tb, a, grid, st);
+      case EPI_PLAIN_F32: return launch_epi<EPI_PLAIN_F32, false>(h, ta, tb, a, grid, st);
+      case EPI_ROUND_BF16_F32: return launch_epi<EPI_ROUND_BF16_F32, false>(h, ta, tb, a, grid, st);
+    }
   }
   set_error("bad epilogue");
   return MG_ERR_CONFIG;

@@ -162,21 +162,31 @@ int launch_dequant(const void* q, const float* s, int64_t rows, int64_t cols, vo
   return MG_OK;
 }
 
-int launch_dequant_packed(const Handle* h, const void* packed, void* bf16_out, cudaStream_t st) {
+// which = 0: W13 of experts [e_lo, e_lo+e_n) -> bf16_out (same element layout as the packed
+// W13); which = 1: W2 likewise into the W2 part of bf16_out
+int launch_dequant_packed(const Handle* h, const void* packed, void* bf16_out, int which, int e_lo, int e_n,
+                          cudaStream_t st) {
   const mg_layer_desc& d = h->d;
   const PackedLayout L = packed_layout(h);
   const uint8_t* base = static_cast<const uint8_t*>(packed);
   const int64_t E = h->e_local, I = d.inter, H = d.hidden;
   __nv_bfloat16* o13 = static_cast<__nv_bfloat16*>(bf16_out);
   __nv_bfloat16* o2 = o13 + E * 2 * I * H;
-  const int grid = 148 * 16;
-  dequant_kernel<<<grid, 256, 0, st>>>(reinterpret_cast<const uint4*>(base + L.w13),
-                                       reinterpret_cast<const float*>(base + L.s13), E * 2 * I,
-                                       static_cast<int>(2 * I), static_cast<int>(H), reinterpret_cast<uint4*>(o13));
-  MG_CUDA(cudaGetLastError());
-  dequant_kernel<<<grid, 256, 0, st>>>(reinterpret_cast<const uint4*>(base + L.w2),
-                                       reinterpret_cast<const float*>(base + L.s2), E * H, static_cast<int>(H),
-                                       static_cast<int>(I), reinterpret_cast<uint4*>(o2));
+  const int grid = 148 * 8;
+  if (e_n <= 0) return MG_OK;
+  if (which == 0) {
+    const int64_t rows = 2 * I, off = e_lo * rows;
+    dequant_kernel<<<grid, 256, 0, st>>>(reinterpret_cast<const uint4*>(base + L.w13 + off * H),
+                                         reinterpret_cast<const float*>(base + L.s13) + off / 128 * (H / 128),
+                                         e_n * rows, static_cast<int>(rows), static_cast<int>(H),
+                                         reinterpret_cast<uint4*>(o13 + off * H));
+  } else {
+    const int64_t rows = H, off = e_lo * rows;
+    dequant_kernel<<<grid, 256, 0, st>>>(reinterpret_cast<const uint4*>(base + L.w2 + off * I),
+                                         reinterpret_cast<const float*>(base + L.s2) + off / 128 * (I / 128),
+                                         e_n * rows, static_cast<int>(rows), static_cast<int>(I),
+                                         reinterpret_cast<uint4*>(o2 + off * I));
+  }
   MG_CUDA(cudaGetLastError());
   return MG_OK;
 }

@@ -295,7 +295,8 @@ __global__ void __launch_bounds__(kPlanTokens) plan_place_kernel(const int32_t* 
 size_t plan_ws_bytes(const Handle* h, int64_t T) {
   int64_t nblk = (T + kPlanTokens - 1) / kPlanTokens;
   if (nblk < 1) nblk = 1;
-  return static_cast<size_t>(nblk) * h->d.n_experts * sizeof(int32_t);
+  // per-block counts, then 2*(E+1) ints used by the expert-parallel entry points
+  return (static_cast<size_t>(nblk) * h->d.n_experts + 2 * (h->d.n_experts + 1)) * sizeof(int32_t);
 }
 
 int launch_permute_plan(const Handle* h, const int32_t* idx, int64_t T, int expert_lo, int n_exp,
@@ -324,10 +325,13 @@ int launch_permute_plan(const Handle* h, const int32_t* idx, int64_t T, int expe
 // ---------------------------------------------------------------------------------------
 // row scatter: one warp per token, x row read once, written to each destination row
 // ---------------------------------------------------------------------------------------
+// PEER: dst_row packs (destination rank << kPeerShift | row) and rows are written to that
+// rank's buffer through its peer mapping (plain stores over NVLink)
+template <bool PEER>
 __global__ void __launch_bounds__(256) permute_rows_kernel(const uint4* __restrict__ x,
                                                            const int32_t* __restrict__ dst_row,
                                                            int64_t T, int k, int vec_per_row,
-                                                           uint4* __restrict__ perm_x) {
+                                                           PeerPtrs bufs) {
   const int lane = threadIdx.x & 31;
   const int64_t t = static_cast<int64_t>(blockIdx.x) * (blockDim.x >> 5) + (threadIdx.x >> 5);
   if (t >= T) return;
@@ -343,7 +347,8 @@ __global__ void __launch_bounds__(256) permute_rows_kernel(const uint4* __restri
     for (int j = 0; j < k; ++j) {
       int32_t d = __shfl_sync(0xFFFFFFFFu, my_dst, j);
       if (d < 0) continue;
-      uint4* dst = perm_x + static_cast<int64_t>(d) * vec_per_row;
+      uint4* dst = static_cast<uint4*>(PEER ? bufs.p[d >> kPeerShift] : bufs.p[0]) +
+                   static_cast<int64_t>(PEER ? (d & kPeerRowMask) : d) * vec_per_row;
 #pragma unroll
       for (int u = 0; u < 4; ++u) {
         int v = v0 + u * 32 + lane;
@@ -358,9 +363,21 @@ int launch_permute_rows(const Handle* h, const void* x, const int32_t* dst_row, 
   if (T == 0) return MG_OK;
   const int warps = 8;
   dim3 grid(static_cast<unsigned>((T + warps - 1) / warps)), block(warps * 32);
-  permute_rows_kernel<<<grid, block, 0, st>>>(static_cast<const uint4*>(x), dst_row, T,
-                                              h->d.top_k, h->d.hidden / 8,
-                                              static_cast<uint4*>(perm_x));
+  PeerPtrs bufs{};
+  bufs.p[0] = perm_x;
+  permute_rows_kernel<false><<<grid, block, 0, st>>>(static_cast<const uint4*>(x), dst_row, T,
+                                                     h->d.top_k, h->d.hidden / 8, bufs);
+  MG_CUDA(cudaGetLastError());
+  return MG_OK;
+}
+
+int launch_dispatch_rows(const Handle* h, const void* x, const int32_t* dst, int64_t T,
+                         const PeerPtrs& peers, cudaStream_t st) {
+  if (T == 0) return MG_OK;
+  const int warps = 8;
+  dim3 grid(static_cast<unsigned>((T + warps - 1) / warps)), block(warps * 32);
+  permute_rows_kernel<true><<<grid, block, 0, st>>>(static_cast<const uint4*>(x), dst, T,
+                                                    h->d.top_k, h->d.hidden / 8, peers);
   MG_CUDA(cudaGetLastError());
   return MG_OK;
 }
@@ -388,8 +405,8 @@ __device__ __forceinline__ float round_bf16(float f) {
   return __bfloat162float(__float2bfloat16_rn(f));
 }
 
-template <int MODE>
-__global__ void __launch_bounds__(256) combine_kernel(const uint4* __restrict__ rows,
+template <int MODE, bool PEER>
+__global__ void __launch_bounds__(256) combine_kernel(PeerPtrs bufs,
                                                       const int32_t* __restrict__ dst_row,
                                                       const int32_t* __restrict__ topk_idx,
                                                       const float* __restrict__ topk_w,
@@ -432,7 +449,10 @@ __global__ void __launch_bounds__(256) combine_kernel(const uint4* __restrict__ 
       float w = __shfl_sync(0xFFFFFFFFu, my_w, j);
       if (d < 0) continue;
       float f[8];
-      unpack8(__ldg(rows + static_cast<int64_t>(d) * vec_per_row + v), f);
+      const uint4* rows = static_cast<const uint4*>(PEER ? bufs.p[d >> kPeerShift] : bufs.p[0]);
+      const int64_t r = PEER ? (d & kPeerRowMask) : d;
+      // peer rows are written by another GPU during this forward: plain (coherent) loads
+      unpack8(PEER ? rows[r * vec_per_row + v] : __ldg(rows + r * vec_per_row + v), f);
 #pragma unroll
       for (int i = 0; i < 8; ++i) {
         float p = __fmul_rn(f[i], w);
@@ -451,17 +471,18 @@ __global__ void __launch_bounds__(256) combine_kernel(const uint4* __restrict__ 
   }
 }
 
-int launch_combine(const Handle* h, const void* out_rows, const int32_t* dst_row,
-                   const int32_t* idx, const float* w, const void* shared, int64_t T, void* y,
-                   cudaStream_t st) {
+template <bool PEER>
+static int launch_combine_impl(const Handle* h, const PeerPtrs& bufs, const int32_t* dst_row,
+                               const int32_t* idx, const float* w, const void* shared, int64_t T, void* y,
+                               cudaStream_t st) {
   if (T == 0) return MG_OK;
   const int warps = 8;
   dim3 grid(static_cast<unsigned>((T + warps - 1) / warps)), block(warps * 32);
   const int k = h->d.top_k, vpr = h->d.hidden / 8;
-#define MG_COMBINE_CASE(M)                                                                  \
-  combine_kernel<M><<<grid, block, 0, st>>>(static_cast<const uint4*>(out_rows), dst_row,   \
-                                            idx, w, static_cast<const uint4*>(shared), T, k, \
-                                            vpr, static_cast<uint4*>(y))
+#define MG_COMBINE_CASE(M)                                                                       \
+  combine_kernel<M, PEER><<<grid, block, 0, st>>>(bufs, dst_row, idx, w,                          \
+                                                  static_cast<const uint4*>(shared), T, k, vpr,   \
+                                                  static_cast<uint4*>(y))
   switch (h->d.combine_mode) {
     case MG_COMBINE_FP32: MG_COMBINE_CASE(MG_COMBINE_FP32); break;
     case MG_COMBINE_BF16_PROD: MG_COMBINE_CASE(MG_COMBINE_BF16_PROD); break;
@@ -470,6 +491,107 @@ int launch_combine(const Handle* h, const void* out_rows, const int32_t* dst_row
   }
 #undef MG_COMBINE_CASE
   MG_CUDA(cudaGetLastError());
+  return MG_OK;
+}
+
+int launch_combine(const Handle* h, const void* out_rows, const int32_t* dst_row,
+                   const int32_t* idx, const float* w, const void* shared, int64_t T, void* y,
+                   cudaStream_t st) {
+  PeerPtrs bufs{};
+  bufs.p[0] = const_cast<void*>(out_rows);
+  return launch_combine_impl<false>(h, bufs, dst_row, idx, w, shared, T, y, st);
+}
+
+int launch_combine_peers(const Handle* h, const PeerPtrs& peers, const int32_t* dst,
+                         const int32_t* idx, const float* w, const void* shared, int64_t T, void* y,
+                         cudaStream_t st) {
+  return launch_combine_impl<true>(h, peers, dst, idx, w, shared, T, y, st);
+}
+
+// ---------------------------------------------------------------------------------------
+// expert-parallel layout: where this rank's rows go in every owner's expert-sorted buffer
+// ---------------------------------------------------------------------------------------
+// counts_all[s][e]: picks of expert e among rank s's tokens.  Owner of e is e / e_local.  In the
+// owner's buffer expert segments start on 128-row boundaries, and inside a segment the rows of
+// source rank 0 come first, then rank 1, ... (tokens ascending within a source rank).
+//   send_base[e]   = owner << kPeerShift | first row of this rank's rows of expert e
+//   recv_counts[j] = rows of local expert j over all sources; recv_pad[j] their padded offsets
+// If an owner would need more than cap_rows rows, its send_base entries become negative (the
+// scatter and combine kernels skip negative destinations) and the status word is set.
+__global__ void __launch_bounds__(512) ep_layout_kernel(const int32_t* __restrict__ counts_all, int n_ranks,
+                                                        int rank, int E, int e_local, int cap_rows,
+                                                        int32_t* __restrict__ send_base,
+                                                        int32_t* __restrict__ recv_counts,
+                                                        int32_t* __restrict__ recv_pad,
+                                                        int32_t* __restrict__ status) {
+  __shared__ int32_t tot[kMaxExperts];
+  __shared__ int32_t before[kMaxExperts];
+  __shared__ int32_t pad[kMaxExperts];
+  __shared__ int32_t over[kMaxPeers];
+  for (int e = threadIdx.x; e < E; e += blockDim.x) {
+    int32_t t = 0, b = 0;
+    for (int s = 0; s < n_ranks; ++s) {
+      int32_t c = counts_all[s * E + e];
+      if (s < rank) b += c;
+      t += c;
+    }
+    tot[e] = t;
+    before[e] = b;
+  }
+  __syncthreads();
+  if (threadIdx.x < n_ranks) {
+    const int d = threadIdx.x;
+    int32_t p = 0;
+    for (int j = 0; j < e_local; ++j) {
+      pad[d * e_local + j] = p;
+      p += (tot[d * e_local + j] + kTileM - 1) / kTileM * kTileM;
+    }
+    over[d] = p > cap_rows;
+    if (d == rank) recv_pad[e_local] = p > cap_rows ? 0 : p;
+    if (p > cap_rows && atomicCAS(status, MG_DEV_OK, MG_DEV_CAPACITY) == MG_DEV_OK) status[1] = d;
+  }
+  __syncthreads();
+  for (int e = threadIdx.x; e < E; e += blockDim.x) {
+    const int d = e / e_local;
+    send_base[e] = over[d] ? kSkipRow : ((d << kPeerShift) | (pad[e] + before[e]));
+    if (d == rank) {
+      const int j = e - d * e_local;
+      recv_counts[j] = over[d] ? 0 : tot[e];
+      recv_pad[j] = over[d] ? 0 : pad[e];
+    }
+  }
+}
+
+int launch_ep_count(const Handle* h, const int32_t* idx, int64_t T, int32_t* counts, void* ws,
+                    cudaStream_t st) {
+  const int E = h->d.n_experts, k = h->d.top_k;
+  int nblk = static_cast<int>((T + kPlanTokens - 1) / kPlanTokens);
+  int32_t* bc = static_cast<int32_t*>(ws);
+  int32_t* scratch = bc + static_cast<size_t>(nblk > 0 ? nblk : 1) * E;   // offsets / pad_offsets, unused here
+  if (nblk > 0) {
+    plan_count_kernel<<<nblk, kPlanTokens, E * sizeof(int32_t), st>>>(idx, T, k, 0, E, bc);
+    MG_CUDA(cudaGetLastError());
+  }
+  plan_scan_kernel<<<1, 1024, 0, st>>>(bc, nblk, E, counts, scratch, scratch + E + 1);
+  MG_CUDA(cudaGetLastError());
+  return MG_OK;
+}
+
+int launch_ep_place(const Handle* h, const int32_t* idx, int64_t T, const int32_t* counts_all,
+                    int cap_rows, void* ws, int32_t* recv_counts, int32_t* recv_pad, int32_t* dst,
+                    cudaStream_t st) {
+  const int E = h->d.n_experts, k = h->d.top_k;
+  int nblk = static_cast<int>((T + kPlanTokens - 1) / kPlanTokens);
+  int32_t* bc = static_cast<int32_t*>(ws);
+  int32_t* send_base = bc + static_cast<size_t>(nblk > 0 ? nblk : 1) * E;
+  ep_layout_kernel<<<1, 512, 0, st>>>(counts_all, h->d.ep_size, h->d.ep_rank, E, h->e_local, cap_rows,
+                                      send_base, recv_counts, recv_pad, h->d_status);
+  MG_CUDA(cudaGetLastError());
+  if (nblk > 0) {
+    size_t smem = static_cast<size_t>(2) * (kPlanTokens / 32) * E * sizeof(int32_t);
+    plan_place_kernel<<<nblk, kPlanTokens, smem, st>>>(idx, T, k, 0, E, bc, send_base, dst);
+    MG_CUDA(cudaGetLastError());
+  }
   return MG_OK;
 }
 

@@ -125,6 +125,10 @@ class MoELayer:
         L.check(self.lib.mg_device_status(self._h, C.byref(code), C.byref(detail)))
         return code.value, detail.value
 
+    def set_option(self, option: int, value: int):
+        L.check(self.lib.mg_set_option(self._h, option, value))
+        self._ws, self._ws_tokens = None, -1        # workspace layout may depend on options
+
     def set_stage_timing(self, enable: bool):
         L.check(self.lib.mg_set_stage_timing(self._h, int(enable)))
 
@@ -244,14 +248,16 @@ class MoELayer:
                                              perm.data_ptr(), self._stream()))
         return perm
 
-    def expert_ffn(self, perm_x: torch.Tensor, pad_offsets: torch.Tensor, counts: torch.Tensor):
-        """-> (h_buf [rows,I], out_rows [rows,H]) over the padded expert-sorted rows."""
+    def expert_ffn(self, perm_x: torch.Tensor, pad_offsets: torch.Tensor, counts: torch.Tensor,
+                   predequant: bool = False):
+        """-> (h_buf [rows,I], out_rows [rows,H]) over the padded expert-sorted rows.
+        predequant=True (FP8 layers) de-quantises the weights into scratch first."""
         rows = perm_x.shape[0]
         hbuf = torch.zeros(rows, self.I, dtype=torch.bfloat16, device=self.device)
         out = torch.zeros(rows, self.H, dtype=torch.bfloat16, device=self.device)
         nb = C.c_size_t()
         L.check(self.lib.mg_dequant_ws_bytes(self._h, C.byref(nb)))
-        deq = torch.empty(nb.value, dtype=torch.uint8, device=self.device) if nb.value else None
+        deq = torch.empty(nb.value, dtype=torch.uint8, device=self.device) if (nb.value and predequant) else None
         with torch.cuda.device(self.device):
             L.check(self.lib.mg_expert_ffn(self._h, perm_x.data_ptr(), pad_offsets.data_ptr(), counts.data_ptr(),
                                            rows, self.packed.data_ptr(), hbuf.data_ptr(), out.data_ptr(),

@@ -16,6 +16,8 @@ GATE_SOFTMAX_GREEDY, GATE_SOFTMAX_GROUP_MAX, GATE_SIGMOID_NOAUX_TC, GATE_SOFTMAX
 COMBINE_FP32, COMBINE_BF16_PROD, COMBINE_BF16_SEQ = 0, 1, 2
 WEIGHT_BF16, WEIGHT_FP8_BLOCK128 = 0, 1
 DEV_OK, DEV_WAIT_TIMEOUT = 0, 1
+OPT_FP8_MODE = 1
+FP8_AUTO, FP8_PREDEQUANT, FP8_IN_KERNEL = 0, 1, 2
 
 
 class LayerDesc(C.Structure):
@@ -52,6 +54,16 @@ SIGNATURES = {
     "mg_moe_forward": [_vp, _vp, _i64, _vp, _vp, _vp, _vp, _sz, _vp, _vp],
     "mg_workspace_ptr": [_vp, _vp, _i64, _i64, _i32, _P(_vp)],
     "mg_last_launch_count": [_vp, _P(_i32)],
+    "mg_ep_alloc": [_sz, _P(_vp)],
+    "mg_ep_free": [_vp],
+    "mg_ep_export": [_vp, _vp],
+    "mg_ep_import": [_vp, _P(_vp)],
+    "mg_ep_unimport": [_vp],
+    "mg_ep_count": [_vp, _vp, _i64, _vp, _vp, _vp],
+    "mg_ep_place": [_vp, _vp, _i64, _vp, _i64, _vp, _vp, _vp, _vp, _vp],
+    "mg_ep_dispatch": [_vp, _vp, _vp, _i64, _P(_vp), _vp],
+    "mg_ep_combine": [_vp, _P(_vp), _vp, _vp, _vp, _vp, _i64, _vp, _vp],
+    "mg_set_option": [_vp, _i32, _i32],
     "mg_set_stage_timing": [_vp, _i32],
     "mg_stage_times": [_vp, _P(C.c_float), _i32],
 }

@@ -219,6 +219,35 @@ def test_all_tokens_to_one_expert(built_lib):
     assert worst < 5e-3
 
 
+def test_fp8_weights_converted_in_the_gemm_equal_dequantise_first(built_lib):
+    """W8A16: converting FP8 tiles inside the grouped GEMM gives the same bits as de-quantising
+    the matrices first (the reference's order, Wrapper.py:481-491) and running the bf16 kernel."""
+    spec = O.LayerSpec(512, 256, 16, 4, 256, 4, 2, O.GATE_SIGMOID_NOAUX_TC, True, 2.5, O.WEIGHT_FP8_BLOCK128,
+                       O.COMBINE_FP32)
+    x, W = O.make_inputs(spec, 900, 51)
+    layer = make_layer(spec, W, DEV)
+    xd = x.to(DEV)
+    idx, w = layer.route_topk(layer.gate_logits(xd))
+    counts, offsets, pad, dst = layer.permute_plan(idx)
+    perm = layer.permute_rows(xd, dst, layer.padded_rows(900 * 4))
+    h1, o1 = layer.expert_ffn(perm, pad, counts, predequant=False)
+    h2, o2 = layer.expert_ffn(perm, pad, counts, predequant=True)
+    _status_ok(layer)
+    live = torch.zeros(perm.shape[0], dtype=torch.bool)
+    live[dst.cpu().long().view(-1)] = True
+    assert torch.equal(h1.cpu()[live].view(torch.int16), h2.cpu()[live].view(torch.int16))
+    assert torch.equal(o1.cpu()[live].view(torch.int16), o2.cpu()[live].view(torch.int16))
+    worst, _ = _check_expert_rows(spec, W, xd, layer, idx)
+    assert worst < 5e-3
+    ys = []
+    for mode in (0, 1, 2, 1):                      # auto, pre-dequantise, in-kernel, again
+        layer.set_option(1, mode)
+        ys.append(layer.forward(xd).cpu())
+        _status_ok(layer)
+    for y in ys[1:]:
+        assert torch.equal(ys[0].view(torch.int16), y.view(torch.int16))
+
+
 # --------------------------------------------------------------------------- combine
 @pytest.mark.parametrize("mode", [O.COMBINE_FP32, O.COMBINE_BF16_PROD, O.COMBINE_BF16_SEQ])
 @pytest.mark.parametrize("with_shared", [False, True])
