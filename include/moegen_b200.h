@@ -182,6 +182,28 @@ int mg_permute_plan(mg_handle h, const int32_t* d_topk_idx, int64_t n_tokens,
                     int32_t* d_counts, int32_t* d_offsets, int32_t* d_pad_offsets,
                     int32_t* d_dst_row, void* d_plan_ws, void* stream);
 
+/* mg_permute_plan for callers that must not allocate device memory and have no scratch
+ * buffer to hand in.  It has no counterpart in the reference.  Such callers exist around this
+ * library: an engine that sized its weight and KV buffers from all the memory that was free at
+ * start-up has nothing left to cudaMalloc later, and inside a decode loop a cudaMalloc would
+ * stall every stream of the device.  The arguments and results are those of mg_permute_plan
+ * without d_plan_ws: the scratch is a fixed array inside the library image (about 516 KiB,
+ * present on every GPU that loads the library, for the life of the process).
+ *  - limit: ceil(n_tokens/256) * n_experts + 2*(n_experts+1) <= 132098 words, i.e. up to 65536
+ *    tokens at 512 experts (more tokens with fewer experts).  Larger requests return
+ *    MG_ERR_LIMIT with a text saying so; use mg_permute_plan then;
+ *  - the call makes no cudaMalloc / cudaFree and calls no allocating routine;
+ *  - the first call on a device looks up the device address of the array (one
+ *    cudaGetSymbolAddress, with the handle's device current); make that first call before any
+ *    stream capture begins;
+ *  - all calls on a device share the one array and it keeps the previous call's contents.  The
+ *    kernels overwrite every word before reading it, so nothing has to be cleared, but two
+ *    calls that overlap on the GPU (different streams, no ordering between them) race on it. */
+int mg_permute_plan_static(mg_handle h, const int32_t* d_topk_idx, int64_t n_tokens,
+                           int32_t expert_lo, int32_t n_plan_experts,
+                           int32_t* d_counts, int32_t* d_offsets, int32_t* d_pad_offsets,
+                           int32_t* d_dst_row, void* stream);
+
 /* perm_x[dst_row[t*k+j], :] = x[t, :] for every pick with dst_row >= 0.
  * Replaces sorted_tokens = x[idxs // k] (modeling_deepseek_v3.py:634). */
 int mg_permute_rows(mg_handle h, const void* d_x, const int32_t* d_dst_row, int64_t n_tokens,

@@ -259,6 +259,17 @@ int mg_permute_plan(mg_handle hh, const int32_t* d_idx, int64_t T, int32_t exper
                              static_cast<cudaStream_t>(stream), nullptr);
 }
 
+int mg_permute_plan_static(mg_handle hh, const int32_t* d_idx, int64_t T, int32_t expert_lo, int32_t n_plan,
+                           int32_t* d_counts, int32_t* d_offsets, int32_t* d_pad, int32_t* d_dst, void* stream) {
+  Handle* h = check(hh);
+  if (!h) return MG_ERR_STATE;
+  MG_REQUIRE(d_idx && d_counts && d_offsets && d_pad && d_dst, MG_ERR_NULL, "mg_permute_plan_static: null pointer");
+  MG_REQUIRE(T >= 0 && expert_lo >= 0 && n_plan >= 1 && expert_lo + n_plan <= h->d.n_experts, MG_ERR_SHAPE,
+             "expert range [%d,%d) outside [0,%d)", expert_lo, expert_lo + n_plan, h->d.n_experts);
+  return launch_permute_plan_static(h, d_idx, T, expert_lo, n_plan, d_counts, d_offsets, d_pad, d_dst,
+                                    static_cast<cudaStream_t>(stream));
+}
+
 int mg_permute_rows(mg_handle hh, const void* d_x, const int32_t* d_dst, int64_t T, void* d_perm, void* stream) {
   Handle* h = check(hh);
   if (!h) return MG_ERR_STATE;

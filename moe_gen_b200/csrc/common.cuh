@@ -68,6 +68,9 @@ size_t plan_ws_bytes(const Handle* h, int64_t T);
 int launch_permute_plan(const Handle* h, const int32_t* idx, int64_t T, int expert_lo, int n_exp,
                         int32_t* counts, int32_t* offsets, int32_t* pad_offsets, int32_t* dst_row,
                         void* ws, cudaStream_t st, int* launches);
+int launch_permute_plan_static(const Handle* h, const int32_t* idx, int64_t T, int expert_lo, int n_exp,
+                               int32_t* counts, int32_t* offsets, int32_t* pad_offsets, int32_t* dst_row,
+                               cudaStream_t st);
 int launch_permute_rows(const Handle* h, const void* x, const int32_t* dst_row, int64_t T,
                         void* perm_x, cudaStream_t st);
 int launch_combine(const Handle* h, const void* out_rows, const int32_t* dst_row,

@@ -1,6 +1,8 @@
 // Routing (scoring + top-k), permute plan (histogram, prefix sums, stable placement),
 // row scatter and weighted combine.  All HBM-bound index/byte work: one warp per token,
 // 128-bit vector accesses on rows.
+#include <mutex>
+
 #include "common.cuh"
 
 namespace mg {
@@ -320,6 +322,55 @@ int launch_permute_plan(const Handle* h, const int32_t* idx, int64_t T, int expe
   }
   if (launches) *launches += nblk > 0 ? 3 : 1;
   return MG_OK;
+}
+
+// ---------------------------------------------------------------------------------------
+// permute plan without any allocation: the scratch lives in the library image
+// ---------------------------------------------------------------------------------------
+// Per-block expert counts for up to kStaticPlanBlocks * kStaticPlanExperts entries (65536
+// tokens at 512 experts; more tokens when there are fewer experts) plus the two small offset
+// arrays.  Every GPU that loads this library carries these ~516 KiB until the process exits.
+constexpr int kStaticPlanBlocks = 256;
+constexpr int kStaticPlanExperts = 512;
+constexpr int kStaticPlanInts = kStaticPlanBlocks * kStaticPlanExperts + 2 * (kStaticPlanExperts + 1);
+static __device__ __align__(256) int32_t g_plan_scratch[kStaticPlanInts];
+
+// In host code `g_plan_scratch` is only a stand-in for the symbol; the address a kernel can use
+// is looked up once per device, with that device current.
+static int static_plan_scratch(int device, int32_t** out) {
+  static std::mutex mu;
+  static int32_t* addr[64] = {nullptr};
+  MG_REQUIRE(device >= 0 && device < 64, MG_ERR_LIMIT, "device ordinal %d out of range", device);
+  std::lock_guard<std::mutex> lock(mu);
+  if (addr[device] == nullptr) {
+    void* p = nullptr;
+    MG_CUDA(cudaGetSymbolAddress(&p, g_plan_scratch));
+    addr[device] = static_cast<int32_t*>(p);
+  }
+  *out = addr[device];
+  return MG_OK;
+}
+
+int launch_permute_plan_static(const Handle* h, const int32_t* idx, int64_t T, int expert_lo, int n_exp,
+                               int32_t* counts, int32_t* offsets, int32_t* pad_offsets, int32_t* dst_row,
+                               cudaStream_t st) {
+  const int64_t nblk = (T + kPlanTokens - 1) / kPlanTokens;
+  const int64_t need = nblk * h->d.n_experts + 2 * (h->d.n_experts + 1);
+  MG_REQUIRE(need <= kStaticPlanInts, MG_ERR_LIMIT,
+             "mg_permute_plan_static: %lld tokens x %d experts need %lld scratch words, the built-in scratch holds "
+             "%d (at most %d tokens at %d experts); use mg_permute_plan with caller-provided scratch",
+             static_cast<long long>(T), h->d.n_experts, static_cast<long long>(need), kStaticPlanInts,
+             kStaticPlanBlocks * kPlanTokens, kStaticPlanExperts);
+  int dev = -1;
+  MG_CUDA(cudaGetDevice(&dev));
+  MG_REQUIRE(dev == h->device, MG_ERR_STATE, "current device %d is not the handle's device %d", dev, h->device);
+  int32_t* scratch = nullptr;
+  int rc = static_plan_scratch(dev, &scratch);
+  if (rc != MG_OK) return rc;
+  // Nothing here needs a cleared scratch: the count kernel writes every per-block entry the scan
+  // and placement kernels read, so whatever the previous call left behind is overwritten first.
+  return launch_permute_plan(h, idx, T, expert_lo, n_exp, counts, offsets, pad_offsets, dst_row, scratch, st,
+                             nullptr);
 }
 
 // ---------------------------------------------------------------------------------------

@@ -46,6 +46,7 @@ SIGNATURES = {
     "mg_route_topk": [_vp, _vp, _vp, _i64, _vp, _vp, _vp],
     "mg_plan_ws_bytes": [_vp, _i64, _P(_sz)],
     "mg_permute_plan": [_vp, _vp, _i64, _i32, _i32, _vp, _vp, _vp, _vp, _vp, _vp],
+    "mg_permute_plan_static": [_vp, _vp, _i64, _i32, _i32, _vp, _vp, _vp, _vp, _vp],
     "mg_permute_rows": [_vp, _vp, _vp, _i64, _vp, _vp],
     "mg_dequant_ws_bytes": [_vp, _P(_sz)],
     "mg_expert_ffn": [_vp, _vp, _vp, _vp, _i64, _vp, _vp, _vp, _vp, _vp],
