@@ -257,6 +257,7 @@ def main():
     H, I, E, k, Is = WORKLOADS[name][:5]
     warmup = max(args.warmup, 3) if args.impl == "ours" else args.warmup
     config = {"workload": WORKLOAD_TEXT[name], "tokens": T, "seed": WORKLOADS[name][13],
+              "parallelism": f"ep{world}" if world > 1 else "single GPU",
               "zipf_alpha": args.zipf, "l2": "inputs exceed L2 (x, routed rows and weights are each >126 MB)"
               if T * H * 2 > 126e6 else "L2 flushed between steps by writing a 256 MB buffer"}
 
@@ -312,7 +313,10 @@ def main():
     code, detail = base.device_status()
     if code != 0:
         raise SystemExit(f"device status {code} (detail {detail}) after warm-up")
-    base.set_stage_timing(True)
+    if world == 1:
+        base.set_stage_timing(True)
+    else:
+        layer.timing = True
     sampler = ClockSampler(local_rank)
     if rank == 0:
         sampler.start()
@@ -333,9 +337,18 @@ def main():
         t = torch.tensor([ms], device=device)
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
         ms = float(t.item())
-    stage_ms = base.stage_times()
-    base.set_stage_timing(False)
-    launches = base.last_launch_count() + (1 if flush is not None else 0)
+    if world == 1:
+        stage_ms = base.stage_times()
+        base.set_stage_timing(False)
+        launches = base.last_launch_count() + (1 if flush is not None else 0)
+        phases = None
+    else:
+        layer.timing = False
+        phases = layer.phase_times()
+        stage_ms = {"expert_gemm1": 0.0}
+        # gate, top-k, count(2), layout, place, dispatch, [shared 2], experts (2, or 4 per chunk when
+        # FP8 weights are pre-dequantised), combine; NCCL kernels not counted
+        launches = 8 + (2 if Is else 0) + (32 if layer.deq is not None else 2)
     code, detail = base.device_status()
     if code != 0:
         raise SystemExit(f"device status {code} (detail {detail}) in the timed region")
@@ -362,7 +375,31 @@ def main():
                "h2d_bytes_per_step": xh.numel() * 2, "d2h_bytes_per_step": yh.numel() * 2,
                "equals_device_path": bool(same), "chunk_tokens": args.chunk_tokens}
     elif not args.no_e2e:
-        e2e = layer.bench_e2e(x, args.steps) if hasattr(layer, "bench_e2e") else None
+        # every rank brings its own token shard from pinned host memory and takes its result back
+        xh = x.cpu().pin_memory()
+        yh = torch.empty_like(xh).pin_memory()
+        xd = torch.empty_like(x)
+
+        def host_step():
+            xd.copy_(xh, non_blocking=True)
+            yh.copy_(layer.forward(xd), non_blocking=True)
+        for _ in range(2):
+            host_step()
+        torch.cuda.synchronize()
+        dist.barrier()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        for _ in range(args.steps):
+            host_step()
+        e1.record()
+        torch.cuda.synchronize()
+        dist.barrier()
+        t = torch.tensor([e0.elapsed_time(e1) / args.steps], device=device)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        e_ms = float(t.item())
+        e2e = {"value": T_total / (e_ms * 1e-3), "unit": "tokens/s", "ms_per_step": e_ms,
+               "h2d_bytes_per_step": xh.numel() * 2 * world, "d2h_bytes_per_step": yh.numel() * 2 * world,
+               "equals_device_path": bool(torch.equal(yh.view(torch.int16), y.cpu().view(torch.int16)))}
 
     if rank != 0:
         if world > 1:
@@ -370,10 +407,16 @@ def main():
         return
 
     alg = algorithmic(name, T_total)
-    t_g1 = stage_ms["expert_gemm1"] * 1e-3
-    tf = alg["gemm1_flops"] / world / t_g1 / 1e12 if t_g1 > 0 else 0.0
+    if world > 1:
+        # expert phase = gate/up GEMM + down GEMM (+ FP8 conversion) of this rank's experts
+        t_g1 = phases["expert_ffn"] * 1e-3
+        tf = (alg["gemm1_flops"] + alg["gemm2_flops"]) / world / t_g1 / 1e12 if t_g1 > 0 else 0.0
+    else:
+        t_g1 = stage_ms["expert_gemm1"] * 1e-3
+        tf = alg["gemm1_flops"] / world / t_g1 / 1e12 if t_g1 > 0 else 0.0
     peak_tf = peaks.get("bf16_tflops_sustained", FALLBACK_PEAKS["bf16_tflops_sustained"])
-    roofline = {"kernel": "grouped_gemm_kernel<SWIGLU> (routed gate/up projections + SiLU*mul)",
+    roofline = {"kernel": "grouped_gemm_kernel<SWIGLU> (routed gate/up projections + SiLU*mul)" if world == 1 else
+                "grouped_gemm_kernel, both expert GEMMs of rank 0 (expert phase of the expert-parallel forward)",
                 "bound": "tensor", "achieved": tf, "peak": peak_tf, "unit": "TFLOP/s", "frac": tf / peak_tf,
                 "peak_kind": f"of {peak_kind} sustained bf16 GEMM", "frac_of_burst": tf / peaks.get("bf16_tflops", 1590.0),
                 "traffic": None}
@@ -395,6 +438,12 @@ def main():
     for st in ("permute_plan", "dequant"):
         if stage_ms.get(st, 0.0) > 0:
             stages[st] = {"ms": round(stage_ms[st], 4)}
+    if phases is not None:
+        stages = {k_: {"ms": round(v, 4)} for k_, v in phases.items()}
+        nv = Tl * k * H * 2 * (world - 1) / world          # bytes this rank sends (and later fetches) over NVLink
+        for ph in ("dispatch", "combine"):
+            if phases[ph] > 0:
+                stages[ph]["nvlink_gbs"] = round(nv / (phases[ph] * 1e-3) / 1e9, 1)
 
     cpu = None
     if not args.no_cpu_baseline:

@@ -1,0 +1,120 @@
+"""Worker functions for the multi-process expert-parallel tests (spawned, one per rank)."""
+import os
+import sys
+
+import numpy as np
+import torch
+import torch.distributed as dist
+
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+if ROOT not in sys.path:
+    sys.path.insert(0, ROOT)
+
+from oracle import moe_oracle as O  # noqa: E402
+
+
+def _init(rank, world, port, backend):
+    os.environ["MASTER_ADDR"] = "127.0.0.1"
+    os.environ["MASTER_PORT"] = str(port)
+    dist.init_process_group(backend, rank=rank, world_size=world)
+
+
+def cpu_ep_worker(rank, world, port, spec, T_global, seed, result):
+    """Expert-parallel layer on CPU ranks (gloo): routing, layout, exchange, experts, return.
+
+    Rows are exchanged by gathering (destination, row) lists, which models 'every rank writes
+    its rows into the owner's buffer'; the layout comes from ep_layout_reference, the host
+    restatement of the device layout kernel."""
+    from moe_gen_b200.ep import PEER_SHIFT, ep_layout_reference
+    _init(rank, world, port, "gloo")
+    torch.set_num_threads(2)
+    x_all, W = O.make_inputs(spec, T_global, seed)
+    Tl = T_global // world
+    x = x_all[rank * Tl:(rank + 1) * Tl]
+    E, El, k = spec.n_experts, spec.n_experts // world, spec.top_k
+    logits = O.gate_logits(x, W.gate_w, bf16_out=(spec.gating == O.GATE_SOFTMAX_TOPK_RENORM))
+    idx, w = O.route(spec, logits, W.bias)
+    counts = torch.bincount(idx.reshape(-1), minlength=E).to(torch.int32)
+    gathered = [torch.empty_like(counts) for _ in range(world)]
+    dist.all_gather(gathered, counts)
+    counts_all = torch.stack(gathered).numpy()
+    cap = ((T_global * k + 127) // 128 + El) * 128
+    send_base, recv_counts, recv_pad, over = ep_layout_reference(counts_all, rank, El, cap)
+    assert not over.any()
+    # stable placement of this rank's picks (tokens ascending inside an expert)
+    flat = idx.reshape(-1)
+    order = flat.argsort(stable=True)
+    off = np.concatenate([[0], np.cumsum(counts.numpy())])
+    dst = np.empty(Tl * k, dtype=np.int64)
+    for pos, f in enumerate(order.tolist()):
+        e = int(flat[f])
+        dst[f] = send_base[e] + (pos - off[e])
+    # dispatch: everybody learns every (dst, row); owners keep what is theirs
+    mine = [(int(d), x[f // k]) for f, d in enumerate(dst.tolist())]
+    everyone = [None] * world
+    dist.all_gather_object(everyone, mine)
+    recv = torch.zeros(cap, spec.hidden, dtype=torch.float32)
+    filled = np.zeros(cap, dtype=np.int32)
+    for lst in everyone:
+        for d, row in lst:
+            if d >> PEER_SHIFT == rank:
+                recv[d & ((1 << PEER_SHIFT) - 1)] = row.float()
+                filled[d & ((1 << PEER_SHIFT) - 1)] += 1
+    # every row of every local segment written exactly once, nothing outside the segments
+    expect = np.zeros(cap, dtype=np.int32)
+    for j in range(El):
+        expect[recv_pad[j]:recv_pad[j] + recv_counts[j]] = 1
+    assert np.array_equal(filled, expect)
+    out = torch.zeros_like(recv)
+    for j in range(El):
+        a, n = int(recv_pad[j]), int(recv_counts[j])
+        if n:
+            e = rank * El + j
+            out[a:a + n] = O.swiglu_mlp(recv[a:a + n], W.w_gate[e].float(), W.w_up[e].float(), W.w_down[e].float())
+    outs = [None] * world
+    dist.all_gather_object(outs, out)
+    rows = torch.stack([outs[int(d) >> PEER_SHIFT][int(d) & ((1 << PEER_SHIFT) - 1)] for d in dst.tolist()])
+    y = (rows.view(Tl, k, -1) * w.unsqueeze(-1)).sum(dim=1)
+    if W.shared is not None:
+        y = y + O.swiglu_mlp(x.float(), *[m.float() for m in W.shared])
+    ys = [None] * world
+    dist.all_gather_object(ys, y)
+    if rank == 0:
+        gold = O.layer_forward(spec, x_all, W, gold_fp32=True)
+        result["rel_l2"] = O.rel_l2(torch.cat(ys), gold["y"])
+        result["counts_ok"] = bool(np.array_equal(counts_all.sum(0), gold["counts"].numpy()))
+    dist.barrier()
+    dist.destroy_process_group()
+
+
+def gpu_ep_worker(rank, world, port, spec, T_global, seed, result):
+    """Expert-parallel layer on GPUs (NCCL + peer memory) against the CPU oracle."""
+    from moe_gen_b200.ep import EPMoELayer
+    from tests.util import make_layer
+    os.environ.setdefault("NCCL_NVLS_ENABLE", "0")
+    torch.cuda.set_device(rank)
+    _init(rank, world, port, "nccl")
+    x_all, W = O.make_inputs(spec, T_global, seed)
+    Tl = T_global // world
+    dev = f"cuda:{rank}"
+    layer = make_layer(spec, W, dev, rank, world)
+    ep = EPMoELayer(layer)
+    x = x_all[rank * Tl:(rank + 1) * Tl].to(dev)
+    ys = []
+    for _ in range(2):                                   # twice: buffers are reused across forwards
+        y = ep.forward(x)
+        torch.cuda.synchronize()
+        ys.append(y.cpu())
+    status = layer.device_status()
+    gath = [None] * world
+    dist.all_gather_object(gath, (ys[0], ys[1], status))
+    if rank == 0:
+        gold = O.layer_forward(spec, x_all, W, gold_fp32=True)
+        y0 = torch.cat([g[0] for g in gath]).float()
+        y1 = torch.cat([g[1] for g in gath]).float()
+        result["rel_l2"] = O.rel_l2(y0, gold["y"])
+        result["repeat_equal"] = bool(torch.equal(y0, y1))
+        result["status"] = [g[2] for g in gath]
+    dist.barrier()
+    ep.close()
+    dist.destroy_process_group()

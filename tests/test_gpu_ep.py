@@ -1,0 +1,40 @@
+"""GPU, 2 ranks on 2 GPUs: expert-parallel forward over peer memory against the CPU oracle.
+Skipped on a single-GPU machine."""
+import socket
+
+import pytest
+import torch
+import torch.multiprocessing as mp
+
+from oracle import moe_oracle as O
+from tests import ep_worker
+
+pytestmark = pytest.mark.gpu
+
+
+def _free_port():
+    with socket.socket() as s:
+        s.bind(("127.0.0.1", 0))
+        return s.getsockname()[1]
+
+
+@pytest.mark.parametrize("spec,T", [
+    (O.LayerSpec(256, 128, 64, 4, 256, 4, 2, O.GATE_SIGMOID_NOAUX_TC, True, 2.5, O.WEIGHT_FP8_BLOCK128, O.COMBINE_FP32), 600),
+    (O.LayerSpec(512, 256, 8, 2, 0, 1, 1, O.GATE_SOFTMAX_TOPK_RENORM, True, 1.0, O.WEIGHT_BF16, O.COMBINE_BF16_SEQ), 1000),
+])
+def test_expert_parallel_on_two_gpus(built_lib, spec, T):
+    if torch.cuda.device_count() < 2:
+        pytest.skip("needs 2 GPUs")
+    ctx = mp.get_context("spawn")
+    with ctx.Manager() as mgr:
+        result = mgr.dict()
+        port = _free_port()
+        procs = [ctx.Process(target=ep_worker.gpu_ep_worker, args=(r, 2, port, spec, T, 9, result)) for r in range(2)]
+        for p in procs:
+            p.start()
+        for p in procs:
+            p.join(timeout=300)
+        assert all(p.exitcode == 0 for p in procs), [p.exitcode for p in procs]
+        assert all(s == (0, 0) for s in result["status"]), result["status"]
+        assert result["repeat_equal"]
+        assert result["rel_l2"] <= (1e-2 if spec.gating != O.GATE_SOFTMAX_TOPK_RENORM else 3e-2)
