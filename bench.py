@@ -247,6 +247,8 @@ def main():
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-e2e", action="store_true")
     ap.add_argument("--chunk-tokens", type=int, default=16384)
+    ap.add_argument("--pair-gemm", type=int, default=-1, help="1/0 force the SM-pair expert GEMM on/off")
+    ap.add_argument("--fp8-mode", type=int, default=-1, help="0 auto, 1 pre-dequantise, 2 convert in the GEMM")
     args = ap.parse_args()
 
     rank = int(os.environ.get("RANK", "0"))
@@ -307,6 +309,10 @@ def main():
         return step()
 
     base = layer.layer if world > 1 else layer
+    if args.pair_gemm >= 0:
+        base.set_option(2, args.pair_gemm)
+    if args.fp8_mode >= 0:
+        base.set_option(1, args.fp8_mode)
     for _ in range(warmup):
         y = run_step()
     torch.cuda.synchronize()

@@ -319,6 +319,9 @@ int mg_last_launch_count(mg_handle h, int32_t* launches);
 #define MG_FP8_AUTO        0
 #define MG_FP8_PREDEQUANT  1
 #define MG_FP8_IN_KERNEL   2
+/* MG_OPT_PAIR_GEMM: 1 = the bf16 expert GEMMs run on SM pairs (clusters of two CTAs,
+ * tcgen05 cta_group::2, 256x256 tiles); 0 = one CTA per SM, 128x256 tiles. */
+#define MG_OPT_PAIR_GEMM   2
 int mg_set_option(mg_handle h, int32_t option, int32_t value);
 
 /* Per-stage device times of mg_moe_forward (no counterpart in the reference, whose

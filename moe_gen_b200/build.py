@@ -37,5 +37,17 @@ def build_library(force: bool = False, verbose: bool = False) -> str:
     return LIB
 
 
+def build_oracle_c() -> str:
+    """Compiles the oracle's C restatement (a checker used by tests, never by the library)."""
+    src = os.path.join(ROOT, "oracle", "route_oracle.c")
+    out = os.path.join(ROOT, "oracle", "libroute_oracle.so")
+    if _stale(out, [src]):
+        r = subprocess.run(["gcc", "-O2", "-std=c11", "-fPIC", "-shared", "-fno-fast-math", src, "-lm", "-o", out],
+                           capture_output=True, text=True)
+        if r.returncode != 0:
+            raise RuntimeError("gcc failed:\n" + r.stdout + r.stderr)
+    return out
+
+
 if __name__ == "__main__":
     print(build_library(force="--force" in sys.argv, verbose="-v" in sys.argv))

@@ -123,6 +123,7 @@ int mg_create(const mg_layer_desc* desc, mg_handle* out) {
   h->last_launches = 0;
   h->stage_timing = false;
   h->opt_fp8_mode = MG_FP8_AUTO;
+  h->opt_pair_gemm = false;
   h->side = nullptr;
   h->ev_entry = nullptr;
   for (int i = 0; i < kDequantChunks; ++i) h->ev_w13[i] = h->ev_w2[i] = nullptr;
@@ -504,6 +505,7 @@ int mg_set_option(mg_handle hh, int32_t option, int32_t value) {
       MG_REQUIRE(value >= MG_FP8_AUTO && value <= MG_FP8_IN_KERNEL, MG_ERR_CONFIG, "bad FP8 mode %d", value);
       h->opt_fp8_mode = value;
       return MG_OK;
+    case MG_OPT_PAIR_GEMM: h->opt_pair_gemm = value != 0; return MG_OK;
     default: set_error("unknown option %d", option); return MG_ERR_CONFIG;
   }
 }

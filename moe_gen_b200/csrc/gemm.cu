@@ -222,6 +222,76 @@ __device__ __forceinline__ void convert16(const uint4& q, float s, uint4& lo, ui
   hi = make_uint4(o[4], o[5], o[6], o[7]);
 }
 
+// One thread = one accumulator row (TMEM lane): read it in 32-column pieces, apply the epilogue,
+// store 64-byte (bf16) or 128-byte (fp32) runs.
+template <int EPI>
+__device__ __forceinline__ void epilogue_rows(uint32_t taddr, const GemmArgs& g, long long row, int n_idx, bool live) {
+  if (EPI == EPI_SWIGLU_BF16) {
+    const int half = g.bn >> 1;
+    __nv_bfloat16* orow = static_cast<__nv_bfloat16*>(g.out) + row * g.ldo + static_cast<long long>(n_idx) * half;
+    for (int c = 0; c < half; c += 32) {
+      uint32_t gr[32], ur[32];
+      tc_ld32(taddr + c, gr);
+      tc_ld32(taddr + half + c, ur);
+      tc_ld_wait();
+      if (live) {
+        uint32_t packed[16];
+#pragma unroll
+        for (int i = 0; i < 16; ++i) {
+          float h0 = silu_f(__uint_as_float(gr[2 * i])) * __uint_as_float(ur[2 * i]);
+          float h1 = silu_f(__uint_as_float(gr[2 * i + 1])) * __uint_as_float(ur[2 * i + 1]);
+          __nv_bfloat162 b = __floats2bfloat162_rn(h0, h1);
+          packed[i] = *reinterpret_cast<uint32_t*>(&b);
+        }
+        uint4* dst = reinterpret_cast<uint4*>(orow + c);
+#pragma unroll
+        for (int i = 0; i < 4; ++i) dst[i] = make_uint4(packed[4 * i], packed[4 * i + 1], packed[4 * i + 2], packed[4 * i + 3]);
+      }
+    }
+  } else if (EPI == EPI_PLAIN_BF16) {
+    __nv_bfloat16* orow = static_cast<__nv_bfloat16*>(g.out) + row * g.ldo + static_cast<long long>(n_idx) * g.bn;
+    for (int c = 0; c < g.bn; c += 32) {
+      uint32_t r[32];
+      tc_ld32(taddr + c, r);
+      tc_ld_wait();
+      if (live) {
+        uint32_t packed[16];
+#pragma unroll
+        for (int i = 0; i < 16; ++i) {
+          __nv_bfloat162 b = __floats2bfloat162_rn(__uint_as_float(r[2 * i]), __uint_as_float(r[2 * i + 1]));
+          packed[i] = *reinterpret_cast<uint32_t*>(&b);
+        }
+        uint4* dst = reinterpret_cast<uint4*>(orow + c);
+#pragma unroll
+        for (int i = 0; i < 4; ++i) dst[i] = make_uint4(packed[4 * i], packed[4 * i + 1], packed[4 * i + 2], packed[4 * i + 3]);
+      }
+    }
+  } else {
+    // fp32 output, N = n_per_group columns in one tile (the router logits)
+    float* orow = static_cast<float*>(g.out) + row * g.ldo;
+    for (int c = 0; c < g.n_per_group; c += 32) {
+      uint32_t r[32];
+      tc_ld32(taddr + c, r);
+      tc_ld_wait();
+      if (live) {
+#pragma unroll
+        for (int i = 0; i < 32; i += 4) {
+          if (c + i < g.n_per_group) {
+            float4 v;
+            v.x = __uint_as_float(r[i]); v.y = __uint_as_float(r[i + 1]);
+            v.z = __uint_as_float(r[i + 2]); v.w = __uint_as_float(r[i + 3]);
+            if (EPI == EPI_ROUND_BF16_F32) {
+              v.x = __bfloat162float(__float2bfloat16_rn(v.x)); v.y = __bfloat162float(__float2bfloat16_rn(v.y));
+              v.z = __bfloat162float(__float2bfloat16_rn(v.z)); v.w = __bfloat162float(__float2bfloat16_rn(v.w));
+            }
+            *reinterpret_cast<float4*>(orow + c + i) = v;
+          }
+        }
+      }
+    }
+  }
+}
+
 template <int EPI, bool F8B>
 __global__ void __launch_bounds__(Cfg<F8B>::THREADS, 1)
 grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
@@ -284,6 +354,9 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
           const uint32_t s = it % STAGES, ph = (it / STAGES) & 1u;
           if (!mbar_wait(smem_u32(&empty[s]), ph ^ 1u, abort_flag, g.status, 1)) break;
           const uint32_t fb = smem_u32(&full[s]);
+#ifdef MG_EXP_NO_TMA
+          if (it >= STAGES) { mbar_arrive(fb); continue; }   // experiment: operands loaded once only
+#endif
           mbar_expect_tx(fb, tx_bytes);
           const uint32_t sa = smem_base + s * STAGE_BYTES;
           tma_load_2d(sa, &tmA, kb * BK, t.row0, fb);
@@ -372,70 +445,9 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
       const uint32_t taddr = tmem_base + acc * ACC_COLS + (static_cast<uint32_t>(quarter * 32) << 16);
       const bool live = row_in_tile < t.valid_rows;
       const long long row = static_cast<long long>(t.row0) + row_in_tile;
-      if (EPI == EPI_SWIGLU_BF16) {
-        const int half = g.bn >> 1;
-        __nv_bfloat16* orow = static_cast<__nv_bfloat16*>(g.out) + row * g.ldo + static_cast<long long>(t.n_idx) * half;
-        for (int c = 0; c < half; c += 32) {
-          uint32_t gr[32], ur[32];
-          tc_ld32(taddr + c, gr);
-          tc_ld32(taddr + half + c, ur);
-          tc_ld_wait();
-          if (live) {
-            uint32_t packed[16];
-#pragma unroll
-            for (int i = 0; i < 16; ++i) {
-              float h0 = silu_f(__uint_as_float(gr[2 * i])) * __uint_as_float(ur[2 * i]);
-              float h1 = silu_f(__uint_as_float(gr[2 * i + 1])) * __uint_as_float(ur[2 * i + 1]);
-              __nv_bfloat162 b = __floats2bfloat162_rn(h0, h1);
-              packed[i] = *reinterpret_cast<uint32_t*>(&b);
-            }
-            uint4* dst = reinterpret_cast<uint4*>(orow + c);
-#pragma unroll
-            for (int i = 0; i < 4; ++i) dst[i] = make_uint4(packed[4 * i], packed[4 * i + 1], packed[4 * i + 2], packed[4 * i + 3]);
-          }
-        }
-      } else if (EPI == EPI_PLAIN_BF16) {
-        __nv_bfloat16* orow = static_cast<__nv_bfloat16*>(g.out) + row * g.ldo + static_cast<long long>(t.n_idx) * g.bn;
-        for (int c = 0; c < g.bn; c += 32) {
-          uint32_t r[32];
-          tc_ld32(taddr + c, r);
-          tc_ld_wait();
-          if (live) {
-            uint32_t packed[16];
-#pragma unroll
-            for (int i = 0; i < 16; ++i) {
-              __nv_bfloat162 b = __floats2bfloat162_rn(__uint_as_float(r[2 * i]), __uint_as_float(r[2 * i + 1]));
-              packed[i] = *reinterpret_cast<uint32_t*>(&b);
-            }
-            uint4* dst = reinterpret_cast<uint4*>(orow + c);
-#pragma unroll
-            for (int i = 0; i < 4; ++i) dst[i] = make_uint4(packed[4 * i], packed[4 * i + 1], packed[4 * i + 2], packed[4 * i + 3]);
-          }
-        }
-      } else {
-        // fp32 output, N = n_per_group columns in one tile (the router logits)
-        float* orow = static_cast<float*>(g.out) + row * g.ldo;
-        for (int c = 0; c < g.n_per_group; c += 32) {
-          uint32_t r[32];
-          tc_ld32(taddr + c, r);
-          tc_ld_wait();
-          if (live) {
-#pragma unroll
-            for (int i = 0; i < 32; i += 4) {
-              if (c + i < g.n_per_group) {
-                float4 v;
-                v.x = __uint_as_float(r[i]); v.y = __uint_as_float(r[i + 1]);
-                v.z = __uint_as_float(r[i + 2]); v.w = __uint_as_float(r[i + 3]);
-                if (EPI == EPI_ROUND_BF16_F32) {
-                  v.x = __bfloat162float(__float2bfloat16_rn(v.x)); v.y = __bfloat162float(__float2bfloat16_rn(v.y));
-                  v.z = __bfloat162float(__float2bfloat16_rn(v.z)); v.w = __bfloat162float(__float2bfloat16_rn(v.w));
-                }
-                *reinterpret_cast<float4*>(orow + c + i) = v;
-              }
-            }
-          }
-        }
-      }
+#ifndef MG_EXP_NO_EPI
+      epilogue_rows<EPI>(taddr, g, row, t.n_idx, live);
+#endif
       // hand the accumulator back to the MMA warp
       tc_fence_before();
       __syncwarp();
@@ -449,6 +461,229 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
     __syncwarp();
     tc_fence_after();
     asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(TMEM_COLS)
+                 : "memory");
+  }
+}
+
+
+// =======================================================================================
+// 2-CTA variant: a cluster of two CTAs (one SM pair) computes a 256 x 256 tile with
+// tcgen05.mma.cta_group::2.  Each CTA stages its own 128 rows of A and its own 128 of the 256
+// B rows, so every SM moves half the B bytes per FLOP of the 1-CTA kernel; the accumulator
+// halves live in each CTA's own TMEM.  CTA rank 0 ("leader") issues the MMAs.  Barriers:
+//   full[s]    leader only; both CTAs' TMA loads complete their bytes on it
+//   empty[s]   one copy per CTA; the leader's commit arrives on both (commit multicast, which
+//              signals barriers and moves no data)
+//   tfull[a]   one copy per CTA, same mechanism, tells each epilogue its half is complete
+//   tempty[a]  leader only; the 4 epilogue warps of both CTAs arrive on it (remote arrive)
+// TMA loads are plain 2-D tile loads (no multicast) of this GPU's own memory.
+// =======================================================================================
+constexpr int STAGES2 = 6;
+constexpr int B2_BYTES = 128 * BK * 2;                  // this CTA's half of the B tile
+constexpr int STAGE2_BYTES = A_BYTES + B2_BYTES;        // 32 KiB
+constexpr int NUM_BARS2 = 2 * STAGES2 + 4;
+constexpr size_t SMEM2_CTRL_BYTES = 8 * NUM_BARS2 + 16 + 4 * (3 * kMaxExperts + 3);
+constexpr size_t GEMM2_SMEM_BYTES = 1024 + STAGES2 * STAGE2_BYTES + SMEM2_CTRL_BYTES;
+constexpr int GROUP_M2 = 8;                             // pair tiles (256 rows) per L2 reuse group
+
+__device__ __forceinline__ uint32_t cluster_ctarank() {
+  uint32_t r;
+  asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(r));
+  return r;
+}
+__device__ __forceinline__ void cluster_sync_all() {
+  asm volatile("barrier.cluster.arrive.release.aligned;\n\tbarrier.cluster.wait.acquire.aligned;" ::: "memory");
+}
+__device__ __forceinline__ uint32_t map_to_cta(uint32_t saddr, uint32_t rank) {
+  uint32_t r;
+  asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(r) : "r"(saddr), "r"(rank));
+  return r;
+}
+__device__ __forceinline__ void mbar_arrive_cluster(uint32_t cluster_addr) {
+  asm volatile("mbarrier.arrive.release.cluster.shared::cluster.b64 _, [%0];" ::"r"(cluster_addr) : "memory");
+}
+// both CTAs of the pair issue it; the completion bytes are counted on the leader's barrier
+__device__ __forceinline__ void tma_load_2d_pair(uint32_t dst, const CUtensorMap* map, int c0, int c1, uint32_t bar) {
+  asm volatile(
+      "cp.async.bulk.tensor.2d.cta_group::2.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];"
+      ::"r"(dst), "l"(map), "r"(bar & 0xFEFFFFFFu), "r"(c0), "r"(c1)
+      : "memory");
+}
+__device__ __forceinline__ void tc_commit_pair(uint32_t bar) {
+  asm volatile(
+      "tcgen05.commit.cta_group::2.mbarrier::arrive::one.shared::cluster.multicast::cluster.b64 [%0], %1;"
+      ::"r"(bar), "h"(static_cast<uint16_t>(3))
+      : "memory");
+}
+__device__ __forceinline__ void tc_mma_bf16_pair(uint32_t d_tmem, uint64_t a_desc, uint64_t b_desc, uint32_t idesc,
+                                                 uint32_t accumulate) {
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "setp.ne.b32 p, %4, 0;\n\t"
+      "tcgen05.mma.cta_group::2.kind::f16 [%0], %1, %2, %3, p;\n\t}"
+      ::"r"(d_tmem), "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate)
+      : "memory");
+}
+
+struct Tile2 {
+  int row0;       // first of the pair's 256 rows
+  int rows_left;  // rows of the expert from row0 on (may exceed 256)
+  int b_row;      // first of the 256 B rows
+  int n_idx;
+};
+
+// s_pp[e] = number of pair tiles (per N tile) of the experts before e
+__device__ __forceinline__ Tile2 locate_tile2(int tile, const int* s_pad, const int* s_cnt, const int* s_pp,
+                                              int n_groups, int n_tiles, int n_per_group) {
+  int lo = 0, hi = n_groups;
+  while (hi - lo > 1) {
+    int mid = (lo + hi) >> 1;
+    if (s_pp[mid] * n_tiles <= tile) lo = mid; else hi = mid;
+  }
+  const int e = lo;
+  const int local = tile - s_pp[e] * n_tiles;
+  const int mp_e = s_pp[e + 1] - s_pp[e];
+  const int per_group = GROUP_M2 * n_tiles;
+  const int grp = local / per_group;
+  const int rem = local - grp * per_group;
+  const int gm = min(GROUP_M2, mp_e - grp * GROUP_M2);
+  const int n = rem / gm;
+  const int mp = grp * GROUP_M2 + (rem - n * gm);
+  Tile2 t;
+  t.row0 = s_pad[e] + mp * 2 * BM;
+  t.rows_left = s_cnt[e] - mp * 2 * BM;
+  t.b_row = e * n_per_group + n * BN_MAX;
+  t.n_idx = n;
+  return t;
+}
+
+template <int EPI>
+__global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(GEMM_THREADS, 1)
+grouped_gemm2_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
+                     const GemmArgs g) {
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  uint64_t* bars = reinterpret_cast<uint64_t*>(smem + STAGES2 * STAGE2_BYTES);
+  uint64_t* full = bars;
+  uint64_t* empty = bars + STAGES2;
+  uint64_t* tfull = bars + 2 * STAGES2;
+  uint64_t* tempty = bars + 2 * STAGES2 + 2;
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + NUM_BARS2);
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
+  int* s_pad = reinterpret_cast<int*>(tmem_slot + 4);
+  int* s_cnt = s_pad + kMaxExperts + 1;
+  int* s_pp = s_cnt + kMaxExperts + 1;
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const uint32_t rank = cluster_ctarank();           // 0 = leader
+  const int pair = blockIdx.x >> 1, n_pairs = gridDim.x >> 1;
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < STAGES2; ++s) { mbar_init(smem_u32(&full[s]), 1); mbar_init(smem_u32(&empty[s]), 1); }
+    for (int a = 0; a < 2; ++a) { mbar_init(smem_u32(&tfull[a]), 1); mbar_init(smem_u32(&tempty[a]), 8); }
+    *abort_flag = 0;
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+  }
+  if (g.pad_offsets != nullptr) {
+    for (int i = threadIdx.x; i <= g.n_groups; i += blockDim.x) s_pad[i] = g.pad_offsets[i];
+    for (int i = threadIdx.x; i < g.n_groups; i += blockDim.x) s_cnt[i] = g.counts[i];
+  } else if (threadIdx.x == 0) {
+    s_pad[0] = 0;
+    s_pad[1] = (g.dense_rows + BM - 1) / BM * BM;
+    s_cnt[0] = g.dense_rows;
+  }
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    int acc = 0;
+    for (int e = 0; e < g.n_groups; ++e) {
+      s_pp[e] = acc;
+      acc += ((s_pad[e + 1] - s_pad[e]) / BM + 1) / 2;
+    }
+    s_pp[g.n_groups] = acc;
+  }
+  if (warp == 1) {
+    __syncwarp();
+    asm volatile("tcgen05.alloc.cta_group::2.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(tmem_slot)),
+                 "r"(TMEM_COLS)
+                 : "memory");
+    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::2.sync.aligned;" ::: "memory");
+  }
+  tc_fence_before();
+  cluster_sync_all();      // barriers of both CTAs initialised, TMEM allocated on both SMs
+  tc_fence_after();
+  const uint32_t tmem_base = *tmem_slot;
+  const int total_tiles = s_pp[g.n_groups] * g.n_tiles;
+  const uint32_t smem_base = smem_u32(smem);
+
+  if (warp == 0) {
+    // ---------------- TMA producer (both CTAs) ----------------
+    if (lane == 0) {
+      uint32_t it = 0;
+      for (int tile = pair; tile < total_tiles && !*abort_flag; tile += n_pairs) {
+        const Tile2 t = locate_tile2(tile, s_pad, s_cnt, s_pp, g.n_groups, g.n_tiles, g.n_per_group);
+        for (int kb = 0; kb < g.k_blocks; ++kb, ++it) {
+          const uint32_t s = it % STAGES2, ph = (it / STAGES2) & 1u;
+          if (!mbar_wait(smem_u32(&empty[s]), ph ^ 1u, abort_flag, g.status, 11)) break;
+          const uint32_t fb = smem_u32(&full[s]);
+          if (rank == 0) mbar_expect_tx(fb, 2 * STAGE2_BYTES);     // both CTAs' A and B halves
+          const uint32_t sa = smem_base + s * STAGE2_BYTES;
+          tma_load_2d_pair(sa, &tmA, kb * BK, t.row0 + static_cast<int>(rank) * BM, fb);
+          tma_load_2d_pair(sa + A_BYTES, &tmB, kb * BK, t.b_row + static_cast<int>(rank) * 128, fb);
+        }
+      }
+    }
+  } else if (warp == 1) {
+    // ---------------- MMA issuer (leader CTA only) ----------------
+    if (lane == 0 && rank == 0) {
+      uint32_t it = 0, tcount = 0;
+      for (int tile = pair; tile < total_tiles && !*abort_flag; tile += n_pairs, ++tcount) {
+        const uint32_t acc = tcount & 1u, acc_ph = (tcount >> 1) & 1u;
+        if (!mbar_wait(smem_u32(&tempty[acc]), acc_ph ^ 1u, abort_flag, g.status, 12)) break;
+        tc_fence_after();
+        const uint32_t d_tmem = tmem_base + acc * ACC_COLS;
+        bool ok = true;
+        for (int kb = 0; kb < g.k_blocks; ++kb, ++it) {
+          const uint32_t s = it % STAGES2, ph = (it / STAGES2) & 1u;
+          if (!mbar_wait(smem_u32(&full[s]), ph, abort_flag, g.status, 13)) { ok = false; break; }
+          tc_fence_after();
+          const uint32_t sa = smem_base + s * STAGE2_BYTES;
+          const uint64_t da = make_smem_desc(sa), db = make_smem_desc(sa + A_BYTES);
+#pragma unroll
+          for (int k = 0; k < BK / 16; ++k)
+            tc_mma_bf16_pair(d_tmem, da + 2 * k, db + 2 * k, g.idesc, (kb | k) != 0 ? 1u : 0u);
+          tc_commit_pair(smem_u32(&empty[s]));
+        }
+        if (!ok) break;
+        tc_commit_pair(smem_u32(&tfull[acc]));
+      }
+    }
+  } else {
+    // ---------------- epilogue (both CTAs, own 128 rows) ----------------
+    const int quarter = warp & 3;
+    const int row_in_half = quarter * 32 + lane;
+    uint32_t tcount = 0;
+    for (int tile = pair; tile < total_tiles && !*abort_flag; tile += n_pairs, ++tcount) {
+      const Tile2 t = locate_tile2(tile, s_pad, s_cnt, s_pp, g.n_groups, g.n_tiles, g.n_per_group);
+      const uint32_t acc = tcount & 1u, acc_ph = (tcount >> 1) & 1u;
+      if (!mbar_wait(smem_u32(&tfull[acc]), acc_ph, abort_flag, g.status, 14)) break;
+      tc_fence_after();
+      const uint32_t taddr = tmem_base + acc * ACC_COLS + (static_cast<uint32_t>(quarter * 32) << 16);
+      const int my_rows = t.rows_left - static_cast<int>(rank) * BM;      // rows of my half that are real
+      const bool live = row_in_half < my_rows;
+      const long long row = static_cast<long long>(t.row0) + rank * BM + row_in_half;
+      epilogue_rows<EPI>(taddr, g, row, t.n_idx, live);
+      tc_fence_before();
+      __syncwarp();
+      if (lane == 0) mbar_arrive_cluster(map_to_cta(smem_u32(&tempty[acc]), 0));
+    }
+  }
+
+  tc_fence_before();
+  cluster_sync_all();      // neither CTA leaves while the other may still signal it or use its TMEM
+  if (warp == 1) {
+    __syncwarp();
+    tc_fence_after();
+    asm volatile("tcgen05.dealloc.cta_group::2.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(TMEM_COLS)
                  : "memory");
   }
 }
@@ -505,6 +740,15 @@ static int launch_epi(const Handle* h, const CUtensorMap& ta, const CUtensorMap&
   return MG_OK;
 }
 
+template <int EPI>
+static int launch_pair(const CUtensorMap& ta, const CUtensorMap& tb, const GemmArgs& args, int grid, cudaStream_t st) {
+  MG_CUDA(cudaFuncSetAttribute(grouped_gemm2_kernel<EPI>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                               static_cast<int>(GEMM2_SMEM_BYTES)));
+  grouped_gemm2_kernel<EPI><<<grid, GEMM_THREADS, GEMM2_SMEM_BYTES, st>>>(ta, tb, args);
+  MG_CUDA(cudaGetLastError());
+  return MG_OK;
+}
+
 int launch_grouped_gemm(const Handle* h, const GemmProblem& p, cudaStream_t st) {
   const bool dense = p.pad_offsets == nullptr;
   if (p.a_rows <= 0 || (dense && p.dense_rows <= 0)) return MG_OK;
@@ -521,11 +765,13 @@ int launch_grouped_gemm(const Handle* h, const GemmProblem& p, cudaStream_t st) 
     MG_REQUIRE(p.n_per_group % BN_MAX == 0, MG_ERR_SHAPE, "GEMM N per expert (%d) must be a multiple of %d",
                p.n_per_group, BN_MAX);
   }
+  // SM pairs (2-CTA tiles of 256 x 256) for the bf16 expert GEMMs unless switched off
+  const bool pair = h->opt_pair_gemm && !f32_out && !p.b_fp8;
   CUtensorMap ta, tb;
   int rc = encode_2d(&ta, p.a, static_cast<uint64_t>(p.a_rows), static_cast<uint64_t>(p.K), BM);
   if (rc != MG_OK) return rc;
-  rc = encode_2d(&tb, p.b, static_cast<uint64_t>(p.n_groups) * p.n_per_group, static_cast<uint64_t>(p.K), bn,
-                 p.b_fp8);
+  rc = encode_2d(&tb, p.b, static_cast<uint64_t>(p.n_groups) * p.n_per_group, static_cast<uint64_t>(p.K),
+                 pair ? 128 : bn, p.b_fp8);
   if (rc != MG_OK) return rc;
   if (p.b_fp8) {
     MG_REQUIRE(!f32_out && p.scales != nullptr && p.K % 128 == 0, MG_ERR_SHAPE,
@@ -560,6 +806,20 @@ int launch_grouped_gemm(const Handle* h, const GemmProblem& p, cudaStream_t st) 
     if (max_tiles < grid) grid = static_cast<int>(max_tiles);
   }
   if (grid < 1) return MG_OK;
+  if (pair) {
+    // UMMA M = 256 across the two CTAs; one cluster per SM pair
+    a.idesc = (1u << 4) | (1u << 7) | (1u << 10) | (static_cast<uint32_t>(bn >> 3) << 17) |
+              (static_cast<uint32_t>(256 >> 4) << 24);
+    int pairs = h->sm_count / 2;
+    long long max_pair_tiles = dense ? ((p.dense_rows + 2 * BM - 1) / (2 * BM)) * a.n_tiles
+                                     : ((p.a_rows / BM + p.n_groups) / 2 + 1) * static_cast<long long>(a.n_tiles);
+    if (max_pair_tiles < pairs) pairs = static_cast<int>(max_pair_tiles);
+    if (pairs < 1) pairs = 1;
+    switch (p.epilogue) {
+      case EPI_SWIGLU_BF16: return launch_pair<EPI_SWIGLU_BF16>(ta, tb, a, 2 * pairs, st);
+      case EPI_PLAIN_BF16: return launch_pair<EPI_PLAIN_BF16>(ta, tb, a, 2 * pairs, st);
+    }
+  }
   if (p.b_fp8) {
     switch (p.epilogue) {
       case EPI_SWIGLU_BF16: return launch_epi<EPI_SWIGLU_BF16, true>(h, ta, tb, a, grid, st);

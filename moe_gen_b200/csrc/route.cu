@@ -94,36 +94,63 @@ __global__ void __launch_bounds__(256) route_topk_kernel(const float* __restrict
   // group-limited selection: keep topk_group groups, others compete with value 0.0
   if (rp.gating == MG_GATE_SOFTMAX_GROUP_MAX || rp.gating == MG_GATE_SIGMOID_NOAUX_TC) {
     const int G = rp.n_group, gsz = E / G;
-    float my_gs = NEG_INF;  // lane g holds the score of group g
-    for (int g = 0; g < G; ++g) {
-      float b1 = NEG_INF, b2 = NEG_INF;  // two largest values of group g seen by this lane
+    float my_gs = NEG_INF;   // score of the group this lane reports (one lane per group)
+    int my_g = -1;
+    const int lanes_per_group = gsz / P;
+    if (gsz % P == 0 && (lanes_per_group & (lanes_per_group - 1)) == 0 && lanes_per_group <= 32) {
+      // a lane's experts all lie in one group and a group is a power-of-two run of lanes:
+      // all groups reduce at once with xor shuffles inside the run
+      float b1 = NEG_INF, b2 = NEG_INF;
 #pragma unroll
       for (int i = 0; i < P; ++i) {
-        int e = lane * P + i;
-        if (e < E && e / gsz == g) {
-          float v = c[i];
-          if (v > b1) { b2 = b1; b1 = v; } else if (v > b2) { b2 = v; }
-        }
+        float v = c[i];
+        if (v > b1) { b2 = b1; b1 = v; } else if (v > b2) { b2 = v; }
       }
-#pragma unroll
-      for (int o = 16; o > 0; o >>= 1) {
+      for (int o = lanes_per_group >> 1; o > 0; o >>= 1) {
         float o1 = __shfl_xor_sync(0xFFFFFFFFu, b1, o);
         float o2 = __shfl_xor_sync(0xFFFFFFFFu, b2, o);
         float hi = fmaxf(b1, o1), lo = fminf(b1, o1);
         b2 = fmaxf(lo, fmaxf(b2, o2));
         b1 = hi;
       }
-      float gscore = rp.gating == MG_GATE_SIGMOID_NOAUX_TC ? __fadd_rn(b1, b2) : b1;
-      if (lane == g) my_gs = gscore;
+      const int g = (lane * P) / gsz;
+      if (lane * P < E && (lane & (lanes_per_group - 1)) == 0) {
+        my_g = g;
+        my_gs = rp.gating == MG_GATE_SIGMOID_NOAUX_TC ? __fadd_rn(b1, b2) : b1;
+      }
+    } else {
+      for (int g = 0; g < G; ++g) {
+        float b1 = NEG_INF, b2 = NEG_INF;  // two largest values of group g seen by this lane
+#pragma unroll
+        for (int i = 0; i < P; ++i) {
+          int e = lane * P + i;
+          if (e < E && e / gsz == g) {
+            float v = c[i];
+            if (v > b1) { b2 = b1; b1 = v; } else if (v > b2) { b2 = v; }
+          }
+        }
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) {
+          float o1 = __shfl_xor_sync(0xFFFFFFFFu, b1, o);
+          float o2 = __shfl_xor_sync(0xFFFFFFFFu, b2, o);
+          float hi = fmaxf(b1, o1), lo = fminf(b1, o1);
+          b2 = fmaxf(lo, fmaxf(b2, o2));
+          b1 = hi;
+        }
+        if (lane == g) {
+          my_g = g;
+          my_gs = rp.gating == MG_GATE_SIGMOID_NOAUX_TC ? __fadd_rn(b1, b2) : b1;
+        }
+      }
     }
+    // topk_group rounds: best score first, equal scores -> lower group id
     uint32_t gmask = 0;
-    bool taken = lane >= G;
+    const uint32_t gkey = ordered_bits(my_gs);
     for (int r = 0; r < rp.topk_group; ++r) {
-      unsigned long long key = taken ? 0ull : make_key(my_gs, lane);
-      key = warp_max_u64(key);
-      int win = static_cast<int>(0xFFFFFFFFu - static_cast<uint32_t>(key));
+      const bool open = my_g >= 0 && !((gmask >> my_g) & 1u);
+      const uint32_t best = __reduce_max_sync(0xFFFFFFFFu, open ? gkey : 0u);
+      const uint32_t win = __reduce_min_sync(0xFFFFFFFFu, (open && gkey == best) ? static_cast<uint32_t>(my_g) : 0xFFFFFFFFu);
       gmask |= 1u << win;
-      if (lane == win) taken = true;
     }
 #pragma unroll
     for (int i = 0; i < P; ++i) {
@@ -132,31 +159,30 @@ __global__ void __launch_bounds__(256) route_topk_kernel(const float* __restrict
     }
   }
 
-  // k rounds of warp arg-max
+  // k rounds of warp arg-max: score descending, equal scores -> lower expert id
   uint32_t taken = 0;
   int my_idx = 0;
   float my_w = 0.f;
   for (int r = 0; r < rp.k; ++r) {
-    unsigned long long best = 0ull;
+    uint32_t bkey = 0u;
+    int bslot = 0;
 #pragma unroll
     for (int i = 0; i < P; ++i) {
-      int e = lane * P + i;
-      if (e < E && !((taken >> i) & 1u)) {
-        unsigned long long key = make_key(c[i], e);
-        best = key > best ? key : best;
-      }
+      const uint32_t key = ((lane * P + i) < E && !((taken >> i) & 1u)) ? ordered_bits(c[i]) : 0u;
+      if (key > bkey) { bkey = key; bslot = i; }          // strict: the lowest index among equals stays
     }
-    best = warp_max_u64(best);
-    int e_win = static_cast<int>(0xFFFFFFFFu - static_cast<uint32_t>(best));
-    int owner = e_win / P, slot = e_win - owner * P;
+    const uint32_t best = __reduce_max_sync(0xFFFFFFFFu, bkey);
+    const uint32_t e_win = __reduce_min_sync(0xFFFFFFFFu, (bkey == best && bkey != 0u) ? static_cast<uint32_t>(lane * P + bslot) : 0xFFFFFFFFu);
+    const int owner = static_cast<int>(e_win) / P;
     float wv = 0.f;
+    if (lane == owner) {
+      taken |= 1u << bslot;
 #pragma unroll
-    for (int i = 0; i < P; ++i) {
-      if (i == slot) wv = rp.gating == MG_GATE_SIGMOID_NOAUX_TC ? s[i] : c[i];
+      for (int i = 0; i < P; ++i)
+        if (i == bslot) wv = rp.gating == MG_GATE_SIGMOID_NOAUX_TC ? s[i] : c[i];
     }
-    if (lane == owner) taken |= 1u << slot;
     wv = __shfl_sync(0xFFFFFFFFu, wv, owner);
-    if (lane == r) { my_idx = e_win; my_w = wv; }
+    if (lane == r) { my_idx = static_cast<int>(e_win); my_w = wv; }
   }
 
   // normalise / scale

@@ -248,6 +248,35 @@ def test_fp8_weights_converted_in_the_gemm_equal_dequantise_first(built_lib):
         assert torch.equal(ys[0].view(torch.int16), y.view(torch.int16))
 
 
+@pytest.mark.parametrize("T", [3, 130, 700, 3000])
+def test_sm_pair_gemm_equals_single_cta_gemm(built_lib, T):
+    """The 2-CTA (cta_group::2) kernel computes the same sums in the same order as the 1-CTA one."""
+    spec = O.LayerSpec(512, 256, 16, 4, 256, combine_mode=O.COMBINE_FP32)
+    x, W = O.make_inputs(spec, T, 60 + T)
+    layer = make_layer(spec, W, DEV)
+    xd = x.to(DEV)
+    gen = torch.Generator().manual_seed(T)
+    scores = torch.rand(T, 16, generator=gen)
+    scores[:, 3] = -1.0
+    scores[:, 7] += 0.6
+    idx = scores.topk(4, dim=-1).indices.to(torch.int32).to(DEV)
+    counts, offsets, pad, dst = layer.permute_plan(idx)
+    perm = layer.permute_rows(xd, dst, layer.padded_rows(T * 4))
+    h1, o1 = layer.expert_ffn(perm, pad, counts)
+    s1 = layer.shared_ffn(xd)
+    layer.set_option(2, 1)
+    h2, o2 = layer.expert_ffn(perm, pad, counts)
+    s2 = layer.shared_ffn(xd)
+    _status_ok(layer)
+    live = torch.zeros(perm.shape[0], dtype=torch.bool)
+    live[dst.cpu().long().view(-1)] = True
+    assert torch.equal(h1.cpu()[live].view(torch.int16), h2.cpu()[live].view(torch.int16))
+    assert torch.equal(o1.cpu()[live].view(torch.int16), o2.cpu()[live].view(torch.int16))
+    assert torch.equal(s1.cpu().view(torch.int16), s2.cpu().view(torch.int16))
+    worst, _ = _check_expert_rows(spec, W, xd, layer, idx)
+    assert worst < 5e-3
+
+
 # --------------------------------------------------------------------------- combine
 @pytest.mark.parametrize("mode", [O.COMBINE_FP32, O.COMBINE_BF16_PROD, O.COMBINE_BF16_SEQ])
 @pytest.mark.parametrize("with_shared", [False, True])

@@ -109,3 +109,57 @@ def test_mixtral_restatement_against_installed_transformers():
     y = (y[0] if isinstance(y, tuple) else y).view(64, 128)
     out = O.layer_forward(spec, x, W)
     assert O.rel_l2(out["y"].float(), y.float()) < 1e-2
+
+
+# ---- the plain-C restatement of routing / permutation / de-quantisation agrees with the fixtures
+def _c_oracle():
+    import ctypes as C
+    from moe_gen_b200 import build
+    lib = C.CDLL(build.build_oracle_c())
+    return lib, C
+
+
+@pytest.mark.parametrize("name", sorted(GATE_CASES))
+def test_c_oracle_routing_matches_reference_fixture(name):
+    lib, C = _c_oracle()
+    cfg, T, seed = GATE_CASES[name]
+    spec = O.named_spec(cfg)
+    g = load_golden(name)
+    gen = torch.Generator().manual_seed(seed)
+    x = torch.randn(T, spec.hidden, generator=gen).to(torch.bfloat16)
+    gw = (torch.randn(spec.n_experts, spec.hidden, generator=gen) * 0.02).to(torch.bfloat16)
+    bias = torch.randn(spec.n_experts, generator=gen) * 0.01 if spec.gating == O.GATE_SIGMOID_NOAUX_TC else None
+    logits = O.gate_logits(x, gw).contiguous()
+    idx = torch.empty(T, spec.top_k, dtype=torch.int32)
+    w = torch.empty(T, spec.top_k, dtype=torch.float32)
+    rc = lib.mgo_route(C.c_void_p(logits.data_ptr()), C.c_void_p(bias.data_ptr() if bias is not None else 0),
+                       C.c_int64(T), spec.n_experts, spec.top_k, spec.n_group, spec.topk_group, spec.gating,
+                       int(spec.norm_topk_prob), C.c_float(spec.routed_scale), C.c_void_p(idx.data_ptr()),
+                       C.c_void_p(w.data_ptr()))
+    assert rc == 0
+    ci, cw = O.canonical_sets(idx.long(), w)
+    assert np.array_equal(ci.numpy().astype(np.int16), g["topk_idx"])
+    assert np.abs(cw.numpy() - g["topk_w"]).max() <= 1e-6 * max(1.0, spec.routed_scale)
+    # slot order too: the torch restatement and the C one agree pick for pick
+    ridx, _ = O.route(spec, logits, bias)
+    assert torch.equal(idx.long(), ridx)
+
+
+def test_c_oracle_plan_and_dequant():
+    lib, C = _c_oracle()
+    gen = torch.Generator().manual_seed(4)
+    idx = torch.rand(500, 64, generator=gen).topk(6, dim=-1).indices.to(torch.int32).contiguous()
+    counts = torch.empty(64, dtype=torch.int32); offsets = torch.empty(65, dtype=torch.int32)
+    order = torch.empty(3000, dtype=torch.int32)
+    assert lib.mgo_permute_plan(C.c_void_p(idx.data_ptr()), C.c_int64(500), 6, 64, C.c_void_p(counts.data_ptr()),
+                                C.c_void_p(offsets.data_ptr()), C.c_void_p(order.data_ptr())) == 0
+    rc, roff, rorder, _ = O.permute_plan(idx.long(), 64)
+    assert torch.equal(counts.long(), rc) and torch.equal(offsets.long(), roff) and torch.equal(order.long(), rorder)
+    w = (torch.randn(256, 384, generator=gen) * 0.02).to(torch.bfloat16)
+    q, s = O.quantize_fp8_block128(w)
+    out = torch.empty(256, 384, dtype=torch.int16)
+    qb = q.view(torch.uint8).contiguous()
+    s = s.contiguous()
+    assert lib.mgo_dequant_fp8(C.c_void_p(qb.data_ptr()), C.c_void_p(s.data_ptr()), C.c_int64(256), C.c_int64(384),
+                               C.c_void_p(out.data_ptr())) == 0
+    assert torch.equal(out, O.dequantize_fp8_block128(q, s).view(torch.int16))
