@@ -625,6 +625,9 @@ grouped_gemm2_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_const
           const uint32_t s = it % STAGES2, ph = (it / STAGES2) & 1u;
           if (!mbar_wait(smem_u32(&empty[s]), ph ^ 1u, abort_flag, g.status, 11)) break;
           const uint32_t fb = smem_u32(&full[s]);
+#ifdef MG_EXP_NO_TMA
+          if (it >= STAGES2) { if (rank == 0) mbar_arrive(fb); continue; }   // experiment: operands loaded once only
+#endif
           if (rank == 0) mbar_expect_tx(fb, 2 * STAGE2_BYTES);     // both CTAs' A and B halves
           const uint32_t sa = smem_base + s * STAGE2_BYTES;
           tma_load_2d_pair(sa, &tmA, kb * BK, t.row0 + static_cast<int>(rank) * BM, fb);
@@ -671,7 +674,9 @@ grouped_gemm2_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_const
       const int my_rows = t.rows_left - static_cast<int>(rank) * BM;      // rows of my half that are real
       const bool live = row_in_half < my_rows;
       const long long row = static_cast<long long>(t.row0) + rank * BM + row_in_half;
+#ifndef MG_EXP_NO_EPI
       epilogue_rows<EPI>(taddr, g, row, t.n_idx, live);
+#endif
       tc_fence_before();
       __syncwarp();
       if (lane == 0) mbar_arrive_cluster(map_to_cta(smem_u32(&tempty[acc]), 0));
