@@ -351,6 +351,8 @@ def main():
     else:
         layer.timing = False
         phases = layer.phase_times()
+        all_phases = [None] * world
+        dist.all_gather_object(all_phases, {k_: round(v, 3) for k_, v in phases.items()})
         stage_ms = {"expert_gemm1": 0.0}
         # gate, top-k, count(2), layout, place, dispatch, [shared 2], experts (2, or 4 per chunk when
         # FP8 weights are pre-dequantised), combine; NCCL kernels not counted
@@ -451,6 +453,7 @@ def main():
             stages[st] = {"ms": round(stage_ms[st], 4)}
     if phases is not None:
         stages = {k_: {"ms": round(v, 4)} for k_, v in phases.items()}
+        stages["by_rank_ms"] = all_phases
         nv = Tl * k * H * 2 * (world - 1) / world          # bytes this rank sends (and later fetches) over NVLink
         for ph in ("dispatch", "combine"):
             if phases[ph] > 0:

@@ -322,6 +322,13 @@ int mg_last_launch_count(mg_handle h, int32_t* launches);
 /* MG_OPT_PAIR_GEMM: 1 = the bf16 expert GEMMs run on SM pairs (clusters of two CTAs,
  * tcgen05 cta_group::2, 256x256 tiles); 0 = one CTA per SM, 128x256 tiles. */
 #define MG_OPT_PAIR_GEMM   2
+/* MG_OPT_KEEP_DEQUANT: 1 = in pre-dequantise mode, a call may reuse the bf16 copy the previous
+ * call on this handle left in the same scratch, if the packed buffer and the stream are the
+ * same and no expert was re-packed in between.  Meant for the token chunks of ONE logical
+ * forward (MoELayer.forward_host sets it around its chunk loop and clears it afterwards), so
+ * that the weights are de-quantised once per forward, not once per chunk.  The caller must
+ * not touch the scratch in between. */
+#define MG_OPT_KEEP_DEQUANT 3
 int mg_set_option(mg_handle h, int32_t option, int32_t value);
 
 /* Per-stage device times of mg_moe_forward (no counterpart in the reference, whose

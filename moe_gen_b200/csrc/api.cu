@@ -124,6 +124,11 @@ int mg_create(const mg_layer_desc* desc, mg_handle* out) {
   h->stage_timing = false;
   h->opt_fp8_mode = MG_FP8_AUTO;
   h->opt_pair_gemm = false;
+  h->opt_keep_dequant = false;
+  h->deq_valid = false;
+  h->deq_scratch = nullptr;
+  h->deq_packed = nullptr;
+  h->deq_stream = nullptr;
   h->side = nullptr;
   h->ev_entry = nullptr;
   for (int i = 0; i < kDequantChunks; ++i) h->ev_w13[i] = h->ev_w2[i] = nullptr;
@@ -206,6 +211,7 @@ int mg_pack_expert(mg_handle hh, int32_t local_expert, const void* d_gate, const
   Handle* h = check(hh);
   if (!h) return MG_ERR_STATE;
   MG_REQUIRE(d_gate && d_up && d_down && d_packed, MG_ERR_NULL, "mg_pack_expert: null pointer");
+  h->deq_valid = false;
   return launch_pack_expert(h, local_expert, d_gate, d_up, d_down, gs, us, ds, d_packed,
                             static_cast<cudaStream_t>(stream));
 }
@@ -338,15 +344,22 @@ static int expert_ffn(Handle* h, const void* perm_x, const int32_t* pad, const i
   if (rc != MG_OK) return rc;
   const int n_chunks = E < kDequantChunks ? E : kDequantChunks;
   const int per = (E + n_chunks - 1) / n_chunks;
-  MG_CUDA(cudaEventRecord(h->ev_entry, st));
-  MG_CUDA(cudaStreamWaitEvent(h->side, h->ev_entry, 0));
-  for (int which = 0; which < 2; ++which) {
-    for (int c = 0; c < n_chunks; ++c) {
-      const int lo = c * per, n = (lo + per <= E ? per : E - lo);
-      rc = launch_dequant_packed(h, packed, deq, which, lo, n, h->side);
-      if (rc != MG_OK) return rc;
-      MG_CUDA(cudaEventRecord(which == 0 ? h->ev_w13[c] : h->ev_w2[c], h->side));
+  // MG_OPT_KEEP_DEQUANT: the copy made by the previous call (same packed buffer, same scratch,
+  // same stream) is still current, e.g. between the token chunks of one host-buffer forward
+  const bool reuse = h->opt_keep_dequant && h->deq_valid && h->deq_scratch == deq && h->deq_packed == packed &&
+                     h->deq_stream == st;
+  if (!reuse) {
+    MG_CUDA(cudaEventRecord(h->ev_entry, st));
+    MG_CUDA(cudaStreamWaitEvent(h->side, h->ev_entry, 0));
+    for (int which = 0; which < 2; ++which) {
+      for (int c = 0; c < n_chunks; ++c) {
+        const int lo = c * per, n = (lo + per <= E ? per : E - lo);
+        rc = launch_dequant_packed(h, packed, deq, which, lo, n, h->side);
+        if (rc != MG_OK) return rc;
+        MG_CUDA(cudaEventRecord(which == 0 ? h->ev_w13[c] : h->ev_w2[c], h->side));
+      }
     }
+    if (launches) *launches += 2 * n_chunks;
   }
   if (timed) mark(h, MG_STAGE_DEQUANT, st);
   const __nv_bfloat16* w13 = static_cast<const __nv_bfloat16*>(deq);
@@ -355,7 +368,7 @@ static int expert_ffn(Handle* h, const void* perm_x, const int32_t* pad, const i
     for (int c = 0; c < n_chunks; ++c) {
       const int lo = c * per, n = (lo + per <= E ? per : E - lo);
       if (n <= 0) continue;
-      MG_CUDA(cudaStreamWaitEvent(st, which == 0 ? h->ev_w13[c] : h->ev_w2[c], 0));
+      if (!reuse) MG_CUDA(cudaStreamWaitEvent(st, which == 0 ? h->ev_w13[c] : h->ev_w2[c], 0));
       p.n_groups = n; p.pad_offsets = pad + lo; p.counts = counts + lo; p.b_fp8 = false; p.scales = nullptr;
       if (which == 0) {
         p.a = perm_x; p.b = w13 + static_cast<size_t>(lo) * 2 * d.inter * d.hidden; p.n_per_group = 2 * d.inter;
@@ -369,7 +382,11 @@ static int expert_ffn(Handle* h, const void* perm_x, const int32_t* pad, const i
     }
     if (timed) mark(h, which == 0 ? MG_STAGE_EXPERT_GEMM1 : MG_STAGE_EXPERT_GEMM2, st);
   }
-  if (launches) *launches += 4 * n_chunks;
+  if (launches) *launches += 2 * n_chunks;
+  h->deq_valid = true;
+  h->deq_scratch = deq;
+  h->deq_packed = packed;
+  h->deq_stream = st;
   return MG_OK;
 }
 
@@ -506,6 +523,10 @@ int mg_set_option(mg_handle hh, int32_t option, int32_t value) {
       h->opt_fp8_mode = value;
       return MG_OK;
     case MG_OPT_PAIR_GEMM: h->opt_pair_gemm = value != 0; return MG_OK;
+    case MG_OPT_KEEP_DEQUANT:
+      h->opt_keep_dequant = value != 0;
+      h->deq_valid = false;          // switching it on or off never trusts an older copy
+      return MG_OK;
     default: set_error("unknown option %d", option); return MG_ERR_CONFIG;
   }
 }

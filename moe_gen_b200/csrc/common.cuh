@@ -43,6 +43,11 @@ struct Handle {
   int e_local;            // experts owned by this rank
   int32_t* d_status;      // [2]: code, detail
   int last_launches;
+  bool opt_keep_dequant;  // reuse the de-quantised copy of the previous call while nothing changed
+  bool deq_valid;
+  const void* deq_scratch;
+  const void* deq_packed;
+  cudaStream_t deq_stream;
   bool opt_pair_gemm;     // bf16 expert GEMMs on SM pairs (tcgen05 cta_group::2)
   int opt_fp8_mode;       // MG_FP8_AUTO / MG_FP8_PREDEQUANT / MG_FP8_IN_KERNEL
   cudaStream_t side;      // de-quantisation runs here, one chunk of experts ahead of the GEMMs

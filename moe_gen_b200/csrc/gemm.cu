@@ -478,12 +478,23 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
 //   tempty[a]  leader only; the 4 epilogue warps of both CTAs arrive on it (remote arrive)
 // TMA loads are plain 2-D tile loads (no multicast) of this GPU's own memory.
 // =======================================================================================
+// W8A16 on SM pairs (F8B): each CTA receives its B half as FP8 bytes and its 8 converter warps
+// write the bf16 half tile; both CTAs' converters arrive on the leader's bready[j]; full[s] is
+// then local to each CTA (its own A and FP8 bytes), because its converters must wait on it.
 constexpr int STAGES2 = 6;
-constexpr int B2_BYTES = 128 * BK * 2;                  // this CTA's half of the B tile
-constexpr int STAGE2_BYTES = A_BYTES + B2_BYTES;        // 32 KiB
-constexpr int NUM_BARS2 = 2 * STAGES2 + 4;
+constexpr int B2_BYTES = 128 * BK * 2;                  // this CTA's half of the B tile, bf16
+constexpr int B2F8_BYTES = 128 * BK;                    // the same half as FP8 bytes
+constexpr int B2_SLOTS = 3;                             // converted half tiles in flight
+constexpr int NUM_BARS2 = 2 * STAGES2 + 4 + 2 * B2_SLOTS;
+template <bool F8B>
+struct Cfg2 {
+  static constexpr int STAGE_BYTES = A_BYTES + (F8B ? B2F8_BYTES : B2_BYTES);      // 24 / 32 KiB
+  static constexpr int RING_BYTES = STAGES2 * STAGE_BYTES + (F8B ? B2_SLOTS * B2_BYTES : 0);
+  static constexpr int THREADS = GEMM_THREADS + (F8B ? CONVERT_THREADS : 0);
+};
 constexpr size_t SMEM2_CTRL_BYTES = 8 * NUM_BARS2 + 16 + 4 * (3 * kMaxExperts + 3);
-constexpr size_t GEMM2_SMEM_BYTES = 1024 + STAGES2 * STAGE2_BYTES + SMEM2_CTRL_BYTES;
+template <bool F8B>
+constexpr size_t gemm2_smem_bytes() { return 1024 + Cfg2<F8B>::RING_BYTES + SMEM2_CTRL_BYTES; }
 constexpr int GROUP_M2 = 8;                             // pair tiles (256 rows) per L2 reuse group
 
 __device__ __forceinline__ uint32_t cluster_ctarank() {
@@ -557,17 +568,20 @@ __device__ __forceinline__ Tile2 locate_tile2(int tile, const int* s_pad, const 
   return t;
 }
 
-template <int EPI>
-__global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(GEMM_THREADS, 1)
+template <int EPI, bool F8B>
+__global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(Cfg2<F8B>::THREADS, 1)
 grouped_gemm2_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
                      const GemmArgs g) {
+  constexpr int STAGE2_BYTES = Cfg2<F8B>::STAGE_BYTES;
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
-  uint64_t* bars = reinterpret_cast<uint64_t*>(smem + STAGES2 * STAGE2_BYTES);
+  uint64_t* bars = reinterpret_cast<uint64_t*>(smem + Cfg2<F8B>::RING_BYTES);
   uint64_t* full = bars;
   uint64_t* empty = bars + STAGES2;
   uint64_t* tfull = bars + 2 * STAGES2;
   uint64_t* tempty = bars + 2 * STAGES2 + 2;
+  uint64_t* bready = bars + 2 * STAGES2 + 4;               // leader: both CTAs' converters arrive
+  uint64_t* bfree = bars + 2 * STAGES2 + 4 + B2_SLOTS;     // per CTA, via the leader's commit
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + NUM_BARS2);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
   int* s_pad = reinterpret_cast<int*>(tmem_slot + 4);
@@ -581,6 +595,10 @@ grouped_gemm2_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_const
   if (threadIdx.x == 0) {
     for (int s = 0; s < STAGES2; ++s) { mbar_init(smem_u32(&full[s]), 1); mbar_init(smem_u32(&empty[s]), 1); }
     for (int a = 0; a < 2; ++a) { mbar_init(smem_u32(&tfull[a]), 1); mbar_init(smem_u32(&tempty[a]), 8); }
+    for (int j = 0; j < B2_SLOTS; ++j) {
+      mbar_init(smem_u32(&bready[j]), 2 * (CONVERT_THREADS / 32));
+      mbar_init(smem_u32(&bfree[j]), 1);
+    }
     *abort_flag = 0;
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
   }
@@ -614,6 +632,7 @@ grouped_gemm2_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_const
   const uint32_t tmem_base = *tmem_slot;
   const int total_tiles = s_pp[g.n_groups] * g.n_tiles;
   const uint32_t smem_base = smem_u32(smem);
+  const uint32_t bslot_base = smem_base + STAGES2 * STAGE2_BYTES;   // W8A16: converted half tiles
 
   if (warp == 0) {
     // ---------------- TMA producer (both CTAs) ----------------
@@ -628,10 +647,16 @@ grouped_gemm2_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_const
 #ifdef MG_EXP_NO_TMA
           if (it >= STAGES2) { if (rank == 0) mbar_arrive(fb); continue; }   // experiment: operands loaded once only
 #endif
-          if (rank == 0) mbar_expect_tx(fb, 2 * STAGE2_BYTES);     // both CTAs' A and B halves
           const uint32_t sa = smem_base + s * STAGE2_BYTES;
-          tma_load_2d_pair(sa, &tmA, kb * BK, t.row0 + static_cast<int>(rank) * BM, fb);
-          tma_load_2d_pair(sa + A_BYTES, &tmB, kb * BK, t.b_row + static_cast<int>(rank) * 128, fb);
+          if (F8B) {
+            mbar_expect_tx(fb, STAGE2_BYTES);                      // this CTA's A and FP8 half, own barrier
+            tma_load_2d(sa, &tmA, kb * BK, t.row0 + static_cast<int>(rank) * BM, fb);
+            tma_load_2d(sa + A_BYTES, &tmB, kb * BK, t.b_row + static_cast<int>(rank) * 128, fb);
+          } else {
+            if (rank == 0) mbar_expect_tx(fb, 2 * STAGE2_BYTES);   // both CTAs' A and B halves
+            tma_load_2d_pair(sa, &tmA, kb * BK, t.row0 + static_cast<int>(rank) * BM, fb);
+            tma_load_2d_pair(sa + A_BYTES, &tmB, kb * BK, t.b_row + static_cast<int>(rank) * 128, fb);
+          }
         }
       }
     }
@@ -648,19 +673,56 @@ grouped_gemm2_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_const
         for (int kb = 0; kb < g.k_blocks; ++kb, ++it) {
           const uint32_t s = it % STAGES2, ph = (it / STAGES2) & 1u;
           if (!mbar_wait(smem_u32(&full[s]), ph, abort_flag, g.status, 13)) { ok = false; break; }
+          const uint32_t j = it % B2_SLOTS, jph = (it / B2_SLOTS) & 1u;
+          if (F8B && !mbar_wait(smem_u32(&bready[j]), jph, abort_flag, g.status, 15)) { ok = false; break; }
           tc_fence_after();
           const uint32_t sa = smem_base + s * STAGE2_BYTES;
-          const uint64_t da = make_smem_desc(sa), db = make_smem_desc(sa + A_BYTES);
+          const uint64_t da = make_smem_desc(sa);
+          const uint64_t db = make_smem_desc(F8B ? bslot_base + j * B2_BYTES : sa + A_BYTES);
 #pragma unroll
           for (int k = 0; k < BK / 16; ++k)
             tc_mma_bf16_pair(d_tmem, da + 2 * k, db + 2 * k, g.idesc, (kb | k) != 0 ? 1u : 0u);
           tc_commit_pair(smem_u32(&empty[s]));
+          if (F8B) tc_commit_pair(smem_u32(&bfree[j]));
         }
         if (!ok) break;
         tc_commit_pair(smem_u32(&tfull[acc]));
       }
     }
-  } else {
+  } else if (F8B && warp >= 6) {
+    // ---------------- FP8 -> bf16 converter (both CTAs, own half of B) ----------------
+    const int ct = threadIdx.x - GEMM_THREADS;
+    uint32_t it = 0;
+    for (int tile = pair; tile < total_tiles && !*abort_flag; tile += n_pairs) {
+      const Tile2 t = locate_tile2(tile, s_pad, s_cnt, s_pp, g.n_groups, g.n_tiles, g.n_per_group);
+      // the half tile is 128 rows = one scale block row
+      const float* srow = g.scales + static_cast<long long>((t.b_row >> 7) + static_cast<int>(rank)) * g.scale_cols;
+      bool ok = true;
+      for (int kb = 0; kb < g.k_blocks; ++kb, ++it) {
+        const uint32_t s = it % STAGES2, ph = (it / STAGES2) & 1u;
+        const uint32_t j = it % B2_SLOTS, jph = (it / B2_SLOTS) & 1u;
+        const float sc = __ldg(srow + (kb >> 1));
+        if (!mbar_wait(smem_u32(&full[s]), ph, abort_flag, g.status, 16)) { ok = false; break; }
+        if (!mbar_wait(smem_u32(&bfree[j]), jph ^ 1u, abort_flag, g.status, 17)) { ok = false; break; }
+        const uint8_t* src = smem + s * STAGE2_BYTES + A_BYTES;
+        uint8_t* dst = smem + STAGES2 * STAGE2_BYTES + j * B2_BYTES;
+#pragma unroll
+        for (int u = ct; u < 128 * (BK / 16); u += CONVERT_THREADS) {
+          const int r = u >> 2, c = u & 3;
+          const uint4 q = *reinterpret_cast<const uint4*>(src + u * 16);
+          uint4 lo, hi;
+          convert16(q, sc, lo, hi);
+          uint8_t* drow = dst + r * 128;
+          *reinterpret_cast<uint4*>(drow + (((2 * c) ^ (r & 7)) << 4)) = lo;
+          *reinterpret_cast<uint4*>(drow + (((2 * c + 1) ^ (r & 7)) << 4)) = hi;
+        }
+        asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+        __syncwarp();
+        if (lane == 0) mbar_arrive_cluster(map_to_cta(smem_u32(&bready[j]), 0));
+      }
+      if (!ok) break;
+    }
+  } else if (warp >= 2 && warp < 6) {
     // ---------------- epilogue (both CTAs, own 128 rows) ----------------
     const int quarter = warp & 3;
     const int row_in_half = quarter * 32 + lane;
@@ -745,11 +807,12 @@ static int launch_epi(const Handle* h, const CUtensorMap& ta, const CUtensorMap&
   return MG_OK;
 }
 
-template <int EPI>
+template <int EPI, bool F8B>
 static int launch_pair(const CUtensorMap& ta, const CUtensorMap& tb, const GemmArgs& args, int grid, cudaStream_t st) {
-  MG_CUDA(cudaFuncSetAttribute(grouped_gemm2_kernel<EPI>, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                               static_cast<int>(GEMM2_SMEM_BYTES)));
-  grouped_gemm2_kernel<EPI><<<grid, GEMM_THREADS, GEMM2_SMEM_BYTES, st>>>(ta, tb, args);
+  constexpr size_t smem = gemm2_smem_bytes<F8B>();
+  MG_CUDA(cudaFuncSetAttribute(grouped_gemm2_kernel<EPI, F8B>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                               static_cast<int>(smem)));
+  grouped_gemm2_kernel<EPI, F8B><<<grid, Cfg2<F8B>::THREADS, smem, st>>>(ta, tb, args);
   MG_CUDA(cudaGetLastError());
   return MG_OK;
 }
@@ -771,7 +834,7 @@ int launch_grouped_gemm(const Handle* h, const GemmProblem& p, cudaStream_t st) 
                p.n_per_group, BN_MAX);
   }
   // SM pairs (2-CTA tiles of 256 x 256) for the bf16 expert GEMMs unless switched off
-  const bool pair = h->opt_pair_gemm && !f32_out && !p.b_fp8;
+  const bool pair = h->opt_pair_gemm && !f32_out;
   CUtensorMap ta, tb;
   int rc = encode_2d(&ta, p.a, static_cast<uint64_t>(p.a_rows), static_cast<uint64_t>(p.K), BM);
   if (rc != MG_OK) return rc;
@@ -820,9 +883,15 @@ int launch_grouped_gemm(const Handle* h, const GemmProblem& p, cudaStream_t st) 
                                      : ((p.a_rows / BM + p.n_groups) / 2 + 1) * static_cast<long long>(a.n_tiles);
     if (max_pair_tiles < pairs) pairs = static_cast<int>(max_pair_tiles);
     if (pairs < 1) pairs = 1;
+    if (p.b_fp8) {
+      switch (p.epilogue) {
+        case EPI_SWIGLU_BF16: return launch_pair<EPI_SWIGLU_BF16, true>(ta, tb, a, 2 * pairs, st);
+        case EPI_PLAIN_BF16: return launch_pair<EPI_PLAIN_BF16, true>(ta, tb, a, 2 * pairs, st);
+      }
+    }
     switch (p.epilogue) {
-      case EPI_SWIGLU_BF16: return launch_pair<EPI_SWIGLU_BF16>(ta, tb, a, 2 * pairs, st);
-      case EPI_PLAIN_BF16: return launch_pair<EPI_PLAIN_BF16>(ta, tb, a, 2 * pairs, st);
+      case EPI_SWIGLU_BF16: return launch_pair<EPI_SWIGLU_BF16, false>(ta, tb, a, 2 * pairs, st);
+      case EPI_PLAIN_BF16: return launch_pair<EPI_PLAIN_BF16, false>(ta, tb, a, 2 * pairs, st);
     }
   }
   if (p.b_fp8) {

@@ -72,6 +72,7 @@ class EPMoELayer:
         self._flag = torch.zeros(1, dtype=torch.int32, device=self.dev)
         self.timing = False                # record CUDA events around the phases of forward()
         self._events: List[list] = []
+        self._side = torch.cuda.Stream(device=self.dev)   # shared expert runs beside the dispatch
 
     # ------------------------------------------------------------------ buffers
     def _setup(self, T: int):
@@ -192,11 +193,15 @@ class EPMoELayer:
                                     self.plan_ws.data_ptr(), self.recv_counts.data_ptr(), self.recv_pad.data_ptr(),
                                     self.dst.data_ptr(), st))
             self._mark(evs)
+            if lay.Is:
+                # the shared expert needs only local data: it goes to a side stream (ordered after the
+                # routing kernels, before the dispatch is enqueued) so that its GEMMs run while the
+                # dispatch below is bound by NVLink
+                self._side.wait_stream(torch.cuda.current_stream())
+                L.check(lib.mg_shared_ffn(h, x2.data_ptr(), T, lay.packed.data_ptr(), self.hs.data_ptr(),
+                                          self.shared_out.data_ptr(), self._side.cuda_stream))
             L.check(lib.mg_ep_dispatch(h, x2.data_ptr(), self.dst.data_ptr(), T, self._peer_recv, st))
             self._mark(evs)
-            if lay.Is:
-                L.check(lib.mg_shared_ffn(h, x2.data_ptr(), T, lay.packed.data_ptr(), self.hs.data_ptr(),
-                                          self.shared_out.data_ptr(), st))
             self._mark(evs)
             self._barrier()                      # all rows have landed in the owners' recv_x
             self._mark(evs)
@@ -205,6 +210,8 @@ class EPMoELayer:
                                       _ptr(self.deq), st))
             self._mark(evs)
             self._barrier()                      # all owners' out_rows are complete
+            if lay.Is:
+                torch.cuda.current_stream().wait_stream(self._side)
             self._mark(evs)
             L.check(lib.mg_ep_combine(h, self._peer_out, self.dst.data_ptr(), self.idx.data_ptr(),
                                       self.w.data_ptr(), _ptr(self.shared_out), T, y.data_ptr(), st))

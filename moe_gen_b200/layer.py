@@ -127,7 +127,8 @@ class MoELayer:
 
     def set_option(self, option: int, value: int):
         L.check(self.lib.mg_set_option(self._h, option, value))
-        self._ws, self._ws_tokens = None, -1        # workspace layout may depend on options
+        if option != L.OPT_KEEP_DEQUANT:
+            self._ws, self._ws_tokens = None, -1    # workspace layout may depend on options
 
     def set_stage_timing(self, enable: bool):
         L.check(self.lib.mg_set_stage_timing(self._h, int(enable)))
@@ -182,6 +183,8 @@ class MoELayer:
             s_in.wait_stream(comp)
             s_out.wait_stream(comp)
             self._workspace(cs)
+            # FP8 layers in pre-dequantise mode: de-quantise once for all chunks of this forward
+            self.set_option(L.OPT_KEEP_DEQUANT, 1)
             for c, t0 in enumerate(range(0, T, cs)):
                 b, n = c & 1, min(cs, T - t0)
                 if c >= 2:
@@ -198,6 +201,7 @@ class MoELayer:
                 with torch.cuda.stream(s_out):
                     y_host[t0:t0 + n].copy_(yout[b][:n], non_blocking=True)
                     ev_out[b].record(s_out)
+            self.set_option(L.OPT_KEEP_DEQUANT, 0)
             s_out.synchronize()
         return y_host
 

@@ -18,6 +18,7 @@ WEIGHT_BF16, WEIGHT_FP8_BLOCK128 = 0, 1
 DEV_OK, DEV_WAIT_TIMEOUT = 0, 1
 OPT_FP8_MODE = 1
 OPT_PAIR_GEMM = 2
+OPT_KEEP_DEQUANT = 3
 FP8_AUTO, FP8_PREDEQUANT, FP8_IN_KERNEL = 0, 1, 2
 
 

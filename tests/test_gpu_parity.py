@@ -240,10 +240,16 @@ def test_fp8_weights_converted_in_the_gemm_equal_dequantise_first(built_lib):
     worst, _ = _check_expert_rows(spec, W, xd, layer, idx)
     assert worst < 5e-3
     ys = []
-    for mode in (0, 1, 2, 1):                      # auto, pre-dequantise, in-kernel, again
-        layer.set_option(1, mode)
-        ys.append(layer.forward(xd).cpu())
+    for pair in (0, 1):                                # one CTA per SM / SM pairs
+        layer.set_option(2, pair)
+        for mode in (0, 1, 2, 1):                      # auto, pre-dequantise, in-kernel, again
+            layer.set_option(1, mode)
+            ys.append(layer.forward(xd).cpu())
+            _status_ok(layer)
+        h3, o3 = layer.expert_ffn(perm, pad, counts, predequant=False)
         _status_ok(layer)
+        assert torch.equal(h1.cpu()[live].view(torch.int16), h3.cpu()[live].view(torch.int16))
+        assert torch.equal(o1.cpu()[live].view(torch.int16), o3.cpu()[live].view(torch.int16))
     for y in ys[1:]:
         assert torch.equal(ys[0].view(torch.int16), y.view(torch.int16))
 
@@ -362,14 +368,27 @@ def test_mixtral_layer(built_lib):
     assert O.rel_l2(y.cpu().float()[same], gold["y"][same]) <= TOL_LAYER
 
 
-def test_forward_host_equals_forward(built_lib):
-    spec = O.LayerSpec(256, 128, 64, 6, 256, 1, 1, O.GATE_SOFTMAX_GREEDY, False, 1.0, O.WEIGHT_BF16,
-                       O.COMBINE_BF16_PROD)
+@pytest.mark.parametrize("fp8", [False, True])
+def test_forward_host_equals_forward(built_lib, fp8):
+    spec = O.LayerSpec(256, 128, 64, 6, 256, 1, 1, O.GATE_SOFTMAX_GREEDY, False, 1.0,
+                       O.WEIGHT_FP8_BLOCK128 if fp8 else O.WEIGHT_BF16, O.COMBINE_BF16_PROD)
     x, W = O.make_inputs(spec, 1000, 33)
     layer = make_layer(spec, W, DEV)
+    if fp8:
+        layer.set_option(1, 1)        # pre-dequantise: the chunks of one host forward share the bf16 copy
     y = layer.forward(x.to(DEV)).cpu()
-    yh = layer.forward_host(x.pin_memory(), chunk_tokens=256)
-    assert torch.equal(y.view(torch.int16), yh.view(torch.int16))
+    for _ in range(2):
+        yh = layer.forward_host(x.pin_memory(), chunk_tokens=256)
+        assert torch.equal(y.view(torch.int16), yh.view(torch.int16))
+    # re-packing an expert must invalidate the kept copy
+    if fp8:
+        (g, gs), (u, us), (d, ds) = W.q_gate[5], W.q_up[5], W.q_down[5]
+        layer.load_expert(0, g, u, d, (gs, us, ds))
+        y2 = layer.forward(x.to(DEV)).cpu()
+        yh2 = layer.forward_host(x.pin_memory(), chunk_tokens=256)
+        assert torch.equal(y2.view(torch.int16), yh2.view(torch.int16))
+        assert not torch.equal(y2.view(torch.int16), y.view(torch.int16))
+    _status_ok(layer)
 
 
 def test_patched_reference_style_module(built_lib):
