@@ -247,6 +247,7 @@ def main():
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-e2e", action="store_true")
     ap.add_argument("--chunk-tokens", type=int, default=16384)
+    ap.add_argument("--micro", type=int, default=2, help="token micro-batches pipelined in the expert-parallel forward")
     ap.add_argument("--pair-gemm", type=int, default=-1, help="1/0 force the SM-pair expert GEMM on/off")
     ap.add_argument("--fp8-mode", type=int, default=-1, help="0 auto, 1 pre-dequantise, 2 convert in the GEMM")
     args = ap.parse_args()
@@ -258,10 +259,12 @@ def main():
     T = args.tokens or WORKLOADS[name][12]
     H, I, E, k, Is = WORKLOADS[name][:5]
     warmup = max(args.warmup, 3) if args.impl == "ours" else args.warmup
+    wbytes = WORKLOADS[name][2] * 3 * I * H * (1 if WORKLOADS[name][10] == 1 else 2)   # expert weights read every step
+    big = T * H * 2 + wbytes > 126e6
     config = {"workload": WORKLOAD_TEXT[name], "tokens": T, "seed": WORKLOADS[name][13],
-              "parallelism": f"ep{world}" if world > 1 else "single GPU",
-              "zipf_alpha": args.zipf, "l2": "inputs exceed L2 (x, routed rows and weights are each >126 MB)"
-              if T * H * 2 > 126e6 else "L2 flushed between steps by writing a 256 MB buffer"}
+              "parallelism": f"ep{world}, {args.micro} micro-batches" if world > 1 else "single GPU",
+              "zipf_alpha": args.zipf, "l2": f"inputs exceed L2: {wbytes / 1e9:.2f} GB of expert weights and {T * H * 2 / 1e6:.0f} MB of "
+                    "hidden states are read every step" if big else "L2 flushed between steps by writing a 256 MB buffer"}
 
     # ------------------------------------------------------------------ reference arm (CPU)
     if args.impl == "reference":
@@ -297,11 +300,11 @@ def main():
     else:
         from moe_gen_b200.ep import EPMoELayer
         assert T % world == 0
-        layer = EPMoELayer(build_layer(name, device, rank, world, args.zipf))
+        layer = EPMoELayer(build_layer(name, device, rank, world, args.zipf), n_micro=args.micro)
         x = make_tokens(name, T // world, device, rank, args.zipf)
         step = lambda: layer.forward(x)                                   # noqa: E731
         T_total = T
-    flush = None if T * H * 2 > 126e6 else torch.empty(256 << 20, dtype=torch.uint8, device=device)
+    flush = None if big else torch.empty(256 << 20, dtype=torch.uint8, device=device)
 
     def run_step():
         if flush is not None:
@@ -416,9 +419,11 @@ def main():
 
     alg = algorithmic(name, T_total)
     if world > 1:
-        # expert phase = gate/up GEMM + down GEMM (+ FP8 conversion) of this rank's experts
+        # expert phase of the first micro-batch = gate/up GEMM + down GEMM (+ FP8 conversion) of this
+        # rank's experts over 1/n_micro of the rows
         t_g1 = phases["expert_ffn"] * 1e-3
-        tf = (alg["gemm1_flops"] + alg["gemm2_flops"]) / world / t_g1 / 1e12 if t_g1 > 0 else 0.0
+        n_mb = len(layer._mbs)
+        tf = (alg["gemm1_flops"] + alg["gemm2_flops"]) / world / n_mb / t_g1 / 1e12 if t_g1 > 0 else 0.0
     else:
         t_g1 = stage_ms["expert_gemm1"] * 1e-3
         tf = alg["gemm1_flops"] / world / t_g1 / 1e12 if t_g1 > 0 else 0.0
@@ -454,10 +459,8 @@ def main():
     if phases is not None:
         stages = {k_: {"ms": round(v, 4)} for k_, v in phases.items()}
         stages["by_rank_ms"] = all_phases
-        nv = Tl * k * H * 2 * (world - 1) / world          # bytes this rank sends (and later fetches) over NVLink
-        for ph in ("dispatch", "combine"):
-            if phases[ph] > 0:
-                stages[ph]["nvlink_gbs"] = round(nv / (phases[ph] * 1e-3) / 1e9, 1)
+        stages["note"] = (f"phases of the first of {len(layer._mbs)} pipelined micro-batches on its stream; "
+                          f"each rank sends and later fetches {Tl * k * H * 2 * (world - 1) / world / 1e6:.0f} MB over NVLink per step")
 
     cpu = None
     if not args.no_cpu_baseline:

@@ -219,6 +219,11 @@ int mg_permute_rows(mg_handle h, const void* d_x, const int32_t* d_dst_row, int6
  * Replaces the expert loop (modeling_deepseek_v3.py:675-691) and
  * DeepseekV3MLP.forward (modeling_deepseek_v3.py:463-467). */
 int mg_dequant_ws_bytes(mg_handle h, size_t* bytes);
+/* Optional: starts the de-quantisation into d_dequant_ws now (on the handle's side stream,
+ * ordered after what `stream` holds), so that it overlaps whatever the caller enqueues before
+ * the mg_expert_ffn call with the same packed buffer, scratch and stream, which then only
+ * waits for it.  No counterpart in the reference. */
+int mg_dequant_start(mg_handle h, const void* d_packed, void* d_dequant_ws, void* stream);
 int mg_expert_ffn(mg_handle h, const void* d_perm_x, const int32_t* d_pad_offsets,
                   const int32_t* d_counts, int64_t n_rows_padded, const void* d_packed,
                   void* d_h_buf, void* d_out_rows, void* d_dequant_ws, void* stream);
@@ -327,7 +332,8 @@ int mg_last_launch_count(mg_handle h, int32_t* launches);
  * same and no expert was re-packed in between.  Meant for the token chunks of ONE logical
  * forward (MoELayer.forward_host sets it around its chunk loop and clears it afterwards), so
  * that the weights are de-quantised once per forward, not once per chunk.  The caller must
- * not touch the scratch in between. */
+ * not touch the scratch in between.  2 = the same, and the calls may be on different streams
+ * whose ordering the caller guarantees (the expert-parallel micro-batches do). */
 #define MG_OPT_KEEP_DEQUANT 3
 int mg_set_option(mg_handle h, int32_t option, int32_t value);
 

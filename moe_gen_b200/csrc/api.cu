@@ -126,6 +126,7 @@ int mg_create(const mg_layer_desc* desc, mg_handle* out) {
   h->opt_pair_gemm = false;
   h->opt_keep_dequant = false;
   h->deq_valid = false;
+  h->deq_inflight = false;
   h->deq_scratch = nullptr;
   h->deq_packed = nullptr;
   h->deq_stream = nullptr;
@@ -212,6 +213,7 @@ int mg_pack_expert(mg_handle hh, int32_t local_expert, const void* d_gate, const
   if (!h) return MG_ERR_STATE;
   MG_REQUIRE(d_gate && d_up && d_down && d_packed, MG_ERR_NULL, "mg_pack_expert: null pointer");
   h->deq_valid = false;
+  h->deq_inflight = false;
   return launch_pack_expert(h, local_expert, d_gate, d_up, d_down, gs, us, ds, d_packed,
                             static_cast<cudaStream_t>(stream));
 }
@@ -309,6 +311,33 @@ static int ensure_side_stream(Handle* h) {
   return MG_OK;
 }
 
+// Launches the chunked de-quantisation of all local experts on the side stream (ordered after
+// what is already on `st`) and remembers that it is in flight for this packed buffer / scratch.
+static int start_dequant(Handle* h, const void* packed, void* deq, cudaStream_t st, int* launches) {
+  int rc = ensure_side_stream(h);
+  if (rc != MG_OK) return rc;
+  const int E = h->e_local;
+  const int n_chunks = E < kDequantChunks ? E : kDequantChunks;
+  const int per = (E + n_chunks - 1) / n_chunks;
+  MG_CUDA(cudaEventRecord(h->ev_entry, st));
+  MG_CUDA(cudaStreamWaitEvent(h->side, h->ev_entry, 0));
+  for (int which = 0; which < 2; ++which) {
+    for (int c = 0; c < n_chunks; ++c) {
+      const int lo = c * per, n = (lo + per <= E ? per : E - lo);
+      rc = launch_dequant_packed(h, packed, deq, which, lo, n, h->side);
+      if (rc != MG_OK) return rc;
+      MG_CUDA(cudaEventRecord(which == 0 ? h->ev_w13[c] : h->ev_w2[c], h->side));
+    }
+  }
+  if (launches) *launches += 2 * n_chunks;
+  h->deq_inflight = true;
+  h->deq_valid = false;
+  h->deq_scratch = deq;
+  h->deq_packed = packed;
+  h->deq_stream = st;
+  return MG_OK;
+}
+
 static int expert_ffn(Handle* h, const void* perm_x, const int32_t* pad, const int32_t* counts, int64_t rows_padded,
                       const void* packed, void* h_buf, void* out_rows, void* deq, cudaStream_t st, int* launches,
                       bool timed = false) {
@@ -346,21 +375,15 @@ static int expert_ffn(Handle* h, const void* perm_x, const int32_t* pad, const i
   const int per = (E + n_chunks - 1) / n_chunks;
   // MG_OPT_KEEP_DEQUANT: the copy made by the previous call (same packed buffer, same scratch,
   // same stream) is still current, e.g. between the token chunks of one host-buffer forward
-  const bool reuse = h->opt_keep_dequant && h->deq_valid && h->deq_scratch == deq && h->deq_packed == packed &&
-                     h->deq_stream == st;
-  if (!reuse) {
-    MG_CUDA(cudaEventRecord(h->ev_entry, st));
-    MG_CUDA(cudaStreamWaitEvent(h->side, h->ev_entry, 0));
-    for (int which = 0; which < 2; ++which) {
-      for (int c = 0; c < n_chunks; ++c) {
-        const int lo = c * per, n = (lo + per <= E ? per : E - lo);
-        rc = launch_dequant_packed(h, packed, deq, which, lo, n, h->side);
-        if (rc != MG_OK) return rc;
-        MG_CUDA(cudaEventRecord(which == 0 ? h->ev_w13[c] : h->ev_w2[c], h->side));
-      }
-    }
-    if (launches) *launches += 2 * n_chunks;
+  // keep-dequant level 2: the caller orders the streams itself (expert-parallel micro-batches)
+  const bool same = h->deq_scratch == deq && h->deq_packed == packed &&
+                    (h->deq_stream == st || h->opt_keep_dequant == 2);
+  const bool reuse = h->opt_keep_dequant && h->deq_valid && same;
+  if (!reuse && !(h->deq_inflight && same)) {       // not started ahead of time by start_dequant
+    rc = start_dequant(h, packed, deq, st, launches);
+    if (rc != MG_OK) return rc;
   }
+  h->deq_inflight = false;
   if (timed) mark(h, MG_STAGE_DEQUANT, st);
   const __nv_bfloat16* w13 = static_cast<const __nv_bfloat16*>(deq);
   const __nv_bfloat16* w2 = w13 + static_cast<size_t>(E) * 2 * d.inter * d.hidden;
@@ -388,6 +411,14 @@ static int expert_ffn(Handle* h, const void* perm_x, const int32_t* pad, const i
   h->deq_packed = packed;
   h->deq_stream = st;
   return MG_OK;
+}
+
+int mg_dequant_start(mg_handle hh, const void* d_packed, void* d_dequant_ws, void* stream) {
+  Handle* h = check(hh);
+  if (!h) return MG_ERR_STATE;
+  MG_REQUIRE(d_packed && d_dequant_ws, MG_ERR_NULL, "mg_dequant_start: null pointer");
+  MG_REQUIRE(h->d.weight_format == MG_WEIGHT_FP8_BLOCK128, MG_ERR_CONFIG, "layer has no FP8 weights");
+  return start_dequant(h, d_packed, d_dequant_ws, static_cast<cudaStream_t>(stream), nullptr);
 }
 
 int mg_expert_ffn(mg_handle hh, const void* d_perm_x, const int32_t* d_pad, const int32_t* d_counts,
@@ -481,7 +512,15 @@ int mg_moe_forward(mg_handle hh, const void* d_x, int64_t T, const void* d_gate_
   void* deq = fp8_predequant(h, T) ? ws + L.off[WS_DEQ] : nullptr;
   int launches = 0;
   if (h->stage_timing) MG_CUDA(cudaEventRecord(h->stage_ev[h->stage_calls % kStageSlots][0], st));
-  int rc = mg_gate_logits(hh, d_x, d_gate_w, T, logits, stream);
+  int rc;
+  if (deq != nullptr && !(h->opt_keep_dequant && h->deq_valid && h->deq_scratch == deq && h->deq_packed == d_packed &&
+                          h->deq_stream == st)) {
+    // the weights do not depend on the routing: their de-quantisation starts now, beside the
+    // router, plan and scatter kernels
+    rc = start_dequant(h, d_packed, deq, st, &launches);
+    if (rc != MG_OK) return rc;
+  }
+  rc = mg_gate_logits(hh, d_x, d_gate_w, T, logits, stream);
   if (rc != MG_OK) return rc;
   mark(h, MG_STAGE_GATE_LOGITS, st);
   rc = launch_route_topk(h, logits, d_bias, T, idx, w, st);
@@ -524,7 +563,8 @@ int mg_set_option(mg_handle hh, int32_t option, int32_t value) {
       return MG_OK;
     case MG_OPT_PAIR_GEMM: h->opt_pair_gemm = value != 0; return MG_OK;
     case MG_OPT_KEEP_DEQUANT:
-      h->opt_keep_dequant = value != 0;
+      MG_REQUIRE(value >= 0 && value <= 2, MG_ERR_CONFIG, "bad keep-dequant level %d", value);
+      h->opt_keep_dequant = value;
       h->deq_valid = false;          // switching it on or off never trusts an older copy
       return MG_OK;
     default: set_error("unknown option %d", option); return MG_ERR_CONFIG;

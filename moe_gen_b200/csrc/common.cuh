@@ -43,8 +43,9 @@ struct Handle {
   int e_local;            // experts owned by this rank
   int32_t* d_status;      // [2]: code, detail
   int last_launches;
-  bool opt_keep_dequant;  // reuse the de-quantised copy of the previous call while nothing changed
+  int opt_keep_dequant;   // 1/2: reuse the de-quantised copy of the previous call while nothing changed
   bool deq_valid;
+  bool deq_inflight;      // start_dequant ran for (deq_packed, deq_scratch, deq_stream); expert_ffn only waits
   const void* deq_scratch;
   const void* deq_packed;
   cudaStream_t deq_stream;

@@ -51,78 +51,103 @@ def ep_layout_reference(counts_all: np.ndarray, rank: int, e_local: int, cap_row
     return send_base, recv_counts, recv_pad, over
 
 
-class EPMoELayer:
-    """Wraps a MoELayer created with ep_rank/ep_size and runs the expert-parallel forward."""
+class _MicroBatch:
+    """Buffers, stream and process group of one token micro-batch of the expert-parallel forward."""
+    pass
 
-    def __init__(self, layer: MoELayer, group: Optional[dist.ProcessGroup] = None, capacity_factor: float = 2.0):
+
+class EPMoELayer:
+    """Wraps a MoELayer created with ep_rank/ep_size and runs the expert-parallel forward.
+
+    n_micro > 1 splits the local tokens into micro-batches that are pipelined: while the experts
+    of one micro-batch run on the tensor cores, the next one's rows travel over NVLink and the
+    previous one's results are gathered back, each micro-batch on its own stream with its own
+    shared buffers and its own NCCL group (so their barriers do not queue behind each other)."""
+
+    PHASES = ["route_dispatch", "expert_ffn", "combine"]
+
+    def __init__(self, layer: MoELayer, group: Optional[dist.ProcessGroup] = None, capacity_factor: float = 2.0,
+                 n_micro: int = 2):
         self.layer = layer
         self.group = group
         self.rank = dist.get_rank(group)
         self.world = dist.get_world_size(group)
         assert layer.desc.ep_size == self.world and layer.desc.ep_rank == self.rank
         self.capacity_factor = capacity_factor
+        self.n_micro = max(1, n_micro)
         self.lib = layer.lib
         self.dev = layer.device
-        self._cap_rows = 0
-        self._own: List[int] = []          # [recv_x, out_rows] device addresses owned by this rank
-        self._peer_recv = None
-        self._peer_out = None
-        self._imported: List[int] = []
+        self._mbs: List[_MicroBatch] = []
         self._tokens = -1
-        self._flag = torch.zeros(1, dtype=torch.int32, device=self.dev)
         self.timing = False                # record CUDA events around the phases of forward()
         self._events: List[list] = []
         self._side = torch.cuda.Stream(device=self.dev)   # shared expert runs beside the dispatch
+        ranks = list(range(self.world)) if group is None else dist.get_process_group_ranks(group)
+        self._groups = [group] + [dist.new_group(ranks) for _ in range(self.n_micro - 1)]
+        self._streams = [torch.cuda.Stream(device=self.dev) for _ in range(self.n_micro)]
+        self.deq = None
 
     # ------------------------------------------------------------------ buffers
     def _setup(self, T: int):
         """(Re)allocates the shared buffers for T local tokens and exchanges their handles."""
         self._release()
         lay = self.layer
-        avg_rows = T * lay.k                               # rows a rank receives when load is even
-        cap = int(min(T * self.world * lay.k, max(avg_rows * self.capacity_factor, avg_rows + 4096)))
-        cap = (cap + TILE_M - 1) // TILE_M * TILE_M + lay.e_local * TILE_M
-        assert cap < (1 << PEER_SHIFT)
-        self._cap_rows = cap
-        nbytes = cap * lay.H * 2
+        E, El, k = lay.E, lay.e_local, lay.k
+        n = self.n_micro if T >= 2 * self.n_micro else 1
+        bounds = [T * i // n for i in range(n + 1)]
         handles = []
         with torch.cuda.device(self.dev):
-            for _ in range(2):
-                p = C.c_void_p()
-                L.check(self.lib.mg_ep_alloc(nbytes, C.byref(p)))
-                hd = (C.c_ubyte * 64)()
-                L.check(self.lib.mg_ep_export(p, hd))
-                self._own.append(p.value)
-                handles.append(bytes(hd))
+            for i in range(n):
+                mb = _MicroBatch()
+                mb.t0, mb.t1 = bounds[i], bounds[i + 1]
+                Tm = mb.t1 - mb.t0
+                avg_rows = Tm * k                              # rows a rank receives when load is even
+                cap = int(min(Tm * self.world * k, max(avg_rows * self.capacity_factor, avg_rows + 4096)))
+                cap = (cap + TILE_M - 1) // TILE_M * TILE_M + El * TILE_M
+                assert cap < (1 << PEER_SHIFT)
+                mb.cap = cap
+                mb.own = []
+                for _ in range(2):                             # recv_x, out_rows
+                    p = C.c_void_p()
+                    L.check(self.lib.mg_ep_alloc(cap * lay.H * 2, C.byref(p)))
+                    hd = (C.c_ubyte * 64)()
+                    L.check(self.lib.mg_ep_export(p, hd))
+                    mb.own.append(p.value)
+                    handles.append(bytes(hd))
+                i32 = dict(dtype=torch.int32, device=self.dev)
+                mb.counts = torch.empty(E, **i32)
+                mb.counts_all = torch.empty(self.world, E, **i32)
+                mb.recv_counts = torch.empty(El, **i32)
+                mb.recv_pad = torch.empty(El + 1, **i32)
+                mb.dst = torch.empty(Tm, k, **i32)
+                mb.idx = torch.empty(Tm, k, **i32)
+                mb.w = torch.empty(Tm, k, dtype=torch.float32, device=self.dev)
+                mb.logits = torch.empty(Tm, E, dtype=torch.float32, device=self.dev)
+                nb = C.c_size_t()
+                L.check(self.lib.mg_plan_ws_bytes(lay._h, Tm, C.byref(nb)))
+                mb.plan_ws = torch.empty(nb.value, dtype=torch.uint8, device=self.dev)
+                mb.h_buf = torch.empty(cap, lay.I, dtype=torch.bfloat16, device=self.dev)
+                mb.flag = torch.zeros(1, dtype=torch.int32, device=self.dev)
+                mb.stream = self._streams[i]
+                mb.group = self._groups[i]
+                mb.imported = []
+                self._mbs.append(mb)
             gathered: List[Optional[list]] = [None] * self.world
             dist.all_gather_object(gathered, handles, group=self.group)
-            recv = (C.c_void_p * self.world)()
-            out = (C.c_void_p * self.world)()
-            for r in range(self.world):
-                if r == self.rank:
-                    recv[r], out[r] = self._own[0], self._own[1]
-                    continue
-                for which, table in ((0, recv), (1, out)):
-                    p = C.c_void_p()
-                    buf = (C.c_ubyte * 64).from_buffer_copy(gathered[r][which])
-                    L.check(self.lib.mg_ep_import(buf, C.byref(p)))
-                    table[r] = p.value
-                    self._imported.append(p.value)
-            self._peer_recv, self._peer_out = recv, out
-            E, El, k = lay.E, lay.e_local, lay.k
-            i32 = dict(dtype=torch.int32, device=self.dev)
-            self.counts = torch.empty(E, **i32)
-            self.counts_all = torch.empty(self.world, E, **i32)
-            self.recv_counts = torch.empty(El, **i32)
-            self.recv_pad = torch.empty(El + 1, **i32)
-            self.dst = torch.empty(T, k, **i32)
-            self.idx = torch.empty(T, k, **i32)
-            self.w = torch.empty(T, k, dtype=torch.float32, device=self.dev)
-            self.logits = torch.empty(T, E, dtype=torch.float32, device=self.dev)
-            nb = C.c_size_t()
-            L.check(self.lib.mg_plan_ws_bytes(lay._h, T, C.byref(nb)))
-            self.plan_ws = torch.empty(nb.value, dtype=torch.uint8, device=self.dev)
-            self.h_buf = torch.empty(cap, lay.I, dtype=torch.bfloat16, device=self.dev)
+            for i, mb in enumerate(self._mbs):
+                recv = (C.c_void_p * self.world)()
+                out = (C.c_void_p * self.world)()
+                for r in range(self.world):
+                    if r == self.rank:
+                        recv[r], out[r] = mb.own[0], mb.own[1]
+                        continue
+                    for which, table in ((0, recv), (1, out)):
+                        p = C.c_void_p()
+                        buf = (C.c_ubyte * 64).from_buffer_copy(gathered[r][2 * i + which])
+                        L.check(self.lib.mg_ep_import(buf, C.byref(p)))
+                        table[r] = p.value
+                        mb.imported.append(p.value)
+                mb.peer_recv, mb.peer_out = recv, out
             self.hs = torch.empty(T, max(lay.Is, 1), dtype=torch.bfloat16, device=self.dev)
             self.shared_out = torch.empty(T, lay.H, dtype=torch.bfloat16, device=self.dev) if lay.Is else None
             nd = C.c_size_t()
@@ -134,36 +159,40 @@ class EPMoELayer:
         dist.barrier(group=self.group)
 
     def _release(self):
-        for p in self._imported:
-            self.lib.mg_ep_unimport(C.c_void_p(p))
-        self._imported = []
-        if self._own:
-            torch.cuda.synchronize(self.dev)
-            if dist.is_initialized():
-                dist.barrier(group=self.group)       # nobody may still be reading our buffers
-            for p in self._own:
+        if not self._mbs:
+            return
+        torch.cuda.synchronize(self.dev)
+        if dist.is_initialized():
+            dist.barrier(group=self.group)       # nobody may still be reading our buffers
+        for mb in self._mbs:
+            for p in mb.imported:
+                self.lib.mg_ep_unimport(C.c_void_p(p))
+        if dist.is_initialized():
+            dist.barrier(group=self.group)       # every mapping of our buffers is closed
+        for mb in self._mbs:
+            for p in mb.own:
                 self.lib.mg_ep_free(C.c_void_p(p))
-        self._own = []
+        self._mbs = []
+        self._tokens = -1
 
     def close(self):
         self._release()
 
-    def _barrier(self):
+    @staticmethod
+    def _barrier(mb):
         # a stream-ordered collective: kernels launched after it on this rank start only after
-        # every rank's earlier kernels have finished
-        dist.all_reduce(self._flag, group=self.group)
+        # every rank's earlier kernels on the micro-batch's stream have finished
+        dist.all_reduce(mb.flag, group=mb.group)
 
-    PHASES = ["gate_route", "count_gather_place", "dispatch", "shared_ffn", "barrier_1", "expert_ffn", "barrier_2",
-              "combine"]
-
-    def _mark(self, evs):
+    def _mark(self, evs, stream):
         if evs is not None:
             e = torch.cuda.Event(enable_timing=True)
-            e.record()
+            e.record(stream)
             evs.append(e)
 
     def phase_times(self) -> dict:
-        """Mean milliseconds per phase over the forwards run with timing on (call after synchronising)."""
+        """Mean milliseconds of the first micro-batch's phases over the forwards run with timing on
+        (call after synchronising).  With pipelining the phases of different micro-batches overlap."""
         out = {p: 0.0 for p in self.PHASES}
         for evs in self._events:
             for i, p in enumerate(self.PHASES):
@@ -178,44 +207,75 @@ class EPMoELayer:
         if T != self._tokens:
             self._setup(T)
         y = torch.empty_like(x2) if out is None else out
-        st = torch.cuda.current_stream().cuda_stream
         h = lay._h
+        cur = torch.cuda.current_stream()
         evs = [] if self.timing else None
+        H2 = lay.H * 2
         with torch.cuda.device(self.dev):
-            self._mark(evs)
-            L.check(lib.mg_gate_logits(h, x2.data_ptr(), lay.gate_w.data_ptr(), T, self.logits.data_ptr(), st))
-            L.check(lib.mg_route_topk(h, self.logits.data_ptr(), _ptr(lay.bias), T, self.idx.data_ptr(),
-                                      self.w.data_ptr(), st))
-            self._mark(evs)
-            L.check(lib.mg_ep_count(h, self.idx.data_ptr(), T, self.counts.data_ptr(), self.plan_ws.data_ptr(), st))
-            dist.all_gather_into_tensor(self.counts_all, self.counts, group=self.group)
-            L.check(lib.mg_ep_place(h, self.idx.data_ptr(), T, self.counts_all.data_ptr(), self._cap_rows,
-                                    self.plan_ws.data_ptr(), self.recv_counts.data_ptr(), self.recv_pad.data_ptr(),
-                                    self.dst.data_ptr(), st))
-            self._mark(evs)
-            if lay.Is:
-                # the shared expert needs only local data: it goes to a side stream (ordered after the
-                # routing kernels, before the dispatch is enqueued) so that its GEMMs run while the
-                # dispatch below is bound by NVLink
-                self._side.wait_stream(torch.cuda.current_stream())
-                L.check(lib.mg_shared_ffn(h, x2.data_ptr(), T, lay.packed.data_ptr(), self.hs.data_ptr(),
-                                          self.shared_out.data_ptr(), self._side.cuda_stream))
-            L.check(lib.mg_ep_dispatch(h, x2.data_ptr(), self.dst.data_ptr(), T, self._peer_recv, st))
-            self._mark(evs)
-            self._mark(evs)
-            self._barrier()                      # all rows have landed in the owners' recv_x
-            self._mark(evs)
-            L.check(lib.mg_expert_ffn(h, self._own[0], self.recv_pad.data_ptr(), self.recv_counts.data_ptr(),
-                                      self._cap_rows, lay.packed.data_ptr(), self.h_buf.data_ptr(), self._own[1],
-                                      _ptr(self.deq), st))
-            self._mark(evs)
-            self._barrier()                      # all owners' out_rows are complete
-            if lay.Is:
-                torch.cuda.current_stream().wait_stream(self._side)
-            self._mark(evs)
-            L.check(lib.mg_ep_combine(h, self._peer_out, self.dst.data_ptr(), self.idx.data_ptr(),
-                                      self.w.data_ptr(), _ptr(self.shared_out), T, y.data_ptr(), st))
-            self._mark(evs)
+            for mb in self._mbs:
+                mb.stream.wait_stream(cur)
+            s0 = self._mbs[0].stream
+            if self.deq is not None:
+                # weights do not depend on the routing: de-quantise once per forward, starting now
+                L.check(lib.mg_set_option(h, L.OPT_KEEP_DEQUANT, 2))
+                L.check(lib.mg_dequant_start(h, lay.packed.data_ptr(), self.deq.data_ptr(), s0.cuda_stream))
+            self._mark(evs, s0)
+            # ---- routing and dispatch of every micro-batch, each on its own stream; the dispatches
+            # follow one another so that the first one has the whole NVLink bandwidth and its experts
+            # can start while the next micro-batch is still travelling
+            sent = None
+            for i, mb in enumerate(self._mbs):
+                st = mb.stream.cuda_stream
+                Tm = mb.t1 - mb.t0
+                xp = x2.data_ptr() + mb.t0 * H2
+                with torch.cuda.stream(mb.stream):
+                    L.check(lib.mg_gate_logits(h, xp, lay.gate_w.data_ptr(), Tm, mb.logits.data_ptr(), st))
+                    L.check(lib.mg_route_topk(h, mb.logits.data_ptr(), _ptr(lay.bias), Tm, mb.idx.data_ptr(),
+                                              mb.w.data_ptr(), st))
+                    L.check(lib.mg_ep_count(h, mb.idx.data_ptr(), Tm, mb.counts.data_ptr(), mb.plan_ws.data_ptr(), st))
+                    dist.all_gather_into_tensor(mb.counts_all, mb.counts, group=mb.group)
+                    L.check(lib.mg_ep_place(h, mb.idx.data_ptr(), Tm, mb.counts_all.data_ptr(), mb.cap,
+                                            mb.plan_ws.data_ptr(), mb.recv_counts.data_ptr(), mb.recv_pad.data_ptr(),
+                                            mb.dst.data_ptr(), st))
+                    if i == 0 and lay.Is:
+                        # the shared expert needs only local data: a side stream, ordered after the first
+                        # routing kernels, runs its GEMMs while the dispatch is bound by NVLink
+                        self._side.wait_stream(mb.stream)
+                        L.check(lib.mg_shared_ffn(h, x2.data_ptr(), T, lay.packed.data_ptr(), self.hs.data_ptr(),
+                                                  self.shared_out.data_ptr(), self._side.cuda_stream))
+                    if sent is not None:
+                        mb.stream.wait_event(sent)
+                    L.check(lib.mg_ep_dispatch(h, xp, mb.dst.data_ptr(), Tm, mb.peer_recv, st))
+                    sent = torch.cuda.Event()
+                    sent.record(mb.stream)
+                    self._barrier(mb)                # all rows have landed in the owners' recv_x
+            self._mark(evs, s0)
+            # ---- experts, one micro-batch after the other on the tensor cores
+            prev = None
+            for mb in self._mbs:
+                with torch.cuda.stream(mb.stream):
+                    if prev is not None:
+                        mb.stream.wait_event(prev)   # also orders the reuse of the de-quantised weights
+                    L.check(lib.mg_expert_ffn(h, mb.own[0], mb.recv_pad.data_ptr(), mb.recv_counts.data_ptr(),
+                                              mb.cap, lay.packed.data_ptr(), mb.h_buf.data_ptr(), mb.own[1],
+                                              _ptr(self.deq), mb.stream.cuda_stream))
+                    prev = torch.cuda.Event()
+                    prev.record(mb.stream)
+                    self._barrier(mb)                # all owners' out_rows of this micro-batch are complete
+            self._mark(evs, s0)
+            # ---- return + combine
+            for mb in self._mbs:
+                with torch.cuda.stream(mb.stream):
+                    if lay.Is:
+                        mb.stream.wait_stream(self._side)
+                    sh = self.shared_out.data_ptr() + mb.t0 * H2 if lay.Is else None
+                    L.check(lib.mg_ep_combine(h, mb.peer_out, mb.dst.data_ptr(), mb.idx.data_ptr(), mb.w.data_ptr(),
+                                              sh, mb.t1 - mb.t0, y.data_ptr() + mb.t0 * H2, mb.stream.cuda_stream))
+            self._mark(evs, s0)
+            if self.deq is not None:
+                L.check(lib.mg_set_option(h, L.OPT_KEEP_DEQUANT, 0))
+            for mb in self._mbs:
+                cur.wait_stream(mb.stream)
         if evs is not None:
             self._events.append(evs)
         return y.view(x.shape)

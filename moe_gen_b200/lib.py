@@ -51,6 +51,7 @@ SIGNATURES = {
     "mg_permute_plan_static": [_vp, _vp, _i64, _i32, _i32, _vp, _vp, _vp, _vp, _vp],
     "mg_permute_rows": [_vp, _vp, _vp, _i64, _vp, _vp],
     "mg_dequant_ws_bytes": [_vp, _P(_sz)],
+    "mg_dequant_start": [_vp, _vp, _vp, _vp],
     "mg_expert_ffn": [_vp, _vp, _vp, _vp, _i64, _vp, _vp, _vp, _vp, _vp],
     "mg_shared_ffn": [_vp, _vp, _i64, _vp, _vp, _vp, _vp],
     "mg_combine": [_vp, _vp, _vp, _vp, _vp, _vp, _i64, _vp, _vp],
