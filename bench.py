@@ -247,7 +247,7 @@ def main():
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-e2e", action="store_true")
     ap.add_argument("--chunk-tokens", type=int, default=16384)
-    ap.add_argument("--micro", type=int, default=2, help="token micro-batches pipelined in the expert-parallel forward")
+    ap.add_argument("--micro", type=int, default=1, help="token micro-batches pipelined in the expert-parallel forward")
     ap.add_argument("--pair-gemm", type=int, default=-1, help="1/0 force the SM-pair expert GEMM on/off")
     ap.add_argument("--fp8-mode", type=int, default=-1, help="0 auto, 1 pre-dequantise, 2 convert in the GEMM")
     args = ap.parse_args()

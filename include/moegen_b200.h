@@ -308,6 +308,13 @@ int mg_ep_combine(mg_handle h, void* const* peer_out, const int32_t* d_dst, cons
 int mg_workspace_ptr(mg_handle h, void* d_workspace, int64_t max_tokens, int64_t max_rows,
                      int32_t which, void** ptr);
 
+/* Self-test of the failure path (no counterpart in the reference, whose get_weights polls
+ * forever: core/GPU_Weight_Buffer/GPU_Weight_Buffer.cpp:171-221): launches one thread that
+ * waits, with the GEMM kernels' bounded-wait helper and a limit of limit_ms (1..1000), on a
+ * barrier nothing completes.  After synchronising, mg_device_status must report
+ * MG_DEV_WAIT_TIMEOUT with detail 99 and the context must still be usable. */
+int mg_selftest_wait_timeout(mg_handle h, int32_t limit_ms, void* stream);
+
 /* Number of kernel launches the last mg_moe_forward on this handle issued. */
 int mg_last_launch_count(mg_handle h, int32_t* launches);
 

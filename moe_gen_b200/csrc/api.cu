@@ -601,6 +601,13 @@ int mg_stage_times(mg_handle hh, float* ms, int32_t n) {
   return MG_OK;
 }
 
+int mg_selftest_wait_timeout(mg_handle hh, int32_t limit_ms, void* stream) {
+  Handle* h = check(hh);
+  if (!h) return MG_ERR_STATE;
+  MG_REQUIRE(limit_ms >= 1 && limit_ms <= 1000, MG_ERR_LIMIT, "limit_ms=%d must be in [1,1000]", limit_ms);
+  return launch_wait_probe(h, limit_ms, static_cast<cudaStream_t>(stream));
+}
+
 int mg_last_launch_count(mg_handle hh, int32_t* launches) {
   Handle* h = check(hh);
   if (!h) return MG_ERR_STATE;

@@ -127,5 +127,6 @@ struct GemmProblem {
   int epilogue;
 };
 int launch_grouped_gemm(const Handle* h, const GemmProblem& p, cudaStream_t st);
+int launch_wait_probe(const Handle* h, int limit_ms, cudaStream_t st);
 
 }  // namespace mg

@@ -100,7 +100,8 @@ __device__ __forceinline__ unsigned long long global_timer() {
 }
 // Bounded wait.  Returns false if the wait ran out or another role already gave up.
 __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile int* abort_flag,
-                                          int32_t* status, int where) {
+                                          int32_t* status, int where,
+                                          unsigned long long limit_ns = WAIT_LIMIT_NS) {
   if (mbar_try_wait(bar, parity)) return true;
   const unsigned long long t0 = global_timer();
   uint32_t spins = 0;
@@ -108,7 +109,7 @@ __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatil
     if (mbar_try_wait(bar, parity)) return true;
     if ((++spins & 63u) == 0u) {
       if (*abort_flag) return false;
-      if (global_timer() - t0 > WAIT_LIMIT_NS) {
+      if (global_timer() - t0 > limit_ns) {
         *abort_flag = 1;
         if (atomicCAS(status, MG_DEV_OK, MG_DEV_WAIT_TIMEOUT) == MG_DEV_OK) status[1] = where;
         return false;
@@ -292,6 +293,24 @@ __device__ __forceinline__ void epilogue_rows(uint32_t taddr, const GemmArgs& g,
   }
 }
 
+// The scales of one 128-row block of B for a whole tile (one per 128 columns of K, at most 128 of
+// them) are fetched once per tile, spread over the lanes of a warp, and handed out by shuffle: a
+// global load per k-block would put an L2 round trip on every k-block's critical path.
+struct TileScales {
+  float v[4];
+  __device__ __forceinline__ void load(const float* row, int n_cols, int lane) {
+#pragma unroll
+    for (int i = 0; i < 4; ++i) v[i] = (i * 32 + lane) < n_cols ? __ldg(row + i * 32 + lane) : 0.f;
+  }
+  __device__ __forceinline__ float get(int col) const {
+    float x = v[0];
+    if (col >= 32) x = v[1];
+    if (col >= 64) x = v[2];
+    if (col >= 96) x = v[3];
+    return __shfl_sync(0xFFFFFFFFu, x, col & 31);
+  }
+};
+
 template <int EPI, bool F8B>
 __global__ void __launch_bounds__(Cfg<F8B>::THREADS, 1)
 grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
@@ -316,7 +335,7 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
   if (threadIdx.x == 0) {
     for (int s = 0; s < STAGES; ++s) { mbar_init(smem_u32(&full[s]), 1); mbar_init(smem_u32(&empty[s]), 1); }
     for (int a = 0; a < 2; ++a) { mbar_init(smem_u32(&tfull[a]), 1); mbar_init(smem_u32(&tempty[a]), 4); }
-    for (int j = 0; j < B_SLOTS; ++j) { mbar_init(smem_u32(&bready[j]), CONVERT_THREADS / 32); mbar_init(smem_u32(&bfree[j]), 1); }
+    for (int j = 0; j < B_SLOTS; ++j) { mbar_init(smem_u32(&bready[j]), CONVERT_THREADS / 64); mbar_init(smem_u32(&bfree[j]), 1); }
     *abort_flag = 0;
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
   }
@@ -397,26 +416,38 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
     }
   } else if (F8B && warp >= 6) {
     // ---------------- FP8 -> bf16 converter (W8A16) ----------------
-    const int ct = threadIdx.x - GEMM_THREADS;          // 0..CONVERT_THREADS-1
+    // Two groups of 4 warps take alternate k-blocks, so each thread pays the per-k-block hand-off
+    // (barrier waits, proxy fence, arrive) half as often; one lane per warp polls the barriers.
+    const int cw = warp - GEMM_THREADS / 32;              // 0..7
+    const uint32_t grp = cw & 1;
+    const int ct = (cw >> 1) * 32 + lane;                 // 0..127 inside the group
     const int units = g.bn * (BK / 16);                   // 16-byte units of the FP8 tile
     uint32_t it = 0;
     for (int tile = blockIdx.x; tile < total_tiles && !*abort_flag; tile += gridDim.x) {
       const Tile t = locate_tile(tile, s_pad, s_cnt, g.n_groups, g.n_tiles, g.n_per_group, g.bn, g.group_m);
       const float* srow = g.scales + static_cast<long long>(t.b_row >> 7) * g.scale_cols;
+      // one scale per 128 rows x 128 columns: rows [0,128) and [128,256) of the tile
       bool ok = true;
       for (int kb = 0; kb < g.k_blocks; ++kb, ++it) {
+        if ((it & 1u) != grp) continue;
         const uint32_t s = it % STAGES, ph = (it / STAGES) & 1u;
         const uint32_t j = it % B_SLOTS, jph = (it / B_SLOTS) & 1u;
-        // one scale per 128 rows x 128 columns: rows [0,128) and [128,256) of the tile
         const float s0 = __ldg(srow + (kb >> 1));
         const float s1 = g.bn > 128 ? __ldg(srow + g.scale_cols + (kb >> 1)) : s0;
-        if (!mbar_wait(smem_u32(&full[s]), ph, abort_flag, g.status, 6)) { ok = false; break; }
-        if (!mbar_wait(smem_u32(&bfree[j]), jph ^ 1u, abort_flag, g.status, 7)) { ok = false; break; }
+        int good = 1;
+        if (lane == 0)
+          good = mbar_wait(smem_u32(&full[s]), ph, abort_flag, g.status, 6) &&
+                 mbar_wait(smem_u32(&bfree[j]), jph ^ 1u, abort_flag, g.status, 7);
+        good = __shfl_sync(0xFFFFFFFFu, good, 0);         // also orders the other lanes after the wait
+        if (!good) { ok = false; break; }
         const uint8_t* src = smem + s * STAGE_BYTES + A_BYTES;
         uint8_t* dst = smem + STAGES * STAGE_BYTES + j * B_BYTES;
 #pragma unroll
-        for (int u = ct; u < units; u += CONVERT_THREADS) {
+        for (int u = ct; u < units; u += CONVERT_THREADS / 2) {
           const int r = u >> 2, c = u & 3;                // row of the tile, 16-byte chunk of its 64 bytes
+#ifdef MG_EXP_F8_NOCONV
+          if (it > 8) continue;                            // experiment: tiles converted only at the start
+#endif
           const uint4 q = *reinterpret_cast<const uint4*>(src + u * 16);
           uint4 lo, hi;
           convert16(q, r < 128 ? s0 : s1, lo, hi);
@@ -426,7 +457,9 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
           *reinterpret_cast<uint4*>(drow + (((2 * c + 1) ^ (r & 7)) << 4)) = hi;
         }
         // make the generic-proxy writes visible to the tensor core's shared-memory reads
+#ifndef MG_EXP_F8_NOFENCE
         asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+#endif
         __syncwarp();
         if (lane == 0) mbar_arrive(smem_u32(&bready[j]));
       }
@@ -481,15 +514,17 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
 // W8A16 on SM pairs (F8B): each CTA receives its B half as FP8 bytes and its 8 converter warps
 // write the bf16 half tile; both CTAs' converters arrive on the leader's bready[j]; full[s] is
 // then local to each CTA (its own A and FP8 bytes), because its converters must wait on it.
-constexpr int STAGES2 = 6;
+constexpr int STAGES2_MAX = 6;                          // bf16: 6 stages of 32 KiB; W8A16: 5 of 24 KiB
 constexpr int B2_BYTES = 128 * BK * 2;                  // this CTA's half of the B tile, bf16
 constexpr int B2F8_BYTES = 128 * BK;                    // the same half as FP8 bytes
-constexpr int B2_SLOTS = 3;                             // converted half tiles in flight
-constexpr int NUM_BARS2 = 2 * STAGES2 + 4 + 2 * B2_SLOTS;
+constexpr int B2_SLOTS = 6;                             // converted half tiles in flight: the hand-off
+                                                        // crosses the SM pair, so it needs depth
+constexpr int NUM_BARS2 = 2 * STAGES2_MAX + 4 + 2 * B2_SLOTS;
 template <bool F8B>
 struct Cfg2 {
   static constexpr int STAGE_BYTES = A_BYTES + (F8B ? B2F8_BYTES : B2_BYTES);      // 24 / 32 KiB
-  static constexpr int RING_BYTES = STAGES2 * STAGE_BYTES + (F8B ? B2_SLOTS * B2_BYTES : 0);
+  static constexpr int STAGES = F8B ? 5 : 6;
+  static constexpr int RING_BYTES = STAGES * STAGE_BYTES + (F8B ? B2_SLOTS * B2_BYTES : 0);
   static constexpr int THREADS = GEMM_THREADS + (F8B ? CONVERT_THREADS : 0);
 };
 constexpr size_t SMEM2_CTRL_BYTES = 8 * NUM_BARS2 + 16 + 4 * (3 * kMaxExperts + 3);
@@ -573,15 +608,16 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(Cfg2<F8B>::THREADS, 
 grouped_gemm2_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
                      const GemmArgs g) {
   constexpr int STAGE2_BYTES = Cfg2<F8B>::STAGE_BYTES;
+  constexpr int STAGES2 = Cfg2<F8B>::STAGES;
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
   uint64_t* bars = reinterpret_cast<uint64_t*>(smem + Cfg2<F8B>::RING_BYTES);
   uint64_t* full = bars;
-  uint64_t* empty = bars + STAGES2;
-  uint64_t* tfull = bars + 2 * STAGES2;
-  uint64_t* tempty = bars + 2 * STAGES2 + 2;
-  uint64_t* bready = bars + 2 * STAGES2 + 4;               // leader: both CTAs' converters arrive
-  uint64_t* bfree = bars + 2 * STAGES2 + 4 + B2_SLOTS;     // per CTA, via the leader's commit
+  uint64_t* empty = bars + STAGES2_MAX;
+  uint64_t* tfull = bars + 2 * STAGES2_MAX;
+  uint64_t* tempty = bars + 2 * STAGES2_MAX + 2;
+  uint64_t* bready = bars + 2 * STAGES2_MAX + 4;               // leader: both CTAs' converters arrive
+  uint64_t* bfree = bars + 2 * STAGES2_MAX + 4 + B2_SLOTS;     // per CTA, via the leader's commit
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + NUM_BARS2);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
   int* s_pad = reinterpret_cast<int*>(tmem_slot + 4);
@@ -596,7 +632,7 @@ grouped_gemm2_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_const
     for (int s = 0; s < STAGES2; ++s) { mbar_init(smem_u32(&full[s]), 1); mbar_init(smem_u32(&empty[s]), 1); }
     for (int a = 0; a < 2; ++a) { mbar_init(smem_u32(&tfull[a]), 1); mbar_init(smem_u32(&tempty[a]), 8); }
     for (int j = 0; j < B2_SLOTS; ++j) {
-      mbar_init(smem_u32(&bready[j]), 2 * (CONVERT_THREADS / 32));
+      mbar_init(smem_u32(&bready[j]), 2 * (CONVERT_THREADS / 64));   // 4 warps of the k-block's group, both CTAs
       mbar_init(smem_u32(&bfree[j]), 1);
     }
     *abort_flag = 0;
@@ -691,24 +727,37 @@ grouped_gemm2_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_const
     }
   } else if (F8B && warp >= 6) {
     // ---------------- FP8 -> bf16 converter (both CTAs, own half of B) ----------------
-    const int ct = threadIdx.x - GEMM_THREADS;
+    // two groups of 4 warps take alternate k-blocks; one lane per warp polls the barriers
+    const int cw = warp - GEMM_THREADS / 32;
+    const uint32_t grp = cw & 1;
+    const int ct = (cw >> 1) * 32 + lane;
     uint32_t it = 0;
     for (int tile = pair; tile < total_tiles && !*abort_flag; tile += n_pairs) {
       const Tile2 t = locate_tile2(tile, s_pad, s_cnt, s_pp, g.n_groups, g.n_tiles, g.n_per_group);
       // the half tile is 128 rows = one scale block row
       const float* srow = g.scales + static_cast<long long>((t.b_row >> 7) + static_cast<int>(rank)) * g.scale_cols;
+      TileScales scs;
+      scs.load(srow, g.scale_cols, lane);
       bool ok = true;
       for (int kb = 0; kb < g.k_blocks; ++kb, ++it) {
+        if ((it & 1u) != grp) continue;
         const uint32_t s = it % STAGES2, ph = (it / STAGES2) & 1u;
         const uint32_t j = it % B2_SLOTS, jph = (it / B2_SLOTS) & 1u;
-        const float sc = __ldg(srow + (kb >> 1));
-        if (!mbar_wait(smem_u32(&full[s]), ph, abort_flag, g.status, 16)) { ok = false; break; }
-        if (!mbar_wait(smem_u32(&bfree[j]), jph ^ 1u, abort_flag, g.status, 17)) { ok = false; break; }
+        const float sc = scs.get(kb >> 1);
+        int good = 1;
+        if (lane == 0)
+          good = mbar_wait(smem_u32(&full[s]), ph, abort_flag, g.status, 16) &&
+                 mbar_wait(smem_u32(&bfree[j]), jph ^ 1u, abort_flag, g.status, 17);
+        good = __shfl_sync(0xFFFFFFFFu, good, 0);
+        if (!good) { ok = false; break; }
         const uint8_t* src = smem + s * STAGE2_BYTES + A_BYTES;
         uint8_t* dst = smem + STAGES2 * STAGE2_BYTES + j * B2_BYTES;
 #pragma unroll
-        for (int u = ct; u < 128 * (BK / 16); u += CONVERT_THREADS) {
+        for (int u = ct; u < 128 * (BK / 16); u += CONVERT_THREADS / 2) {
           const int r = u >> 2, c = u & 3;
+#ifdef MG_EXP_F8_NOCONV
+          if (it > 8) continue;                            // experiment: tiles converted only at the start
+#endif
           const uint4 q = *reinterpret_cast<const uint4*>(src + u * 16);
           uint4 lo, hi;
           convert16(q, sc, lo, hi);
@@ -753,6 +802,25 @@ grouped_gemm2_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_const
     asm volatile("tcgen05.dealloc.cta_group::2.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(TMEM_COLS)
                  : "memory");
   }
+}
+
+// Self-test of the bounded wait: one thread waits on a barrier that nothing will ever complete,
+// with a short limit; the wait must give up, record MG_DEV_WAIT_TIMEOUT and let the kernel end.
+__global__ void wait_probe_kernel(unsigned long long limit_ns, int32_t* status) {
+  __shared__ uint64_t bar;
+  __shared__ int abort_flag;
+  if (threadIdx.x == 0) {
+    mbar_init(smem_u32(&bar), 1);
+    abort_flag = 0;
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    mbar_wait(smem_u32(&bar), 0, &abort_flag, status, 99, limit_ns);
+  }
+}
+
+int launch_wait_probe(const Handle* h, int limit_ms, cudaStream_t st) {
+  wait_probe_kernel<<<1, 32, 0, st>>>(static_cast<unsigned long long>(limit_ms) * 1000000ull, h->d_status);
+  MG_CUDA(cudaGetLastError());
+  return MG_OK;
 }
 
 // ---- host side ------------------------------------------------------------------------
@@ -842,8 +910,8 @@ int launch_grouped_gemm(const Handle* h, const GemmProblem& p, cudaStream_t st) 
                  pair ? 128 : bn, p.b_fp8);
   if (rc != MG_OK) return rc;
   if (p.b_fp8) {
-    MG_REQUIRE(!f32_out && p.scales != nullptr && p.K % 128 == 0, MG_ERR_SHAPE,
-               "FP8 weights need scales, K a multiple of 128 and a bf16 epilogue");
+    MG_REQUIRE(!f32_out && p.scales != nullptr && p.K % 128 == 0 && p.K <= 128 * 128, MG_ERR_SHAPE,
+               "FP8 weights need scales, K a multiple of 128 up to 16384 and a bf16 epilogue");
   }
 
   GemmArgs a;

@@ -67,7 +67,7 @@ class EPMoELayer:
     PHASES = ["route_dispatch", "expert_ffn", "combine"]
 
     def __init__(self, layer: MoELayer, group: Optional[dist.ProcessGroup] = None, capacity_factor: float = 2.0,
-                 n_micro: int = 2):
+                 n_micro: int = 1):
         self.layer = layer
         self.group = group
         self.rank = dist.get_rank(group)

@@ -425,3 +425,23 @@ def test_patched_reference_style_module(built_lib):
     assert y.shape == (2, 32, 256)
     gold = O.layer_forward(spec, x, W, gold_fp32=True)
     assert O.rel_l2(y.view(64, 256).cpu().float(), gold["y"]) <= TOL_LAYER
+
+
+def test_bounded_wait_gives_up_and_reports(built_lib):
+    """Failure detection without a fault: a wait that nothing satisfies runs out after its limit,
+    the kernel returns, the status word says so, and the context keeps working."""
+    import time
+    spec = O.LayerSpec(256, 128, 8, 2)
+    x, W = O.make_inputs(spec, 64, 1)
+    layer = make_layer(spec, W, DEV)
+    t0 = time.time()
+    rc = layer.lib.mg_selftest_wait_timeout(layer._h, 50, torch.cuda.current_stream().cuda_stream)
+    assert rc == 0
+    torch.cuda.synchronize()
+    assert 0.04 < time.time() - t0 < 5.0
+    assert layer.device_status() == (1, 99)          # MG_DEV_WAIT_TIMEOUT, where = 99
+    assert layer.device_status() == (0, 0)           # reading clears it
+    y = layer.forward(x.to(DEV))                     # the context is intact
+    torch.cuda.synchronize()
+    assert layer.device_status() == (0, 0)
+    assert O.rel_l2(y.cpu().float(), O.layer_forward(spec, x, W, gold_fp32=True)["y"]) <= TOL_LAYER
