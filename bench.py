@@ -221,6 +221,52 @@ def cpu_reference(name: str, t_sample: int, steps: int, warmup: int, zipf=0.0):
 
 
 # --------------------------------------------------------------------------------------
+# correctness gate printed beside the timing (single GPU): a few tokens recomputed with plain
+# torch fp32 ops on the device from the same seeded weights
+# --------------------------------------------------------------------------------------
+def sample_check(name: str, layer, x: torch.Tensor, y: torch.Tensor, zipf: float, n_tokens: int = 4):
+    import torch.nn.functional as F
+    H, I, E, k, Is, G, keep, gating, norm, scale, wfmt, comb, _, seed = WORKLOADS[name]
+    dev = x.device
+    T = x.shape[0]
+    idx, w = layer.route_topk(layer.gate_logits(x))
+    # routing from fp32 (CUDA-core) logits, as the reference computes them
+    if gating == 3:
+        lg = F.linear(x, layer.gate_w).float()
+    else:
+        lg = F.linear(x.float(), layer.gate_w.float())
+    idx2, _ = layer.route_topk(lg.contiguous())
+    differ = int((idx.sort(1).values != idx2.sort(1).values).any(1).sum())
+    ge = torch.Generator(device=dev)
+
+    def mats_of(e):
+        ge.manual_seed(seed * 100003 + e)
+        mats = [(torch.randn(r, c, generator=ge, device=dev) * 0.02).to(torch.bfloat16)
+                for r, c in ((I, H), (I, H), (H, I))]
+        if wfmt == 1:
+            mats = [layer.dequant_fp8(*quantize_fp8_block128_gpu(m)) for m in mats]
+        return [m.float() for m in mats]
+
+    def mlp(xt, g_, u_, d_):
+        return F.linear(F.silu(F.linear(xt, g_)) * F.linear(xt, u_), d_)
+
+    shared = None
+    if Is:
+        ge.manual_seed(seed * 100003 + 99991)
+        shared = [(torch.randn(r, c, generator=ge, device=dev) * 0.02).to(torch.bfloat16).float()
+                  for r, c in ((Is, H), (Is, H), (H, Is))]
+    worst = 0.0
+    for t in [int(v) for v in torch.linspace(0, T - 1, n_tokens)]:
+        xt = x[t:t + 1].float()
+        ref = mlp(xt, *shared) if shared else torch.zeros(1, H, device=dev)
+        for j in range(k):
+            ref = ref + float(w[t, j]) * mlp(xt, *mats_of(int(idx[t, j])))
+        err = float((y[t:t + 1].float() - ref).norm() / ref.norm())
+        worst = max(worst, err)
+    return {"sampled_tokens": n_tokens, "worst_rel_l2_vs_torch_fp32": worst, "tolerance": 1e-2,
+            "tokens_routed_differently_from_fp32_logits": differ, "tokens": T}
+
+
 def algorithmic(name: str, T: int):
     H, I, E, k, Is = WORKLOADS[name][:5]
     R = T * k
@@ -246,6 +292,7 @@ def main():
     ap.add_argument("--cpu-sample-tokens", type=int, default=4096)
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-e2e", action="store_true")
+    ap.add_argument("--no-check", action="store_true")
     ap.add_argument("--chunk-tokens", type=int, default=16384)
     ap.add_argument("--micro", type=int, default=1, help="token micro-batches pipelined in the expert-parallel forward")
     ap.add_argument("--pair-gemm", type=int, default=-1, help="1/0 force the SM-pair expert GEMM on/off")
@@ -462,6 +509,11 @@ def main():
         stages["note"] = (f"phases of the first of {len(layer._mbs)} pipelined micro-batches on its stream; "
                           f"each rank sends and later fetches {Tl * k * H * 2 * (world - 1) / world / 1e6:.0f} MB over NVLink per step")
 
+    check = None
+    if world == 1 and not args.no_check:
+        check = sample_check(name, layer, x, y, args.zipf)
+        if check["worst_rel_l2_vs_torch_fp32"] > 1e-2:
+            raise SystemExit(f"correctness gate failed: {check}")
     cpu = None
     if not args.no_cpu_baseline:
         r = cpu_reference(name, min(args.cpu_sample_tokens, T), 2, 1, args.zipf)
@@ -472,7 +524,7 @@ def main():
            "warmup": warmup, "ms_per_step": ms_per_step, "higher_is_better": True, "scaling": "strong",
            "vs_baseline": None, "dtype": "bf16", "data": "synthetic", "config": config, "clocks": clocks,
            "e2e": e2e, "gpu_launches": launches * args.steps, "roofline": roofline, "cpu_baseline": cpu,
-           "stages": stages,
+           "stages": stages, "check": check,
            "layer_tflops": (alg["gemm1_flops"] + alg["gemm2_flops"] + alg["shared_flops"] + alg["gate_flops"])
            / (ms_per_step * 1e-3) / 1e12 / world}
     print(json.dumps(out), flush=True)
