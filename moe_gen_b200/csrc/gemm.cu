@@ -232,10 +232,18 @@ __device__ __forceinline__ void epilogue_rows(uint32_t taddr, const GemmArgs& g,
     __nv_bfloat16* orow = static_cast<__nv_bfloat16*>(g.out) + row * g.ldo + static_cast<long long>(n_idx) * half;
     for (int c = 0; c < half; c += 32) {
       uint32_t gr[32], ur[32];
+#ifdef MG_EXP_EPI_NOLOAD
+      for (int i = 0; i < 32; ++i) { gr[i] = c + i; ur[i] = c - i; }
+#else
       tc_ld32(taddr + c, gr);
       tc_ld32(taddr + half + c, ur);
       tc_ld_wait();
+#endif
+#ifdef MG_EXP_EPI_NOSTORE
+      if (live && gr[5] == 0x7fc12345u) {
+#else
       if (live) {
+#endif
         uint32_t packed[16];
 #pragma unroll
         for (int i = 0; i < 16; ++i) {
@@ -253,9 +261,17 @@ __device__ __forceinline__ void epilogue_rows(uint32_t taddr, const GemmArgs& g,
     __nv_bfloat16* orow = static_cast<__nv_bfloat16*>(g.out) + row * g.ldo + static_cast<long long>(n_idx) * g.bn;
     for (int c = 0; c < g.bn; c += 32) {
       uint32_t r[32];
+#ifdef MG_EXP_EPI_NOLOAD
+      for (int i = 0; i < 32; ++i) r[i] = c + i;
+#else
       tc_ld32(taddr + c, r);
       tc_ld_wait();
+#endif
+#ifdef MG_EXP_EPI_NOSTORE
+      if (live && r[5] == 0x7fc12345u) {
+#else
       if (live) {
+#endif
         uint32_t packed[16];
 #pragma unroll
         for (int i = 0; i < 16; ++i) {

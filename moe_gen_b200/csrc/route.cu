@@ -516,26 +516,48 @@ __global__ void __launch_bounds__(256) combine_kernel(PeerPtrs bufs,
       if (rj == lane) order_src = j;
     }
   }
+  // per pick: weight and the address of its row (nullptr = skipped pick), in the order of the adds
+  const uint4* base[kMaxTopK];
+  float wj[kMaxTopK];
+#pragma unroll
+  for (int s = 0; s < kMaxTopK; ++s) {
+    const int j = (MODE == MG_COMBINE_BF16_SEQ ? __shfl_sync(0xFFFFFFFFu, order_src, s & 31) : s) & 31;
+    const int32_t d = __shfl_sync(0xFFFFFFFFu, my_dst, j);
+    const float w = __shfl_sync(0xFFFFFFFFu, my_w, j);
+    const bool use = s < k && d >= 0;
+    wj[s] = use ? w : 0.f;
+    const uint4* rows = static_cast<const uint4*>(PEER ? bufs.p[use ? (d >> kPeerShift) : 0] : bufs.p[0]);
+    base[s] = use ? rows + static_cast<int64_t>(PEER ? (d & kPeerRowMask) : d) * vec_per_row : nullptr;
+  }
   for (int v = lane; v < vec_per_row; v += 32) {
     float acc[8];
 #pragma unroll
     for (int i = 0; i < 8; ++i) acc[i] = 0.f;
-    for (int step = 0; step < k; ++step) {
-      int j = MODE == MG_COMBINE_BF16_SEQ ? __shfl_sync(0xFFFFFFFFu, order_src, step) : step;
-      int32_t d = __shfl_sync(0xFFFFFFFFu, my_dst, j);
-      float w = __shfl_sync(0xFFFFFFFFu, my_w, j);
-      if (d < 0) continue;
-      float f[8];
-      const uint4* rows = static_cast<const uint4*>(PEER ? bufs.p[d >> kPeerShift] : bufs.p[0]);
-      const int64_t r = PEER ? (d & kPeerRowMask) : d;
-      // peer rows are written by another GPU during this forward: plain (coherent) loads
-      unpack8(PEER ? rows[r * vec_per_row + v] : __ldg(rows + r * vec_per_row + v), f);
 #pragma unroll
-      for (int i = 0; i < 8; ++i) {
-        float p = __fmul_rn(f[i], w);
-        if (MODE == MG_COMBINE_FP32) acc[i] = __fadd_rn(acc[i], p);
-        else if (MODE == MG_COMBINE_BF16_PROD) acc[i] = __fadd_rn(acc[i], round_bf16(p));
-        else acc[i] = round_bf16(__fadd_rn(acc[i], round_bf16(p)));
+    for (int s0 = 0; s0 < kMaxTopK; s0 += 4) {
+      if (s0 < k) {
+        // four row loads in flight before the first is consumed
+        uint4 val[4];
+#pragma unroll
+        for (int u = 0; u < 4; ++u) {
+          val[u] = make_uint4(0u, 0u, 0u, 0u);
+          // peer rows are written by another GPU during this forward: plain (coherent) loads
+          if (base[s0 + u] != nullptr) val[u] = PEER ? base[s0 + u][v] : __ldg(base[s0 + u] + v);
+        }
+#pragma unroll
+        for (int u = 0; u < 4; ++u) {
+          float f[8];
+          unpack8(val[u], f);
+          const float w = wj[s0 + u];
+#pragma unroll
+          for (int i = 0; i < 8; ++i) {
+            // a skipped pick contributes w = 0 and f = 0: adding 0 changes nothing in any mode
+            float p = __fmul_rn(f[i], w);
+            if (MODE == MG_COMBINE_FP32) acc[i] = __fadd_rn(acc[i], p);
+            else if (MODE == MG_COMBINE_BF16_PROD) acc[i] = __fadd_rn(acc[i], round_bf16(p));
+            else acc[i] = round_bf16(__fadd_rn(acc[i], round_bf16(p)));
+          }
+        }
       }
     }
     if (shared != nullptr) {

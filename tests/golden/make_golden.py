@@ -1,9 +1,9 @@
 """Generate the golden fixtures in this folder from the reference itself.
 
-Run where the MoE-Gen reference tree is available (its root is passed with
---reference, default /root/reference):
+Run where the MoE-Gen reference tree is available; its root is passed with --reference
+(or the MOEGEN_REFERENCE environment variable):
 
-    PYTHONDONTWRITEBYTECODE=1 python tests/golden/make_golden.py
+    PYTHONDONTWRITEBYTECODE=1 python tests/golden/make_golden.py --reference <MoE-Gen checkout>
 
 What it does, per case:
   1. draws the seeded synthetic inputs (oracle.moe_oracle.make_inputs);
@@ -116,7 +116,7 @@ def build_ref_module(spec: O.LayerSpec, W: O.LayerWeights, v2, v3, C2, C3):
 
 def main():
     ap = argparse.ArgumentParser()
-    ap.add_argument("--reference", default="/root/reference")
+    ap.add_argument("--reference", default=os.environ.get("MOEGEN_REFERENCE"), required="MOEGEN_REFERENCE" not in os.environ)
     args = ap.parse_args()
     v2, v3, C2, C3, ref_dequant = load_reference(args.reference)
     torch.set_num_threads(max(1, os.cpu_count() or 1))

@@ -445,3 +445,71 @@ def test_bounded_wait_gives_up_and_reports(built_lib):
     torch.cuda.synchronize()
     assert layer.device_status() == (0, 0)
     assert O.rel_l2(y.cpu().float(), O.layer_forward(spec, x, W, gold_fp32=True)["y"]) <= TOL_LAYER
+
+
+@pytest.mark.parametrize("n_ranks", [2, 4])
+def test_expert_parallel_ranks_emulated_on_one_gpu(built_lib, n_ranks):
+    """The expert-parallel kernels (layout, peer scatter, peer gather) run for every rank in turn in
+    one process, the 'peer' buffers being ordinary allocations of this GPU.  The result must equal
+    the single-GPU forward bit for bit, and the layout must equal its host restatement."""
+    import ctypes as C
+    from moe_gen_b200 import lib as L
+    from moe_gen_b200.ep import ep_layout_reference
+    spec = O.LayerSpec(256, 128, 32, 4, 128, 4, 2, O.GATE_SIGMOID_NOAUX_TC, True, 2.5, O.WEIGHT_FP8_BLOCK128,
+                       O.COMBINE_FP32)
+    T = 120 * n_ranks
+    x, W = O.make_inputs(spec, T, 71)
+    xd = x.to(DEV)
+    full = make_layer(spec, W, DEV)
+    y_ref = full.forward(xd).cpu()
+    Tl, E, El, k, H = T // n_ranks, 32, 32 // n_ranks, 4, 256
+    ranks = [make_layer(spec, W, DEV, r, n_ranks) for r in range(n_ranks)]
+    lib = ranks[0].lib
+    st = torch.cuda.current_stream().cuda_stream
+    cap = ((T * k + 127) // 128 + El) * 128
+    recv = [torch.zeros(cap, H, dtype=torch.bfloat16, device=DEV) for _ in range(n_ranks)]
+    outb = [torch.zeros(cap, H, dtype=torch.bfloat16, device=DEV) for _ in range(n_ranks)]
+    peer_recv = (C.c_void_p * n_ranks)(*[t.data_ptr() for t in recv])
+    peer_out = (C.c_void_p * n_ranks)(*[t.data_ptr() for t in outb])
+    i32 = dict(dtype=torch.int32, device=DEV)
+    idx, w, counts, plan_ws = [], [], [], []
+    for r, lay in enumerate(ranks):
+        xs = xd[r * Tl:(r + 1) * Tl]
+        i_, w_ = lay.route_topk(lay.gate_logits(xs))
+        nb = C.c_size_t()
+        L.check(lib.mg_plan_ws_bytes(lay._h, Tl, C.byref(nb)))
+        ws = torch.empty(nb.value, dtype=torch.uint8, device=DEV)
+        c = torch.empty(E, **i32)
+        L.check(lib.mg_ep_count(lay._h, i_.data_ptr(), Tl, c.data_ptr(), ws.data_ptr(), st))
+        idx.append(i_); w.append(w_); counts.append(c); plan_ws.append(ws)
+    counts_all = torch.stack(counts).contiguous()
+    dst, rc, rp = [], [], []
+    for r, lay in enumerate(ranks):
+        d = torch.empty(Tl, k, **i32); c = torch.empty(El, **i32); p = torch.empty(El + 1, **i32)
+        L.check(lib.mg_ep_place(lay._h, idx[r].data_ptr(), Tl, counts_all.data_ptr(), cap, plan_ws[r].data_ptr(),
+                                c.data_ptr(), p.data_ptr(), d.data_ptr(), st))
+        L.check(lib.mg_ep_dispatch(lay._h, xd[r * Tl:(r + 1) * Tl].data_ptr(), d.data_ptr(), Tl, peer_recv, st))
+        dst.append(d); rc.append(c); rp.append(p)
+        base, ref_c, ref_p, over = ep_layout_reference(counts_all.cpu().numpy(), r, El, cap)
+        assert not over.any()
+        assert np.array_equal(c.cpu().numpy(), ref_c) and np.array_equal(p.cpu().numpy(), ref_p)
+        # first row of every expert's run on this rank equals the host layout
+        flat_idx, flat_dst = idx[r].cpu().view(-1).long(), d.cpu().view(-1).long()
+        for e in flat_idx.unique().tolist():
+            assert int(flat_dst[flat_idx == e].min()) == int(base[e])
+    for r, lay in enumerate(ranks):
+        hb = torch.zeros(cap, spec.inter, dtype=torch.bfloat16, device=DEV)
+        L.check(lib.mg_expert_ffn(lay._h, recv[r].data_ptr(), rp[r].data_ptr(), rc[r].data_ptr(), cap,
+                                  lay.packed.data_ptr(), hb.data_ptr(), outb[r].data_ptr(), None, st))
+    ys = []
+    for r, lay in enumerate(ranks):
+        xs = xd[r * Tl:(r + 1) * Tl]
+        sh = lay.shared_ffn(xs)
+        y = torch.empty(Tl, H, dtype=torch.bfloat16, device=DEV)
+        L.check(lib.mg_ep_combine(lay._h, peer_out, dst[r].data_ptr(), idx[r].data_ptr(), w[r].data_ptr(),
+                                  sh.data_ptr(), Tl, y.data_ptr(), st))
+        ys.append(y)
+    torch.cuda.synchronize()
+    for lay in ranks:
+        assert lay.device_status() == (0, 0)
+    assert torch.equal(torch.cat(ys).cpu().view(torch.int16), y_ref.view(torch.int16))
