@@ -66,7 +66,7 @@ struct GemmArgs {
 
 constexpr size_t SMEM_CTRL_BYTES = 8 * NUM_BARS + 16 + 4 * (2 * kMaxExperts + 2);
 template <bool F8B>
-constexpr size_t gemm_smem_bytes() { return 1024 + Cfg<F8B>::RING_BYTES + SMEM_CTRL_BYTES; }
+constexpr size_t gemm_smem_bytes() { return 1024 + Cfg<F8B>::RING_BYTES + SMEM_CTRL_BYTES + 128 + 4 * 2 * 2048; }
 
 // ---- PTX wrappers ---------------------------------------------------------------------
 __device__ __forceinline__ uint32_t smem_u32(const void* p) {
@@ -223,68 +223,84 @@ __device__ __forceinline__ void convert16(const uint4& q, float s, uint4& lo, ui
   hi = make_uint4(o[4], o[5], o[6], o[7]);
 }
 
-// One thread = one accumulator row (TMEM lane): read it in 32-column pieces, apply the epilogue,
-// store 64-byte (bf16) or 128-byte (fp32) runs.
+// ---- epilogue ---------------------------------------------------------------------------
+// bf16 outputs leave through shared memory: each epilogue warp owns 32 rows, writes a 32-row x
+// 32-column piece (2 KiB) into one of its two staging buffers and one lane hands it to TMA
+// (cp.async.bulk.tensor store), so the global writes are full lines issued asynchronously
+// instead of 64-byte runs per thread.  Rows of a piece that lie in an expert's padding are
+// written too (they belong to nobody); rows beyond the tensor are clipped by TMA.
+constexpr int EPI_PIECE_BYTES = 32 * 64;                 // 32 rows x 32 bf16
+constexpr int EPI_STAGE_BYTES = 4 * 2 * EPI_PIECE_BYTES; // 4 warps x 2 buffers
+
+__device__ __forceinline__ void tma_store_2d(const CUtensorMap* map, int c0, int c1, uint32_t src) {
+  asm volatile("cp.async.bulk.tensor.2d.global.shared::cta.bulk_group [%0, {%1, %2}], [%3];" ::"l"(map), "r"(c0),
+               "r"(c1), "r"(src)
+               : "memory");
+  asm volatile("cp.async.bulk.commit_group;" ::: "memory");
+}
+
+struct EpiWarp {
+  uint8_t* stage;      // this warp's two staging buffers
+  uint32_t pieces;     // pieces issued so far (selects the buffer)
+  int lane;
+};
+
+// stores 32 bf16 (packed[16]) of this thread's row as one row of the warp's piece and sends it
+__device__ __forceinline__ void send_piece(EpiWarp& w, const CUtensorMap* tmC, const uint32_t* packed, int col0,
+                                           int row_first, bool warp_live) {
+  if (!warp_live) return;                                // uniform per warp
+  uint8_t* buf = w.stage + (w.pieces & 1u) * EPI_PIECE_BYTES;
+  // the store issued two pieces ago has finished reading this buffer
+  if (w.lane == 0) asm volatile("cp.async.bulk.wait_group.read 1;" ::: "memory");
+  __syncwarp();
+  uint4* dst = reinterpret_cast<uint4*>(buf + w.lane * 64);
+#pragma unroll
+  for (int i = 0; i < 4; ++i)
+    dst[i] = make_uint4(packed[4 * i], packed[4 * i + 1], packed[4 * i + 2], packed[4 * i + 3]);
+  asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+  __syncwarp();
+  if (w.lane == 0) tma_store_2d(tmC, col0, row_first, smem_u32(buf));
+  ++w.pieces;
+}
+
+// One thread = one accumulator row (TMEM lane): read it in 32-column pieces, apply the epilogue.
+// `row` is this thread's global row, `row_first` the first row of its warp, `live` whether the
+// row belongs to the expert, `warp_live` whether any row of the warp does.
 template <int EPI>
-__device__ __forceinline__ void epilogue_rows(uint32_t taddr, const GemmArgs& g, long long row, int n_idx, bool live) {
+__device__ __forceinline__ void epilogue_rows(uint32_t taddr, const GemmArgs& g, const CUtensorMap* tmC, EpiWarp& w,
+                                              long long row, int row_first, int n_idx, bool live, bool warp_live) {
   if (EPI == EPI_SWIGLU_BF16) {
     const int half = g.bn >> 1;
-    __nv_bfloat16* orow = static_cast<__nv_bfloat16*>(g.out) + row * g.ldo + static_cast<long long>(n_idx) * half;
     for (int c = 0; c < half; c += 32) {
       uint32_t gr[32], ur[32];
-#ifdef MG_EXP_EPI_NOLOAD
-      for (int i = 0; i < 32; ++i) { gr[i] = c + i; ur[i] = c - i; }
-#else
       tc_ld32(taddr + c, gr);
       tc_ld32(taddr + half + c, ur);
       tc_ld_wait();
-#endif
-#ifdef MG_EXP_EPI_NOSTORE
-      if (live && gr[5] == 0x7fc12345u) {
-#else
-      if (live) {
-#endif
-        uint32_t packed[16];
+      uint32_t packed[16];
 #pragma unroll
-        for (int i = 0; i < 16; ++i) {
-          float h0 = silu_f(__uint_as_float(gr[2 * i])) * __uint_as_float(ur[2 * i]);
-          float h1 = silu_f(__uint_as_float(gr[2 * i + 1])) * __uint_as_float(ur[2 * i + 1]);
-          __nv_bfloat162 b = __floats2bfloat162_rn(h0, h1);
-          packed[i] = *reinterpret_cast<uint32_t*>(&b);
-        }
-        uint4* dst = reinterpret_cast<uint4*>(orow + c);
-#pragma unroll
-        for (int i = 0; i < 4; ++i) dst[i] = make_uint4(packed[4 * i], packed[4 * i + 1], packed[4 * i + 2], packed[4 * i + 3]);
+      for (int i = 0; i < 16; ++i) {
+        float h0 = silu_f(__uint_as_float(gr[2 * i])) * __uint_as_float(ur[2 * i]);
+        float h1 = silu_f(__uint_as_float(gr[2 * i + 1])) * __uint_as_float(ur[2 * i + 1]);
+        __nv_bfloat162 b2 = __floats2bfloat162_rn(h0, h1);
+        packed[i] = *reinterpret_cast<uint32_t*>(&b2);
       }
+      send_piece(w, tmC, packed, n_idx * half + c, row_first, warp_live);
     }
   } else if (EPI == EPI_PLAIN_BF16) {
-    __nv_bfloat16* orow = static_cast<__nv_bfloat16*>(g.out) + row * g.ldo + static_cast<long long>(n_idx) * g.bn;
     for (int c = 0; c < g.bn; c += 32) {
       uint32_t r[32];
-#ifdef MG_EXP_EPI_NOLOAD
-      for (int i = 0; i < 32; ++i) r[i] = c + i;
-#else
       tc_ld32(taddr + c, r);
       tc_ld_wait();
-#endif
-#ifdef MG_EXP_EPI_NOSTORE
-      if (live && r[5] == 0x7fc12345u) {
-#else
-      if (live) {
-#endif
-        uint32_t packed[16];
+      uint32_t packed[16];
 #pragma unroll
-        for (int i = 0; i < 16; ++i) {
-          __nv_bfloat162 b = __floats2bfloat162_rn(__uint_as_float(r[2 * i]), __uint_as_float(r[2 * i + 1]));
-          packed[i] = *reinterpret_cast<uint32_t*>(&b);
-        }
-        uint4* dst = reinterpret_cast<uint4*>(orow + c);
-#pragma unroll
-        for (int i = 0; i < 4; ++i) dst[i] = make_uint4(packed[4 * i], packed[4 * i + 1], packed[4 * i + 2], packed[4 * i + 3]);
+      for (int i = 0; i < 16; ++i) {
+        __nv_bfloat162 b2 = __floats2bfloat162_rn(__uint_as_float(r[2 * i]), __uint_as_float(r[2 * i + 1]));
+        packed[i] = *reinterpret_cast<uint32_t*>(&b2);
       }
+      send_piece(w, tmC, packed, n_idx * g.bn + c, row_first, warp_live);
     }
   } else {
-    // fp32 output, N = n_per_group columns in one tile (the router logits)
+    // fp32 output, N = n_per_group columns in one tile (the router logits): direct stores
     float* orow = static_cast<float*>(g.out) + row * g.ldo;
     for (int c = 0; c < g.n_per_group; c += 32) {
       uint32_t r[32];
@@ -309,6 +325,12 @@ __device__ __forceinline__ void epilogue_rows(uint32_t taddr, const GemmArgs& g,
   }
 }
 
+// all stores of this warp have left shared memory and reached global memory
+__device__ __forceinline__ void epilogue_drain(const EpiWarp& w) {
+  if (w.lane == 0) asm volatile("cp.async.bulk.wait_group 0;" ::: "memory");
+  __syncwarp();
+}
+
 // The scales of one 128-row block of B for a whole tile (one per 128 columns of K, at most 128 of
 // them) are fetched once per tile, spread over the lanes of a warp, and handed out by shuffle: a
 // global load per k-block would put an L2 round trip on every k-block's critical path.
@@ -330,7 +352,7 @@ struct TileScales {
 template <int EPI, bool F8B>
 __global__ void __launch_bounds__(Cfg<F8B>::THREADS, 1)
 grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
-                    const GemmArgs g) {
+                    const __grid_constant__ CUtensorMap tmC, const GemmArgs g) {
   constexpr int STAGE_BYTES = Cfg<F8B>::STAGE_BYTES;
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
@@ -345,6 +367,8 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
   int* s_pad = reinterpret_cast<int*>(tmem_slot + 4);
   int* s_cnt = s_pad + kMaxExperts + 1;
+  uint8_t* epi_stage = reinterpret_cast<uint8_t*>(
+      (reinterpret_cast<uintptr_t>(smem + Cfg<F8B>::RING_BYTES + SMEM_CTRL_BYTES) + 127) & ~uintptr_t(127));
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
 
@@ -485,6 +509,7 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
     // ---------------- epilogue ----------------
     const int quarter = warp & 3;             // TMEM lanes [32*quarter, 32*quarter+32)
     const int row_in_tile = quarter * 32 + lane;
+    EpiWarp ew{epi_stage + quarter * 2 * EPI_PIECE_BYTES, 0u, lane};
     uint32_t tcount = 0;
     for (int tile = blockIdx.x; tile < total_tiles && !*abort_flag; tile += gridDim.x, ++tcount) {
       const Tile t = locate_tile(tile, s_pad, s_cnt, g.n_groups, g.n_tiles, g.n_per_group, g.bn, g.group_m);
@@ -495,13 +520,14 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
       const bool live = row_in_tile < t.valid_rows;
       const long long row = static_cast<long long>(t.row0) + row_in_tile;
 #ifndef MG_EXP_NO_EPI
-      epilogue_rows<EPI>(taddr, g, row, t.n_idx, live);
+      epilogue_rows<EPI>(taddr, g, &tmC, ew, row, t.row0 + quarter * 32, t.n_idx, live, quarter * 32 < t.valid_rows);
 #endif
       // hand the accumulator back to the MMA warp
       tc_fence_before();
       __syncwarp();
       if (lane == 0) mbar_arrive(smem_u32(&tempty[acc]));
     }
+    epilogue_drain(ew);
   }
 
   tc_fence_before();
@@ -533,7 +559,7 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
 constexpr int STAGES2_MAX = 6;                          // bf16: 6 stages of 32 KiB; W8A16: 5 of 24 KiB
 constexpr int B2_BYTES = 128 * BK * 2;                  // this CTA's half of the B tile, bf16
 constexpr int B2F8_BYTES = 128 * BK;                    // the same half as FP8 bytes
-constexpr int B2_SLOTS = 6;                             // converted half tiles in flight: the hand-off
+constexpr int B2_SLOTS = 5;                             // converted half tiles in flight: the hand-off
                                                         // crosses the SM pair, so it needs depth
 constexpr int NUM_BARS2 = 2 * STAGES2_MAX + 4 + 2 * B2_SLOTS;
 template <bool F8B>
@@ -545,7 +571,7 @@ struct Cfg2 {
 };
 constexpr size_t SMEM2_CTRL_BYTES = 8 * NUM_BARS2 + 16 + 4 * (3 * kMaxExperts + 3);
 template <bool F8B>
-constexpr size_t gemm2_smem_bytes() { return 1024 + Cfg2<F8B>::RING_BYTES + SMEM2_CTRL_BYTES; }
+constexpr size_t gemm2_smem_bytes() { return 1024 + Cfg2<F8B>::RING_BYTES + SMEM2_CTRL_BYTES + 128 + 4 * 2 * 2048; }
 constexpr int GROUP_M2 = 8;                             // pair tiles (256 rows) per L2 reuse group
 
 __device__ __forceinline__ uint32_t cluster_ctarank() {
@@ -622,7 +648,7 @@ __device__ __forceinline__ Tile2 locate_tile2(int tile, const int* s_pad, const 
 template <int EPI, bool F8B>
 __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(Cfg2<F8B>::THREADS, 1)
 grouped_gemm2_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
-                     const GemmArgs g) {
+                     const __grid_constant__ CUtensorMap tmC, const GemmArgs g) {
   constexpr int STAGE2_BYTES = Cfg2<F8B>::STAGE_BYTES;
   constexpr int STAGES2 = Cfg2<F8B>::STAGES;
   extern __shared__ uint8_t smem_raw[];
@@ -639,6 +665,8 @@ grouped_gemm2_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_const
   int* s_pad = reinterpret_cast<int*>(tmem_slot + 4);
   int* s_cnt = s_pad + kMaxExperts + 1;
   int* s_pp = s_cnt + kMaxExperts + 1;
+  uint8_t* epi_stage = reinterpret_cast<uint8_t*>(
+      (reinterpret_cast<uintptr_t>(smem + Cfg2<F8B>::RING_BYTES + SMEM2_CTRL_BYTES) + 127) & ~uintptr_t(127));
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const uint32_t rank = cluster_ctarank();           // 0 = leader
@@ -791,6 +819,7 @@ grouped_gemm2_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_const
     // ---------------- epilogue (both CTAs, own 128 rows) ----------------
     const int quarter = warp & 3;
     const int row_in_half = quarter * 32 + lane;
+    EpiWarp ew{epi_stage + quarter * 2 * EPI_PIECE_BYTES, 0u, lane};
     uint32_t tcount = 0;
     for (int tile = pair; tile < total_tiles && !*abort_flag; tile += n_pairs, ++tcount) {
       const Tile2 t = locate_tile2(tile, s_pad, s_cnt, s_pp, g.n_groups, g.n_tiles, g.n_per_group);
@@ -802,12 +831,14 @@ grouped_gemm2_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_const
       const bool live = row_in_half < my_rows;
       const long long row = static_cast<long long>(t.row0) + rank * BM + row_in_half;
 #ifndef MG_EXP_NO_EPI
-      epilogue_rows<EPI>(taddr, g, row, t.n_idx, live);
+      epilogue_rows<EPI>(taddr, g, &tmC, ew, row, t.row0 + static_cast<int>(rank) * BM + quarter * 32, t.n_idx, live,
+                         quarter * 32 < my_rows);
 #endif
       tc_fence_before();
       __syncwarp();
       if (lane == 0) mbar_arrive_cluster(map_to_cta(smem_u32(&tempty[acc]), 0));
     }
+    epilogue_drain(ew);
   }
 
   tc_fence_before();
@@ -861,18 +892,19 @@ static EncodeTiledFn get_encode_fn() {
 
 // bf16 operands land 128B-swizzled (what the UMMA descriptor expects); FP8 bytes land as plain
 // rows of 64 bytes for the converter warps
+// `out_piece`: the 32 x 32 bf16 pieces the epilogue stores (plain rows of 64 bytes)
 static int encode_2d(CUtensorMap* map, const void* base, uint64_t rows, uint64_t cols, uint32_t box_rows,
-                     bool fp8 = false) {
+                     bool fp8 = false, bool out_piece = false) {
   EncodeTiledFn fn = get_encode_fn();
   MG_REQUIRE(fn != nullptr, MG_ERR_DRIVER, "cuTensorMapEncodeTiled not available from the driver");
   cuuint64_t dims[2] = {cols, rows};
   cuuint64_t strides[1] = {cols * (fp8 ? 1 : 2)};
-  cuuint32_t box[2] = {static_cast<cuuint32_t>(BK), box_rows};
+  cuuint32_t box[2] = {static_cast<cuuint32_t>(out_piece ? 32 : BK), box_rows};
   cuuint32_t estr[2] = {1, 1};
   CUresult r = fn(map, fp8 ? CU_TENSOR_MAP_DATA_TYPE_UINT8 : CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2,
                   const_cast<void*>(base), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
-                  fp8 ? CU_TENSOR_MAP_SWIZZLE_NONE : CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
-                  CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+                  (fp8 || out_piece) ? CU_TENSOR_MAP_SWIZZLE_NONE : CU_TENSOR_MAP_SWIZZLE_128B,
+                  CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
   MG_REQUIRE(r == CUDA_SUCCESS, MG_ERR_DRIVER, "cuTensorMapEncodeTiled failed (%d) rows=%llu cols=%llu box=%u",
              static_cast<int>(r), static_cast<unsigned long long>(rows), static_cast<unsigned long long>(cols),
              box_rows);
@@ -880,23 +912,24 @@ static int encode_2d(CUtensorMap* map, const void* base, uint64_t rows, uint64_t
 }
 
 template <int EPI, bool F8B>
-static int launch_epi(const Handle* h, const CUtensorMap& ta, const CUtensorMap& tb, const GemmArgs& args,
-                      int grid, cudaStream_t st) {
+static int launch_epi(const Handle* h, const CUtensorMap& ta, const CUtensorMap& tb, const CUtensorMap& tc,
+                      const GemmArgs& args, int grid, cudaStream_t st) {
   // per device, and cheap: set on every launch rather than tracking which devices have it
   constexpr size_t smem = gemm_smem_bytes<F8B>();
   MG_CUDA(cudaFuncSetAttribute(grouped_gemm_kernel<EPI, F8B>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                static_cast<int>(smem)));
-  grouped_gemm_kernel<EPI, F8B><<<grid, Cfg<F8B>::THREADS, smem, st>>>(ta, tb, args);
+  grouped_gemm_kernel<EPI, F8B><<<grid, Cfg<F8B>::THREADS, smem, st>>>(ta, tb, tc, args);
   MG_CUDA(cudaGetLastError());
   return MG_OK;
 }
 
 template <int EPI, bool F8B>
-static int launch_pair(const CUtensorMap& ta, const CUtensorMap& tb, const GemmArgs& args, int grid, cudaStream_t st) {
+static int launch_pair(const CUtensorMap& ta, const CUtensorMap& tb, const CUtensorMap& tc, const GemmArgs& args,
+                       int grid, cudaStream_t st) {
   constexpr size_t smem = gemm2_smem_bytes<F8B>();
   MG_CUDA(cudaFuncSetAttribute(grouped_gemm2_kernel<EPI, F8B>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                static_cast<int>(smem)));
-  grouped_gemm2_kernel<EPI, F8B><<<grid, Cfg2<F8B>::THREADS, smem, st>>>(ta, tb, args);
+  grouped_gemm2_kernel<EPI, F8B><<<grid, Cfg2<F8B>::THREADS, smem, st>>>(ta, tb, tc, args);
   MG_CUDA(cudaGetLastError());
   return MG_OK;
 }
@@ -925,6 +958,13 @@ int launch_grouped_gemm(const Handle* h, const GemmProblem& p, cudaStream_t st) 
   rc = encode_2d(&tb, p.b, static_cast<uint64_t>(p.n_groups) * p.n_per_group, static_cast<uint64_t>(p.K),
                  pair ? 128 : bn, p.b_fp8);
   if (rc != MG_OK) return rc;
+  CUtensorMap tc = ta;   // unused by the fp32 epilogue
+  if (!f32_out) {
+    // output tensor [a_rows, ldo] bf16, written in 32 x 32 pieces
+    MG_REQUIRE(p.ldo % 8 == 0, MG_ERR_SHAPE, "output row length %lld must be a multiple of 8", static_cast<long long>(p.ldo));
+    rc = encode_2d(&tc, p.out, static_cast<uint64_t>(p.a_rows), static_cast<uint64_t>(p.ldo), 32, false, true);
+    if (rc != MG_OK) return rc;
+  }
   if (p.b_fp8) {
     MG_REQUIRE(!f32_out && p.scales != nullptr && p.K % 128 == 0 && p.K <= 128 * 128, MG_ERR_SHAPE,
                "FP8 weights need scales, K a multiple of 128 up to 16384 and a bf16 epilogue");
@@ -969,26 +1009,26 @@ int launch_grouped_gemm(const Handle* h, const GemmProblem& p, cudaStream_t st) 
     if (pairs < 1) pairs = 1;
     if (p.b_fp8) {
       switch (p.epilogue) {
-        case EPI_SWIGLU_BF16: return launch_pair<EPI_SWIGLU_BF16, true>(ta, tb, a, 2 * pairs, st);
-        case EPI_PLAIN_BF16: return launch_pair<EPI_PLAIN_BF16, true>(ta, tb, a, 2 * pairs, st);
+        case EPI_SWIGLU_BF16: return launch_pair<EPI_SWIGLU_BF16, true>(ta, tb, tc, a, 2 * pairs, st);
+        case EPI_PLAIN_BF16: return launch_pair<EPI_PLAIN_BF16, true>(ta, tb, tc, a, 2 * pairs, st);
       }
     }
     switch (p.epilogue) {
-      case EPI_SWIGLU_BF16: return launch_pair<EPI_SWIGLU_BF16, false>(ta, tb, a, 2 * pairs, st);
-      case EPI_PLAIN_BF16: return launch_pair<EPI_PLAIN_BF16, false>(ta, tb, a, 2 * pairs, st);
+      case EPI_SWIGLU_BF16: return launch_pair<EPI_SWIGLU_BF16, false>(ta, tb, tc, a, 2 * pairs, st);
+      case EPI_PLAIN_BF16: return launch_pair<EPI_PLAIN_BF16, false>(ta, tb, tc, a, 2 * pairs, st);
     }
   }
   if (p.b_fp8) {
     switch (p.epilogue) {
-      case EPI_SWIGLU_BF16: return launch_epi<EPI_SWIGLU_BF16, true>(h, ta, tb, a, grid, st);
-      case EPI_PLAIN_BF16: return launch_epi<EPI_PLAIN_BF16, true>(h, ta, tb, a, grid, st);
+      case EPI_SWIGLU_BF16: return launch_epi<EPI_SWIGLU_BF16, true>(h, ta, tb, tc, a, grid, st);
+      case EPI_PLAIN_BF16: return launch_epi<EPI_PLAIN_BF16, true>(h, ta, tb, tc, a, grid, st);
     }
   } else {
     switch (p.epilogue) {
-      case EPI_SWIGLU_BF16: return launch_epi<EPI_SWIGLU_BF16, false>(h, ta, tb, a, grid, st);
-      case EPI_PLAIN_BF16: return launch_epi<EPI_PLAIN_BF16, false>(h, ta, tb, a, grid, st);
-      case EPI_PLAIN_F32: return launch_epi<EPI_PLAIN_F32, false>(h, ta, tb, a, grid, st);
-      case EPI_ROUND_BF16_F32: return launch_epi<EPI_ROUND_BF16_F32, false>(h, ta, tb, a, grid, st);
+      case EPI_SWIGLU_BF16: return launch_epi<EPI_SWIGLU_BF16, false>(h, ta, tb, tc, a, grid, st);
+      case EPI_PLAIN_BF16: return launch_epi<EPI_PLAIN_BF16, false>(h, ta, tb, tc, a, grid, st);
+      case EPI_PLAIN_F32: return launch_epi<EPI_PLAIN_F32, false>(h, ta, tb, tc, a, grid, st);
+      case EPI_ROUND_BF16_F32: return launch_epi<EPI_ROUND_BF16_F32, false>(h, ta, tb, tc, a, grid, st);
     }
   }
   set_error("bad epilogue");
