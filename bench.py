@@ -297,6 +297,7 @@ def main():
     ap.add_argument("--micro", type=int, default=1, help="token micro-batches pipelined in the expert-parallel forward")
     ap.add_argument("--pair-gemm", type=int, default=-1, help="1/0 force the SM-pair expert GEMM on/off")
     ap.add_argument("--fp8-mode", type=int, default=-1, help="0 auto, 1 pre-dequantise, 2 convert in the GEMM")
+    ap.add_argument("--fp8-tall", type=int, default=-1, help="convert-in-GEMM tile height: 0 128 rows, 1 auto, 2 256 rows")
     args = ap.parse_args()
 
     rank = int(os.environ.get("RANK", "0"))
@@ -363,6 +364,8 @@ def main():
         base.set_option(2, args.pair_gemm)
     if args.fp8_mode >= 0:
         base.set_option(1, args.fp8_mode)
+    if args.fp8_tall >= 0:
+        base.set_option(4, args.fp8_tall)
     for _ in range(warmup):
         y = run_step()
     torch.cuda.synchronize()

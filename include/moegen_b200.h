@@ -324,8 +324,8 @@ int mg_last_launch_count(mg_handle h, int32_t* launches);
  *                      experts ahead of the bf16 grouped GEMMs, on a side stream (the reference
  *                      de-quantises per expert call, moe_gen/models/Wrapper.py:481-491);
  *   MG_FP8_IN_KERNEL   the grouped GEMMs convert FP8 weight tiles to bf16 in shared memory;
- *   MG_FP8_AUTO        (default) in-kernel while an expert sees at most 256 rows on average
- *                      (the layer is then bound by streaming the FP8 bytes), else pre-dequantise.
+ *   MG_FP8_AUTO        (default) in-kernel while an expert sees fewer than 1024 rows on average
+ *                      (measured cross-over on the DeepSeek-V3 shape), else pre-dequantise.
  * All give bit-identical results.  Set before asking mg_workspace_bytes. */
 #define MG_OPT_FP8_MODE    1
 #define MG_FP8_AUTO        0
@@ -334,6 +334,15 @@ int mg_last_launch_count(mg_handle h, int32_t* launches);
 /* MG_OPT_PAIR_GEMM: 1 = the bf16 expert GEMMs run on SM pairs (clusters of two CTAs,
  * tcgen05 cta_group::2, 256x256 tiles); 0 = one CTA per SM, 128x256 tiles. */
 #define MG_OPT_PAIR_GEMM   2
+/* MG_OPT_FP8_M256: tile height of the convert-in-the-GEMM kernels: 0 = 128 rows, 1 (default) =
+ * 256 rows (one converted weight tile feeds two MMAs) when experts average at least 120 rows,
+ * 2 = always 256. */
+#define MG_OPT_FP8_M256    4
+/* MG_OPT_BATCH_TOKENS: a caller that feeds one batch through mg_moe_forward in chunks sets the
+ * batch's total token count here (0 = off, the default); MG_FP8_AUTO then decides on the larger
+ * of this and the call's T, because the de-quantised copy can serve every chunk
+ * (MG_OPT_KEEP_DEQUANT).  Set before asking mg_workspace_bytes. */
+#define MG_OPT_BATCH_TOKENS 5
 /* MG_OPT_KEEP_DEQUANT: 1 = in pre-dequantise mode, a call may reuse the bf16 copy the previous
  * call on this handle left in the same scratch, if the packed buffer and the stream are the
  * same and no expert was re-packed in between.  Meant for the token chunks of ONE logical

@@ -49,6 +49,8 @@ struct Handle {
   const void* deq_scratch;
   const void* deq_packed;
   cudaStream_t deq_stream;
+  int64_t opt_batch_tokens;  // total tokens of a batch fed in chunks (0 = unknown), for the AUTO rule
+  int opt_fp8_m256;       // in-kernel FP8: 0 = 128-row tiles, 1 = 256-row tiles when experts are big, 2 = always
   bool opt_pair_gemm;     // bf16 expert GEMMs on SM pairs (tcgen05 cta_group::2)
   int opt_fp8_mode;       // MG_FP8_AUTO / MG_FP8_PREDEQUANT / MG_FP8_IN_KERNEL
   cudaStream_t side;      // de-quantisation runs here, one chunk of experts ahead of the GEMMs

@@ -230,7 +230,6 @@ __device__ __forceinline__ void convert16(const uint4& q, float s, uint4& lo, ui
 // instead of 64-byte runs per thread.  Rows of a piece that lie in an expert's padding are
 // written too (they belong to nobody); rows beyond the tensor are clipped by TMA.
 constexpr int EPI_PIECE_BYTES = 32 * 64;                 // 32 rows x 32 bf16
-constexpr int EPI_STAGE_BYTES = 4 * 2 * EPI_PIECE_BYTES; // 4 warps x 2 buffers
 
 __device__ __forceinline__ void tma_store_2d(const CUtensorMap* map, int c0, int c1, uint32_t src) {
   asm volatile("cp.async.bulk.tensor.2d.global.shared::cta.bulk_group [%0, {%1, %2}], [%3];" ::"l"(map), "r"(c0),
@@ -240,18 +239,22 @@ __device__ __forceinline__ void tma_store_2d(const CUtensorMap* map, int c0, int
 }
 
 struct EpiWarp {
-  uint8_t* stage;      // this warp's two staging buffers
+  uint8_t* stage;      // this warp's staging buffers
   uint32_t pieces;     // pieces issued so far (selects the buffer)
   int lane;
+  int nbuf;            // 2 staging buffers, or 1 where shared memory is short
 };
 
 // stores 32 bf16 (packed[16]) of this thread's row as one row of the warp's piece and sends it
 __device__ __forceinline__ void send_piece(EpiWarp& w, const CUtensorMap* tmC, const uint32_t* packed, int col0,
                                            int row_first, bool warp_live) {
   if (!warp_live) return;                                // uniform per warp
-  uint8_t* buf = w.stage + (w.pieces & 1u) * EPI_PIECE_BYTES;
-  // the store issued two pieces ago has finished reading this buffer
-  if (w.lane == 0) asm volatile("cp.async.bulk.wait_group.read 1;" ::: "memory");
+  uint8_t* buf = w.stage + (w.nbuf == 2 ? (w.pieces & 1u) : 0u) * EPI_PIECE_BYTES;
+  // the store that last used this buffer has finished reading it
+  if (w.lane == 0) {
+    if (w.nbuf == 2) asm volatile("cp.async.bulk.wait_group.read 1;" ::: "memory");
+    else asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory");
+  }
   __syncwarp();
   uint4* dst = reinterpret_cast<uint4*>(buf + w.lane * 64);
 #pragma unroll
@@ -509,7 +512,7 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
     // ---------------- epilogue ----------------
     const int quarter = warp & 3;             // TMEM lanes [32*quarter, 32*quarter+32)
     const int row_in_tile = quarter * 32 + lane;
-    EpiWarp ew{epi_stage + quarter * 2 * EPI_PIECE_BYTES, 0u, lane};
+    EpiWarp ew{epi_stage + quarter * 2 * EPI_PIECE_BYTES, 0u, lane, 2};
     uint32_t tcount = 0;
     for (int tile = blockIdx.x; tile < total_tiles && !*abort_flag; tile += gridDim.x, ++tcount) {
       const Tile t = locate_tile(tile, s_pad, s_cnt, g.n_groups, g.n_tiles, g.n_per_group, g.bn, g.group_m);
@@ -819,7 +822,7 @@ grouped_gemm2_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_const
     // ---------------- epilogue (both CTAs, own 128 rows) ----------------
     const int quarter = warp & 3;
     const int row_in_half = quarter * 32 + lane;
-    EpiWarp ew{epi_stage + quarter * 2 * EPI_PIECE_BYTES, 0u, lane};
+    EpiWarp ew{epi_stage + quarter * 2 * EPI_PIECE_BYTES, 0u, lane, 2};
     uint32_t tcount = 0;
     for (int tile = pair; tile < total_tiles && !*abort_flag; tile += n_pairs, ++tcount) {
       const Tile2 t = locate_tile2(tile, s_pad, s_cnt, s_pp, g.n_groups, g.n_tiles, g.n_per_group);
@@ -847,6 +850,254 @@ grouped_gemm2_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_const
     __syncwarp();
     tc_fence_after();
     asm volatile("tcgen05.dealloc.cta_group::2.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(TMEM_COLS)
+                 : "memory");
+  }
+}
+
+
+// =======================================================================================
+// W8A16 with 256-row tiles on one CTA: the converted B tile (256 x 64 bf16) is used by two MMAs,
+// one per 128-row half of A, accumulating into the two 256-column halves of tensor memory.  The
+// FP8 -> bf16 conversion is then paid once per 256 rows instead of once per 128.  The converter
+// warps read the FP8 bytes straight from global memory into registers, four k-blocks ahead, so
+// the bytes never pass through shared memory (whose bandwidth is what limits these kernels); TMA
+// carries A only.  Both accumulators are in use, so a tile's epilogue is not overlapped with the
+// next tile's main loop (the converters and the TMA ring do run ahead into it).
+// =======================================================================================
+constexpr int M256_STAGES = 3;                                      // A: 256 rows x 64 bf16 = 32 KiB each
+constexpr int M256_A_BYTES = 2 * A_BYTES;
+constexpr int M256_SLOTS = 3;                                       // converted B tiles, 32 KiB each
+constexpr int M256_RING_BYTES = M256_STAGES * M256_A_BYTES + M256_SLOTS * B_BYTES;
+constexpr int M256_BARS = 2 * M256_STAGES + 2 + 2 * M256_SLOTS;
+constexpr size_t M256_CTRL_BYTES = 8 * M256_BARS + 16 + 4 * (3 * kMaxExperts + 3);
+constexpr size_t M256_SMEM_BYTES = 1024 + M256_RING_BYTES + M256_CTRL_BYTES + 128 + 4 * 2 * EPI_PIECE_BYTES;
+constexpr int M256_THREADS = GEMM_THREADS + CONVERT_THREADS;
+constexpr int M256_UNITS = 256 * (BK / 16) / CONVERT_THREADS;       // 16-byte FP8 units per thread per k-block
+
+// where the converter's load (or convert) cursor stands: k-block `kb` of tile `tile`
+struct B8Cursor {
+  int tile, kb;
+  const uint8_t* src;     // this thread's first unit of the current k-block
+  const float* srow;      // scales of the tile's first 128 B rows
+};
+
+template <int EPI>
+__global__ void __launch_bounds__(M256_THREADS, 1)
+grouped_gemm_m256_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmC,
+                         const uint8_t* __restrict__ b8, const GemmArgs g) {
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  uint64_t* bars = reinterpret_cast<uint64_t*>(smem + M256_RING_BYTES);
+  uint64_t* full = bars;
+  uint64_t* empty = bars + M256_STAGES;
+  uint64_t* tfull = bars + 2 * M256_STAGES;
+  uint64_t* tempty = tfull + 1;
+  uint64_t* bready = tempty + 1;
+  uint64_t* bfree = bready + M256_SLOTS;
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + M256_BARS);
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
+  int* s_pad = reinterpret_cast<int*>(tmem_slot + 4);
+  int* s_cnt = s_pad + kMaxExperts + 1;
+  int* s_pp = s_cnt + kMaxExperts + 1;
+  uint8_t* epi_stage = reinterpret_cast<uint8_t*>(
+      (reinterpret_cast<uintptr_t>(smem + M256_RING_BYTES + M256_CTRL_BYTES) + 127) & ~uintptr_t(127));
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < M256_STAGES; ++s) { mbar_init(smem_u32(&full[s]), 1); mbar_init(smem_u32(&empty[s]), 1); }
+    mbar_init(smem_u32(tfull), 1);
+    mbar_init(smem_u32(tempty), 4);
+    for (int j = 0; j < M256_SLOTS; ++j) { mbar_init(smem_u32(&bready[j]), CONVERT_THREADS / 32); mbar_init(smem_u32(&bfree[j]), 1); }
+    *abort_flag = 0;
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+  }
+  for (int i = threadIdx.x; i <= g.n_groups; i += blockDim.x) s_pad[i] = g.pad_offsets[i];
+  for (int i = threadIdx.x; i < g.n_groups; i += blockDim.x) s_cnt[i] = g.counts[i];
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    int acc = 0;
+    for (int e = 0; e < g.n_groups; ++e) {
+      s_pp[e] = acc;
+      acc += ((s_pad[e + 1] - s_pad[e]) / BM + 1) / 2;
+    }
+    s_pp[g.n_groups] = acc;
+  }
+  if (warp == 1) {
+    __syncwarp();
+    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(tmem_slot)),
+                 "r"(TMEM_COLS)
+                 : "memory");
+    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = *tmem_slot;
+  const int total_tiles = s_pp[g.n_groups] * g.n_tiles;
+  const uint32_t smem_base = smem_u32(smem);
+  const uint32_t bslot_base = smem_base + M256_STAGES * M256_A_BYTES;
+
+  if (warp == 0) {
+    // ---------------- TMA producer: 256 rows of A per k-block, one box ----------------
+    if (lane == 0) {
+      uint32_t it = 0;
+      for (int tile = blockIdx.x; tile < total_tiles && !*abort_flag; tile += gridDim.x) {
+        const Tile2 t = locate_tile2(tile, s_pad, s_cnt, s_pp, g.n_groups, g.n_tiles, g.n_per_group);
+        for (int kb = 0; kb < g.k_blocks; ++kb, ++it) {
+          const uint32_t s = it % M256_STAGES, ph = (it / M256_STAGES) & 1u;
+          if (!mbar_wait(smem_u32(&empty[s]), ph ^ 1u, abort_flag, g.status, 21)) break;
+          const uint32_t fb = smem_u32(&full[s]);
+          mbar_expect_tx(fb, M256_A_BYTES);
+          tma_load_2d(smem_base + s * M256_A_BYTES, &tmA, kb * BK, t.row0, fb);
+        }
+      }
+    }
+  } else if (warp == 1) {
+    // ---------------- MMA issuer ----------------
+    if (lane == 0) {
+      uint32_t it = 0, tcount = 0;
+      for (int tile = blockIdx.x; tile < total_tiles && !*abort_flag; tile += gridDim.x, ++tcount) {
+        // a tile with at most 128 live rows needs the first half only
+        const int n_sub =
+            locate_tile2(tile, s_pad, s_cnt, s_pp, g.n_groups, g.n_tiles, g.n_per_group).rows_left > BM ? 2 : 1;
+        if (!mbar_wait(smem_u32(tempty), (tcount & 1u) ^ 1u, abort_flag, g.status, 22)) break;
+        tc_fence_after();
+        bool ok = true;
+        for (int kb = 0; kb < g.k_blocks; ++kb, ++it) {
+          const uint32_t s = it % M256_STAGES, ph = (it / M256_STAGES) & 1u;
+          const uint32_t j = it % M256_SLOTS, jph = (it / M256_SLOTS) & 1u;
+          if (!mbar_wait(smem_u32(&full[s]), ph, abort_flag, g.status, 23)) { ok = false; break; }
+          if (!mbar_wait(smem_u32(&bready[j]), jph, abort_flag, g.status, 25)) { ok = false; break; }
+          tc_fence_after();
+          const uint32_t sa = smem_base + s * M256_A_BYTES;
+          const uint64_t db = make_smem_desc(bslot_base + j * B_BYTES);
+          for (int sub = 0; sub < n_sub; ++sub) {
+            const uint64_t da = make_smem_desc(sa + sub * A_BYTES);
+#pragma unroll
+            for (int k = 0; k < BK / 16; ++k)
+              tc_mma_bf16(tmem_base + sub * ACC_COLS, da + 2 * k, db + 2 * k, g.idesc, (kb | k) != 0 ? 1u : 0u);
+          }
+          tc_commit(smem_u32(&empty[s]));
+          tc_commit(smem_u32(&bfree[j]));
+        }
+        if (!ok) break;
+        tc_commit(smem_u32(tfull));
+      }
+    }
+  } else if (warp >= 6) {
+    // ---------------- FP8 -> bf16 converter: global -> registers -> swizzled shared ----------------
+    const int ct = threadIdx.x - GEMM_THREADS;             // 0..255; unit i of this thread is row ct/4 + 64 i
+    const int r0 = ct >> 2, c = ct & 3;
+    const long long row_bytes = static_cast<long long>(g.k_blocks) * BK;     // FP8: one byte per element
+    const int my_tiles = blockIdx.x < total_tiles ? (total_tiles - blockIdx.x + gridDim.x - 1) / gridDim.x : 0;
+    const uint32_t n_it = static_cast<uint32_t>(my_tiles) * g.k_blocks;
+
+    auto seek = [&](B8Cursor& cur) {                        // point the cursor at k-block 0 of cur.tile
+      const Tile2 t = locate_tile2(cur.tile, s_pad, s_cnt, s_pp, g.n_groups, g.n_tiles, g.n_per_group);
+      cur.kb = 0;
+      cur.src = b8 + (static_cast<long long>(t.b_row) + r0) * row_bytes + c * 16;
+      cur.srow = g.scales + static_cast<long long>(t.b_row >> 7) * g.scale_cols;
+    };
+    auto step = [&](B8Cursor& cur) {
+      if (++cur.kb == g.k_blocks) {
+        cur.tile += gridDim.x;
+        if (cur.tile < total_tiles) seek(cur);
+      } else {
+        cur.src += BK;
+      }
+    };
+    auto fetch = [&](B8Cursor& cur, uint4 (&q)[M256_UNITS]) {
+      if (cur.tile >= total_tiles) return;
+#ifdef MG_EXP_M256_NOFETCH
+      if (cur.kb > 1) { step(cur); return; }               // experiment: FP8 bytes loaded at a tile's start only
+#endif
+#pragma unroll
+      for (int i = 0; i < M256_UNITS; ++i)
+        q[i] = __ldg(reinterpret_cast<const uint4*>(cur.src + static_cast<long long>(64 * i) * row_bytes));
+      step(cur);
+    };
+    // converts the fetched k-block `it` into its slot; false when a wait gave up
+    auto emit = [&](B8Cursor& cur, const uint4 (&q)[M256_UNITS], uint32_t it) -> bool {
+      const uint32_t j = it % M256_SLOTS, jph = (it / M256_SLOTS) & 1u;
+      const float s0 = __ldg(cur.srow + (cur.kb >> 1));
+      const float s1 = __ldg(cur.srow + g.scale_cols + (cur.kb >> 1));
+      int good = 1;
+      if (lane == 0) good = mbar_wait(smem_u32(&bfree[j]), jph ^ 1u, abort_flag, g.status, 27);
+      good = __shfl_sync(0xFFFFFFFFu, good, 0);
+      if (!good) return false;
+      uint8_t* dst = smem + M256_STAGES * M256_A_BYTES + j * B_BYTES;
+#pragma unroll
+      for (int i = 0; i < M256_UNITS; ++i) {
+#ifdef MG_EXP_M256_NOCONV
+        if (it > 8) continue;                               // experiment: tiles converted at the start only
+#endif
+        const int r = r0 + 64 * i;
+        uint4 lo, hi;
+        convert16(q[i], i < M256_UNITS / 2 ? s0 : s1, lo, hi);
+        uint8_t* drow = dst + r * 128;
+        *reinterpret_cast<uint4*>(drow + (((2 * c) ^ (r & 7)) << 4)) = lo;
+        *reinterpret_cast<uint4*>(drow + (((2 * c + 1) ^ (r & 7)) << 4)) = hi;
+      }
+      asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+      __syncwarp();
+      if (lane == 0) mbar_arrive(smem_u32(&bready[j]));
+      step(cur);
+      return true;
+    };
+
+    if (n_it > 0) {
+      B8Cursor ld{static_cast<int>(blockIdx.x), 0, nullptr, nullptr}, cv = ld;
+      seek(ld);
+      cv = ld;
+      // four k-blocks of FP8 bytes in flight in registers: the converters are the busiest warps, so
+      // the distance has to cover memory latency in units of their own work, not of the MMAs'
+      uint4 qa[M256_UNITS], qb[M256_UNITS], qc[M256_UNITS], qd[M256_UNITS];
+      fetch(ld, qa);
+      fetch(ld, qb);
+      fetch(ld, qc);
+      fetch(ld, qd);
+      for (uint32_t it = 0; it < n_it && !*abort_flag; it += 4) {
+        if (!emit(cv, qa, it)) break;
+        fetch(ld, qa);
+        if (it + 1 >= n_it || !emit(cv, qb, it + 1)) break;
+        fetch(ld, qb);
+        if (it + 2 >= n_it || !emit(cv, qc, it + 2)) break;
+        fetch(ld, qc);
+        if (it + 3 >= n_it || !emit(cv, qd, it + 3)) break;
+        fetch(ld, qd);
+      }
+    }
+  } else {
+    // ---------------- epilogue: both 128-row halves, one after the other ----------------
+    const int quarter = warp & 3;
+    EpiWarp ew{epi_stage + quarter * 2 * EPI_PIECE_BYTES, 0u, lane, 2};
+    uint32_t tcount = 0;
+    for (int tile = blockIdx.x; tile < total_tiles && !*abort_flag; tile += gridDim.x, ++tcount) {
+      const Tile2 t = locate_tile2(tile, s_pad, s_cnt, s_pp, g.n_groups, g.n_tiles, g.n_per_group);
+      if (!mbar_wait(smem_u32(tfull), tcount & 1u, abort_flag, g.status, 24)) break;
+      tc_fence_after();
+#pragma unroll 1
+      for (int sub = 0; sub < 2; ++sub) {
+        const int first = sub * BM + quarter * 32;                 // first row of this warp inside the tile
+        if (first >= t.rows_left) break;                           // nothing of this warp's to store
+        const uint32_t taddr = tmem_base + sub * ACC_COLS + (static_cast<uint32_t>(quarter * 32) << 16);
+        const bool live = first + lane < t.rows_left;
+        epilogue_rows<EPI>(taddr, g, &tmC, ew, static_cast<long long>(t.row0) + first + lane, t.row0 + first, t.n_idx,
+                           live, first < t.rows_left);
+      }
+      tc_fence_before();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(smem_u32(tempty));
+    }
+    epilogue_drain(ew);
+  }
+
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 1) {
+    __syncwarp();
+    tc_fence_after();
+    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(TMEM_COLS)
                  : "memory");
   }
 }
@@ -934,6 +1185,16 @@ static int launch_pair(const CUtensorMap& ta, const CUtensorMap& tb, const CUten
   return MG_OK;
 }
 
+template <int EPI>
+static int launch_m256(const CUtensorMap& ta, const CUtensorMap& tc, const void* b8, const GemmArgs& args, int grid,
+                       cudaStream_t st) {
+  MG_CUDA(cudaFuncSetAttribute(grouped_gemm_m256_kernel<EPI>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                               static_cast<int>(M256_SMEM_BYTES)));
+  grouped_gemm_m256_kernel<EPI><<<grid, M256_THREADS, M256_SMEM_BYTES, st>>>(ta, tc, static_cast<const uint8_t*>(b8), args);
+  MG_CUDA(cudaGetLastError());
+  return MG_OK;
+}
+
 int launch_grouped_gemm(const Handle* h, const GemmProblem& p, cudaStream_t st) {
   const bool dense = p.pad_offsets == nullptr;
   if (p.a_rows <= 0 || (dense && p.dense_rows <= 0)) return MG_OK;
@@ -952,8 +1213,13 @@ int launch_grouped_gemm(const Handle* h, const GemmProblem& p, cudaStream_t st) 
   }
   // SM pairs (2-CTA tiles of 256 x 256) for the bf16 expert GEMMs unless switched off
   const bool pair = h->opt_pair_gemm && !f32_out;
+  // FP8 weights converted in the kernel: 256-row tiles once experts average 120 live rows (a_rows
+  // also counts up to 127 rows of padding per expert); below that most tall tiles would be half
+  // empty and the 128-row kernel, which overlaps its epilogue, does the same work sooner
+  const bool m256 = p.b_fp8 && !pair && !f32_out && h->opt_fp8_m256 && !dense &&
+                    p.a_rows >= static_cast<int64_t>(p.n_groups) * (h->opt_fp8_m256 == 2 ? 0 : 120 + 127);
   CUtensorMap ta, tb;
-  int rc = encode_2d(&ta, p.a, static_cast<uint64_t>(p.a_rows), static_cast<uint64_t>(p.K), BM);
+  int rc = encode_2d(&ta, p.a, static_cast<uint64_t>(p.a_rows), static_cast<uint64_t>(p.K), m256 ? 2 * BM : BM);
   if (rc != MG_OK) return rc;
   rc = encode_2d(&tb, p.b, static_cast<uint64_t>(p.n_groups) * p.n_per_group, static_cast<uint64_t>(p.K),
                  pair ? 128 : bn, p.b_fp8);
@@ -998,6 +1264,14 @@ int launch_grouped_gemm(const Handle* h, const GemmProblem& p, cudaStream_t st) 
     if (max_tiles < grid) grid = static_cast<int>(max_tiles);
   }
   if (grid < 1) return MG_OK;
+  if (m256) {
+    long long tall_tiles = ((p.a_rows / BM + p.n_groups) / 2 + 1) * static_cast<long long>(a.n_tiles);
+    int ctas = tall_tiles < h->sm_count ? static_cast<int>(tall_tiles) : h->sm_count;
+    switch (p.epilogue) {
+      case EPI_SWIGLU_BF16: return launch_m256<EPI_SWIGLU_BF16>(ta, tc, p.b, a, ctas, st);
+      case EPI_PLAIN_BF16: return launch_m256<EPI_PLAIN_BF16>(ta, tc, p.b, a, ctas, st);
+    }
+  }
   if (pair) {
     // UMMA M = 256 across the two CTAs; one cluster per SM pair
     a.idesc = (1u << 4) | (1u << 7) | (1u << 10) | (static_cast<uint32_t>(bn >> 3) << 17) |

@@ -153,7 +153,8 @@ class EPMoELayer:
             nd = C.c_size_t()
             L.check(self.lib.mg_dequant_ws_bytes(lay._h, C.byref(nd)))
             # FP8: pre-dequantise when an expert sees many rows (same rule as the single-GPU path)
-            use_deq = nd.value > 0 and T * self.world * k > 256 * E
+            mode = lay.options.get(L.OPT_FP8_MODE, 0)
+            use_deq = nd.value > 0 and (mode == 1 or (mode == 0 and T * self.world * k >= 1024 * E))
             self.deq = torch.empty(nd.value, dtype=torch.uint8, device=self.dev) if use_deq else None
         self._tokens = T
         dist.barrier(group=self.group)

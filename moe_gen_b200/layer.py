@@ -46,6 +46,7 @@ class MoELayer:
         self.bias: Optional[torch.Tensor] = None
         self._ws: Optional[torch.Tensor] = None
         self._ws_tokens = -1
+        self.options = {}                       # option id -> last value set
 
     # ------------------------------------------------------------------ lifetime
     def close(self):
@@ -127,6 +128,7 @@ class MoELayer:
 
     def set_option(self, option: int, value: int):
         L.check(self.lib.mg_set_option(self._h, option, value))
+        self.options[option] = value
         if option != L.OPT_KEEP_DEQUANT:
             self._ws, self._ws_tokens = None, -1    # workspace layout may depend on options
 
@@ -182,6 +184,10 @@ class MoELayer:
             ev_out = [torch.cuda.Event() for _ in range(2)]
             s_in.wait_stream(comp)
             s_out.wait_stream(comp)
+            # the FP8 mode is chosen for the whole batch, not per chunk
+            hint = self.desc.weight_format == L.WEIGHT_FP8_BLOCK128 and T > cs
+            if hint:
+                self.set_option(L.OPT_BATCH_TOKENS, T)
             self._workspace(cs)
             # FP8 layers in pre-dequantise mode: de-quantise once for all chunks of this forward
             self.set_option(L.OPT_KEEP_DEQUANT, 1)
@@ -203,6 +209,8 @@ class MoELayer:
                     ev_out[b].record(s_out)
             self.set_option(L.OPT_KEEP_DEQUANT, 0)
             s_out.synchronize()
+            if hint:
+                self.set_option(L.OPT_BATCH_TOKENS, 0)
         return y_host
 
     # ------------------------------------------------------------------ stages

@@ -237,6 +237,12 @@ def test_fp8_weights_converted_in_the_gemm_equal_dequantise_first(built_lib):
     live[dst.cpu().long().view(-1)] = True
     assert torch.equal(h1.cpu()[live].view(torch.int16), h2.cpu()[live].view(torch.int16))
     assert torch.equal(o1.cpu()[live].view(torch.int16), o2.cpu()[live].view(torch.int16))
+    for tall in (0, 2, 1):                             # 128-row tiles, 256-row tiles, by expert size
+        layer.set_option(4, tall)
+        h4, o4 = layer.expert_ffn(perm, pad, counts, predequant=False)
+        _status_ok(layer)
+        assert torch.equal(h1.cpu()[live].view(torch.int16), h4.cpu()[live].view(torch.int16))
+        assert torch.equal(o1.cpu()[live].view(torch.int16), o4.cpu()[live].view(torch.int16))
     worst, _ = _check_expert_rows(spec, W, xd, layer, idx)
     assert worst < 5e-3
     ys = []
