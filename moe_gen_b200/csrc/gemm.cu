@@ -31,7 +31,7 @@ constexpr int STAGES = 4;
 constexpr int A_BYTES = BM * BK * 2;         // 16 KiB
 constexpr int B_BYTES = BN_MAX * BK * 2;     // 32 KiB
 constexpr int B8_BYTES = BN_MAX * BK;         // 16 KiB: the same tile as FP8 bytes
-constexpr int B_SLOTS = 2;                   // converted bf16 B tiles in flight (W8A16 variant)
+constexpr int B_SLOTS = 3;                   // converted bf16 B tiles in flight (W8A16 variant)
 constexpr int GEMM_THREADS = 192;
 constexpr int CONVERT_THREADS = 256;
 constexpr int NUM_BARS = 2 * STAGES + 4 + 2 * B_SLOTS;
@@ -39,7 +39,8 @@ constexpr int NUM_BARS = 2 * STAGES + 4 + 2 * B_SLOTS;
 template <bool F8B>
 struct Cfg {
   static constexpr int STAGE_BYTES = A_BYTES + (F8B ? B8_BYTES : B_BYTES);
-  static constexpr int RING_BYTES = STAGES * STAGE_BYTES + (F8B ? B_SLOTS * B_BYTES : 0);
+  static constexpr int NS = F8B ? 3 : STAGES;       // W8A16: a stage less, a converted-tile slot more
+  static constexpr int RING_BYTES = NS * STAGE_BYTES + (F8B ? B_SLOTS * B_BYTES : 0);
   static constexpr int THREADS = GEMM_THREADS + (F8B ? CONVERT_THREADS : 0);
 };
 constexpr int TMEM_COLS = 512;
@@ -357,6 +358,7 @@ __global__ void __launch_bounds__(Cfg<F8B>::THREADS, 1)
 grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
                     const __grid_constant__ CUtensorMap tmC, const GemmArgs g) {
   constexpr int STAGE_BYTES = Cfg<F8B>::STAGE_BYTES;
+  constexpr int NS = Cfg<F8B>::NS;
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
   uint64_t* bars = reinterpret_cast<uint64_t*>(smem + Cfg<F8B>::RING_BYTES);
@@ -376,7 +378,7 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
 
   if (threadIdx.x == 0) {
-    for (int s = 0; s < STAGES; ++s) { mbar_init(smem_u32(&full[s]), 1); mbar_init(smem_u32(&empty[s]), 1); }
+    for (int s = 0; s < NS; ++s) { mbar_init(smem_u32(&full[s]), 1); mbar_init(smem_u32(&empty[s]), 1); }
     for (int a = 0; a < 2; ++a) { mbar_init(smem_u32(&tfull[a]), 1); mbar_init(smem_u32(&tempty[a]), 4); }
     for (int j = 0; j < B_SLOTS; ++j) { mbar_init(smem_u32(&bready[j]), CONVERT_THREADS / 64); mbar_init(smem_u32(&bfree[j]), 1); }
     *abort_flag = 0;
@@ -403,7 +405,7 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
   const uint32_t tmem_base = *tmem_slot;
   const int total_tiles = ((s_pad[g.n_groups] - s_pad[0]) / BM) * g.n_tiles;
   const uint32_t smem_base = smem_u32(smem);
-  const uint32_t bslot_base = smem_base + STAGES * STAGE_BYTES;   // W8A16: converted B tiles
+  const uint32_t bslot_base = smem_base + NS * STAGE_BYTES;   // W8A16: converted B tiles
 
   if (warp == 0) {
     // ---------------- TMA producer ----------------
@@ -413,11 +415,11 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
       for (int tile = blockIdx.x; tile < total_tiles && !*abort_flag; tile += gridDim.x) {
         const Tile t = locate_tile(tile, s_pad, s_cnt, g.n_groups, g.n_tiles, g.n_per_group, g.bn, g.group_m);
         for (int kb = 0; kb < g.k_blocks; ++kb, ++it) {
-          const uint32_t s = it % STAGES, ph = (it / STAGES) & 1u;
+          const uint32_t s = it % NS, ph = (it / NS) & 1u;
           if (!mbar_wait(smem_u32(&empty[s]), ph ^ 1u, abort_flag, g.status, 1)) break;
           const uint32_t fb = smem_u32(&full[s]);
 #ifdef MG_EXP_NO_TMA
-          if (it >= STAGES) { mbar_arrive(fb); continue; }   // experiment: operands loaded once only
+          if (it >= NS) { mbar_arrive(fb); continue; }   // experiment: operands loaded once only
 #endif
           mbar_expect_tx(fb, tx_bytes);
           const uint32_t sa = smem_base + s * STAGE_BYTES;
@@ -437,7 +439,7 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
         const uint32_t d_tmem = tmem_base + acc * ACC_COLS;
         bool ok = true;
         for (int kb = 0; kb < g.k_blocks; ++kb, ++it) {
-          const uint32_t s = it % STAGES, ph = (it / STAGES) & 1u;
+          const uint32_t s = it % NS, ph = (it / NS) & 1u;
           if (!mbar_wait(smem_u32(&full[s]), ph, abort_flag, g.status, 3)) { ok = false; break; }
           const uint32_t j = it % B_SLOTS, jph = (it / B_SLOTS) & 1u;
           if (F8B && !mbar_wait(smem_u32(&bready[j]), jph, abort_flag, g.status, 5)) { ok = false; break; }
@@ -473,7 +475,7 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
       bool ok = true;
       for (int kb = 0; kb < g.k_blocks; ++kb, ++it) {
         if ((it & 1u) != grp) continue;
-        const uint32_t s = it % STAGES, ph = (it / STAGES) & 1u;
+        const uint32_t s = it % NS, ph = (it / NS) & 1u;
         const uint32_t j = it % B_SLOTS, jph = (it / B_SLOTS) & 1u;
         const float s0 = __ldg(srow + (kb >> 1));
         const float s1 = g.bn > 128 ? __ldg(srow + g.scale_cols + (kb >> 1)) : s0;
@@ -484,7 +486,7 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
         good = __shfl_sync(0xFFFFFFFFu, good, 0);         // also orders the other lanes after the wait
         if (!good) { ok = false; break; }
         const uint8_t* src = smem + s * STAGE_BYTES + A_BYTES;
-        uint8_t* dst = smem + STAGES * STAGE_BYTES + j * B_BYTES;
+        uint8_t* dst = smem + NS * STAGE_BYTES + j * B_BYTES;
 #pragma unroll
         for (int u = ct; u < units; u += CONVERT_THREADS / 2) {
           const int r = u >> 2, c = u & 3;                // row of the tile, 16-byte chunk of its 64 bytes
@@ -856,23 +858,35 @@ grouped_gemm2_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_const
 
 
 // =======================================================================================
-// W8A16 with 256-row tiles on one CTA: the converted B tile (256 x 64 bf16) is used by two MMAs,
-// one per 128-row half of A, accumulating into the two 256-column halves of tensor memory.  The
-// FP8 -> bf16 conversion is then paid once per 256 rows instead of once per 128.  The converter
-// warps read the FP8 bytes straight from global memory into registers, four k-blocks ahead, so
-// the bytes never pass through shared memory (whose bandwidth is what limits these kernels); TMA
-// carries A only.  Both accumulators are in use, so a tile's epilogue is not overlapped with the
-// next tile's main loop (the converters and the TMA ring do run ahead into it).
+// W8A16 on one CTA: FP8 weight tiles are converted to bf16 inside the kernel.  The 8 converter
+// warps read the FP8 bytes straight from global memory into registers, four k-blocks ahead,
+// scale them, and write the bf16 tile, swizzled as TMA would, into one of a ring of slots for
+// the MMA warp; the bytes never pass through shared memory as FP8 (shared-memory bandwidth is
+// what limits these kernels) and TMA carries A only.
+//   TM = 128: one MMA per k-block, two accumulators in tensor memory (the epilogue of a tile
+//             overlaps the next tile's main loop).  Not dispatched: with few rows per expert the
+//             weights stream from HBM, register loads then expose its latency, and the TMA-staged
+//             grouped_gemm_kernel<EPI, true> measured 1.35x faster (2.54 against 3.50 ms for the
+//             gate/up GEMM of 256 DeepSeek-V3 experts at 32 rows each).
+//   TM = 256: the converted tile feeds two MMAs, one per 128-row half of A, into the two halves
+//             of tensor memory, so the conversion is paid once per 256 rows.  Both accumulators
+//             are in use, so a tile's epilogue is not overlapped (the converters and the TMA
+//             ring do run ahead into it); a tile with at most 128 live rows skips the second MMA.
 // =======================================================================================
-constexpr int M256_STAGES = 3;                                      // A: 256 rows x 64 bf16 = 32 KiB each
-constexpr int M256_A_BYTES = 2 * A_BYTES;
-constexpr int M256_SLOTS = 3;                                       // converted B tiles, 32 KiB each
-constexpr int M256_RING_BYTES = M256_STAGES * M256_A_BYTES + M256_SLOTS * B_BYTES;
-constexpr int M256_BARS = 2 * M256_STAGES + 2 + 2 * M256_SLOTS;
-constexpr size_t M256_CTRL_BYTES = 8 * M256_BARS + 16 + 4 * (3 * kMaxExperts + 3);
-constexpr size_t M256_SMEM_BYTES = 1024 + M256_RING_BYTES + M256_CTRL_BYTES + 128 + 4 * 2 * EPI_PIECE_BYTES;
-constexpr int M256_THREADS = GEMM_THREADS + CONVERT_THREADS;
-constexpr int M256_UNITS = 256 * (BK / 16) / CONVERT_THREADS;       // 16-byte FP8 units per thread per k-block
+template <int TM>
+struct CfgW8 {
+  static constexpr int SUBS = TM / BM;                               // MMAs per k-block
+  static constexpr int A_STAGE = SUBS * A_BYTES;                     // 16 / 32 KiB
+  static constexpr int STAGES = TM == 128 ? 4 : 3;
+  static constexpr int SLOTS = TM == 128 ? 4 : 3;                    // converted B tiles, 32 KiB each
+  static constexpr int NACC = TM == 128 ? 2 : 1;                     // accumulator sets
+  static constexpr int RING_BYTES = STAGES * A_STAGE + SLOTS * B_BYTES;
+  static constexpr int BARS = 2 * STAGES + 2 * NACC + 2 * SLOTS;
+  static constexpr size_t CTRL_BYTES = 8 * BARS + 16 + 4 * (3 * kMaxExperts + 3);
+  static constexpr size_t SMEM_BYTES = 1024 + RING_BYTES + CTRL_BYTES + 128 + 4 * 2 * EPI_PIECE_BYTES;
+};
+constexpr int W8_THREADS = GEMM_THREADS + CONVERT_THREADS;
+constexpr int W8_UNITS = 256 * (BK / 16) / CONVERT_THREADS;         // 16-byte FP8 units per thread per k-block
 
 // where the converter's load (or convert) cursor stands: k-block `kb` of tile `tile`
 struct B8Cursor {
@@ -881,40 +895,63 @@ struct B8Cursor {
   const float* srow;      // scales of the tile's first 128 B rows
 };
 
-template <int EPI>
-__global__ void __launch_bounds__(M256_THREADS, 1)
-grouped_gemm_m256_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmC,
-                         const uint8_t* __restrict__ b8, const GemmArgs g) {
+template <int TM>
+__device__ __forceinline__ Tile2 locate_w8(int tile, const int* s_pad, const int* s_cnt, const int* s_pp,
+                                           const GemmArgs& g) {
+  if (TM == 256) return locate_tile2(tile, s_pad, s_cnt, s_pp, g.n_groups, g.n_tiles, g.n_per_group);
+  const Tile t = locate_tile(tile, s_pad, s_cnt, g.n_groups, g.n_tiles, g.n_per_group, g.bn, g.group_m);
+  Tile2 r;
+  r.row0 = t.row0;
+  r.rows_left = t.valid_rows;
+  r.b_row = t.b_row;
+  r.n_idx = t.n_idx;
+  return r;
+}
+
+// 16 bytes of weights, read once by this SM: no L1 allocation; a miss brings 256 bytes of the
+// row into L2, which the next three k-blocks then find there
+__device__ __forceinline__ uint4 ld_weights16(const uint8_t* p) {
+  uint4 v;
+  asm volatile("ld.global.nc.L1::no_allocate.L2::256B.v4.u32 {%0, %1, %2, %3}, [%4];"
+               : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w)
+               : "l"(p));
+  return v;
+}
+
+template <int EPI, int TM>
+__global__ void __launch_bounds__(W8_THREADS, 1)
+grouped_gemm_w8_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmC,
+                       const uint8_t* __restrict__ b8, const GemmArgs g) {
+  using C = CfgW8<TM>;
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
-  uint64_t* bars = reinterpret_cast<uint64_t*>(smem + M256_RING_BYTES);
+  uint64_t* bars = reinterpret_cast<uint64_t*>(smem + C::RING_BYTES);
   uint64_t* full = bars;
-  uint64_t* empty = bars + M256_STAGES;
-  uint64_t* tfull = bars + 2 * M256_STAGES;
-  uint64_t* tempty = tfull + 1;
-  uint64_t* bready = tempty + 1;
-  uint64_t* bfree = bready + M256_SLOTS;
-  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + M256_BARS);
+  uint64_t* empty = bars + C::STAGES;
+  uint64_t* tfull = bars + 2 * C::STAGES;
+  uint64_t* tempty = tfull + C::NACC;
+  uint64_t* bready = tempty + C::NACC;
+  uint64_t* bfree = bready + C::SLOTS;
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + C::BARS);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
   int* s_pad = reinterpret_cast<int*>(tmem_slot + 4);
   int* s_cnt = s_pad + kMaxExperts + 1;
   int* s_pp = s_cnt + kMaxExperts + 1;
   uint8_t* epi_stage = reinterpret_cast<uint8_t*>(
-      (reinterpret_cast<uintptr_t>(smem + M256_RING_BYTES + M256_CTRL_BYTES) + 127) & ~uintptr_t(127));
+      (reinterpret_cast<uintptr_t>(smem + C::RING_BYTES + C::CTRL_BYTES) + 127) & ~uintptr_t(127));
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   if (threadIdx.x == 0) {
-    for (int s = 0; s < M256_STAGES; ++s) { mbar_init(smem_u32(&full[s]), 1); mbar_init(smem_u32(&empty[s]), 1); }
-    mbar_init(smem_u32(tfull), 1);
-    mbar_init(smem_u32(tempty), 4);
-    for (int j = 0; j < M256_SLOTS; ++j) { mbar_init(smem_u32(&bready[j]), CONVERT_THREADS / 32); mbar_init(smem_u32(&bfree[j]), 1); }
+    for (int s = 0; s < C::STAGES; ++s) { mbar_init(smem_u32(&full[s]), 1); mbar_init(smem_u32(&empty[s]), 1); }
+    for (int a = 0; a < C::NACC; ++a) { mbar_init(smem_u32(&tfull[a]), 1); mbar_init(smem_u32(&tempty[a]), 4); }
+    for (int j = 0; j < C::SLOTS; ++j) { mbar_init(smem_u32(&bready[j]), CONVERT_THREADS / 32); mbar_init(smem_u32(&bfree[j]), 1); }
     *abort_flag = 0;
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
   }
   for (int i = threadIdx.x; i <= g.n_groups; i += blockDim.x) s_pad[i] = g.pad_offsets[i];
   for (int i = threadIdx.x; i < g.n_groups; i += blockDim.x) s_cnt[i] = g.counts[i];
   __syncthreads();
-  if (threadIdx.x == 0) {
+  if (TM == 256 && threadIdx.x == 0) {
     int acc = 0;
     for (int e = 0; e < g.n_groups; ++e) {
       s_pp[e] = acc;
@@ -933,22 +970,23 @@ grouped_gemm_m256_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_c
   __syncthreads();
   tc_fence_after();
   const uint32_t tmem_base = *tmem_slot;
-  const int total_tiles = s_pp[g.n_groups] * g.n_tiles;
+  const int total_tiles =
+      TM == 256 ? s_pp[g.n_groups] * g.n_tiles : ((s_pad[g.n_groups] - s_pad[0]) / BM) * g.n_tiles;
   const uint32_t smem_base = smem_u32(smem);
-  const uint32_t bslot_base = smem_base + M256_STAGES * M256_A_BYTES;
+  const uint32_t bslot_base = smem_base + C::STAGES * C::A_STAGE;
 
   if (warp == 0) {
-    // ---------------- TMA producer: 256 rows of A per k-block, one box ----------------
+    // ---------------- TMA producer: TM rows of A per k-block, one box ----------------
     if (lane == 0) {
       uint32_t it = 0;
       for (int tile = blockIdx.x; tile < total_tiles && !*abort_flag; tile += gridDim.x) {
-        const Tile2 t = locate_tile2(tile, s_pad, s_cnt, s_pp, g.n_groups, g.n_tiles, g.n_per_group);
+        const Tile2 t = locate_w8<TM>(tile, s_pad, s_cnt, s_pp, g);
         for (int kb = 0; kb < g.k_blocks; ++kb, ++it) {
-          const uint32_t s = it % M256_STAGES, ph = (it / M256_STAGES) & 1u;
+          const uint32_t s = it % C::STAGES, ph = (it / C::STAGES) & 1u;
           if (!mbar_wait(smem_u32(&empty[s]), ph ^ 1u, abort_flag, g.status, 21)) break;
           const uint32_t fb = smem_u32(&full[s]);
-          mbar_expect_tx(fb, M256_A_BYTES);
-          tma_load_2d(smem_base + s * M256_A_BYTES, &tmA, kb * BK, t.row0, fb);
+          mbar_expect_tx(fb, C::A_STAGE);
+          tma_load_2d(smem_base + s * C::A_STAGE, &tmA, kb * BK, t.row0, fb);
         }
       }
     }
@@ -957,31 +995,33 @@ grouped_gemm_m256_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_c
     if (lane == 0) {
       uint32_t it = 0, tcount = 0;
       for (int tile = blockIdx.x; tile < total_tiles && !*abort_flag; tile += gridDim.x, ++tcount) {
-        // a tile with at most 128 live rows needs the first half only
-        const int n_sub =
-            locate_tile2(tile, s_pad, s_cnt, s_pp, g.n_groups, g.n_tiles, g.n_per_group).rows_left > BM ? 2 : 1;
-        if (!mbar_wait(smem_u32(tempty), (tcount & 1u) ^ 1u, abort_flag, g.status, 22)) break;
+        // a 256-row tile with at most 128 live rows needs its first half only
+        const int n_sub = (TM == 256 && locate_w8<TM>(tile, s_pad, s_cnt, s_pp, g).rows_left > BM) ? 2 : 1;
+        const uint32_t acc = C::NACC == 2 ? (tcount & 1u) : 0u;
+        const uint32_t acc_ph = C::NACC == 2 ? ((tcount >> 1) & 1u) : (tcount & 1u);
+        if (!mbar_wait(smem_u32(&tempty[acc]), acc_ph ^ 1u, abort_flag, g.status, 22)) break;
         tc_fence_after();
         bool ok = true;
         for (int kb = 0; kb < g.k_blocks; ++kb, ++it) {
-          const uint32_t s = it % M256_STAGES, ph = (it / M256_STAGES) & 1u;
-          const uint32_t j = it % M256_SLOTS, jph = (it / M256_SLOTS) & 1u;
+          const uint32_t s = it % C::STAGES, ph = (it / C::STAGES) & 1u;
+          const uint32_t j = it % C::SLOTS, jph = (it / C::SLOTS) & 1u;
           if (!mbar_wait(smem_u32(&full[s]), ph, abort_flag, g.status, 23)) { ok = false; break; }
           if (!mbar_wait(smem_u32(&bready[j]), jph, abort_flag, g.status, 25)) { ok = false; break; }
           tc_fence_after();
-          const uint32_t sa = smem_base + s * M256_A_BYTES;
+          const uint32_t sa = smem_base + s * C::A_STAGE;
           const uint64_t db = make_smem_desc(bslot_base + j * B_BYTES);
           for (int sub = 0; sub < n_sub; ++sub) {
             const uint64_t da = make_smem_desc(sa + sub * A_BYTES);
+            const uint32_t d_tmem = tmem_base + (acc + sub) * ACC_COLS;
 #pragma unroll
             for (int k = 0; k < BK / 16; ++k)
-              tc_mma_bf16(tmem_base + sub * ACC_COLS, da + 2 * k, db + 2 * k, g.idesc, (kb | k) != 0 ? 1u : 0u);
+              tc_mma_bf16(d_tmem, da + 2 * k, db + 2 * k, g.idesc, (kb | k) != 0 ? 1u : 0u);
           }
           tc_commit(smem_u32(&empty[s]));
           tc_commit(smem_u32(&bfree[j]));
         }
         if (!ok) break;
-        tc_commit(smem_u32(tfull));
+        tc_commit(smem_u32(&tfull[acc]));
       }
     }
   } else if (warp >= 6) {
@@ -993,7 +1033,7 @@ grouped_gemm_m256_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_c
     const uint32_t n_it = static_cast<uint32_t>(my_tiles) * g.k_blocks;
 
     auto seek = [&](B8Cursor& cur) {                        // point the cursor at k-block 0 of cur.tile
-      const Tile2 t = locate_tile2(cur.tile, s_pad, s_cnt, s_pp, g.n_groups, g.n_tiles, g.n_per_group);
+      const Tile2 t = locate_w8<TM>(cur.tile, s_pad, s_cnt, s_pp, g);
       cur.kb = 0;
       cur.src = b8 + (static_cast<long long>(t.b_row) + r0) * row_bytes + c * 16;
       cur.srow = g.scales + static_cast<long long>(t.b_row >> 7) * g.scale_cols;
@@ -1006,34 +1046,33 @@ grouped_gemm_m256_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_c
         cur.src += BK;
       }
     };
-    auto fetch = [&](B8Cursor& cur, uint4 (&q)[M256_UNITS]) {
+    auto fetch = [&](B8Cursor& cur, uint4 (&q)[W8_UNITS]) {
       if (cur.tile >= total_tiles) return;
-#ifdef MG_EXP_M256_NOFETCH
+#ifdef MG_EXP_W8_NOFETCH
       if (cur.kb > 1) { step(cur); return; }               // experiment: FP8 bytes loaded at a tile's start only
 #endif
 #pragma unroll
-      for (int i = 0; i < M256_UNITS; ++i)
-        q[i] = __ldg(reinterpret_cast<const uint4*>(cur.src + static_cast<long long>(64 * i) * row_bytes));
+      for (int i = 0; i < W8_UNITS; ++i) q[i] = ld_weights16(cur.src + static_cast<long long>(64 * i) * row_bytes);
       step(cur);
     };
     // converts the fetched k-block `it` into its slot; false when a wait gave up
-    auto emit = [&](B8Cursor& cur, const uint4 (&q)[M256_UNITS], uint32_t it) -> bool {
-      const uint32_t j = it % M256_SLOTS, jph = (it / M256_SLOTS) & 1u;
+    auto emit = [&](B8Cursor& cur, const uint4 (&q)[W8_UNITS], uint32_t it) -> bool {
+      const uint32_t j = it % C::SLOTS, jph = (it / C::SLOTS) & 1u;
       const float s0 = __ldg(cur.srow + (cur.kb >> 1));
       const float s1 = __ldg(cur.srow + g.scale_cols + (cur.kb >> 1));
       int good = 1;
       if (lane == 0) good = mbar_wait(smem_u32(&bfree[j]), jph ^ 1u, abort_flag, g.status, 27);
       good = __shfl_sync(0xFFFFFFFFu, good, 0);
       if (!good) return false;
-      uint8_t* dst = smem + M256_STAGES * M256_A_BYTES + j * B_BYTES;
+      uint8_t* dst = smem + C::STAGES * C::A_STAGE + j * B_BYTES;
 #pragma unroll
-      for (int i = 0; i < M256_UNITS; ++i) {
-#ifdef MG_EXP_M256_NOCONV
+      for (int i = 0; i < W8_UNITS; ++i) {
+#ifdef MG_EXP_W8_NOCONV
         if (it > 8) continue;                               // experiment: tiles converted at the start only
 #endif
         const int r = r0 + 64 * i;
         uint4 lo, hi;
-        convert16(q[i], i < M256_UNITS / 2 ? s0 : s1, lo, hi);
+        convert16(q[i], i < W8_UNITS / 2 ? s0 : s1, lo, hi);
         uint8_t* drow = dst + r * 128;
         *reinterpret_cast<uint4*>(drow + (((2 * c) ^ (r & 7)) << 4)) = lo;
         *reinterpret_cast<uint4*>(drow + (((2 * c + 1) ^ (r & 7)) << 4)) = hi;
@@ -1046,12 +1085,12 @@ grouped_gemm_m256_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_c
     };
 
     if (n_it > 0) {
-      B8Cursor ld{static_cast<int>(blockIdx.x), 0, nullptr, nullptr}, cv = ld;
+      B8Cursor ld{static_cast<int>(blockIdx.x), 0, nullptr, nullptr}, cv;
       seek(ld);
       cv = ld;
       // four k-blocks of FP8 bytes in flight in registers: the converters are the busiest warps, so
       // the distance has to cover memory latency in units of their own work, not of the MMAs'
-      uint4 qa[M256_UNITS], qb[M256_UNITS], qc[M256_UNITS], qd[M256_UNITS];
+      uint4 qa[W8_UNITS], qb[W8_UNITS], qc[W8_UNITS], qd[W8_UNITS];
       fetch(ld, qa);
       fetch(ld, qb);
       fetch(ld, qc);
@@ -1068,26 +1107,28 @@ grouped_gemm_m256_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_c
       }
     }
   } else {
-    // ---------------- epilogue: both 128-row halves, one after the other ----------------
+    // ---------------- epilogue: the tile's 128-row halves, one after the other ----------------
     const int quarter = warp & 3;
     EpiWarp ew{epi_stage + quarter * 2 * EPI_PIECE_BYTES, 0u, lane, 2};
     uint32_t tcount = 0;
     for (int tile = blockIdx.x; tile < total_tiles && !*abort_flag; tile += gridDim.x, ++tcount) {
-      const Tile2 t = locate_tile2(tile, s_pad, s_cnt, s_pp, g.n_groups, g.n_tiles, g.n_per_group);
-      if (!mbar_wait(smem_u32(tfull), tcount & 1u, abort_flag, g.status, 24)) break;
+      const Tile2 t = locate_w8<TM>(tile, s_pad, s_cnt, s_pp, g);
+      const uint32_t acc = C::NACC == 2 ? (tcount & 1u) : 0u;
+      const uint32_t acc_ph = C::NACC == 2 ? ((tcount >> 1) & 1u) : (tcount & 1u);
+      if (!mbar_wait(smem_u32(&tfull[acc]), acc_ph, abort_flag, g.status, 24)) break;
       tc_fence_after();
 #pragma unroll 1
-      for (int sub = 0; sub < 2; ++sub) {
+      for (int sub = 0; sub < C::SUBS; ++sub) {
         const int first = sub * BM + quarter * 32;                 // first row of this warp inside the tile
         if (first >= t.rows_left) break;                           // nothing of this warp's to store
-        const uint32_t taddr = tmem_base + sub * ACC_COLS + (static_cast<uint32_t>(quarter * 32) << 16);
+        const uint32_t taddr = tmem_base + (acc + sub) * ACC_COLS + (static_cast<uint32_t>(quarter * 32) << 16);
         const bool live = first + lane < t.rows_left;
         epilogue_rows<EPI>(taddr, g, &tmC, ew, static_cast<long long>(t.row0) + first + lane, t.row0 + first, t.n_idx,
-                           live, first < t.rows_left);
+                           live, true);
       }
       tc_fence_before();
       __syncwarp();
-      if (lane == 0) mbar_arrive(smem_u32(tempty));
+      if (lane == 0) mbar_arrive(smem_u32(&tempty[acc]));
     }
     epilogue_drain(ew);
   }
@@ -1185,12 +1226,14 @@ static int launch_pair(const CUtensorMap& ta, const CUtensorMap& tb, const CUten
   return MG_OK;
 }
 
-template <int EPI>
-static int launch_m256(const CUtensorMap& ta, const CUtensorMap& tc, const void* b8, const GemmArgs& args, int grid,
-                       cudaStream_t st) {
-  MG_CUDA(cudaFuncSetAttribute(grouped_gemm_m256_kernel<EPI>, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                               static_cast<int>(M256_SMEM_BYTES)));
-  grouped_gemm_m256_kernel<EPI><<<grid, M256_THREADS, M256_SMEM_BYTES, st>>>(ta, tc, static_cast<const uint8_t*>(b8), args);
+template <int EPI, int TM>
+static int launch_w8(const CUtensorMap& ta, const CUtensorMap& tc, const void* b8, const GemmArgs& args, int grid,
+                     cudaStream_t st) {
+  constexpr size_t smem = CfgW8<TM>::SMEM_BYTES;
+  static_assert(smem <= 232448, "shared memory of the W8A16 kernel exceeds the 227 KiB a CTA may have");
+  MG_CUDA(cudaFuncSetAttribute(grouped_gemm_w8_kernel<EPI, TM>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                               static_cast<int>(smem)));
+  grouped_gemm_w8_kernel<EPI, TM><<<grid, W8_THREADS, smem, st>>>(ta, tc, static_cast<const uint8_t*>(b8), args);
   MG_CUDA(cudaGetLastError());
   return MG_OK;
 }
@@ -1213,10 +1256,11 @@ int launch_grouped_gemm(const Handle* h, const GemmProblem& p, cudaStream_t st) 
   }
   // SM pairs (2-CTA tiles of 256 x 256) for the bf16 expert GEMMs unless switched off
   const bool pair = h->opt_pair_gemm && !f32_out;
-  // FP8 weights converted in the kernel: 256-row tiles once experts average 120 live rows (a_rows
-  // also counts up to 127 rows of padding per expert); below that most tall tiles would be half
-  // empty and the 128-row kernel, which overlaps its epilogue, does the same work sooner
-  const bool m256 = p.b_fp8 && !pair && !f32_out && h->opt_fp8_m256 && !dense &&
+  // FP8 weights converted in the kernel (one CTA per SM): 256-row tiles once experts average 120
+  // live rows (a_rows also counts up to 127 rows of padding per expert); below that most tall tiles
+  // would be half empty, the layer is bound by streaming the weights from HBM, and the 128-row
+  // kernel, whose FP8 bytes arrive by TMA, streams them faster than register loads do
+  const bool m256 = p.b_fp8 && !pair && !f32_out && !dense && h->opt_fp8_m256 &&
                     p.a_rows >= static_cast<int64_t>(p.n_groups) * (h->opt_fp8_m256 == 2 ? 0 : 120 + 127);
   CUtensorMap ta, tb;
   int rc = encode_2d(&ta, p.a, static_cast<uint64_t>(p.a_rows), static_cast<uint64_t>(p.K), m256 ? 2 * BM : BM);
@@ -1268,8 +1312,8 @@ int launch_grouped_gemm(const Handle* h, const GemmProblem& p, cudaStream_t st) 
     long long tall_tiles = ((p.a_rows / BM + p.n_groups) / 2 + 1) * static_cast<long long>(a.n_tiles);
     int ctas = tall_tiles < h->sm_count ? static_cast<int>(tall_tiles) : h->sm_count;
     switch (p.epilogue) {
-      case EPI_SWIGLU_BF16: return launch_m256<EPI_SWIGLU_BF16>(ta, tc, p.b, a, ctas, st);
-      case EPI_PLAIN_BF16: return launch_m256<EPI_PLAIN_BF16>(ta, tc, p.b, a, ctas, st);
+      case EPI_SWIGLU_BF16: return launch_w8<EPI_SWIGLU_BF16, 256>(ta, tc, p.b, a, ctas, st);
+      case EPI_PLAIN_BF16: return launch_w8<EPI_PLAIN_BF16, 256>(ta, tc, p.b, a, ctas, st);
     }
   }
   if (pair) {
