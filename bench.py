@@ -484,10 +484,11 @@ def main():
                 "peak_kind": f"of {peak_kind} sustained bf16 GEMM", "frac_of_burst": tf / peaks.get("bf16_tflops", 1590.0),
                 "traffic": None}
     if world == 1 and name == "v3" and args.fp8_mode in (-1, 0, 1) and T == WORKLOADS["v3"][12]:
-        # DRAM bytes of one launch (one chunk of 32 experts): 1.10 x the algorithmic 3.09 GB, the ratio
-        # ncu measured on the 4-expert launches of the v3_small case (profiles/grouped_gemm_gate_up__v3_small.md)
-        roofline["traffic"] = 3.4e9
-        roofline["traffic_note"] = "bytes per launch, scaled from the ncu capture of the v3_small case"
+        # DRAM bytes of one launch (one chunk of 32 experts): mean of the 8 launches of a forward at this
+        # size, ncu's dram__bytes_read.sum + dram__bytes_write.sum (1-pass counters); the algorithmic
+        # bytes are 3.09 GB (profiles/grouped_gemm_gate_up__v3_small.md)
+        roofline["traffic"] = 4.88e9
+        roofline["traffic_note"] = "bytes per launch, ncu 1-pass DRAM counters on this workload"
     hbm = peaks.get("hbm_gbs", FALLBACK_PEAKS["hbm_gbs"])
     Tl = T_total // world
     algl = algorithmic(name, Tl)
