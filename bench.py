@@ -295,6 +295,10 @@ def main():
     ap.add_argument("--no-check", action="store_true")
     ap.add_argument("--chunk-tokens", type=int, default=16384)
     ap.add_argument("--micro", type=int, default=1, help="token micro-batches pipelined in the expert-parallel forward")
+    ap.add_argument("--capacity-factor", type=float, default=0.0,
+                    help="expert-parallel receive buffers, in multiples of the mean rows per GPU (default 2, 8 with --zipf)")
+    ap.add_argument("--ep-dedup", type=int, default=1,
+                    help="expert parallel: 1 sends one row per (token, destination GPU), 0 one per (token, expert)")
     ap.add_argument("--pair-gemm", type=int, default=-1, help="1/0 force the SM-pair expert GEMM on/off")
     ap.add_argument("--fp8-mode", type=int, default=-1, help="0 auto, 1 pre-dequantise, 2 convert in the GEMM")
     ap.add_argument("--fp8-tall", type=int, default=-1, help="convert-in-GEMM tile height: 0 128 rows, 1 auto, 2 256 rows")
@@ -348,7 +352,10 @@ def main():
     else:
         from moe_gen_b200.ep import EPMoELayer
         assert T % world == 0
-        layer = EPMoELayer(build_layer(name, device, rank, world, args.zipf), n_micro=args.micro)
+        # skewed routing can send most rows to one GPU: size the receive buffers for it
+        cap = args.capacity_factor if args.capacity_factor > 0 else (float(world) if args.zipf > 0 else 2.0)
+        layer = EPMoELayer(build_layer(name, device, rank, world, args.zipf), capacity_factor=cap, n_micro=args.micro,
+                           dedup=bool(args.ep_dedup))
         x = make_tokens(name, T // world, device, rank, args.zipf)
         step = lambda: layer.forward(x)                                   # noqa: E731
         T_total = T
@@ -462,6 +469,16 @@ def main():
                "h2d_bytes_per_step": xh.numel() * 2 * world, "d2h_bytes_per_step": yh.numel() * 2 * world,
                "equals_device_path": bool(torch.equal(yh.view(torch.int16), y.cpu().view(torch.int16)))}
 
+    # rows each GPU's experts receive (all ranks' picks), for the load-balance figures
+    ep_load = None
+    if world > 1:
+        idx_l, _ = base.route_topk(base.gate_logits(x))
+        hist = torch.bincount(idx_l.view(-1).long(), minlength=E).to(torch.int64)
+        dist.all_reduce(hist)
+        per_gpu = hist.view(world, E // world).sum(1).cpu().tolist()
+        ep_load = {"rows_per_gpu": per_gpu, "max_over_mean": max(per_gpu) * world / max(sum(per_gpu), 1),
+                   "capacity_factor": cap}
+
     if rank != 0:
         if world > 1:
             dist.destroy_process_group()
@@ -528,7 +545,7 @@ def main():
            "warmup": warmup, "ms_per_step": ms_per_step, "higher_is_better": True, "scaling": "strong",
            "vs_baseline": None, "dtype": "bf16", "data": "synthetic", "config": config, "clocks": clocks,
            "e2e": e2e, "gpu_launches": launches * args.steps, "roofline": roofline, "cpu_baseline": cpu,
-           "stages": stages, "check": check,
+           "stages": stages, "check": check, "ep_load": ep_load,
            "layer_tflops": (alg["gemm1_flops"] + alg["gemm2_flops"] + alg["shared_flops"] + alg["gate_flops"])
            / (ms_per_step * 1e-3) / 1e12 / world}
     print(json.dumps(out), flush=True)

@@ -296,6 +296,22 @@ int mg_ep_place(mg_handle h, const int32_t* d_topk_idx, int64_t n_tokens, const 
 int mg_ep_dispatch(mg_handle h, const void* d_x, const int32_t* d_dst, int64_t n_tokens,
                    void* const* peer_recv, void* stream);
 
+/* The same dispatch with one row per (token, destination rank) on the wire instead of one per
+ * (token, expert): with group-limited routing several of a token's experts live on the same rank
+ * (DeepSeek-V3 on 8 ranks: 8 picks on at most 4 ranks).  Every rank owns a duplicate table of
+ * cap_rows int32 next to its recv_x (peer_dup[ep_size], mapped like peer_recv):
+ *   1. the owner sets its table to -1 (mg_ep_clear_duplicates) before the ranks exchange counts,
+ *   2. mg_ep_dispatch_dedup sends the row of a token's first pick on a rank and, for its later
+ *      picks on that rank, writes the first pick's row number into the owner's table,
+ *   3. after the barrier that follows the dispatch the owner copies those rows inside its own
+ *      recv_x (mg_ep_fill_duplicates), then runs mg_expert_ffn.
+ * recv_x ends up bit-identical to what mg_ep_dispatch leaves.  No reference counterpart: its
+ * all_to_all sends every (token, expert) row (modeling_deepseek_v3.py:656-659). */
+int mg_ep_clear_duplicates(mg_handle h, void* d_dup, int64_t cap_rows, void* stream);
+int mg_ep_dispatch_dedup(mg_handle h, const void* d_x, const int32_t* d_dst, int64_t n_tokens,
+                         void* const* peer_recv, void* const* peer_dup, void* stream);
+int mg_ep_fill_duplicates(mg_handle h, void* d_recv_x, const void* d_dup, int64_t cap_rows, void* stream);
+
 /* peer_out[ep_size]: every rank's out_rows.  Replaces the return all_to_all and the
  * weighted sum (modeling_deepseek_v3.py:692-710). */
 int mg_ep_combine(mg_handle h, void* const* peer_out, const int32_t* d_dst, const int32_t* d_topk_idx,

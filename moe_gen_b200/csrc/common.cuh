@@ -88,7 +88,8 @@ int launch_combine(const Handle* h, const void* out_rows, const int32_t* dst_row
 
 struct PeerPtrs { void* p[kMaxPeers]; };
 int launch_dispatch_rows(const Handle* h, const void* x, const int32_t* dst, int64_t T,
-                         const PeerPtrs& peers, cudaStream_t st);
+                         const PeerPtrs& peers, const PeerPtrs* dups, cudaStream_t st);
+int launch_fill_duplicates(const Handle* h, void* rows, const int32_t* dup, int64_t n_rows, cudaStream_t st);
 int launch_combine_peers(const Handle* h, const PeerPtrs& peers, const int32_t* dst,
                          const int32_t* idx, const float* w, const void* shared, int64_t T, void* y,
                          cudaStream_t st);

@@ -91,7 +91,38 @@ int mg_ep_dispatch(mg_handle hh, const void* d_x, const int32_t* d_dst, int64_t 
   PeerPtrs peers;
   int rc = gather_peers(h, peer_recv, &peers);
   if (rc != MG_OK) return rc;
-  return launch_dispatch_rows(h, d_x, d_dst, T, peers, static_cast<cudaStream_t>(stream));
+  return launch_dispatch_rows(h, d_x, d_dst, T, peers, nullptr, static_cast<cudaStream_t>(stream));
+}
+
+int mg_ep_dispatch_dedup(mg_handle hh, const void* d_x, const int32_t* d_dst, int64_t T, void* const* peer_recv,
+                         void* const* peer_dup, void* stream) {
+  Handle* h = check_handle(hh);
+  if (!h) return MG_ERR_STATE;
+  MG_REQUIRE(T >= 0, MG_ERR_SHAPE, "negative token count");
+  if (T == 0) return MG_OK;
+  MG_REQUIRE(d_x && d_dst, MG_ERR_NULL, "mg_ep_dispatch_dedup: null pointer");
+  PeerPtrs peers, dups;
+  int rc = gather_peers(h, peer_recv, &peers);
+  if (rc != MG_OK) return rc;
+  rc = gather_peers(h, peer_dup, &dups);
+  if (rc != MG_OK) return rc;
+  return launch_dispatch_rows(h, d_x, d_dst, T, peers, &dups, static_cast<cudaStream_t>(stream));
+}
+
+int mg_ep_clear_duplicates(mg_handle hh, void* d_dup, int64_t cap_rows, void* stream) {
+  Handle* h = check_handle(hh);
+  if (!h) return MG_ERR_STATE;
+  MG_REQUIRE(d_dup && cap_rows >= 0, MG_ERR_NULL, "mg_ep_clear_duplicates: bad argument");
+  MG_CUDA(cudaMemsetAsync(d_dup, 0xFF, static_cast<size_t>(cap_rows) * 4, static_cast<cudaStream_t>(stream)));
+  return MG_OK;
+}
+
+int mg_ep_fill_duplicates(mg_handle hh, void* d_recv_x, const void* d_dup, int64_t cap_rows, void* stream) {
+  Handle* h = check_handle(hh);
+  if (!h) return MG_ERR_STATE;
+  MG_REQUIRE(d_recv_x && d_dup && cap_rows >= 0, MG_ERR_NULL, "mg_ep_fill_duplicates: bad argument");
+  return launch_fill_duplicates(h, d_recv_x, static_cast<const int32_t*>(d_dup), cap_rows,
+                                static_cast<cudaStream_t>(stream));
 }
 
 int mg_ep_combine(mg_handle hh, void* const* peer_out, const int32_t* d_dst, const int32_t* d_topk_idx,

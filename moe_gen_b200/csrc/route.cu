@@ -403,16 +403,32 @@ int launch_permute_plan_static(const Handle* h, const int32_t* idx, int64_t T, i
 // row scatter: one warp per token, x row read once, written to each destination row
 // ---------------------------------------------------------------------------------------
 // PEER: dst_row packs (destination rank << kPeerShift | row) and rows are written to that
-// rank's buffer through its peer mapping (plain stores over NVLink)
-template <bool PEER>
+// rank's buffer through its peer mapping (plain stores over NVLink).
+// DEDUP: when several picks of a token go to the same rank, only the first one's row travels; for
+// the others the kernel writes, into the destination rank's duplicate table at the pick's row, the
+// row of that first pick, and the owner copies the row locally (fill_duplicate_rows_kernel).
+template <bool PEER, bool DEDUP>
 __global__ void __launch_bounds__(256) permute_rows_kernel(const uint4* __restrict__ x,
                                                            const int32_t* __restrict__ dst_row,
                                                            int64_t T, int k, int vec_per_row,
-                                                           PeerPtrs bufs) {
+                                                           PeerPtrs bufs, PeerPtrs dups) {
   const int lane = threadIdx.x & 31;
   const int64_t t = static_cast<int64_t>(blockIdx.x) * (blockDim.x >> 5) + (threadIdx.x >> 5);
   if (t >= T) return;
   int32_t my_dst = lane < k ? dst_row[t * k + lane] : -1;
+  uint32_t skip = 0;                           // bit j: pick j's row is copied on its owner
+  if (DEDUP) {
+    int my_first = -1;                         // earliest pick of this token with my destination rank
+    for (int j = 0; j < k; ++j) {
+      const int32_t d = __shfl_sync(0xFFFFFFFFu, my_dst, j);
+      if (my_first < 0 && j < lane && d >= 0 && my_dst >= 0 && (d >> kPeerShift) == (my_dst >> kPeerShift))
+        my_first = j;
+    }
+    const int32_t first_dst = __shfl_sync(0xFFFFFFFFu, my_dst, my_first < 0 ? 0 : my_first);
+    if (my_first >= 0)
+      static_cast<int32_t*>(dups.p[my_dst >> kPeerShift])[my_dst & kPeerRowMask] = first_dst & kPeerRowMask;
+    skip = __ballot_sync(0xFFFFFFFFu, my_first >= 0);
+  }
   const uint4* src = x + t * vec_per_row;
   for (int v0 = 0; v0 < vec_per_row; v0 += 128) {
     uint4 val[4];
@@ -423,7 +439,7 @@ __global__ void __launch_bounds__(256) permute_rows_kernel(const uint4* __restri
     }
     for (int j = 0; j < k; ++j) {
       int32_t d = __shfl_sync(0xFFFFFFFFu, my_dst, j);
-      if (d < 0) continue;
+      if (d < 0 || ((skip >> j) & 1u)) continue;
       uint4* dst = static_cast<uint4*>(PEER ? bufs.p[d >> kPeerShift] : bufs.p[0]) +
                    static_cast<int64_t>(PEER ? (d & kPeerRowMask) : d) * vec_per_row;
 #pragma unroll
@@ -435,6 +451,34 @@ __global__ void __launch_bounds__(256) permute_rows_kernel(const uint4* __restri
   }
 }
 
+// Owner side of the de-duplicated dispatch: row r with dup[r] >= 0 becomes a copy of row dup[r]
+// (both in this rank's receive buffer).  Rows without an entry keep the -1 the owner wrote before
+// the dispatch.
+__global__ void __launch_bounds__(256) fill_duplicate_rows_kernel(uint4* __restrict__ rows,
+                                                                  const int32_t* __restrict__ dup,
+                                                                  int64_t n_rows, int vec_per_row) {
+  const int lane = threadIdx.x & 31;
+  const int64_t r = static_cast<int64_t>(blockIdx.x) * (blockDim.x >> 5) + (threadIdx.x >> 5);
+  if (r >= n_rows) return;
+  const int32_t s = dup[r];
+  if (s < 0) return;
+  const uint4* src = rows + static_cast<int64_t>(s) * vec_per_row;
+  uint4* dst = rows + r * vec_per_row;
+  for (int v0 = 0; v0 < vec_per_row; v0 += 128) {
+    uint4 val[4];
+#pragma unroll
+    for (int u = 0; u < 4; ++u) {
+      int v = v0 + u * 32 + lane;
+      if (v < vec_per_row) val[u] = src[v];
+    }
+#pragma unroll
+    for (int u = 0; u < 4; ++u) {
+      int v = v0 + u * 32 + lane;
+      if (v < vec_per_row) dst[v] = val[u];
+    }
+  }
+}
+
 int launch_permute_rows(const Handle* h, const void* x, const int32_t* dst_row, int64_t T,
                         void* perm_x, cudaStream_t st) {
   if (T == 0) return MG_OK;
@@ -442,19 +486,32 @@ int launch_permute_rows(const Handle* h, const void* x, const int32_t* dst_row, 
   dim3 grid(static_cast<unsigned>((T + warps - 1) / warps)), block(warps * 32);
   PeerPtrs bufs{};
   bufs.p[0] = perm_x;
-  permute_rows_kernel<false><<<grid, block, 0, st>>>(static_cast<const uint4*>(x), dst_row, T,
-                                                     h->d.top_k, h->d.hidden / 8, bufs);
+  permute_rows_kernel<false, false><<<grid, block, 0, st>>>(static_cast<const uint4*>(x), dst_row, T,
+                                                            h->d.top_k, h->d.hidden / 8, bufs, bufs);
   MG_CUDA(cudaGetLastError());
   return MG_OK;
 }
 
 int launch_dispatch_rows(const Handle* h, const void* x, const int32_t* dst, int64_t T,
-                         const PeerPtrs& peers, cudaStream_t st) {
+                         const PeerPtrs& peers, const PeerPtrs* dups, cudaStream_t st) {
   if (T == 0) return MG_OK;
   const int warps = 8;
   dim3 grid(static_cast<unsigned>((T + warps - 1) / warps)), block(warps * 32);
-  permute_rows_kernel<true><<<grid, block, 0, st>>>(static_cast<const uint4*>(x), dst, T,
-                                                    h->d.top_k, h->d.hidden / 8, peers);
+  if (dups != nullptr)
+    permute_rows_kernel<true, true><<<grid, block, 0, st>>>(static_cast<const uint4*>(x), dst, T,
+                                                            h->d.top_k, h->d.hidden / 8, peers, *dups);
+  else
+    permute_rows_kernel<true, false><<<grid, block, 0, st>>>(static_cast<const uint4*>(x), dst, T,
+                                                             h->d.top_k, h->d.hidden / 8, peers, peers);
+  MG_CUDA(cudaGetLastError());
+  return MG_OK;
+}
+
+int launch_fill_duplicates(const Handle* h, void* rows, const int32_t* dup, int64_t n_rows, cudaStream_t st) {
+  if (n_rows == 0) return MG_OK;
+  const int warps = 8;
+  dim3 grid(static_cast<unsigned>((n_rows + warps - 1) / warps)), block(warps * 32);
+  fill_duplicate_rows_kernel<<<grid, block, 0, st>>>(static_cast<uint4*>(rows), dup, n_rows, h->d.hidden / 8);
   MG_CUDA(cudaGetLastError());
   return MG_OK;
 }

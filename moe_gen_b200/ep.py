@@ -67,7 +67,7 @@ class EPMoELayer:
     PHASES = ["route_dispatch", "expert_ffn", "combine"]
 
     def __init__(self, layer: MoELayer, group: Optional[dist.ProcessGroup] = None, capacity_factor: float = 2.0,
-                 n_micro: int = 1):
+                 n_micro: int = 1, dedup: bool = True):
         self.layer = layer
         self.group = group
         self.rank = dist.get_rank(group)
@@ -75,6 +75,9 @@ class EPMoELayer:
         assert layer.desc.ep_size == self.world and layer.desc.ep_rank == self.rank
         self.capacity_factor = capacity_factor
         self.n_micro = max(1, n_micro)
+        # one row per (token, destination rank) over NVLink; the owner copies the rows of a token's
+        # further experts on that rank (pays off when top_k exceeds the number of ranks a token reaches)
+        self.dedup = dedup
         self.lib = layer.lib
         self.dev = layer.device
         self._mbs: List[_MicroBatch] = []
@@ -107,9 +110,9 @@ class EPMoELayer:
                 assert cap < (1 << PEER_SHIFT)
                 mb.cap = cap
                 mb.own = []
-                for _ in range(2):                             # recv_x, out_rows
+                for nbytes in (cap * lay.H * 2, cap * lay.H * 2, cap * 4):   # recv_x, out_rows, duplicate table
                     p = C.c_void_p()
-                    L.check(self.lib.mg_ep_alloc(cap * lay.H * 2, C.byref(p)))
+                    L.check(self.lib.mg_ep_alloc(nbytes, C.byref(p)))
                     hd = (C.c_ubyte * 64)()
                     L.check(self.lib.mg_ep_export(p, hd))
                     mb.own.append(p.value)
@@ -137,17 +140,18 @@ class EPMoELayer:
             for i, mb in enumerate(self._mbs):
                 recv = (C.c_void_p * self.world)()
                 out = (C.c_void_p * self.world)()
+                dup = (C.c_void_p * self.world)()
                 for r in range(self.world):
                     if r == self.rank:
-                        recv[r], out[r] = mb.own[0], mb.own[1]
+                        recv[r], out[r], dup[r] = mb.own[0], mb.own[1], mb.own[2]
                         continue
-                    for which, table in ((0, recv), (1, out)):
+                    for which, table in ((0, recv), (1, out), (2, dup)):
                         p = C.c_void_p()
-                        buf = (C.c_ubyte * 64).from_buffer_copy(gathered[r][2 * i + which])
+                        buf = (C.c_ubyte * 64).from_buffer_copy(gathered[r][3 * i + which])
                         L.check(self.lib.mg_ep_import(buf, C.byref(p)))
                         table[r] = p.value
                         mb.imported.append(p.value)
-                mb.peer_recv, mb.peer_out = recv, out
+                mb.peer_recv, mb.peer_out, mb.peer_dup = recv, out, dup
             self.hs = torch.empty(T, max(lay.Is, 1), dtype=torch.bfloat16, device=self.dev)
             self.shared_out = torch.empty(T, lay.H, dtype=torch.bfloat16, device=self.dev) if lay.Is else None
             nd = C.c_size_t()
@@ -230,6 +234,9 @@ class EPMoELayer:
                 Tm = mb.t1 - mb.t0
                 xp = x2.data_ptr() + mb.t0 * H2
                 with torch.cuda.stream(mb.stream):
+                    if self.dedup:
+                        # before this rank joins the count exchange, i.e. before any rank can dispatch
+                        L.check(lib.mg_ep_clear_duplicates(h, mb.own[2], mb.cap, st))
                     L.check(lib.mg_gate_logits(h, xp, lay.gate_w.data_ptr(), Tm, mb.logits.data_ptr(), st))
                     L.check(lib.mg_route_topk(h, mb.logits.data_ptr(), _ptr(lay.bias), Tm, mb.idx.data_ptr(),
                                               mb.w.data_ptr(), st))
@@ -246,10 +253,15 @@ class EPMoELayer:
                                                   self.shared_out.data_ptr(), self._side.cuda_stream))
                     if sent is not None:
                         mb.stream.wait_event(sent)
-                    L.check(lib.mg_ep_dispatch(h, xp, mb.dst.data_ptr(), Tm, mb.peer_recv, st))
+                    if self.dedup:
+                        L.check(lib.mg_ep_dispatch_dedup(h, xp, mb.dst.data_ptr(), Tm, mb.peer_recv, mb.peer_dup, st))
+                    else:
+                        L.check(lib.mg_ep_dispatch(h, xp, mb.dst.data_ptr(), Tm, mb.peer_recv, st))
                     sent = torch.cuda.Event()
                     sent.record(mb.stream)
                     self._barrier(mb)                # all rows have landed in the owners' recv_x
+                    if self.dedup:
+                        L.check(lib.mg_ep_fill_duplicates(h, mb.own[0], mb.own[2], mb.cap, st))
             self._mark(evs, s0)
             # ---- experts, one micro-batch after the other on the tensor cores
             prev = None

@@ -69,6 +69,9 @@ SIGNATURES = {
     "mg_ep_count": [_vp, _vp, _i64, _vp, _vp, _vp],
     "mg_ep_place": [_vp, _vp, _i64, _vp, _i64, _vp, _vp, _vp, _vp, _vp],
     "mg_ep_dispatch": [_vp, _vp, _vp, _i64, _P(_vp), _vp],
+    "mg_ep_dispatch_dedup": [_vp, _vp, _vp, _i64, _P(_vp), _P(_vp), _vp],
+    "mg_ep_clear_duplicates": [_vp, _vp, _i64, _vp],
+    "mg_ep_fill_duplicates": [_vp, _vp, _vp, _i64, _vp],
     "mg_ep_combine": [_vp, _P(_vp), _vp, _vp, _vp, _vp, _i64, _vp, _vp],
     "mg_set_option": [_vp, _i32, _i32],
     "mg_set_stage_timing": [_vp, _i32],

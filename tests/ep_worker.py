@@ -105,9 +105,13 @@ def gpu_ep_worker(rank, world, port, spec, T_global, seed, result):
         y = ep.forward(x)
         torch.cuda.synchronize()
         ys.append(y.cpu())
+    ep.dedup = False                                     # one row per (token, expert) on the wire
+    y_plain = ep.forward(x)
+    torch.cuda.synchronize()
+    same = bool(torch.equal(y_plain.cpu().view(torch.int16), ys[0].view(torch.int16)))
     status = layer.device_status()
     gath = [None] * world
-    dist.all_gather_object(gath, (ys[0], ys[1], status))
+    dist.all_gather_object(gath, (ys[0], ys[1], status, same))
     if rank == 0:
         gold = O.layer_forward(spec, x_all, W, gold_fp32=True)
         y0 = torch.cat([g[0] for g in gath]).float()
@@ -115,6 +119,7 @@ def gpu_ep_worker(rank, world, port, spec, T_global, seed, result):
         result["rel_l2"] = O.rel_l2(y0, gold["y"])
         result["repeat_equal"] = bool(torch.equal(y0, y1))
         result["status"] = [g[2] for g in gath]
+        result["dedup_equal"] = all(g[3] for g in gath)
     dist.barrier()
     ep.close()
     dist.destroy_process_group()

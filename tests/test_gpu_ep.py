@@ -37,4 +37,5 @@ def test_expert_parallel_on_two_gpus(built_lib, spec, T):
         assert all(p.exitcode == 0 for p in procs), [p.exitcode for p in procs]
         assert all(s == (0, 0) for s in result["status"]), result["status"]
         assert result["repeat_equal"]
+        assert result["dedup_equal"]          # de-duplicated dispatch leaves the same rows as the plain one
         assert result["rel_l2"] <= (1e-2 if spec.gating != O.GATE_SOFTMAX_TOPK_RENORM else 3e-2)

@@ -453,8 +453,9 @@ def test_bounded_wait_gives_up_and_reports(built_lib):
     assert O.rel_l2(y.cpu().float(), O.layer_forward(spec, x, W, gold_fp32=True)["y"]) <= TOL_LAYER
 
 
+@pytest.mark.parametrize("dedup", [False, True])
 @pytest.mark.parametrize("n_ranks", [2, 4])
-def test_expert_parallel_ranks_emulated_on_one_gpu(built_lib, n_ranks):
+def test_expert_parallel_ranks_emulated_on_one_gpu(built_lib, n_ranks, dedup):
     """The expert-parallel kernels (layout, peer scatter, peer gather) run for every rank in turn in
     one process, the 'peer' buffers being ordinary allocations of this GPU.  The result must equal
     the single-GPU forward bit for bit, and the layout must equal its host restatement."""
@@ -478,6 +479,10 @@ def test_expert_parallel_ranks_emulated_on_one_gpu(built_lib, n_ranks):
     peer_recv = (C.c_void_p * n_ranks)(*[t.data_ptr() for t in recv])
     peer_out = (C.c_void_p * n_ranks)(*[t.data_ptr() for t in outb])
     i32 = dict(dtype=torch.int32, device=DEV)
+    dupt = [torch.zeros(cap, **i32) for _ in range(n_ranks)]
+    peer_dup = (C.c_void_p * n_ranks)(*[t.data_ptr() for t in dupt])
+    for r, lay in enumerate(ranks):
+        L.check(lib.mg_ep_clear_duplicates(lay._h, dupt[r].data_ptr(), cap, st))
     idx, w, counts, plan_ws = [], [], [], []
     for r, lay in enumerate(ranks):
         xs = xd[r * Tl:(r + 1) * Tl]
@@ -494,7 +499,11 @@ def test_expert_parallel_ranks_emulated_on_one_gpu(built_lib, n_ranks):
         d = torch.empty(Tl, k, **i32); c = torch.empty(El, **i32); p = torch.empty(El + 1, **i32)
         L.check(lib.mg_ep_place(lay._h, idx[r].data_ptr(), Tl, counts_all.data_ptr(), cap, plan_ws[r].data_ptr(),
                                 c.data_ptr(), p.data_ptr(), d.data_ptr(), st))
-        L.check(lib.mg_ep_dispatch(lay._h, xd[r * Tl:(r + 1) * Tl].data_ptr(), d.data_ptr(), Tl, peer_recv, st))
+        if dedup:
+            L.check(lib.mg_ep_dispatch_dedup(lay._h, xd[r * Tl:(r + 1) * Tl].data_ptr(), d.data_ptr(), Tl, peer_recv,
+                                             peer_dup, st))
+        else:
+            L.check(lib.mg_ep_dispatch(lay._h, xd[r * Tl:(r + 1) * Tl].data_ptr(), d.data_ptr(), Tl, peer_recv, st))
         dst.append(d); rc.append(c); rp.append(p)
         base, ref_c, ref_p, over = ep_layout_reference(counts_all.cpu().numpy(), r, El, cap)
         assert not over.any()
@@ -503,6 +512,20 @@ def test_expert_parallel_ranks_emulated_on_one_gpu(built_lib, n_ranks):
         flat_idx, flat_dst = idx[r].cpu().view(-1).long(), d.cpu().view(-1).long()
         for e in flat_idx.unique().tolist():
             assert int(flat_dst[flat_idx == e].min()) == int(base[e])
+    if dedup:
+        # with 4 picks on 2 or 4 ranks some picks must share a rank: the tables are in use
+        assert sum(int((t >= 0).sum()) for t in dupt) > 0
+        for r, lay in enumerate(ranks):
+            L.check(lib.mg_ep_fill_duplicates(lay._h, recv[r].data_ptr(), dupt[r].data_ptr(), cap, st))
+        # every live row of every receive buffer holds the hidden state of the token that picked it
+        for r in range(n_ranks):
+            got = recv[r].cpu()
+            for s_ in range(n_ranks):
+                d_ = dst[s_].cpu().long().view(-1)
+                mine = (d_ >> 24) == r
+                rows = d_[mine] & 0xFFFFFF
+                toks = torch.arange(Tl).repeat_interleave(k)[mine] + s_ * Tl
+                assert torch.equal(got[rows].view(torch.int16), x[toks].view(torch.int16))
     for r, lay in enumerate(ranks):
         hb = torch.zeros(cap, spec.inter, dtype=torch.bfloat16, device=DEV)
         L.check(lib.mg_expert_ffn(lay._h, recv[r].data_ptr(), rp[r].data_ptr(), rc[r].data_ptr(), cap,
