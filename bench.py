@@ -293,6 +293,7 @@ def main():
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-e2e", action="store_true")
     ap.add_argument("--no-check", action="store_true")
+    ap.add_argument("--no-glue", action="store_true", help="skip the RMSNorm / residual-add measurement")
     ap.add_argument("--chunk-tokens", type=int, default=16384)
     ap.add_argument("--micro", type=int, default=1, help="token micro-batches pipelined in the expert-parallel forward")
     ap.add_argument("--capacity-factor", type=float, default=0.0,
@@ -535,6 +536,35 @@ def main():
         check = sample_check(name, layer, x, y, args.zipf)
         if check["worst_rel_l2_vs_torch_fp32"] > 1e-2:
             raise SystemExit(f"correctness gate failed: {check}")
+    # ---- decoder-layer glue: RMSNorm in front of the block, residual add inside the combine ----
+    glue = None
+    if world == 1 and not args.no_glue:
+        gw = (1.0 + 0.1 * torch.randn(H, device=device)).to(torch.bfloat16)
+        xn = torch.empty_like(x)
+        for _ in range(3):
+            layer.rmsnorm(x, gw, 1e-6, out=xn)
+        g0, g1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        g0.record()
+        for _ in range(20):
+            layer.rmsnorm(x, gw, 1e-6, out=xn)
+        g1.record()
+        torch.cuda.synchronize()
+        n_ms = g0.elapsed_time(g1) / 20
+        yb = torch.empty_like(x)
+        for _ in range(2):
+            layer.block_forward(x, gw, 1e-6, out=yb)
+        g0.record()
+        for _ in range(max(2, args.steps // 4)):
+            layer.block_forward(x, gw, 1e-6, out=yb)
+        g1.record()
+        torch.cuda.synchronize()
+        b_ms = g0.elapsed_time(g1) / max(2, args.steps // 4)
+        want = (x.float() + layer.forward(xn).float()).to(torch.bfloat16)
+        nbytes = 2 * T * H * 2 + H * 2
+        glue = {"rmsnorm_ms": round(n_ms, 4), "rmsnorm_gbs": round(nbytes / n_ms / 1e6, 1),
+                "rmsnorm_frac_of_hbm": round(nbytes / n_ms / 1e6 / hbm, 3), "block_ms": round(b_ms, 3),
+                "block_equals_norm_forward_add": bool(torch.equal(yb.view(torch.int16), want.view(torch.int16))),
+                "note": "block = hidden + moe(rmsnorm(hidden)); rmsnorm moves T*H*2 bytes in and out"}
     cpu = None
     if not args.no_cpu_baseline:
         r = cpu_reference(name, min(args.cpu_sample_tokens, T), 2, 1, args.zipf)
@@ -545,7 +575,7 @@ def main():
            "warmup": warmup, "ms_per_step": ms_per_step, "higher_is_better": True, "scaling": "strong",
            "vs_baseline": None, "dtype": "bf16", "data": "synthetic", "config": config, "clocks": clocks,
            "e2e": e2e, "gpu_launches": launches * args.steps, "roofline": roofline, "cpu_baseline": cpu,
-           "stages": stages, "check": check, "ep_load": ep_load,
+           "stages": stages, "check": check, "ep_load": ep_load, "glue": glue,
            "layer_tflops": (alg["gemm1_flops"] + alg["gemm2_flops"] + alg["shared_flops"] + alg["gate_flops"])
            / (ms_per_step * 1e-3) / 1e12 / world}
     print(json.dumps(out), flush=True)

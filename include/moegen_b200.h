@@ -318,6 +318,25 @@ int mg_ep_combine(mg_handle h, void* const* peer_out, const int32_t* d_dst, cons
                   const float* d_topk_w, const void* d_shared_out, int64_t n_tokens, void* d_y,
                   void* stream);
 
+/* ---- decoder-layer glue either side of the block -------------------------------------
+ * The caller of the MoE block normalises the residual stream in front of it and adds the block's
+ * output back (modeling_deepseek_v3.py:1361-1365: residual = h; h = post_attention_layernorm(h);
+ * h = mlp(h); h = residual + h).
+ *
+ * mg_rmsnorm: out[T,H] = weight * bf16(x * rsqrt(mean(x^2) + eps)); x, weight [H], out bf16;
+ * fp32 statistics (DeepseekV3RMSNorm.forward, modeling_deepseek_v3.py:125-150, with the bf16
+ * weight the model holds after model.to(bfloat16)).
+ *
+ * mg_moe_block_forward: out = hidden + moe(rmsnorm(hidden)).  The normalised rows go to d_xnorm
+ * ([T,H] bf16, caller's scratch, distinct from hidden and out); the residual add happens in the
+ * combine kernel (the block's output is rounded to bf16 first, as the reference's bf16 module
+ * output is), so d_out may be d_hidden.  Workspace as for mg_moe_forward. */
+int mg_rmsnorm(mg_handle h, const void* d_x, const void* d_weight, float eps, int64_t n_tokens,
+               void* d_out, void* stream);
+int mg_moe_block_forward(mg_handle h, const void* d_hidden, const void* d_norm_weight, float eps,
+                         int64_t n_tokens, const void* d_gate_w, const float* d_bias, const void* d_packed,
+                         void* d_xnorm, void* d_workspace, size_t workspace_bytes, void* d_out, void* stream);
+
 /* Pointers into a workspace laid out by mg_moe_forward, for tests and tools:
  * which = 0 logits, 1 topk_idx, 2 topk_w, 3 counts, 4 offsets, 5 pad_offsets,
  * 6 dst_row, 7 perm_x, 8 h_buf, 9 out_rows. */

@@ -471,7 +471,7 @@ int mg_combine(mg_handle hh, const void* d_out_rows, const int32_t* d_dst, const
   if (!h) return MG_ERR_STATE;
   MG_REQUIRE(d_out_rows && d_dst && d_idx && d_w && d_y, MG_ERR_NULL, "mg_combine: null pointer");
   MG_REQUIRE(T >= 0, MG_ERR_SHAPE, "negative token count");
-  return launch_combine(h, d_out_rows, d_dst, d_idx, d_w, d_shared, T, d_y, static_cast<cudaStream_t>(stream));
+  return launch_combine(h, d_out_rows, d_dst, d_idx, d_w, d_shared, nullptr, T, d_y, static_cast<cudaStream_t>(stream));
 }
 
 int mg_workspace_ptr(mg_handle hh, void* d_ws, int64_t max_tokens, int64_t max_rows, int32_t which, void** ptr) {
@@ -483,8 +483,10 @@ int mg_workspace_ptr(mg_handle hh, void* d_ws, int64_t max_tokens, int64_t max_r
   return MG_OK;
 }
 
-int mg_moe_forward(mg_handle hh, const void* d_x, int64_t T, const void* d_gate_w, const float* d_bias,
-                   const void* d_packed, void* d_ws, size_t ws_bytes, void* d_y, void* stream) {
+// d_residual: nullptr, or [T,H] bf16 added to the block's bf16 output in the combine (may be d_y)
+static int moe_forward_impl(mg_handle hh, const void* d_x, int64_t T, const void* d_gate_w, const float* d_bias,
+                            const void* d_packed, void* d_ws, size_t ws_bytes, const void* d_residual, void* d_y,
+                            void* stream) {
   Handle* h = check(hh);
   if (!h) return MG_ERR_STATE;
   MG_REQUIRE(T >= 0, MG_ERR_SHAPE, "negative token count");
@@ -549,13 +551,46 @@ int mg_moe_forward(mg_handle hh, const void* d_x, int64_t T, const void* d_gate_
     mark(h, MG_STAGE_SHARED_GEMM1, st);
   }
   mark(h, MG_STAGE_SHARED_GEMM2, st);
-  rc = launch_combine(h, orow, dst, idx, w, sh, T, d_y, st);
+  rc = launch_combine(h, orow, dst, idx, w, sh, d_residual, T, d_y, st);
   if (rc != MG_OK) return rc;
   mark(h, MG_STAGE_COMBINE, st);
   launches += 1;
   h->last_launches = launches;
   if (h->stage_timing) ++h->stage_calls;
   return MG_OK;
+}
+
+int mg_moe_forward(mg_handle hh, const void* d_x, int64_t T, const void* d_gate_w, const float* d_bias,
+                   const void* d_packed, void* d_ws, size_t ws_bytes, void* d_y, void* stream) {
+  return moe_forward_impl(hh, d_x, T, d_gate_w, d_bias, d_packed, d_ws, ws_bytes, nullptr, d_y, stream);
+}
+
+int mg_rmsnorm(mg_handle hh, const void* d_x, const void* d_weight, float eps, int64_t T, void* d_out,
+               void* stream) {
+  Handle* h = check(hh);
+  if (!h) return MG_ERR_STATE;
+  MG_REQUIRE(T >= 0, MG_ERR_SHAPE, "negative token count");
+  if (T == 0) return MG_OK;
+  MG_REQUIRE(d_x && d_weight && d_out, MG_ERR_NULL, "mg_rmsnorm: null pointer");
+  MG_REQUIRE(eps >= 0.f, MG_ERR_CONFIG, "mg_rmsnorm: negative eps");
+  return launch_rmsnorm(h, d_x, d_weight, eps, T, d_out, static_cast<cudaStream_t>(stream));
+}
+
+int mg_moe_block_forward(mg_handle hh, const void* d_hidden, const void* d_norm_weight, float eps, int64_t T,
+                         const void* d_gate_w, const float* d_bias, const void* d_packed, void* d_xnorm,
+                         void* d_ws, size_t ws_bytes, void* d_out, void* stream) {
+  Handle* h = check(hh);
+  if (!h) return MG_ERR_STATE;
+  MG_REQUIRE(T >= 0, MG_ERR_SHAPE, "negative token count");
+  if (T == 0) { h->last_launches = 0; return MG_OK; }
+  MG_REQUIRE(d_hidden && d_norm_weight && d_xnorm && d_out, MG_ERR_NULL, "mg_moe_block_forward: null pointer");
+  MG_REQUIRE(d_xnorm != d_hidden && d_xnorm != d_out, MG_ERR_CONFIG,
+             "mg_moe_block_forward: the normalised rows need a buffer of their own");
+  int rc = mg_rmsnorm(hh, d_hidden, d_norm_weight, eps, T, d_xnorm, stream);
+  if (rc != MG_OK) return rc;
+  rc = moe_forward_impl(hh, d_xnorm, T, d_gate_w, d_bias, d_packed, d_ws, ws_bytes, d_hidden, d_out, stream);
+  if (rc == MG_OK) h->last_launches += 1;
+  return rc;
 }
 
 int mg_set_option(mg_handle hh, int32_t option, int32_t value) {

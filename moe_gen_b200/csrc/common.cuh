@@ -83,7 +83,9 @@ int launch_permute_plan_static(const Handle* h, const int32_t* idx, int64_t T, i
 int launch_permute_rows(const Handle* h, const void* x, const int32_t* dst_row, int64_t T,
                         void* perm_x, cudaStream_t st);
 int launch_combine(const Handle* h, const void* out_rows, const int32_t* dst_row,
-                   const int32_t* idx, const float* w, const void* shared, int64_t T, void* y,
+                   const int32_t* idx, const float* w, const void* shared, const void* residual, int64_t T,
+                   void* y, cudaStream_t st);
+int launch_rmsnorm(const Handle* h, const void* x, const void* weight, float eps, int64_t T, void* out,
                    cudaStream_t st);
 
 struct PeerPtrs { void* p[kMaxPeers]; };

@@ -545,8 +545,9 @@ __global__ void __launch_bounds__(256) combine_kernel(PeerPtrs bufs,
                                                       const int32_t* __restrict__ topk_idx,
                                                       const float* __restrict__ topk_w,
                                                       const uint4* __restrict__ shared,
+                                                      const uint4* residual,
                                                       int64_t T, int k, int vec_per_row,
-                                                      uint4* __restrict__ y) {
+                                                      uint4* y) {
   const int lane = threadIdx.x & 31;
   const int64_t t = static_cast<int64_t>(blockIdx.x) * (blockDim.x >> 5) + (threadIdx.x >> 5);
   if (t >= T) return;
@@ -623,21 +624,29 @@ __global__ void __launch_bounds__(256) combine_kernel(PeerPtrs bufs,
 #pragma unroll
       for (int i = 0; i < 8; ++i) acc[i] = __fadd_rn(round_bf16(acc[i]), f[i]);
     }
+    if (residual != nullptr) {
+      // decoder-layer glue: the block's bf16 output is added to the bf16 residual stream (y may alias it)
+      float f[8];
+      unpack8(residual[t * vec_per_row + v], f);
+#pragma unroll
+      for (int i = 0; i < 8; ++i) acc[i] = __fadd_rn(round_bf16(acc[i]), f[i]);
+    }
     y[t * vec_per_row + v] = pack8(acc);
   }
 }
 
 template <bool PEER>
 static int launch_combine_impl(const Handle* h, const PeerPtrs& bufs, const int32_t* dst_row,
-                               const int32_t* idx, const float* w, const void* shared, int64_t T, void* y,
-                               cudaStream_t st) {
+                               const int32_t* idx, const float* w, const void* shared, const void* residual,
+                               int64_t T, void* y, cudaStream_t st) {
   if (T == 0) return MG_OK;
   const int warps = 8;
   dim3 grid(static_cast<unsigned>((T + warps - 1) / warps)), block(warps * 32);
   const int k = h->d.top_k, vpr = h->d.hidden / 8;
 #define MG_COMBINE_CASE(M)                                                                       \
   combine_kernel<M, PEER><<<grid, block, 0, st>>>(bufs, dst_row, idx, w,                          \
-                                                  static_cast<const uint4*>(shared), T, k, vpr,   \
+                                                  static_cast<const uint4*>(shared),              \
+                                                  static_cast<const uint4*>(residual), T, k, vpr, \
                                                   static_cast<uint4*>(y))
   switch (h->d.combine_mode) {
     case MG_COMBINE_FP32: MG_COMBINE_CASE(MG_COMBINE_FP32); break;
@@ -651,17 +660,77 @@ static int launch_combine_impl(const Handle* h, const PeerPtrs& bufs, const int3
 }
 
 int launch_combine(const Handle* h, const void* out_rows, const int32_t* dst_row,
-                   const int32_t* idx, const float* w, const void* shared, int64_t T, void* y,
-                   cudaStream_t st) {
+                   const int32_t* idx, const float* w, const void* shared, const void* residual, int64_t T,
+                   void* y, cudaStream_t st) {
   PeerPtrs bufs{};
   bufs.p[0] = const_cast<void*>(out_rows);
-  return launch_combine_impl<false>(h, bufs, dst_row, idx, w, shared, T, y, st);
+  return launch_combine_impl<false>(h, bufs, dst_row, idx, w, shared, residual, T, y, st);
 }
 
 int launch_combine_peers(const Handle* h, const PeerPtrs& peers, const int32_t* dst,
                          const int32_t* idx, const float* w, const void* shared, int64_t T, void* y,
                          cudaStream_t st) {
-  return launch_combine_impl<true>(h, peers, dst, idx, w, shared, T, y, st);
+  return launch_combine_impl<true>(h, peers, dst, idx, w, shared, nullptr, T, y, st);
+}
+
+// ---------------------------------------------------------------------------------------
+// RMSNorm in front of the block: out = w * bf16(x * rsqrt(mean(x^2) + eps)), one CTA per row.
+// fp32 statistics, the normalised value rounded to bf16 before the bf16 weight multiplies it
+// (DeepseekV3RMSNorm.forward, modeling_deepseek_v3.py:125-150).  Division and square root are the
+// IEEE ones, as on the host.
+// ---------------------------------------------------------------------------------------
+constexpr int kNormThreads = 256;
+constexpr int kNormCached = 4;     // 16-byte vectors of the row a thread keeps in registers
+
+__global__ void __launch_bounds__(kNormThreads) rmsnorm_kernel(const uint4* __restrict__ x,
+                                                               const uint4* __restrict__ weight, float eps,
+                                                               int vec_per_row, uint4* __restrict__ out) {
+  __shared__ float partial[kNormThreads / 32];
+  __shared__ float s_scale;
+  const int64_t row = blockIdx.x;
+  const uint4* src = x + row * vec_per_row;
+  uint4 keep[kNormCached];
+  float sum = 0.f;
+  int n = 0;
+  for (int v = threadIdx.x; v < vec_per_row; v += kNormThreads, ++n) {
+    const uint4 q = __ldg(src + v);
+    if (n < kNormCached) keep[n] = q;
+    float f[8];
+    unpack8(q, f);
+#pragma unroll
+    for (int i = 0; i < 8; ++i) sum = fmaf(f[i], f[i], sum);
+  }
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) sum += __shfl_xor_sync(0xFFFFFFFFu, sum, o);
+  if ((threadIdx.x & 31) == 0) partial[threadIdx.x >> 5] = sum;
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    float tot = 0.f;
+    for (int i = 0; i < kNormThreads / 32; ++i) tot += partial[i];
+    s_scale = 1.0f / sqrtf(tot / static_cast<float>(vec_per_row * 8) + eps);
+  }
+  __syncthreads();
+  const float scale = s_scale;
+  n = 0;
+  for (int v = threadIdx.x; v < vec_per_row; v += kNormThreads, ++n) {
+    const uint4 q = n < kNormCached ? keep[n] : __ldg(src + v);
+    float f[8], w[8];
+    unpack8(q, f);
+    unpack8(__ldg(weight + v), w);
+#pragma unroll
+    for (int i = 0; i < 8; ++i) f[i] = __fmul_rn(w[i], round_bf16(__fmul_rn(f[i], scale)));
+    out[row * vec_per_row + v] = pack8(f);
+  }
+}
+
+int launch_rmsnorm(const Handle* h, const void* x, const void* weight, float eps, int64_t T, void* out,
+                   cudaStream_t st) {
+  if (T == 0) return MG_OK;
+  rmsnorm_kernel<<<static_cast<unsigned>(T), kNormThreads, 0, st>>>(
+      static_cast<const uint4*>(x), static_cast<const uint4*>(weight), eps, h->d.hidden / 8,
+      static_cast<uint4*>(out));
+  MG_CUDA(cudaGetLastError());
+  return MG_OK;
 }
 
 // ---------------------------------------------------------------------------------------

@@ -160,6 +160,10 @@ class EPMoELayer:
             mode = lay.options.get(L.OPT_FP8_MODE, 0)
             use_deq = nd.value > 0 and (mode == 1 or (mode == 0 and T * self.world * k >= 1024 * E))
             self.deq = torch.empty(nd.value, dtype=torch.uint8, device=self.dev) if use_deq else None
+            if nd.value > 0 and L.OPT_FP8_M256 not in lay.options:
+                # the library picks the tile height of its convert-in-the-GEMM kernels from the rows of
+                # the buffer it is given; here that is the receive capacity, so decide from the batch
+                L.check(self.lib.mg_set_option(lay._h, L.OPT_FP8_M256, 2 if T * self.world * k >= 120 * E else 0))
         self._tokens = T
         dist.barrier(group=self.group)
 

@@ -163,6 +163,45 @@ class MoELayer:
 
     __call__ = forward
 
+    # ------------------------------------------------------------------ decoder-layer glue
+    def rmsnorm(self, x: torch.Tensor, weight: torch.Tensor, eps: float = 1e-6,
+                out: Optional[torch.Tensor] = None) -> torch.Tensor:
+        """weight * bf16(x * rsqrt(mean(x^2) + eps)): the reference's DeepseekV3RMSNorm
+        (modeling_deepseek_v3.py:125-150) with the bf16 weight of a bfloat16 model."""
+        x2 = x.reshape(-1, self.H)
+        self._check_in(x2, torch.bfloat16, "hidden_states")
+        self._check_in(weight, torch.bfloat16, "norm weight")
+        if weight.numel() != self.H:
+            raise ValueError(f"norm weight has {weight.numel()} elements, hidden size is {self.H}")
+        y = torch.empty_like(x2) if out is None else out
+        with torch.cuda.device(self.device):
+            L.check(self.lib.mg_rmsnorm(self._h, x2.data_ptr(), weight.data_ptr(), float(eps), x2.shape[0],
+                                        y.data_ptr(), self._stream()))
+        return y.view(x.shape)
+
+    def block_forward(self, hidden: torch.Tensor, norm_weight: torch.Tensor, eps: float = 1e-6,
+                      out: Optional[torch.Tensor] = None) -> torch.Tensor:
+        """hidden + moe(rmsnorm(hidden)): the decoder layer's second half
+        (modeling_deepseek_v3.py:1361-1365) with the residual add done by the combine kernel.
+        out may be hidden itself (in-place update of the residual stream)."""
+        shape = hidden.shape
+        h2 = hidden.reshape(-1, self.H)
+        self._check_in(h2, torch.bfloat16, "hidden_states")
+        self._check_in(norm_weight, torch.bfloat16, "norm weight")
+        if norm_weight.numel() != self.H:
+            raise ValueError(f"norm weight has {norm_weight.numel()} elements, hidden size is {self.H}")
+        T = h2.shape[0]
+        ws = self._workspace(T)
+        if getattr(self, "_xnorm", None) is None or self._xnorm.shape[0] < T:
+            self._xnorm = torch.empty(max(T, 1), self.H, dtype=torch.bfloat16, device=self.device)
+        y = torch.empty_like(h2) if out is None else out.reshape(-1, self.H)
+        with torch.cuda.device(self.device):
+            L.check(self.lib.mg_moe_block_forward(self._h, h2.data_ptr(), norm_weight.data_ptr(), float(eps), T,
+                                                  self.gate_w.data_ptr(), _ptr(self.bias), self.packed.data_ptr(),
+                                                  self._xnorm.data_ptr(), ws.data_ptr(), ws.numel(), y.data_ptr(),
+                                                  self._stream()))
+        return y.view(shape)
+
     def forward_host(self, x_host: torch.Tensor, y_host: Optional[torch.Tensor] = None,
                      chunk_tokens: int = 8192) -> torch.Tensor:
         """Host-buffer entry: x_host [T,H] bf16 in (preferably pinned) host memory -> y_host.

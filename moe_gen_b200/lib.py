@@ -73,6 +73,8 @@ SIGNATURES = {
     "mg_ep_clear_duplicates": [_vp, _vp, _i64, _vp],
     "mg_ep_fill_duplicates": [_vp, _vp, _vp, _i64, _vp],
     "mg_ep_combine": [_vp, _P(_vp), _vp, _vp, _vp, _vp, _i64, _vp, _vp],
+    "mg_rmsnorm": [_vp, _vp, _vp, C.c_float, _i64, _vp, _vp],
+    "mg_moe_block_forward": [_vp, _vp, _vp, C.c_float, _i64, _vp, _vp, _vp, _vp, _vp, _sz, _vp, _vp],
     "mg_set_option": [_vp, _i32, _i32],
     "mg_set_stage_timing": [_vp, _i32],
     "mg_stage_times": [_vp, _P(C.c_float), _i32],

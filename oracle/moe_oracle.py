@@ -361,6 +361,30 @@ def layer_forward(spec: LayerSpec, x: torch.Tensor, W: LayerWeights, gold_fp32: 
             "offsets": offsets, "order": order, "src_token": src}
 
 
+def rmsnorm(x: torch.Tensor, weight: torch.Tensor, eps: float) -> torch.Tensor:
+    """DeepseekV3RMSNorm.forward (modeling_deepseek_v3.py:125-150; V2 has the same class):
+    fp32 statistics, the normalised value cast back to the input dtype, then multiplied by
+    the weight (bf16 in a model moved to bfloat16, so the product rounds to bf16 once more)."""
+    h = x.to(torch.float32)
+    variance = h.pow(2).mean(-1, keepdim=True)
+    h = h * torch.rsqrt(variance + eps)
+    return weight * h.to(x.dtype)
+
+
+def block_forward(spec: LayerSpec, hidden: torch.Tensor, norm_w: torch.Tensor, eps: float, W: LayerWeights,
+                  gold_fp32: bool = False) -> Dict[str, torch.Tensor]:
+    """The decoder layer's second half (modeling_deepseek_v3.py:1361-1365): residual = h;
+    h = post_attention_layernorm(h); h = mlp(h); h = residual + h.  gold_fp32 as in layer_forward
+    (fp32 parameters and input, the normalisation included)."""
+    if gold_fp32:
+        xn = rmsnorm(hidden.float(), norm_w.float(), eps)
+        out = layer_forward(spec, xn, W, gold_fp32=True)
+        return {"y": hidden.float() + out["y"], "x_norm": xn, "moe": out}
+    xn = rmsnorm(hidden, norm_w, eps)
+    out = layer_forward(spec, xn, W)
+    return {"y": hidden + out["y"], "x_norm": xn, "moe": out}
+
+
 def rel_l2(a: torch.Tensor, b: torch.Tensor) -> float:
     a = a.double(); b = b.double()
     return float((a - b).norm() / b.norm().clamp_min(1e-30))

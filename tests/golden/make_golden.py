@@ -117,9 +117,41 @@ def build_ref_module(spec: O.LayerSpec, W: O.LayerWeights, v2, v3, C2, C3):
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--reference", default=os.environ.get("MOEGEN_REFERENCE"), required="MOEGEN_REFERENCE" not in os.environ)
+    ap.add_argument("--only", default="", help="'block': write only the decoder-layer-glue fixture")
     args = ap.parse_args()
     v2, v3, C2, C3, ref_dequant = load_reference(args.reference)
     torch.set_num_threads(max(1, os.cpu_count() or 1))
+
+    # ---- decoder-layer glue: the reference's RMSNorm in front of its V3 block, residual added after
+    #      (modeling_deepseek_v3.py:1361-1365), on the inputs of the small bf16 V3 case
+    spec, T, seed = CASES["v3_noaux_small_bf16"]
+    hidden, W = O.make_inputs(spec, T, seed)
+    g = torch.Generator().manual_seed(seed + 1000)
+    norm_w = (1.0 + 0.1 * torch.randn(spec.hidden, generator=g)).to(torch.bfloat16)
+    eps = 1e-6
+    norm = v3.DeepseekV3RMSNorm(spec.hidden, eps=eps)
+    norm.weight.data = norm_w.clone()
+    m = build_ref_module(spec, W, v2, v3, C2, C3)
+    with torch.no_grad():
+        xn_ref = norm(hidden)
+        y_blk = hidden + m(xn_ref.view(1, T, spec.hidden)).view(T, spec.hidden)
+        m32 = build_ref_module(spec, W, v2, v3, C2, C3).float()
+        m32.gate.e_score_correction_bias.data = W.bias.clone()
+        norm32 = v3.DeepseekV3RMSNorm(spec.hidden, eps=eps)
+        norm32.weight.data = norm_w.float()
+        y_blk_gold = hidden.float() + m32(norm32(hidden.float()).view(1, T, spec.hidden)).view(T, spec.hidden)
+    ob = O.block_forward(spec, hidden, norm_w, eps, W)
+    assert xn_ref.dtype == torch.bfloat16 and torch.equal(ob["x_norm"], xn_ref), "rmsnorm restatement not bit-exact"
+    r_blk = O.rel_l2(ob["y"].float(), y_blk.float())
+    r_blk_gold = O.rel_l2(O.block_forward(spec, hidden, norm_w, eps, W, gold_fp32=True)["y"], y_blk_gold)
+    assert r_blk < 2e-3 and r_blk_gold < 1e-5, (r_blk, r_blk_gold)
+    np.savez_compressed(os.path.join(HERE, "block_v3_small.npz"), T=T, seed=seed, eps=eps,
+                        input_digest=digest(hidden, norm_w, W.gate_w), norm_w=bits(norm_w),
+                        x_norm_bf16=bits(xn_ref), y_block_bf16=bits(y_blk),
+                        y_block_gold_fp32=y_blk_gold.numpy().astype(np.float32))
+    print(f"block_v3_small: ok  rel(oracle,ref)={r_blk:.2e} rel(oracle_gold,ref_gold)={r_blk_gold:.2e}")
+    if args.only == "block":
+        return
 
     # ---- whole-layer cases -------------------------------------------------
     for name, (spec, T, seed) in CASES.items():

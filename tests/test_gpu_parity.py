@@ -342,6 +342,60 @@ def test_layer_against_reference_fixture(built_lib, name):
     assert O.rel_l2(y.cpu().float(), bf16_from_bits(g["y_ref_bf16"]).float()) < 1.5e-2
 
 
+# --------------------------------------------------------------------------- decoder-layer glue
+def _bf16_ulps(a: torch.Tensor, b: torch.Tensor) -> torch.Tensor:
+    """Distance in bf16 steps between two bf16 tensors of the same sign pattern (monotone integer map)."""
+    def key(t):
+        i = t.view(torch.int16).to(torch.int32)
+        return torch.where(i < 0, -(i & 0x7FFF), i)
+    return (key(a) - key(b)).abs()
+
+
+@pytest.mark.parametrize("T,H", [(1, 256), (77, 2048), (300, 7168), (5, 16384)])
+def test_rmsnorm_matches_oracle(built_lib, T, H):
+    """fp32 statistics summed in a different order than torch's: a value may land on the neighbouring
+    bf16 when its fp32 product sits on a rounding boundary; nothing further than one step."""
+    from moe_gen_b200 import MoELayer
+    layer = MoELayer(hidden=H, inter=128, n_experts=8, top_k=2, device=DEV)     # no weights needed
+    g = torch.Generator().manual_seed(T + H)
+    x = (torch.randn(T, H, generator=g) * 3.0).to(torch.bfloat16)
+    x[0, : H // 2] = 0                                            # zeros stay zeros
+    w = (1.0 + 0.1 * torch.randn(H, generator=g)).to(torch.bfloat16)
+    ref = O.rmsnorm(x, w, 1e-6)
+    got = layer.rmsnorm(x.to(DEV), w.to(DEV), 1e-6).cpu()
+    _status_ok(layer)
+    d = _bf16_ulps(got, ref)
+    assert int(d.max()) <= 1
+    assert float((d > 0).float().mean()) < 2e-3
+
+
+def test_block_forward_against_reference_fixture(built_lib):
+    """hidden + moe(rmsnorm(hidden)) against the output recorded from the reference's RMSNorm and V3
+    block (fp32 gold: 1e-2 relative L2, as for the block alone), out of place and in place."""
+    spec, T, seed = CASES["v3_noaux_small_bf16"]
+    g = load_golden("block_v3_small")
+    hidden, W = O.make_inputs(spec, T, seed)
+    norm_w = bf16_from_bits(g["norm_w"])
+    eps = float(g["eps"])
+    layer = make_layer(spec, W, DEV)
+    hd, wd = hidden.to(DEV), norm_w.to(DEV)
+    xn = layer.rmsnorm(hd, wd, eps)
+    d = _bf16_ulps(xn.cpu(), bf16_from_bits(g["x_norm_bf16"]))
+    assert int(d.max()) <= 1 and float((d > 0).float().mean()) < 2e-3
+    y = layer.block_forward(hd, wd, eps)
+    _status_ok(layer)
+    assert O.rel_l2(y.cpu().float(), torch.from_numpy(g["y_block_gold_fp32"])) <= TOL_LAYER
+    assert O.rel_l2(y.cpu().float(), bf16_from_bits(g["y_block_bf16"]).float()) < 1.5e-2
+    # the same sums in the same order as forward() on the normalised rows plus one bf16 add
+    y2 = (hd.float() + layer.forward(xn).float()).to(torch.bfloat16)
+    assert torch.equal(y.view(torch.int16), y2.view(torch.int16))
+    inplace = hd.clone()
+    layer.block_forward(inplace, wd, eps, out=inplace)
+    _status_ok(layer)
+    assert torch.equal(inplace.view(torch.int16), y.view(torch.int16))
+    assert layer.block_forward(hd[:0], wd, eps).shape == (0, spec.hidden)
+
+
 @pytest.mark.parametrize("T", [0, 1, 127, 129])
 def test_layer_edge_token_counts(built_lib, T):
     spec = O.LayerSpec(256, 128, 64, 6, 256, 1, 1, O.GATE_SOFTMAX_GREEDY, False, 1.0, O.WEIGHT_BF16,

@@ -37,6 +37,21 @@ def test_layer_matches_reference_fixture(name):
     assert float(g["ref_bf16_vs_gold"]) < 1e-2
 
 
+def test_decoder_glue_matches_reference_fixture():
+    """RMSNorm in front of the block and the residual add behind it, as recorded from the reference's
+    DeepseekV3RMSNorm + DeepseekV3MoE: the normalisation bit for bit."""
+    spec, T, seed = CASES["v3_noaux_small_bf16"]
+    g = load_golden("block_v3_small")
+    hidden, W = O.make_inputs(spec, T, seed)
+    norm_w = bf16_from_bits(g["norm_w"])
+    assert _digest(hidden, norm_w, W.gate_w) == str(g["input_digest"]), "seeded inputs drifted"
+    out = O.block_forward(spec, hidden, norm_w, float(g["eps"]), W)
+    assert torch.equal(out["x_norm"].view(torch.int16), bf16_from_bits(g["x_norm_bf16"]).view(torch.int16))
+    assert O.rel_l2(out["y"].float(), bf16_from_bits(g["y_block_bf16"]).float()) < 2e-3
+    gold = O.block_forward(spec, hidden, norm_w, float(g["eps"]), W, gold_fp32=True)
+    assert O.rel_l2(gold["y"], torch.from_numpy(g["y_block_gold_fp32"])) < 1e-5
+
+
 @pytest.mark.parametrize("name", sorted(GATE_CASES))
 def test_gate_matches_reference_fixture(name):
     cfg, T, seed = GATE_CASES[name]
