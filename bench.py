@@ -80,12 +80,8 @@ def quantize_fp8_block128_gpu(w: torch.Tensor):
     return q.view(m, n).contiguous(), (amax / 448.0).view(m // 128, n // 128).contiguous()
 
 
-def build_layer(name: str, device, ep_rank=0, ep_size=1, zipf=0.0):
-    from moe_gen_b200 import MoELayer
+def router_tensors(name: str, device, zipf=0.0):
     H, I, E, k, Is, G, keep, gating, norm, scale, wfmt, comb, _, seed = WORKLOADS[name]
-    layer = MoELayer(hidden=H, inter=I, n_experts=E, top_k=k, inter_shared=Is, n_group=G, topk_group=keep,
-                     gating=gating, norm_topk_prob=norm, routed_scale=scale, weight_format=wfmt,
-                     combine_mode=comb, ep_rank=ep_rank, ep_size=ep_size, device=device)
     g = torch.Generator(device=device).manual_seed(seed)           # same on every rank
     gate_w = (torch.randn(E, H, generator=g, device=device) * 0.02).to(torch.bfloat16)
     bias = torch.randn(E, generator=g, device=device) * 0.01 if gating == 2 else None
@@ -97,22 +93,54 @@ def build_layer(name: str, device, ep_rank=0, ep_size=1, zipf=0.0):
         col = torch.empty(E, device=device)
         col[perm] = (b - b.mean()).float()
         gate_w[:, 0] = col.to(torch.bfloat16)
-    layer.set_router(gate_w, bias)
+    return gate_w, bias
+
+
+def expert_tensors(name: str, device, e: int):
+    """Global expert e (e = -1: the shared expert): bf16 matrices, or (fp8, scale) pairs for W8A16 layers."""
+    H, I, E, k, Is, G, keep, gating, norm, scale, wfmt, comb, _, seed = WORKLOADS[name]
     ge = torch.Generator(device=device)
-    for i in range(layer.e_local):
-        ge.manual_seed(seed * 100003 + layer.expert_lo + i)        # per global expert id
-        mats = [(torch.randn(r, c, generator=ge, device=device) * 0.02).to(torch.bfloat16)
-                for r, c in ((I, H), (I, H), (H, I))]
-        if wfmt == 1:
-            qs = [quantize_fp8_block128_gpu(m) for m in mats]
-            layer.load_expert(i, qs[0][0], qs[1][0], qs[2][0], (qs[0][1], qs[1][1], qs[2][1]))
-        else:
-            layer.load_expert(i, *mats)
-    if Is:
+    if e < 0:
         ge.manual_seed(seed * 100003 + 99991)
-        layer.load_shared(*[(torch.randn(r, c, generator=ge, device=device) * 0.02).to(torch.bfloat16)
-                            for r, c in ((Is, H), (Is, H), (H, Is))])
+        return [(torch.randn(r, c, generator=ge, device=device) * 0.02).to(torch.bfloat16)
+                for r, c in ((Is, H), (Is, H), (H, Is))]
+    ge.manual_seed(seed * 100003 + e)                               # per global expert id
+    mats = [(torch.randn(r, c, generator=ge, device=device) * 0.02).to(torch.bfloat16)
+            for r, c in ((I, H), (I, H), (H, I))]
+    return [quantize_fp8_block128_gpu(m) for m in mats] if wfmt == 1 else mats
+
+
+def build_layer(name: str, device, ep_rank=0, ep_size=1, zipf=0.0, load=True):
+    from moe_gen_b200 import MoELayer
+    H, I, E, k, Is, G, keep, gating, norm, scale, wfmt, comb, _, seed = WORKLOADS[name]
+    layer = MoELayer(hidden=H, inter=I, n_experts=E, top_k=k, inter_shared=Is, n_group=G, topk_group=keep,
+                     gating=gating, norm_topk_prob=norm, routed_scale=scale, weight_format=wfmt,
+                     combine_mode=comb, ep_rank=ep_rank, ep_size=ep_size, device=device)
+    if not load:
+        return layer
+    layer.set_router(*router_tensors(name, device, zipf))
+    for i in range(layer.e_local):
+        ws = expert_tensors(name, device, layer.expert_lo + i)
+        if wfmt == 1:
+            layer.load_expert(i, ws[0][0], ws[1][0], ws[2][0], (ws[0][1], ws[1][1], ws[2][1]))
+        else:
+            layer.load_expert(i, *ws)
+    if Is:
+        layer.load_shared(*expert_tensors(name, device, -1))
     return layer
+
+
+def write_layer_checkpoint(name: str, path: str, device, zipf=0.0):
+    """The workload's layer as one safetensors shard in the DeepSeek naming (block 0)."""
+    from moe_gen_b200 import ingest as ING
+    E, Is = WORKLOADS[name][2], WORKLOADS[name][4]
+    gate_w, bias = router_tensors(name, device, zipf)
+
+    def cpu(ws):
+        return [tuple(t.cpu() for t in w) if isinstance(w, tuple) else w.cpu() for w in ws]
+    experts = [cpu(expert_tensors(name, device, e)) for e in range(E)]
+    shared = cpu(expert_tensors(name, device, -1)) if Is else None
+    ING.export_moe_layer(path, 0, gate_w.cpu(), None if bias is None else bias.cpu(), experts, shared)
 
 
 def make_tokens(name: str, T: int, device, rank=0, zipf=0.0):
@@ -293,6 +321,8 @@ def main():
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-e2e", action="store_true")
     ap.add_argument("--no-check", action="store_true")
+    ap.add_argument("--ingest", action="store_true",
+                    help="also time checkpoint ingest: the layer written as a safetensors shard, then file -> packed buffer")
     ap.add_argument("--no-glue", action="store_true", help="skip the RMSNorm / residual-add measurement")
     ap.add_argument("--chunk-tokens", type=int, default=16384)
     ap.add_argument("--micro", type=int, default=1, help="token micro-batches pipelined in the expert-parallel forward")
@@ -565,6 +595,26 @@ def main():
                 "rmsnorm_frac_of_hbm": round(nbytes / n_ms / 1e6 / hbm, 3), "block_ms": round(b_ms, 3),
                 "block_equals_norm_forward_add": bool(torch.equal(yb.view(torch.int16), want.view(torch.int16))),
                 "note": "block = hidden + moe(rmsnorm(hidden)); rmsnorm moves T*H*2 bytes in and out"}
+    # ---- checkpoint ingest: safetensors shard (page cache) -> pinned staging -> packed expert buffer ----
+    ing = None
+    if world == 1 and args.ingest:
+        import tempfile
+        from moe_gen_b200 import ingest as ING
+        with tempfile.TemporaryDirectory() as td:
+            path = os.path.join(td, "model-00001-of-00001.safetensors")
+            write_layer_checkpoint(name, path, device, args.zipf)
+            fresh = build_layer(name, device, zipf=args.zipf, load=False)
+            ck = ING.Checkpoint(path)
+            ING.load_moe_layer(fresh, ck, 0)                      # first pass warms the page cache
+            st_ = ING.load_moe_layer(fresh, ck, 0)
+            ck.close()
+            same = bool(torch.equal(fresh.packed, layer.packed))
+            yi = fresh.forward(x)
+            ing = {"gb_per_s": round(st_["gb_per_s"], 2), "seconds": round(st_["seconds"], 3), "bytes": st_["bytes"],
+                   "packed_equals_direct_load": same,
+                   "forward_equals": bool(torch.equal(yi.view(torch.int16), y.view(torch.int16))),
+                   "note": "file in the page cache; 8 copy threads into pinned staging, H2D and packing overlapped"}
+            del fresh
     cpu = None
     if not args.no_cpu_baseline:
         r = cpu_reference(name, min(args.cpu_sample_tokens, T), 2, 1, args.zipf)
@@ -575,7 +625,7 @@ def main():
            "warmup": warmup, "ms_per_step": ms_per_step, "higher_is_better": True, "scaling": "strong",
            "vs_baseline": None, "dtype": "bf16", "data": "synthetic", "config": config, "clocks": clocks,
            "e2e": e2e, "gpu_launches": launches * args.steps, "roofline": roofline, "cpu_baseline": cpu,
-           "stages": stages, "check": check, "ep_load": ep_load, "glue": glue,
+           "stages": stages, "check": check, "ep_load": ep_load, "glue": glue, "ingest": ing,
            "layer_tflops": (alg["gemm1_flops"] + alg["gemm2_flops"] + alg["shared_flops"] + alg["gate_flops"])
            / (ms_per_step * 1e-3) / 1e12 / world}
     print(json.dumps(out), flush=True)

@@ -41,7 +41,8 @@ class MoELayer:
             L.check(self.lib.mg_create(C.byref(self.desc), C.byref(self._h)))
             n = C.c_size_t()
             L.check(self.lib.mg_packed_weight_bytes(self._h, C.byref(n)))
-            self.packed = torch.empty(n.value, dtype=torch.uint8, device=self.device)
+            # zeroed: the alignment gaps between its sections are never written
+            self.packed = torch.zeros(n.value, dtype=torch.uint8, device=self.device)
         self.gate_w: Optional[torch.Tensor] = None
         self.bias: Optional[torch.Tensor] = None
         self._ws: Optional[torch.Tensor] = None
