@@ -64,6 +64,9 @@ static WsLayout ws_layout(const Handle* h, int64_t T, int64_t R) {
   WsLayout L;
   size_t off = 0;
   auto take = [&](int which, size_t bytes) { L.off[which] = off; off += (bytes + 255) / 256 * 256; };
+  // first, so that its address does not depend on T: calls with different token counts on one
+  // workspace can then share the de-quantised copy (MG_OPT_KEEP_DEQUANT)
+  take(WS_DEQ, fp8_predequant(h, T) ? dequant_ws(h) : 0);
   take(WS_LOGITS, static_cast<size_t>(T) * d.n_experts * 4);
   take(WS_IDX, static_cast<size_t>(T) * d.top_k * 4);
   take(WS_W, static_cast<size_t>(T) * d.top_k * 4);
@@ -77,7 +80,6 @@ static WsLayout ws_layout(const Handle* h, int64_t T, int64_t R) {
   take(WS_PLAN, plan_ws_bytes(h, T));
   take(WS_HS, static_cast<size_t>(T) * d.inter_shared * 2);
   take(WS_SHARED, d.inter_shared ? static_cast<size_t>(T) * d.hidden * 2 : 0);
-  take(WS_DEQ, fp8_predequant(h, T) ? dequant_ws(h) : 0);
   L.total = off;
   return L;
 }

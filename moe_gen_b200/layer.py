@@ -203,15 +203,35 @@ class MoELayer:
                                                   self._stream()))
         return y.view(shape)
 
+    @staticmethod
+    def host_chunks(T: int, chunk_tokens: int) -> list:
+        """Token counts of the chunks forward_host uses.  The copy-in of the first chunk and the
+        copy-out of the last one cannot overlap with compute, so those two are half a chunk; the ones
+        between them are one and a half, because every chunk streams all expert weights once."""
+        c = max(1, chunk_tokens)
+        if T <= 2 * c:
+            return [min(c, T - t0) for t0 in range(0, max(T, 1), c)] if T > 0 else []
+        edge = max(128, c // 2)
+        rest = T - 2 * edge
+        n_mid = max(1, -(-rest // (c + c // 2)))
+        base = -(-rest // n_mid)
+        base = -(-base // 128) * 128
+        mids = []
+        while rest > 0:
+            mids.append(min(base, rest))
+            rest -= mids[-1]
+        return [edge] + mids + [edge]
+
     def forward_host(self, x_host: torch.Tensor, y_host: Optional[torch.Tensor] = None,
                      chunk_tokens: int = 8192) -> torch.Tensor:
         """Host-buffer entry: x_host [T,H] bf16 in (preferably pinned) host memory -> y_host.
-        Tokens are independent, so chunks are copied in, computed and copied out on three
-        streams; returns after the last copy has finished."""
+        Tokens are independent, so chunks (host_chunks) are copied in, computed and copied out on
+        three streams; returns after the last copy has finished."""
         T = x_host.shape[0]
         if y_host is None:
             y_host = torch.empty_like(x_host, pin_memory=x_host.is_pinned())
-        cs = min(chunk_tokens, max(T, 1))
+        sizes = self.host_chunks(T, chunk_tokens)
+        cs = max(sizes) if sizes else 1
         with torch.cuda.device(self.device):
             if getattr(self, "_hb", None) is None or self._hb[0].shape[0] < cs:
                 self._hb = [torch.empty(cs, self.H, dtype=torch.bfloat16, device=self.device) for _ in range(4)]
@@ -231,8 +251,9 @@ class MoELayer:
             self._workspace(cs)
             # FP8 layers in pre-dequantise mode: de-quantise once for all chunks of this forward
             self.set_option(L.OPT_KEEP_DEQUANT, 1)
-            for c, t0 in enumerate(range(0, T, cs)):
-                b, n = c & 1, min(cs, T - t0)
+            t0 = 0
+            for c, n in enumerate(sizes):
+                b = c & 1
                 if c >= 2:
                     s_in.wait_event(ev_done[b])
                 with torch.cuda.stream(s_in):
@@ -247,6 +268,7 @@ class MoELayer:
                 with torch.cuda.stream(s_out):
                     y_host[t0:t0 + n].copy_(yout[b][:n], non_blocking=True)
                     ev_out[b].record(s_out)
+                t0 += n
             self.set_option(L.OPT_KEEP_DEQUANT, 0)
             s_out.synchronize()
             if hint:
