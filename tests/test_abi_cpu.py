@@ -67,3 +67,16 @@ def test_missing_library_fails_loudly(monkeypatch, tmp_path):
     monkeypatch.setattr(L, "LIB_PATH", str(tmp_path / "nope.so"))
     with pytest.raises(RuntimeError, match="no CPU or PyTorch fallback"):
         L.load()
+
+
+def test_host_chunk_schedule_covers_every_token_once():
+    """forward_host's chunk sizes: they add up to T; with more than two chunks the first and last
+    are half a chunk and none exceeds twice the nominal size."""
+    from moe_gen_b200.layer import MoELayer
+    for T in (0, 1, 100, 8192, 8193, 16384, 16385, 20000, 40000, 65536, 100001):
+        for c in (128, 4096, 8192, 16384):
+            sizes = MoELayer.host_chunks(T, c)
+            assert sum(sizes) == T and all(n > 0 for n in sizes), (T, c, sizes)
+            assert all(n <= 2 * c for n in sizes), (T, c, sizes)
+            if T > 2 * c:
+                assert sizes[0] == sizes[-1] == max(128, c // 2)
