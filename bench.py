@@ -328,6 +328,8 @@ def main():
     ap.add_argument("--micro", type=int, default=1, help="token micro-batches pipelined in the expert-parallel forward")
     ap.add_argument("--capacity-factor", type=float, default=0.0,
                     help="expert-parallel receive buffers, in multiples of the mean rows per GPU (default 2, 8 with --zipf)")
+    ap.add_argument("--ep-chunks", type=int, default=2,
+                    help="expert parallel, host-buffer path: parts each rank's tokens are fed in")
     ap.add_argument("--ep-dedup", type=int, default=1,
                     help="expert parallel: 1 sends one row per (token, destination GPU), 0 one per (token, expert)")
     ap.add_argument("--pair-gemm", type=int, default=-1, help="1/0 force the SM-pair expert GEMM on/off")
@@ -477,11 +479,9 @@ def main():
         # every rank brings its own token shard from pinned host memory and takes its result back
         xh = x.cpu().pin_memory()
         yh = torch.empty_like(xh).pin_memory()
-        xd = torch.empty_like(x)
 
         def host_step():
-            xd.copy_(xh, non_blocking=True)
-            yh.copy_(layer.forward(xd), non_blocking=True)
+            layer.forward_host(xh, yh, n_chunks=args.ep_chunks)
         for _ in range(2):
             host_step()
         torch.cuda.synchronize()
@@ -498,7 +498,8 @@ def main():
         e_ms = float(t.item())
         e2e = {"value": T_total / (e_ms * 1e-3), "unit": "tokens/s", "ms_per_step": e_ms,
                "h2d_bytes_per_step": xh.numel() * 2 * world, "d2h_bytes_per_step": yh.numel() * 2 * world,
-               "equals_device_path": bool(torch.equal(yh.view(torch.int16), y.cpu().view(torch.int16)))}
+               "equals_device_path": bool(torch.equal(yh.view(torch.int16), y.cpu().view(torch.int16))),
+               "chunks_per_rank": args.ep_chunks}
 
     # rows each GPU's experts receive (all ranks' picks), for the load-balance figures
     ep_load = None

@@ -89,6 +89,7 @@ class EPMoELayer:
         self._groups = [group] + [dist.new_group(ranks) for _ in range(self.n_micro - 1)]
         self._streams = [torch.cuda.Stream(device=self.dev) for _ in range(self.n_micro)]
         self.deq = None
+        self._batch_tokens = 0             # local tokens of the batch forward_host is feeding in parts
 
     # ------------------------------------------------------------------ buffers
     def _setup(self, T: int):
@@ -158,7 +159,8 @@ class EPMoELayer:
             L.check(self.lib.mg_dequant_ws_bytes(lay._h, C.byref(nd)))
             # FP8: pre-dequantise when an expert sees many rows (same rule as the single-GPU path)
             mode = lay.options.get(L.OPT_FP8_MODE, 0)
-            use_deq = nd.value > 0 and (mode == 1 or (mode == 0 and T * self.world * k >= 1024 * E))
+            Tb = max(T, self._batch_tokens)    # parts of one batch share the de-quantised copy
+            use_deq = nd.value > 0 and (mode == 1 or (mode == 0 and Tb * self.world * k >= 1024 * E))
             self.deq = torch.empty(nd.value, dtype=torch.uint8, device=self.dev) if use_deq else None
             if nd.value > 0 and L.OPT_FP8_M256 not in lay.options:
                 # the library picks the tile height of its convert-in-the-GEMM kernels from the rows of
@@ -209,7 +211,55 @@ class EPMoELayer:
         return out
 
     # ------------------------------------------------------------------ forward
-    def forward(self, x: torch.Tensor, out: Optional[torch.Tensor] = None) -> torch.Tensor:
+    def forward_host(self, x_host: torch.Tensor, y_host: Optional[torch.Tensor] = None,
+                     n_chunks: int = 2) -> torch.Tensor:
+        """This rank's tokens from (pinned) host memory and the result back to it: the local tokens
+        go through forward() in n_chunks equal parts, copy-in, compute and copy-out on three streams.
+        Every rank must call it with the same token count and n_chunks (each part is a collective
+        forward).  FP8 layers de-quantise once for all parts."""
+        T = x_host.shape[0]
+        if y_host is None:
+            y_host = torch.empty_like(x_host, pin_memory=x_host.is_pinned())
+        n = n_chunks if n_chunks > 1 and T % n_chunks == 0 and T >= 2 * n_chunks else 1
+        cs = T // n
+        H = self.layer.H
+        with torch.cuda.device(self.dev):
+            if getattr(self, "_hb", None) is None or self._hb[0].shape[0] != cs:
+                self._hb = [torch.empty(cs, H, dtype=torch.bfloat16, device=self.dev) for _ in range(4)]
+                self._hs = [torch.cuda.Stream(device=self.dev), torch.cuda.Stream(device=self.dev)]
+            xin, yout = self._hb[:2], self._hb[2:]
+            s_in, s_out = self._hs
+            comp = torch.cuda.current_stream()
+            ev_in = [torch.cuda.Event() for _ in range(2)]
+            ev_done = [torch.cuda.Event() for _ in range(2)]
+            ev_out = [torch.cuda.Event() for _ in range(2)]
+            s_in.wait_stream(comp)
+            s_out.wait_stream(comp)
+            self._batch_tokens = T
+            for c in range(n):
+                b, t0 = c & 1, c * cs
+                if c >= 2:
+                    s_in.wait_event(ev_done[b])
+                with torch.cuda.stream(s_in):
+                    xin[b].copy_(x_host[t0:t0 + cs], non_blocking=True)
+                    ev_in[b].record(s_in)
+                comp.wait_event(ev_in[b])
+                if c >= 2:
+                    comp.wait_event(ev_out[b])
+                self.forward(xin[b], out=yout[b], _first=(c == 0), _last=(c == n - 1))
+                ev_done[b].record(comp)
+                s_out.wait_event(ev_done[b])
+                with torch.cuda.stream(s_out):
+                    y_host[t0:t0 + cs].copy_(yout[b], non_blocking=True)
+                    ev_out[b].record(s_out)
+            self._batch_tokens = 0
+            s_out.synchronize()
+        return y_host
+
+    def forward(self, x: torch.Tensor, out: Optional[torch.Tensor] = None, _first: bool = True,
+                _last: bool = True) -> torch.Tensor:
+        """_first / _last: set by forward_host for the parts of one batch; the FP8 weights are
+        de-quantised in the first part and the copy is released after the last."""
         lay, lib = self.layer, self.lib
         x2 = x.reshape(-1, lay.H)
         T = x2.shape[0]
@@ -224,7 +274,7 @@ class EPMoELayer:
             for mb in self._mbs:
                 mb.stream.wait_stream(cur)
             s0 = self._mbs[0].stream
-            if self.deq is not None:
+            if self.deq is not None and _first:
                 # weights do not depend on the routing: de-quantise once per forward, starting now
                 L.check(lib.mg_set_option(h, L.OPT_KEEP_DEQUANT, 2))
                 L.check(lib.mg_dequant_start(h, lay.packed.data_ptr(), self.deq.data_ptr(), s0.cuda_stream))
@@ -289,7 +339,7 @@ class EPMoELayer:
                     L.check(lib.mg_ep_combine(h, mb.peer_out, mb.dst.data_ptr(), mb.idx.data_ptr(), mb.w.data_ptr(),
                                               sh, mb.t1 - mb.t0, y.data_ptr() + mb.t0 * H2, mb.stream.cuda_stream))
             self._mark(evs, s0)
-            if self.deq is not None:
+            if self.deq is not None and _last:
                 L.check(lib.mg_set_option(h, L.OPT_KEEP_DEQUANT, 0))
             for mb in self._mbs:
                 cur.wait_stream(mb.stream)

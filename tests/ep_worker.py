@@ -109,6 +109,10 @@ def gpu_ep_worker(rank, world, port, spec, T_global, seed, result):
     y_plain = ep.forward(x)
     torch.cuda.synchronize()
     same = bool(torch.equal(y_plain.cpu().view(torch.int16), ys[0].view(torch.int16)))
+    # host buffers in two parts per rank (last: it re-allocates the shared buffers for the part size)
+    ep.dedup = True
+    yh = ep.forward_host(x.cpu().pin_memory(), n_chunks=2)
+    same = same and bool(torch.equal(yh.view(torch.int16), ys[0].view(torch.int16)))
     status = layer.device_status()
     gath = [None] * world
     dist.all_gather_object(gath, (ys[0], ys[1], status, same))
