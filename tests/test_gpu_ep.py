@@ -1,5 +1,6 @@
-"""GPU, 2 ranks on 2 GPUs: expert-parallel forward over peer memory against the CPU oracle.
-Skipped on a single-GPU machine."""
+"""GPU: expert-parallel forward over peer memory against the CPU oracle, as 2 ranks on 2 GPUs
+(skipped on a single-GPU machine) and as a group of one rank, which runs the same host code,
+collectives and kernels on one GPU."""
 import socket
 
 import pytest
@@ -22,14 +23,16 @@ def _free_port():
     (O.LayerSpec(256, 128, 64, 4, 256, 4, 2, O.GATE_SIGMOID_NOAUX_TC, True, 2.5, O.WEIGHT_FP8_BLOCK128, O.COMBINE_FP32), 600),
     (O.LayerSpec(512, 256, 8, 2, 0, 1, 1, O.GATE_SOFTMAX_TOPK_RENORM, True, 1.0, O.WEIGHT_BF16, O.COMBINE_BF16_SEQ), 1000),
 ])
-def test_expert_parallel_on_two_gpus(built_lib, spec, T):
-    if torch.cuda.device_count() < 2:
-        pytest.skip("needs 2 GPUs")
+@pytest.mark.parametrize("world", [1, 2])
+def test_expert_parallel_on_gpus(built_lib, spec, T, world):
+    if torch.cuda.device_count() < world:
+        pytest.skip(f"needs {world} GPUs")
     ctx = mp.get_context("spawn")
     with ctx.Manager() as mgr:
         result = mgr.dict()
         port = _free_port()
-        procs = [ctx.Process(target=ep_worker.gpu_ep_worker, args=(r, 2, port, spec, T, 9, result)) for r in range(2)]
+        procs = [ctx.Process(target=ep_worker.gpu_ep_worker, args=(r, world, port, spec, T, 9, result))
+                 for r in range(world)]
         for p in procs:
             p.start()
         for p in procs:
