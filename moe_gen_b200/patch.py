@@ -117,3 +117,37 @@ def patch_moe_module(module, device=None, return_router_logits: Optional[bool] =
     module.forward = forward
     module._moegen_b200_layer = layer
     return layer
+
+
+def patch_decoder_layer(decoder_layer, device=None) -> MoELayer:
+    """Replaces the forward of a reference DeepseekV2/V3DecoderLayer whose `.mlp` is a MoE block
+    (modeling_deepseek_v3.py:1302-1375).  Attention and its residual add stay as they are; the three
+    steps behind them - post_attention_layernorm, mlp, residual add - become one call,
+    `MoELayer.block_forward`, which normalises, runs the block and adds the residual inside the
+    combine kernel, updating the hidden states in place.  Same arguments and return tuple as the
+    reference's forward."""
+    layer = patch_moe_module(decoder_layer.mlp, device)
+    norm = decoder_layer.post_attention_layernorm
+    eps = float(getattr(norm, "variance_epsilon", getattr(norm, "eps", 1e-6)))
+
+    def forward(hidden_states, attention_mask=None, position_ids=None, past_key_value=None,
+                output_attentions=False, use_cache=False, **kwargs):
+        residual = hidden_states
+        hidden_states = decoder_layer.input_layernorm(hidden_states)
+        hidden_states, self_attn_weights, present_key_value = decoder_layer.self_attn(
+            hidden_states=hidden_states, attention_mask=attention_mask, position_ids=position_ids,
+            past_key_value=past_key_value, output_attentions=output_attentions, use_cache=use_cache, **kwargs)
+        hidden_states = (residual + hidden_states).contiguous()
+        w = norm.weight
+        if w.dtype != torch.bfloat16 or w.device != hidden_states.device:
+            w = w.detach().to(hidden_states.device, torch.bfloat16)
+        hidden_states = layer.block_forward(hidden_states, w, eps, out=hidden_states)
+        outputs = (hidden_states,)
+        if output_attentions:
+            outputs += (self_attn_weights,)
+        if use_cache:
+            outputs += (present_key_value,)
+        return outputs
+
+    decoder_layer.forward = forward
+    return layer

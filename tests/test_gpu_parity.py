@@ -486,6 +486,40 @@ def test_patched_reference_style_module(built_lib):
     gold = O.layer_forward(spec, x, W, gold_fp32=True)
     assert O.rel_l2(y.view(64, 256).cpu().float(), gold["y"]) <= TOL_LAYER
 
+    # the decoder layer around it: attention (a stand-in here) and its residual add stay, the
+    # norm / block / residual add behind them become one fused call
+    from moe_gen_b200 import patch_decoder_layer
+
+    class Norm(nn.Module):
+        def __init__(self, w):
+            super().__init__()
+            self.weight, self.variance_epsilon = nn.Parameter(w), 1e-6
+
+        def forward(self, h):
+            return O.rmsnorm(h.cpu(), self.weight.detach().cpu(), self.variance_epsilon).to(h.device)
+
+    class Attn(nn.Module):
+        def forward(self, hidden_states, **kw):
+            return hidden_states * 0.5, None, None
+
+    class DeepseekV3DecoderLayer(nn.Module):
+        pass
+    g = torch.Generator().manual_seed(8)
+    dl = DeepseekV3DecoderLayer().eval()
+    dl.input_layernorm = Norm((1.0 + 0.1 * torch.randn(256, generator=g)).to(torch.bfloat16))
+    dl.post_attention_layernorm = Norm((1.0 + 0.1 * torch.randn(256, generator=g)).to(torch.bfloat16))
+    dl.self_attn = Attn()
+    mod2 = DeepseekV3MoE().eval()
+    mod2.config, mod2.gate, mod2.experts, mod2.shared_experts = mod.config, mod.gate, mod.experts, mod.shared_experts
+    dl.mlp = mod2
+    patch_decoder_layer(dl, device=DEV)
+    h0 = x.view(2, 32, 256).to(DEV)
+    (out,) = dl(h0)
+    h1 = (x + dl.input_layernorm(x) * 0.5)                        # what reaches the second half, on CPU
+    want = O.block_forward(spec, h1, dl.post_attention_layernorm.weight.detach(), 1e-6, W, gold_fp32=True)["y"]
+    assert out.shape == (2, 32, 256)
+    assert O.rel_l2(out.view(64, 256).cpu().float(), want) <= TOL_LAYER
+
 
 def test_bounded_wait_gives_up_and_reports(built_lib):
     """Failure detection without a fault: a wait that nothing satisfies runs out after its limit,
