@@ -908,19 +908,10 @@ __device__ __forceinline__ Tile2 locate_w8(int tile, const int* s_pad, const int
   return r;
 }
 
-// 16 bytes of weights, read once by this SM: no L1 allocation; a miss brings 256 bytes of the
-// row into L2, which the next three k-blocks then find there
-__device__ __forceinline__ uint4 ld_weights16(const uint8_t* p) {
-#ifdef MG_EXP_W8_PLAIN_LDG
-  return __ldg(reinterpret_cast<const uint4*>(p));
-#else
-  uint4 v;
-  asm volatile("ld.global.nc.L1::no_allocate.L2::256B.v4.u32 {%0, %1, %2, %3}, [%4];"
-               : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w)
-               : "l"(p));
-  return v;
-#endif
-}
+// 16 bytes of weights through the read-only path.  Plain: with `.L1::no_allocate.L2::256B` on the
+// load the 256-row kernel was 15-25 % slower (21.8 against 17.2 ms for the gate/up GEMM of 256
+// DeepSeek-V3 experts at 1024 rows each).
+__device__ __forceinline__ uint4 ld_weights16(const uint8_t* p) { return __ldg(reinterpret_cast<const uint4*>(p)); }
 
 template <int EPI, int TM>
 __global__ void __launch_bounds__(W8_THREADS, 1)
