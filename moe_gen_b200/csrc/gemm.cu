@@ -866,7 +866,7 @@ grouped_gemm2_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_const
 //   TM = 128: one MMA per k-block, two accumulators in tensor memory (the epilogue of a tile
 //             overlaps the next tile's main loop).  Not dispatched: with few rows per expert the
 //             weights stream from HBM, register loads then expose its latency, and the TMA-staged
-//             grouped_gemm_kernel<EPI, true> measured 1.35x faster (2.54 against 3.50 ms for the
+//             grouped_gemm_kernel<EPI, true> measured 1.25x faster (2.56 against 3.20 ms for the
 //             gate/up GEMM of 256 DeepSeek-V3 experts at 32 rows each).
 //   TM = 256: the converted tile feeds two MMAs, one per 128-row half of A, into the two halves
 //             of tensor memory, so the conversion is paid once per 256 rows.  Both accumulators
@@ -1303,6 +1303,14 @@ int launch_grouped_gemm(const Handle* h, const GemmProblem& p, cudaStream_t st) 
     if (max_tiles < grid) grid = static_cast<int>(max_tiles);
   }
   if (grid < 1) return MG_OK;
+#ifdef MG_EXP_W8_TM128
+  if (p.b_fp8 && !pair && !f32_out && !dense && !m256) {   // experiment: register-fed kernel for 128-row tiles too
+    switch (p.epilogue) {
+      case EPI_SWIGLU_BF16: return launch_w8<EPI_SWIGLU_BF16, 128>(ta, tc, p.b, a, grid, st);
+      case EPI_PLAIN_BF16: return launch_w8<EPI_PLAIN_BF16, 128>(ta, tc, p.b, a, grid, st);
+    }
+  }
+#endif
   if (m256) {
     long long tall_tiles = ((p.a_rows / BM + p.n_groups) / 2 + 1) * static_cast<long long>(a.n_tiles);
     int ctas = tall_tiles < h->sm_count ? static_cast<int>(tall_tiles) : h->sm_count;
