@@ -546,7 +546,7 @@ __global__ void __launch_bounds__(256) combine_kernel(PeerPtrs bufs,
                                                       const float* __restrict__ topk_w,
                                                       const uint4* __restrict__ shared,
                                                       const uint4* residual,
-                                                      int64_t T, int k, int vec_per_row,
+                                                      int64_t T, int k, int vec_per_row, int v_chunk,
                                                       uint4* y) {
   const int lane = threadIdx.x & 31;
   const int64_t t = static_cast<int64_t>(blockIdx.x) * (blockDim.x >> 5) + (threadIdx.x >> 5);
@@ -587,7 +587,11 @@ __global__ void __launch_bounds__(256) combine_kernel(PeerPtrs bufs,
     const uint4* rows = static_cast<const uint4*>(PEER ? bufs.p[use ? (d >> kPeerShift) : 0] : bufs.p[0]);
     base[s] = use ? rows + static_cast<int64_t>(PEER ? (d & kPeerRowMask) : d) * vec_per_row : nullptr;
   }
-  for (int v = lane; v < vec_per_row; v += 32) {
+  // blockIdx.y: the slice of the row this block's warps cover (small batches are spread over more
+  // warps than tokens so that the gather is not one latency chain per token)
+  const int v_begin = blockIdx.y * v_chunk;
+  const int v_end = min(vec_per_row, v_begin + v_chunk);
+  for (int v = v_begin + lane; v < v_end; v += 32) {
     float acc[8];
 #pragma unroll
     for (int i = 0; i < 8; ++i) acc[i] = 0.f;
@@ -641,13 +645,20 @@ static int launch_combine_impl(const Handle* h, const PeerPtrs& bufs, const int3
                                int64_t T, void* y, cudaStream_t st) {
   if (T == 0) return MG_OK;
   const int warps = 8;
-  dim3 grid(static_cast<unsigned>((T + warps - 1) / warps)), block(warps * 32);
   const int k = h->d.top_k, vpr = h->d.hidden / 8;
+  // at least ~16 warps per SM: with few tokens every row is cut into slices of whole 32-vector steps
+  const int steps = (vpr + 31) / 32;
+  int64_t slices = (static_cast<int64_t>(h->sm_count) * 16 + T - 1) / T;
+  if (slices > steps) slices = steps;
+  if (slices < 1) slices = 1;
+  const int v_chunk = static_cast<int>((steps + slices - 1) / slices) * 32;
+  dim3 grid(static_cast<unsigned>((T + warps - 1) / warps), static_cast<unsigned>((vpr + v_chunk - 1) / v_chunk));
+  dim3 block(warps * 32);
 #define MG_COMBINE_CASE(M)                                                                       \
   combine_kernel<M, PEER><<<grid, block, 0, st>>>(bufs, dst_row, idx, w,                          \
                                                   static_cast<const uint4*>(shared),              \
                                                   static_cast<const uint4*>(residual), T, k, vpr, \
-                                                  static_cast<uint4*>(y))
+                                                  v_chunk, static_cast<uint4*>(y))
   switch (h->d.combine_mode) {
     case MG_COMBINE_FP32: MG_COMBINE_CASE(MG_COMBINE_FP32); break;
     case MG_COMBINE_BF16_PROD: MG_COMBINE_CASE(MG_COMBINE_BF16_PROD); break;
