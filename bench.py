@@ -328,7 +328,7 @@ def main():
     ap.add_argument("--micro", type=int, default=1, help="token micro-batches pipelined in the expert-parallel forward")
     ap.add_argument("--capacity-factor", type=float, default=0.0,
                     help="expert-parallel receive buffers, in multiples of the mean rows per GPU (default 2, 8 with --zipf)")
-    ap.add_argument("--ep-chunks", type=int, default=1,
+    ap.add_argument("--ep-chunks", type=int, default=2,
                     help="expert parallel, host-buffer path: parts each rank's tokens are fed in")
     ap.add_argument("--ep-dedup", type=int, default=1,
                     help="expert parallel: 1 sends one row per (token, destination GPU), 0 one per (token, expert)")
