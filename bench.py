@@ -321,6 +321,8 @@ def main():
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-e2e", action="store_true")
     ap.add_argument("--no-check", action="store_true")
+    ap.add_argument("--stream-groups", type=int, default=0,
+                    help="also time the layer with its expert weights streamed from pinned host memory in this many groups")
     ap.add_argument("--ingest", action="store_true",
                     help="also time checkpoint ingest: the layer written as a safetensors shard, then file -> packed buffer")
     ap.add_argument("--no-glue", action="store_true", help="skip the RMSNorm / residual-add measurement")
@@ -616,6 +618,42 @@ def main():
                    "forward_equals": bool(torch.equal(yi.view(torch.int16), y.view(torch.int16))),
                    "note": "file in the page cache; 8 copy threads into pinned staging, H2D and packing overlapped"}
             del fresh
+    # ---- expert weights streamed from pinned host memory, group by group, beside the GEMMs ----
+    streamed = None
+    if world == 1 and args.stream_groups > 0:
+        from moe_gen_b200.stream import StreamedMoELayer
+        Hh, Ii, Ee, kk, Iss, Gg, keep, gating, norm, scale, wfmt, comb = WORKLOADS[name][:12]
+        sl = StreamedMoELayer(group_experts=Ee // args.stream_groups, slots=2, device=device, hidden=Hh, inter=Ii,
+                              n_experts=Ee, top_k=kk, inter_shared=Iss, n_group=Gg, topk_group=keep, gating=gating,
+                              norm_topk_prob=norm, routed_scale=scale, weight_format=wfmt, combine_mode=comb)
+        sl.set_router(*router_tensors(name, device, args.zipf))
+        if Iss:
+            sl.load_shared(*expert_tensors(name, device, -1))
+        for e in range(Ee):
+            ws_ = expert_tensors(name, device, e)
+            if wfmt == 1:
+                sl.load_expert(e, ws_[0][0], ws_[1][0], ws_[2][0], (ws_[0][1], ws_[1][1], ws_[2][1]))
+            else:
+                sl.load_expert(e, *ws_)
+        for _ in range(2):
+            ys = sl.forward(x)
+        torch.cuda.synchronize()
+        n_s = max(2, args.steps // 4)
+        s0, s1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        s0.record()
+        for _ in range(n_s):
+            ys = sl.forward(x)
+        s1.record()
+        torch.cuda.synchronize()
+        s_ms = s0.elapsed_time(s1) / n_s
+        moved = sl._expert_bytes() * sl.groups
+        streamed = {"groups": sl.groups, "slots": sl.slots, "ms_per_step": round(s_ms, 3),
+                    "tokens_per_s": round(T / (s_ms * 1e-3), 1), "h2d_bytes_per_step": moved,
+                    "h2d_gb_per_s": round(moved / s_ms / 1e6, 2),
+                    "equals_resident_path": bool(torch.equal(ys.view(torch.int16), y.view(torch.int16))),
+                    "note": "expert weights cross PCIe on every step; the copy of a group overlaps the previous group's GEMMs"}
+        sl.close()
+        del sl
     cpu = None
     if not args.no_cpu_baseline:
         r = cpu_reference(name, min(args.cpu_sample_tokens, T), 2, 1, args.zipf)
@@ -626,7 +664,7 @@ def main():
            "warmup": warmup, "ms_per_step": ms_per_step, "higher_is_better": True, "scaling": "strong",
            "vs_baseline": None, "dtype": "bf16", "data": "synthetic", "config": config, "clocks": clocks,
            "e2e": e2e, "gpu_launches": launches * args.steps, "roofline": roofline, "cpu_baseline": cpu,
-           "stages": stages, "check": check, "ep_load": ep_load, "glue": glue, "ingest": ing,
+           "stages": stages, "check": check, "ep_load": ep_load, "glue": glue, "ingest": ing, "streamed": streamed,
            "layer_tflops": (alg["gemm1_flops"] + alg["gemm2_flops"] + alg["shared_flops"] + alg["gate_flops"])
            / (ms_per_step * 1e-3) / 1e12 / world}
     print(json.dumps(out), flush=True)
