@@ -378,6 +378,13 @@ int mg_last_launch_count(mg_handle h, int32_t* launches);
  * of this and the call's T, because the de-quantised copy can serve every chunk
  * (MG_OPT_KEEP_DEQUANT).  Set before asking mg_workspace_bytes. */
 #define MG_OPT_BATCH_TOKENS 5
+/* MG_OPT_SHARED_EARLY: 1 = mg_moe_forward runs the shared expert's two GEMMs on a library
+ * stream beside the top-k, plan and scatter kernels (ordered after the router GEMM by an event,
+ * joined before the combine); 0 = on the caller's stream after the routed experts; 2 (default) = 1 for
+ * calls of at most 4096 tokens, where the kernels are short enough to gain from running side by
+ * side, else 0.  When the shared expert runs early the
+ * stage times of the shared expert (mg_stage_times) read as the wait at the join, not as its GEMMs. */
+#define MG_OPT_SHARED_EARLY 6
 /* MG_OPT_KEEP_DEQUANT: 1 = in pre-dequantise mode, a call may reuse the bf16 copy the previous
  * call on this handle left in the same scratch, if the packed buffer and the stream are the
  * same and no expert was re-packed in between.  Meant for the token chunks of ONE logical

@@ -55,6 +55,9 @@ struct Handle {
   int opt_fp8_mode;       // MG_FP8_AUTO / MG_FP8_PREDEQUANT / MG_FP8_IN_KERNEL
   cudaStream_t side;      // de-quantisation runs here, one chunk of experts ahead of the GEMMs
   cudaEvent_t ev_entry, ev_w13[kDequantChunks], ev_w2[kDequantChunks];
+  cudaStream_t side2;     // the shared expert's GEMMs run here beside the routing and scatter kernels
+  cudaEvent_t ev_shared_in, ev_shared_out;
+  int opt_shared_early;
   bool stage_timing;      // record an event after every stage of mg_moe_forward
   int stage_calls;        // forwards recorded since timing was enabled
   cudaEvent_t stage_ev[kStageSlots][MG_STAGE_COUNT + 1];   // ring of event sets, one per forward

@@ -21,6 +21,7 @@ OPT_PAIR_GEMM = 2
 OPT_KEEP_DEQUANT = 3
 OPT_FP8_M256 = 4
 OPT_BATCH_TOKENS = 5
+OPT_SHARED_EARLY = 6
 FP8_AUTO, FP8_PREDEQUANT, FP8_IN_KERNEL = 0, 1, 2
 
 

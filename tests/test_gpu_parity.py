@@ -396,6 +396,22 @@ def test_block_forward_against_reference_fixture(built_lib):
     assert layer.block_forward(hd[:0], wd, eps).shape == (0, spec.hidden)
 
 
+def test_shared_expert_beside_the_routing_kernels_equals_after_the_experts(built_lib):
+    """MG_OPT_SHARED_EARLY only moves the shared expert's GEMMs to another stream."""
+    spec, T, seed = CASES["v3_noaux_small_bf16"]
+    x, W = O.make_inputs(spec, T, seed)
+    layer = make_layer(spec, W, DEV)
+    xd = x.to(DEV)
+    ys = []
+    for mode in (0, 1, 2, 0):
+        layer.set_option(6, mode)
+        for _ in range(2):
+            ys.append(layer.forward(xd).clone())
+        _status_ok(layer)
+    for y in ys[1:]:
+        assert torch.equal(ys[0].view(torch.int16), y.view(torch.int16))
+
+
 @pytest.mark.parametrize("T", [0, 1, 127, 129])
 def test_layer_edge_token_counts(built_lib, T):
     spec = O.LayerSpec(256, 128, 64, 6, 256, 1, 1, O.GATE_SOFTMAX_GREEDY, False, 1.0, O.WEIGHT_BF16,
