@@ -113,6 +113,11 @@ def gpu_ep_worker(rank, world, port, spec, T_global, seed, result):
     ep.dedup = True
     yh = ep.forward_host(x.cpu().pin_memory(), n_chunks=2)
     same = same and bool(torch.equal(yh.view(torch.int16), ys[0].view(torch.int16)))
+    # two pipelined micro-batches, each with its own stream, buffers and process group
+    ep_m = EPMoELayer(layer, n_micro=2)
+    y_m = ep_m.forward(x)
+    torch.cuda.synchronize()
+    same = same and bool(torch.equal(y_m.cpu().view(torch.int16), ys[0].view(torch.int16)))
     status = layer.device_status()
     gath = [None] * world
     dist.all_gather_object(gath, (ys[0], ys[1], status, same))
@@ -125,5 +130,6 @@ def gpu_ep_worker(rank, world, port, spec, T_global, seed, result):
         result["status"] = [g[2] for g in gath]
         result["dedup_equal"] = all(g[3] for g in gath)
     dist.barrier()
+    ep_m.close()
     ep.close()
     dist.destroy_process_group()
