@@ -67,7 +67,7 @@ struct GemmArgs {
 
 constexpr size_t SMEM_CTRL_BYTES = 8 * NUM_BARS + 16 + 4 * (2 * kMaxExperts + 2);
 template <bool F8B>
-constexpr size_t gemm_smem_bytes() { return 1024 + Cfg<F8B>::RING_BYTES + SMEM_CTRL_BYTES + 128 + 4 * 2 * 2048; }
+constexpr size_t gemm_smem_bytes() { return 1024 + Cfg<F8B>::RING_BYTES + SMEM_CTRL_BYTES + 1024 + 4 * 2 * 2048; }
 
 // ---- PTX wrappers ---------------------------------------------------------------------
 __device__ __forceinline__ uint32_t smem_u32(const void* p) {
@@ -257,10 +257,13 @@ __device__ __forceinline__ void send_piece(EpiWarp& w, const CUtensorMap* tmC, c
     else asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory");
   }
   __syncwarp();
+  // the piece is laid out as TMA's SWIZZLE_64B expects it (16-byte chunk index XOR bits 7-8 of the
+  // offset = (row / 2) mod 4), which also spreads a quarter-warp's stores over all banks
   uint4* dst = reinterpret_cast<uint4*>(buf + w.lane * 64);
+  const int sw = (w.lane >> 1) & 3;
 #pragma unroll
   for (int i = 0; i < 4; ++i)
-    dst[i] = make_uint4(packed[4 * i], packed[4 * i + 1], packed[4 * i + 2], packed[4 * i + 3]);
+    dst[i ^ sw] = make_uint4(packed[4 * i], packed[4 * i + 1], packed[4 * i + 2], packed[4 * i + 3]);
   asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
   __syncwarp();
   if (w.lane == 0) tma_store_2d(tmC, col0, row_first, smem_u32(buf));
@@ -373,7 +376,7 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
   int* s_pad = reinterpret_cast<int*>(tmem_slot + 4);
   int* s_cnt = s_pad + kMaxExperts + 1;
   uint8_t* epi_stage = reinterpret_cast<uint8_t*>(
-      (reinterpret_cast<uintptr_t>(smem + Cfg<F8B>::RING_BYTES + SMEM_CTRL_BYTES) + 127) & ~uintptr_t(127));
+      (reinterpret_cast<uintptr_t>(smem + Cfg<F8B>::RING_BYTES + SMEM_CTRL_BYTES) + 1023) & ~uintptr_t(1023));
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
 
@@ -576,7 +579,7 @@ struct Cfg2 {
 };
 constexpr size_t SMEM2_CTRL_BYTES = 8 * NUM_BARS2 + 16 + 4 * (3 * kMaxExperts + 3);
 template <bool F8B>
-constexpr size_t gemm2_smem_bytes() { return 1024 + Cfg2<F8B>::RING_BYTES + SMEM2_CTRL_BYTES + 128 + 4 * 2 * 2048; }
+constexpr size_t gemm2_smem_bytes() { return 1024 + Cfg2<F8B>::RING_BYTES + SMEM2_CTRL_BYTES + 1024 + 4 * 2 * 2048; }
 constexpr int GROUP_M2 = 8;                             // pair tiles (256 rows) per L2 reuse group
 
 __device__ __forceinline__ uint32_t cluster_ctarank() {
@@ -671,7 +674,7 @@ grouped_gemm2_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_const
   int* s_cnt = s_pad + kMaxExperts + 1;
   int* s_pp = s_cnt + kMaxExperts + 1;
   uint8_t* epi_stage = reinterpret_cast<uint8_t*>(
-      (reinterpret_cast<uintptr_t>(smem + Cfg2<F8B>::RING_BYTES + SMEM2_CTRL_BYTES) + 127) & ~uintptr_t(127));
+      (reinterpret_cast<uintptr_t>(smem + Cfg2<F8B>::RING_BYTES + SMEM2_CTRL_BYTES) + 1023) & ~uintptr_t(1023));
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const uint32_t rank = cluster_ctarank();           // 0 = leader
@@ -883,7 +886,7 @@ struct CfgW8 {
   static constexpr int RING_BYTES = STAGES * A_STAGE + SLOTS * B_BYTES;
   static constexpr int BARS = 2 * STAGES + 2 * NACC + 2 * SLOTS;
   static constexpr size_t CTRL_BYTES = 8 * BARS + 16 + 4 * (3 * kMaxExperts + 3);
-  static constexpr size_t SMEM_BYTES = 1024 + RING_BYTES + CTRL_BYTES + 128 + 4 * 2 * EPI_PIECE_BYTES;
+  static constexpr size_t SMEM_BYTES = 1024 + RING_BYTES + CTRL_BYTES + 1024 + 4 * 2 * EPI_PIECE_BYTES;
 };
 constexpr int W8_THREADS = GEMM_THREADS + CONVERT_THREADS;
 constexpr int W8_UNITS = 256 * (BK / 16) / CONVERT_THREADS;         // 16-byte FP8 units per thread per k-block
@@ -933,7 +936,7 @@ grouped_gemm_w8_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_con
   int* s_cnt = s_pad + kMaxExperts + 1;
   int* s_pp = s_cnt + kMaxExperts + 1;
   uint8_t* epi_stage = reinterpret_cast<uint8_t*>(
-      (reinterpret_cast<uintptr_t>(smem + C::RING_BYTES + C::CTRL_BYTES) + 127) & ~uintptr_t(127));
+      (reinterpret_cast<uintptr_t>(smem + C::RING_BYTES + C::CTRL_BYTES) + 1023) & ~uintptr_t(1023));
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   if (threadIdx.x == 0) {
@@ -1179,7 +1182,7 @@ static EncodeTiledFn get_encode_fn() {
 
 // bf16 operands land 128B-swizzled (what the UMMA descriptor expects); FP8 bytes land as plain
 // rows of 64 bytes for the converter warps
-// `out_piece`: the 32 x 32 bf16 pieces the epilogue stores (plain rows of 64 bytes)
+// `out_piece`: the 32 x 32 bf16 pieces the epilogue stores (rows of 64 bytes, SWIZZLE_64B in shared memory)
 static int encode_2d(CUtensorMap* map, const void* base, uint64_t rows, uint64_t cols, uint32_t box_rows,
                      bool fp8 = false, bool out_piece = false) {
   EncodeTiledFn fn = get_encode_fn();
@@ -1190,7 +1193,8 @@ static int encode_2d(CUtensorMap* map, const void* base, uint64_t rows, uint64_t
   cuuint32_t estr[2] = {1, 1};
   CUresult r = fn(map, fp8 ? CU_TENSOR_MAP_DATA_TYPE_UINT8 : CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2,
                   const_cast<void*>(base), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
-                  (fp8 || out_piece) ? CU_TENSOR_MAP_SWIZZLE_NONE : CU_TENSOR_MAP_SWIZZLE_128B,
+                  out_piece ? CU_TENSOR_MAP_SWIZZLE_64B
+                            : fp8 ? CU_TENSOR_MAP_SWIZZLE_NONE : CU_TENSOR_MAP_SWIZZLE_128B,
                   CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
   MG_REQUIRE(r == CUDA_SUCCESS, MG_ERR_DRIVER, "cuTensorMapEncodeTiled failed (%d) rows=%llu cols=%llu box=%u",
              static_cast<int>(r), static_cast<unsigned long long>(rows), static_cast<unsigned long long>(cols),
