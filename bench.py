@@ -570,7 +570,8 @@ def main():
         stages = {k_: {"ms": round(v, 4)} for k_, v in phases.items()}
         stages["by_rank_ms"] = all_phases
         stages["note"] = (f"phases of the first of {len(layer._mbs)} pipelined micro-batches on its stream; "
-                          f"each rank sends and later fetches {Tl * k * H * 2 * (world - 1) / world / 1e6:.0f} MB over NVLink per step")
+                          f"each rank fetches {Tl * k * H * 2 * (world - 1) / world / 1e6:.0f} MB over NVLink per step in the combine "
+                          f"and sends at most that in the dispatch (one row per token and destination GPU)")
 
     check = None
     if world == 1 and not args.no_check:
