@@ -541,7 +541,7 @@ def main():
     if world == 1 and name == "v3" and args.fp8_mode in (-1, 0, 1) and T == WORKLOADS["v3"][12]:
         # DRAM bytes of one launch (one chunk of 32 experts): mean of the 8 launches of a forward at this
         # size, ncu's dram__bytes_read.sum + dram__bytes_write.sum (1-pass counters); the algorithmic
-        # bytes are 3.09 GB (profiles/grouped_gemm_gate_up__v3_small.md)
+        # bytes are 3.09 GB
         roofline["traffic"] = 4.88e9
         roofline["traffic_note"] = "bytes per launch, ncu 1-pass DRAM counters on this workload"
     hbm = peaks.get("hbm_gbs", FALLBACK_PEAKS["hbm_gbs"])

@@ -252,6 +252,17 @@ int mg_moe_forward(mg_handle h, const void* d_x, int64_t n_tokens,
                    const void* d_gate_w, const float* d_bias, const void* d_packed,
                    void* d_workspace, size_t workspace_bytes, void* d_y, void* stream);
 
+/* The same layer on router logits the caller computed: logits[T,E] fp32 replace the library's
+ * router product, everything after it is mg_moe_forward.  The reference computes its logits with an
+ * fp32 matrix product (F.linear(x.float(), W.float()), modeling_deepseek_v3.py:503-508); the
+ * library's own router product accumulates on the tensor cores, whose rounding can differ in the
+ * last bits and flip a selection between two experts whose scores are within about 1e-4 of each
+ * other.  A caller that needs the selection of its own fp32 logits bit for bit passes them here:
+ * scoring, top-k and every later stage are exact functions of these logits. */
+int mg_moe_forward_from_logits(mg_handle h, const void* d_x, int64_t n_tokens, const float* d_logits,
+                               const float* d_bias, const void* d_packed, void* d_workspace,
+                               size_t workspace_bytes, void* d_y, void* stream);
+
 /* ---- expert parallelism (ep_size > 1): one process per GPU ------------------- */
 /* The reference's expert-parallel branch (modeling_deepseek_v3.py:636-672,692-700) exchanges
  * counts with all_to_all_single, rows with two all_to_all calls and regroups on the host.

@@ -1,4 +1,4 @@
-"""Builds libmoegen_b200.so (and the oracle's C restatement) in-tree with nvcc / gcc.
+"""Builds libmoegen_b200.so in-tree with nvcc.
 
 The library is sm_100a only; there is no other target and no fallback."""
 from __future__ import annotations
@@ -35,18 +35,6 @@ def build_library(force: bool = False, verbose: bool = False) -> str:
         if verbose:
             sys.stderr.write(r.stderr)
     return LIB
-
-
-def build_oracle_c() -> str:
-    """Compiles the oracle's C restatement (a checker used by tests, never by the library)."""
-    src = os.path.join(ROOT, "oracle", "route_oracle.c")
-    out = os.path.join(ROOT, "oracle", "libroute_oracle.so")
-    if _stale(out, [src]):
-        r = subprocess.run(["gcc", "-O2", "-std=c11", "-fPIC", "-shared", "-fno-fast-math", src, "-lm", "-o", out],
-                           capture_output=True, text=True)
-        if r.returncode != 0:
-            raise RuntimeError("gcc failed:\n" + r.stdout + r.stderr)
-    return out
 
 
 if __name__ == "__main__":

@@ -490,14 +490,15 @@ int mg_workspace_ptr(mg_handle hh, void* d_ws, int64_t max_tokens, int64_t max_r
 }
 
 // d_residual: nullptr, or [T,H] bf16 added to the block's bf16 output in the combine (may be d_y)
+// d_logits_in: nullptr, or caller-computed fp32 router logits [T,E] used in place of the router GEMM
 static int moe_forward_impl(mg_handle hh, const void* d_x, int64_t T, const void* d_gate_w, const float* d_bias,
                             const void* d_packed, void* d_ws, size_t ws_bytes, const void* d_residual, void* d_y,
-                            void* stream) {
+                            void* stream, const float* d_logits_in = nullptr) {
   Handle* h = check(hh);
   if (!h) return MG_ERR_STATE;
   MG_REQUIRE(T >= 0, MG_ERR_SHAPE, "negative token count");
   if (T == 0) { h->last_launches = 0; return MG_OK; }   // empty batch: nothing to read or write
-  MG_REQUIRE(d_x && d_gate_w && d_packed && d_ws && d_y, MG_ERR_NULL, "mg_moe_forward: null pointer");
+  MG_REQUIRE(d_x && (d_gate_w || d_logits_in) && d_packed && d_ws && d_y, MG_ERR_NULL, "mg_moe_forward: null pointer");
   MG_REQUIRE(h->d.ep_size == 1, MG_ERR_CONFIG, "mg_moe_forward is the single-GPU path (ep_size == 1)");
   MG_REQUIRE(h->d.gating != MG_GATE_SIGMOID_NOAUX_TC || d_bias != nullptr, MG_ERR_NULL,
              "noaux_tc gating needs e_score_correction_bias");
@@ -533,8 +534,13 @@ static int moe_forward_impl(mg_handle hh, const void* d_x, int64_t T, const void
     rc = start_dequant(h, d_packed, deq, st, &launches);
     if (rc != MG_OK) return rc;
   }
-  rc = mg_gate_logits(hh, d_x, d_gate_w, T, logits, stream);
-  if (rc != MG_OK) return rc;
+  if (d_logits_in != nullptr) {
+    logits = const_cast<float*>(d_logits_in);      // only read from here on
+  } else {
+    rc = mg_gate_logits(hh, d_x, d_gate_w, T, logits, stream);
+    if (rc != MG_OK) return rc;
+    launches += 1;
+  }
   mark(h, MG_STAGE_GATE_LOGITS, st);
   // The shared expert needs only x: its GEMMs (tensor-bound) run on a second stream beside the
   // top-k, plan and scatter kernels (HBM- and latency-bound) instead of after the routed experts.
@@ -557,7 +563,7 @@ static int moe_forward_impl(mg_handle hh, const void* d_x, int64_t T, const void
   rc = launch_route_topk(h, logits, d_bias, T, idx, w, st);
   if (rc != MG_OK) return rc;
   mark(h, MG_STAGE_ROUTE_TOPK, st);
-  launches += 2;
+  launches += 1;
   rc = launch_permute_plan(h, idx, T, 0, d.n_experts, counts, offsets, pad, dst, plan, st, &launches);
   if (rc != MG_OK) return rc;
   mark(h, MG_STAGE_PERMUTE_PLAN, st);
@@ -590,6 +596,12 @@ static int moe_forward_impl(mg_handle hh, const void* d_x, int64_t T, const void
 int mg_moe_forward(mg_handle hh, const void* d_x, int64_t T, const void* d_gate_w, const float* d_bias,
                    const void* d_packed, void* d_ws, size_t ws_bytes, void* d_y, void* stream) {
   return moe_forward_impl(hh, d_x, T, d_gate_w, d_bias, d_packed, d_ws, ws_bytes, nullptr, d_y, stream);
+}
+
+int mg_moe_forward_from_logits(mg_handle hh, const void* d_x, int64_t T, const float* d_logits, const float* d_bias,
+                               const void* d_packed, void* d_ws, size_t ws_bytes, void* d_y, void* stream) {
+  MG_REQUIRE(d_logits != nullptr || T == 0, MG_ERR_NULL, "mg_moe_forward_from_logits: null logits");
+  return moe_forward_impl(hh, d_x, T, nullptr, d_bias, d_packed, d_ws, ws_bytes, nullptr, d_y, stream, d_logits);
 }
 
 int mg_rmsnorm(mg_handle hh, const void* d_x, const void* d_weight, float eps, int64_t T, void* d_out,

@@ -35,6 +35,19 @@ int cuda_fail(cudaError_t e, const char* what);   // records text, returns (int)
     if (!(cond)) { ::mg::set_error(__VA_ARGS__); return (code); }        \
   } while (0)
 
+// encoded TMA descriptors of the (pointer, shape, box) combinations a handle has launched with
+struct TensorMapCache {
+  static constexpr int kEntries = 96;
+  struct Entry {
+    const void* base;
+    uint64_t rows, cols;
+    uint32_t box_rows, kind;
+    CUtensorMap map;
+  };
+  Entry e[kEntries];
+  int used = 0, next = 0;
+};
+
 struct Handle {
   uint32_t magic;
   mg_layer_desc d;
@@ -61,6 +74,7 @@ struct Handle {
   bool stage_timing;      // record an event after every stage of mg_moe_forward
   int stage_calls;        // forwards recorded since timing was enabled
   cudaEvent_t stage_ev[kStageSlots][MG_STAGE_COUNT + 1];   // ring of event sets, one per forward
+  mutable TensorMapCache tmaps;
 };
 constexpr uint32_t kMagic = 0x4d474232u;  // "MGB2"
 

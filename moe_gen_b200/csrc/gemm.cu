@@ -421,9 +421,6 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
           const uint32_t s = it % NS, ph = (it / NS) & 1u;
           if (!mbar_wait(smem_u32(&empty[s]), ph ^ 1u, abort_flag, g.status, 1)) break;
           const uint32_t fb = smem_u32(&full[s]);
-#ifdef MG_EXP_NO_TMA
-          if (it >= NS) { mbar_arrive(fb); continue; }   // experiment: operands loaded once only
-#endif
           mbar_expect_tx(fb, tx_bytes);
           const uint32_t sa = smem_base + s * STAGE_BYTES;
           tma_load_2d(sa, &tmA, kb * BK, t.row0, fb);
@@ -493,9 +490,6 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
 #pragma unroll
         for (int u = ct; u < units; u += CONVERT_THREADS / 2) {
           const int r = u >> 2, c = u & 3;                // row of the tile, 16-byte chunk of its 64 bytes
-#ifdef MG_EXP_F8_NOCONV
-          if (it > 8) continue;                            // experiment: tiles converted only at the start
-#endif
           const uint4 q = *reinterpret_cast<const uint4*>(src + u * 16);
           uint4 lo, hi;
           convert16(q, r < 128 ? s0 : s1, lo, hi);
@@ -505,9 +499,7 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
           *reinterpret_cast<uint4*>(drow + (((2 * c + 1) ^ (r & 7)) << 4)) = hi;
         }
         // make the generic-proxy writes visible to the tensor core's shared-memory reads
-#ifndef MG_EXP_F8_NOFENCE
         asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
-#endif
         __syncwarp();
         if (lane == 0) mbar_arrive(smem_u32(&bready[j]));
       }
@@ -527,9 +519,7 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
       const uint32_t taddr = tmem_base + acc * ACC_COLS + (static_cast<uint32_t>(quarter * 32) << 16);
       const bool live = row_in_tile < t.valid_rows;
       const long long row = static_cast<long long>(t.row0) + row_in_tile;
-#ifndef MG_EXP_NO_EPI
       epilogue_rows<EPI>(taddr, g, &tmC, ew, row, t.row0 + quarter * 32, t.n_idx, live, quarter * 32 < t.valid_rows);
-#endif
       // hand the accumulator back to the MMA warp
       tc_fence_before();
       __syncwarp();
@@ -580,7 +570,6 @@ struct Cfg2 {
 constexpr size_t SMEM2_CTRL_BYTES = 8 * NUM_BARS2 + 16 + 4 * (3 * kMaxExperts + 3);
 template <bool F8B>
 constexpr size_t gemm2_smem_bytes() { return 1024 + Cfg2<F8B>::RING_BYTES + SMEM2_CTRL_BYTES + 1024 + 4 * 2 * 2048; }
-constexpr int GROUP_M2 = 8;                             // pair tiles (256 rows) per L2 reuse group
 
 __device__ __forceinline__ uint32_t cluster_ctarank() {
   uint32_t r;
@@ -628,9 +617,12 @@ struct Tile2 {
   int n_idx;
 };
 
-// s_pp[e] = number of pair tiles (per N tile) of the experts before e
-__device__ __forceinline__ Tile2 locate_tile2(int tile, const int* s_pad, const int* s_cnt, const int* s_pp,
-                                              int n_groups, int n_tiles, int n_per_group) {
+// A tile of SUB row tiles (SUB x 128 rows).  s_pp[e] = number of such tiles (per N tile) of the
+// experts before e; tiles that cover 2048 rows form one L2 reuse group (N-major inside it).
+template <int SUB>
+__device__ __forceinline__ Tile2 locate_tile_sub(int tile, const int* s_pad, const int* s_cnt, const int* s_pp,
+                                                 int n_groups, int n_tiles, int n_per_group) {
+  constexpr int GROUP = 2048 / (SUB * BM);
   int lo = 0, hi = n_groups;
   while (hi - lo > 1) {
     int mid = (lo + hi) >> 1;
@@ -639,18 +631,22 @@ __device__ __forceinline__ Tile2 locate_tile2(int tile, const int* s_pad, const 
   const int e = lo;
   const int local = tile - s_pp[e] * n_tiles;
   const int mp_e = s_pp[e + 1] - s_pp[e];
-  const int per_group = GROUP_M2 * n_tiles;
+  const int per_group = GROUP * n_tiles;
   const int grp = local / per_group;
   const int rem = local - grp * per_group;
-  const int gm = min(GROUP_M2, mp_e - grp * GROUP_M2);
+  const int gm = min(GROUP, mp_e - grp * GROUP);
   const int n = rem / gm;
-  const int mp = grp * GROUP_M2 + (rem - n * gm);
+  const int mp = grp * GROUP + (rem - n * gm);
   Tile2 t;
-  t.row0 = s_pad[e] + mp * 2 * BM;
-  t.rows_left = s_cnt[e] - mp * 2 * BM;
+  t.row0 = s_pad[e] + mp * SUB * BM;
+  t.rows_left = s_cnt[e] - mp * SUB * BM;
   t.b_row = e * n_per_group + n * BN_MAX;
   t.n_idx = n;
   return t;
+}
+__device__ __forceinline__ Tile2 locate_tile2(int tile, const int* s_pad, const int* s_cnt, const int* s_pp,
+                                              int n_groups, int n_tiles, int n_per_group) {
+  return locate_tile_sub<2>(tile, s_pad, s_cnt, s_pp, n_groups, n_tiles, n_per_group);
 }
 
 template <int EPI, bool F8B>
@@ -732,9 +728,6 @@ grouped_gemm2_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_const
           const uint32_t s = it % STAGES2, ph = (it / STAGES2) & 1u;
           if (!mbar_wait(smem_u32(&empty[s]), ph ^ 1u, abort_flag, g.status, 11)) break;
           const uint32_t fb = smem_u32(&full[s]);
-#ifdef MG_EXP_NO_TMA
-          if (it >= STAGES2) { if (rank == 0) mbar_arrive(fb); continue; }   // experiment: operands loaded once only
-#endif
           const uint32_t sa = smem_base + s * STAGE2_BYTES;
           if (F8B) {
             mbar_expect_tx(fb, STAGE2_BYTES);                      // this CTA's A and FP8 half, own barrier
@@ -807,9 +800,6 @@ grouped_gemm2_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_const
 #pragma unroll
         for (int u = ct; u < 128 * (BK / 16); u += CONVERT_THREADS / 2) {
           const int r = u >> 2, c = u & 3;
-#ifdef MG_EXP_F8_NOCONV
-          if (it > 8) continue;                            // experiment: tiles converted only at the start
-#endif
           const uint4 q = *reinterpret_cast<const uint4*>(src + u * 16);
           uint4 lo, hi;
           convert16(q, sc, lo, hi);
@@ -838,10 +828,8 @@ grouped_gemm2_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_const
       const int my_rows = t.rows_left - static_cast<int>(rank) * BM;      // rows of my half that are real
       const bool live = row_in_half < my_rows;
       const long long row = static_cast<long long>(t.row0) + rank * BM + row_in_half;
-#ifndef MG_EXP_NO_EPI
       epilogue_rows<EPI>(taddr, g, &tmC, ew, row, t.row0 + static_cast<int>(rank) * BM + quarter * 32, t.n_idx, live,
                          quarter * 32 < my_rows);
-#endif
       tc_fence_before();
       __syncwarp();
       if (lane == 0) mbar_arrive_cluster(map_to_cta(smem_u32(&tempty[acc]), 0));
@@ -1046,9 +1034,6 @@ grouped_gemm_w8_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_con
     };
     auto fetch = [&](B8Cursor& cur, uint4 (&q)[W8_UNITS]) {
       if (cur.tile >= total_tiles) return;
-#ifdef MG_EXP_W8_NOFETCH
-      if (cur.kb > 1) { step(cur); return; }               // experiment: FP8 bytes loaded at a tile's start only
-#endif
 #pragma unroll
       for (int i = 0; i < W8_UNITS; ++i) q[i] = ld_weights16(cur.src + static_cast<long long>(64 * i) * row_bytes);
       step(cur);
@@ -1065,9 +1050,6 @@ grouped_gemm_w8_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_con
       uint8_t* dst = smem + C::STAGES * C::A_STAGE + j * B_BYTES;
 #pragma unroll
       for (int i = 0; i < W8_UNITS; ++i) {
-#ifdef MG_EXP_W8_NOCONV
-        if (it > 8) continue;                               // experiment: tiles converted at the start only
-#endif
         const int r = r0 + 64 * i;
         uint4 lo, hi;
         convert16(q[i], i < W8_UNITS / 2 ? s0 : s1, lo, hi);
@@ -1183,8 +1165,19 @@ static EncodeTiledFn get_encode_fn() {
 // bf16 operands land 128B-swizzled (what the UMMA descriptor expects); FP8 bytes land as plain
 // rows of 64 bytes for the converter warps
 // `out_piece`: the 32 x 32 bf16 pieces the epilogue stores (rows of 64 bytes, SWIZZLE_64B in shared memory)
-static int encode_2d(CUtensorMap* map, const void* base, uint64_t rows, uint64_t cols, uint32_t box_rows,
-                     bool fp8 = false, bool out_piece = false) {
+// A layer calls the same few (pointer, shape) combinations on every forward, so the encoded maps
+// are kept in the handle: a forward at decode sizes is short enough for ~60 driver calls to show.
+static int encode_2d(const Handle* h, CUtensorMap* map, const void* base, uint64_t rows, uint64_t cols,
+                     uint32_t box_rows, bool fp8 = false, bool out_piece = false) {
+  const uint32_t kind = (fp8 ? 1u : 0u) | (out_piece ? 2u : 0u);
+  TensorMapCache& c = h->tmaps;
+  for (int i = 0; i < c.used; ++i) {
+    const TensorMapCache::Entry& e = c.e[i];
+    if (e.base == base && e.rows == rows && e.cols == cols && e.box_rows == box_rows && e.kind == kind) {
+      *map = e.map;
+      return MG_OK;
+    }
+  }
   EncodeTiledFn fn = get_encode_fn();
   MG_REQUIRE(fn != nullptr, MG_ERR_DRIVER, "cuTensorMapEncodeTiled not available from the driver");
   cuuint64_t dims[2] = {cols, rows};
@@ -1199,39 +1192,55 @@ static int encode_2d(CUtensorMap* map, const void* base, uint64_t rows, uint64_t
   MG_REQUIRE(r == CUDA_SUCCESS, MG_ERR_DRIVER, "cuTensorMapEncodeTiled failed (%d) rows=%llu cols=%llu box=%u",
              static_cast<int>(r), static_cast<unsigned long long>(rows), static_cast<unsigned long long>(cols),
              box_rows);
+  TensorMapCache::Entry& e = c.e[c.next];
+  e.base = base; e.rows = rows; e.cols = cols; e.box_rows = box_rows; e.kind = kind; e.map = *map;
+  c.next = (c.next + 1) % TensorMapCache::kEntries;
+  if (c.used < TensorMapCache::kEntries) ++c.used;
+  return MG_OK;
+}
+
+// the opt-in to more than 48 KiB of dynamic shared memory is a per-device attribute of the kernel:
+// set once per (kernel, device)
+template <typename K>
+static int allow_smem(K kernel, size_t bytes, int device, bool (&done)[64]) {
+  if (device >= 0 && device < 64 && done[device]) return MG_OK;
+  MG_CUDA(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(bytes)));
+  if (device >= 0 && device < 64) done[device] = true;
   return MG_OK;
 }
 
 template <int EPI, bool F8B>
 static int launch_epi(const Handle* h, const CUtensorMap& ta, const CUtensorMap& tb, const CUtensorMap& tc,
                       const GemmArgs& args, int grid, cudaStream_t st) {
-  // per device, and cheap: set on every launch rather than tracking which devices have it
   constexpr size_t smem = gemm_smem_bytes<F8B>();
-  MG_CUDA(cudaFuncSetAttribute(grouped_gemm_kernel<EPI, F8B>, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                               static_cast<int>(smem)));
+  static bool done[64];
+  int rc = allow_smem(grouped_gemm_kernel<EPI, F8B>, smem, h->device, done);
+  if (rc != MG_OK) return rc;
   grouped_gemm_kernel<EPI, F8B><<<grid, Cfg<F8B>::THREADS, smem, st>>>(ta, tb, tc, args);
   MG_CUDA(cudaGetLastError());
   return MG_OK;
 }
 
 template <int EPI, bool F8B>
-static int launch_pair(const CUtensorMap& ta, const CUtensorMap& tb, const CUtensorMap& tc, const GemmArgs& args,
-                       int grid, cudaStream_t st) {
+static int launch_pair(const Handle* h, const CUtensorMap& ta, const CUtensorMap& tb, const CUtensorMap& tc,
+                       const GemmArgs& args, int grid, cudaStream_t st) {
   constexpr size_t smem = gemm2_smem_bytes<F8B>();
-  MG_CUDA(cudaFuncSetAttribute(grouped_gemm2_kernel<EPI, F8B>, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                               static_cast<int>(smem)));
+  static bool done[64];
+  int rc = allow_smem(grouped_gemm2_kernel<EPI, F8B>, smem, h->device, done);
+  if (rc != MG_OK) return rc;
   grouped_gemm2_kernel<EPI, F8B><<<grid, Cfg2<F8B>::THREADS, smem, st>>>(ta, tb, tc, args);
   MG_CUDA(cudaGetLastError());
   return MG_OK;
 }
 
 template <int EPI, int TM>
-static int launch_w8(const CUtensorMap& ta, const CUtensorMap& tc, const void* b8, const GemmArgs& args, int grid,
-                     cudaStream_t st) {
+static int launch_w8(const Handle* h, const CUtensorMap& ta, const CUtensorMap& tc, const void* b8,
+                     const GemmArgs& args, int grid, cudaStream_t st) {
   constexpr size_t smem = CfgW8<TM>::SMEM_BYTES;
   static_assert(smem <= 232448, "shared memory of the W8A16 kernel exceeds the 227 KiB a CTA may have");
-  MG_CUDA(cudaFuncSetAttribute(grouped_gemm_w8_kernel<EPI, TM>, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                               static_cast<int>(smem)));
+  static bool done[64];
+  int rc = allow_smem(grouped_gemm_w8_kernel<EPI, TM>, smem, h->device, done);
+  if (rc != MG_OK) return rc;
   grouped_gemm_w8_kernel<EPI, TM><<<grid, W8_THREADS, smem, st>>>(ta, tc, static_cast<const uint8_t*>(b8), args);
   MG_CUDA(cudaGetLastError());
   return MG_OK;
@@ -1253,7 +1262,7 @@ int launch_grouped_gemm(const Handle* h, const GemmProblem& p, cudaStream_t st) 
     MG_REQUIRE(p.n_per_group % BN_MAX == 0, MG_ERR_SHAPE, "GEMM N per expert (%d) must be a multiple of %d",
                p.n_per_group, BN_MAX);
   }
-  // SM pairs (2-CTA tiles of 256 x 256) for the bf16 expert GEMMs unless switched off
+  // SM pairs (2-CTA tiles of 256 x 256) for the bf16 expert GEMMs when switched on
   const bool pair = h->opt_pair_gemm && !f32_out;
   // FP8 weights converted in the kernel (one CTA per SM): 256-row tiles once experts average 120
   // live rows (a_rows also counts up to 127 rows of padding per expert); below that most tall tiles
@@ -1262,16 +1271,16 @@ int launch_grouped_gemm(const Handle* h, const GemmProblem& p, cudaStream_t st) 
   const bool m256 = p.b_fp8 && !pair && !f32_out && !dense && h->opt_fp8_m256 &&
                     p.a_rows >= static_cast<int64_t>(p.n_groups) * (h->opt_fp8_m256 == 2 ? 0 : 120 + 127);
   CUtensorMap ta, tb;
-  int rc = encode_2d(&ta, p.a, static_cast<uint64_t>(p.a_rows), static_cast<uint64_t>(p.K), m256 ? 2 * BM : BM);
+  int rc = encode_2d(h, &ta, p.a, static_cast<uint64_t>(p.a_rows), static_cast<uint64_t>(p.K), m256 ? 2 * BM : BM);
   if (rc != MG_OK) return rc;
-  rc = encode_2d(&tb, p.b, static_cast<uint64_t>(p.n_groups) * p.n_per_group, static_cast<uint64_t>(p.K),
+  rc = encode_2d(h, &tb, p.b, static_cast<uint64_t>(p.n_groups) * p.n_per_group, static_cast<uint64_t>(p.K),
                  pair ? 128 : bn, p.b_fp8);
   if (rc != MG_OK) return rc;
   CUtensorMap tc = ta;   // unused by the fp32 epilogue
   if (!f32_out) {
     // output tensor [a_rows, ldo] bf16, written in 32 x 32 pieces
     MG_REQUIRE(p.ldo % 8 == 0, MG_ERR_SHAPE, "output row length %lld must be a multiple of 8", static_cast<long long>(p.ldo));
-    rc = encode_2d(&tc, p.out, static_cast<uint64_t>(p.a_rows), static_cast<uint64_t>(p.ldo), 32, false, true);
+    rc = encode_2d(h, &tc, p.out, static_cast<uint64_t>(p.a_rows), static_cast<uint64_t>(p.ldo), 32, false, true);
     if (rc != MG_OK) return rc;
   }
   if (p.b_fp8) {
@@ -1307,20 +1316,12 @@ int launch_grouped_gemm(const Handle* h, const GemmProblem& p, cudaStream_t st) 
     if (max_tiles < grid) grid = static_cast<int>(max_tiles);
   }
   if (grid < 1) return MG_OK;
-#ifdef MG_EXP_W8_TM128
-  if (p.b_fp8 && !pair && !f32_out && !dense && !m256) {   // experiment: register-fed kernel for 128-row tiles too
-    switch (p.epilogue) {
-      case EPI_SWIGLU_BF16: return launch_w8<EPI_SWIGLU_BF16, 128>(ta, tc, p.b, a, grid, st);
-      case EPI_PLAIN_BF16: return launch_w8<EPI_PLAIN_BF16, 128>(ta, tc, p.b, a, grid, st);
-    }
-  }
-#endif
   if (m256) {
     long long tall_tiles = ((p.a_rows / BM + p.n_groups) / 2 + 1) * static_cast<long long>(a.n_tiles);
     int ctas = tall_tiles < h->sm_count ? static_cast<int>(tall_tiles) : h->sm_count;
     switch (p.epilogue) {
-      case EPI_SWIGLU_BF16: return launch_w8<EPI_SWIGLU_BF16, 256>(ta, tc, p.b, a, ctas, st);
-      case EPI_PLAIN_BF16: return launch_w8<EPI_PLAIN_BF16, 256>(ta, tc, p.b, a, ctas, st);
+      case EPI_SWIGLU_BF16: return launch_w8<EPI_SWIGLU_BF16, 256>(h, ta, tc, p.b, a, ctas, st);
+      case EPI_PLAIN_BF16: return launch_w8<EPI_PLAIN_BF16, 256>(h, ta, tc, p.b, a, ctas, st);
     }
   }
   if (pair) {
@@ -1334,13 +1335,13 @@ int launch_grouped_gemm(const Handle* h, const GemmProblem& p, cudaStream_t st) 
     if (pairs < 1) pairs = 1;
     if (p.b_fp8) {
       switch (p.epilogue) {
-        case EPI_SWIGLU_BF16: return launch_pair<EPI_SWIGLU_BF16, true>(ta, tb, tc, a, 2 * pairs, st);
-        case EPI_PLAIN_BF16: return launch_pair<EPI_PLAIN_BF16, true>(ta, tb, tc, a, 2 * pairs, st);
+        case EPI_SWIGLU_BF16: return launch_pair<EPI_SWIGLU_BF16, true>(h, ta, tb, tc, a, 2 * pairs, st);
+        case EPI_PLAIN_BF16: return launch_pair<EPI_PLAIN_BF16, true>(h, ta, tb, tc, a, 2 * pairs, st);
       }
     }
     switch (p.epilogue) {
-      case EPI_SWIGLU_BF16: return launch_pair<EPI_SWIGLU_BF16, false>(ta, tb, tc, a, 2 * pairs, st);
-      case EPI_PLAIN_BF16: return launch_pair<EPI_PLAIN_BF16, false>(ta, tb, tc, a, 2 * pairs, st);
+      case EPI_SWIGLU_BF16: return launch_pair<EPI_SWIGLU_BF16, false>(h, ta, tb, tc, a, 2 * pairs, st);
+      case EPI_PLAIN_BF16: return launch_pair<EPI_PLAIN_BF16, false>(h, ta, tb, tc, a, 2 * pairs, st);
     }
   }
   if (p.b_fp8) {

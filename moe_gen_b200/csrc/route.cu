@@ -249,35 +249,52 @@ __global__ void __launch_bounds__(kPlanTokens) plan_count_kernel(const int32_t* 
     block_counts[static_cast<int64_t>(blockIdx.x) * n + e] = hist[e];
 }
 
-// one block: per expert, turn block_counts[:,e] into an exclusive prefix over blocks and
-// produce counts / offsets / pad_offsets
-__global__ void __launch_bounds__(1024) plan_scan_kernel(int32_t* __restrict__ block_counts,
-                                                         int nblk, int n,
-                                                         int32_t* __restrict__ counts,
-                                                         int32_t* __restrict__ offsets,
-                                                         int32_t* __restrict__ pad_offsets) {
-  __shared__ int32_t tot[kMaxExperts];
-  for (int e = threadIdx.x; e < n; e += blockDim.x) {
-    int32_t run = 0;
-    for (int b = 0; b < nblk; ++b) {
-      int32_t c = block_counts[static_cast<int64_t>(b) * n + e];
-      block_counts[static_cast<int64_t>(b) * n + e] = run;
-      run += c;
+// one warp per expert: turns block_counts[:, e] into an exclusive prefix over the blocks (32 blocks
+// per step, warp scan) and writes the expert's total
+__global__ void __launch_bounds__(256) plan_scan_kernel(int32_t* __restrict__ block_counts, int nblk, int n,
+                                                        int32_t* __restrict__ counts) {
+  const int lane = threadIdx.x & 31;
+  const int e = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+  if (e >= n) return;
+  int32_t run = 0;
+  for (int b0 = 0; b0 < nblk; b0 += 32) {
+    const int b = b0 + lane;
+    const int32_t c = b < nblk ? block_counts[static_cast<int64_t>(b) * n + e] : 0;
+    int32_t inc = c;                                   // inclusive scan over the 32 lanes
+#pragma unroll
+    for (int o = 1; o < 32; o <<= 1) {
+      const int32_t v = __shfl_up_sync(0xFFFFFFFFu, inc, o);
+      if (lane >= o) inc += v;
     }
-    tot[e] = run;
-    counts[e] = run;
+    if (b < nblk) block_counts[static_cast<int64_t>(b) * n + e] = run + inc - c;
+    run += __shfl_sync(0xFFFFFFFFu, inc, 31);
   }
+  if (lane == 0) counts[e] = run;
+}
+
+// one block: offsets = exclusive scan of counts, pad_offsets = the same over counts rounded up to
+// whole 128-row tiles (n <= kMaxExperts = 512 = one value per thread)
+__global__ void __launch_bounds__(kMaxExperts) plan_offsets_kernel(const int32_t* __restrict__ counts, int n,
+                                                                   int32_t* __restrict__ offsets,
+                                                                   int32_t* __restrict__ pad_offsets) {
+  __shared__ int32_t warp_o[kMaxExperts / 32], warp_p[kMaxExperts / 32];
+  const int e = threadIdx.x, lane = e & 31, w = e >> 5;
+  const int32_t c = e < n ? counts[e] : 0;
+  const int32_t cp = (c + kTileM - 1) / kTileM * kTileM;
+  int32_t io = c, ip = cp;
+#pragma unroll
+  for (int o = 1; o < 32; o <<= 1) {
+    const int32_t vo = __shfl_up_sync(0xFFFFFFFFu, io, o), vp = __shfl_up_sync(0xFFFFFFFFu, ip, o);
+    if (lane >= o) { io += vo; ip += vp; }
+  }
+  if (lane == 31) { warp_o[w] = io; warp_p[w] = ip; }
   __syncthreads();
-  if (threadIdx.x == 0) {
-    int32_t o = 0, p = 0;
-    for (int e = 0; e < n; ++e) {
-      offsets[e] = o;
-      pad_offsets[e] = p;
-      o += tot[e];
-      p += (tot[e] + kTileM - 1) / kTileM * kTileM;
-    }
-    offsets[n] = o;
-    pad_offsets[n] = p;
+  int32_t bo = 0, bp = 0;
+  for (int i = 0; i < w; ++i) { bo += warp_o[i]; bp += warp_p[i]; }
+  if (e < n) {
+    offsets[e] = bo + io - c;
+    pad_offsets[e] = bp + ip - cp;
+    if (e == n - 1) { offsets[n] = bo + io; pad_offsets[n] = bp + ip; }
   }
 }
 
@@ -338,7 +355,9 @@ int launch_permute_plan(const Handle* h, const int32_t* idx, int64_t T, int expe
                                                                           n_exp, bc);
     MG_CUDA(cudaGetLastError());
   }
-  plan_scan_kernel<<<1, 1024, 0, st>>>(bc, nblk, n_exp, counts, offsets, pad_offsets);
+  plan_scan_kernel<<<(n_exp + 7) / 8, 256, 0, st>>>(bc, nblk, n_exp, counts);
+  MG_CUDA(cudaGetLastError());
+  plan_offsets_kernel<<<1, kMaxExperts, 0, st>>>(counts, n_exp, offsets, pad_offsets);
   MG_CUDA(cudaGetLastError());
   if (nblk > 0) {
     size_t smem = static_cast<size_t>(2) * (kPlanTokens / 32) * n_exp * sizeof(int32_t);
@@ -346,7 +365,7 @@ int launch_permute_plan(const Handle* h, const int32_t* idx, int64_t T, int expe
                                                        pad_offsets, dst_row);
     MG_CUDA(cudaGetLastError());
   }
-  if (launches) *launches += nblk > 0 ? 3 : 1;
+  if (launches) *launches += nblk > 0 ? 4 : 2;
   return MG_OK;
 }
 
@@ -803,12 +822,11 @@ int launch_ep_count(const Handle* h, const int32_t* idx, int64_t T, int32_t* cou
   const int E = h->d.n_experts, k = h->d.top_k;
   int nblk = static_cast<int>((T + kPlanTokens - 1) / kPlanTokens);
   int32_t* bc = static_cast<int32_t*>(ws);
-  int32_t* scratch = bc + static_cast<size_t>(nblk > 0 ? nblk : 1) * E;   // offsets / pad_offsets, unused here
   if (nblk > 0) {
     plan_count_kernel<<<nblk, kPlanTokens, E * sizeof(int32_t), st>>>(idx, T, k, 0, E, bc);
     MG_CUDA(cudaGetLastError());
   }
-  plan_scan_kernel<<<1, 1024, 0, st>>>(bc, nblk, E, counts, scratch, scratch + E + 1);
+  plan_scan_kernel<<<(E + 7) / 8, 256, 0, st>>>(bc, nblk, E, counts);
   MG_CUDA(cudaGetLastError());
   return MG_OK;
 }

@@ -164,6 +164,25 @@ class MoELayer:
 
     __call__ = forward
 
+    def forward_from_logits(self, x: torch.Tensor, logits: torch.Tensor, out: Optional[torch.Tensor] = None):
+        """The layer on router logits the caller computed ([T,E] fp32, e.g. F.linear(x.float(),
+        W.float()) as the reference's MoEGate does, modeling_deepseek_v3.py:503-508): the routing is
+        then an exact function of those logits."""
+        shape = x.shape
+        x2 = x.reshape(-1, self.H)
+        self._check_in(x2, torch.bfloat16, "hidden_states")
+        self._check_in(logits, torch.float32, "logits")
+        T = x2.shape[0]
+        if tuple(logits.shape) != (T, self.E):
+            raise ValueError(f"logits {tuple(logits.shape)}, expected {(T, self.E)}")
+        ws = self._workspace(T)
+        y = torch.empty_like(x2) if out is None else out
+        with torch.cuda.device(self.device):
+            L.check(self.lib.mg_moe_forward_from_logits(self._h, x2.data_ptr(), T, logits.data_ptr(), _ptr(self.bias),
+                                                        self.packed.data_ptr(), ws.data_ptr(), ws.numel(),
+                                                        y.data_ptr(), self._stream()))
+        return y.view(shape)
+
     # ------------------------------------------------------------------ decoder-layer glue
     def rmsnorm(self, x: torch.Tensor, weight: torch.Tensor, eps: float = 1e-6,
                 out: Optional[torch.Tensor] = None) -> torch.Tensor:

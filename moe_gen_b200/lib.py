@@ -59,6 +59,7 @@ SIGNATURES = {
     "mg_shared_ffn": [_vp, _vp, _i64, _vp, _vp, _vp, _vp],
     "mg_combine": [_vp, _vp, _vp, _vp, _vp, _vp, _i64, _vp, _vp],
     "mg_moe_forward": [_vp, _vp, _i64, _vp, _vp, _vp, _vp, _sz, _vp, _vp],
+    "mg_moe_forward_from_logits": [_vp, _vp, _i64, _vp, _vp, _vp, _vp, _sz, _vp, _vp],
     "mg_workspace_ptr": [_vp, _vp, _i64, _i64, _i32, _P(_vp)],
     "mg_selftest_wait_timeout": [_vp, _i32, _vp],
     "mg_last_launch_count": [_vp, _P(_i32)],

@@ -129,8 +129,8 @@ def test_mixtral_restatement_against_installed_transformers():
 # ---- the plain-C restatement of routing / permutation / de-quantisation agrees with the fixtures
 def _c_oracle():
     import ctypes as C
-    from moe_gen_b200 import build
-    lib = C.CDLL(build.build_oracle_c())
+    from oracle.build_oracle import build_oracle_c
+    lib = C.CDLL(build_oracle_c())
     return lib, C
 
 
