@@ -112,6 +112,13 @@ const char* mg_last_error(void);
  * the streams it used.  *code gets MG_DEV_*; *detail a kernel-specific value. */
 int mg_device_status(mg_handle h, int32_t* code, int32_t* detail);
 
+/* The same two words copied to host_words[2] (pinned host memory) by an asynchronous copy on `stream`:
+ * no host synchronisation and no clearing.  A caller that cannot afford a synchronising read after every
+ * forward (the expert-parallel layer) enqueues this behind its kernels and looks at the words once an
+ * event recorded after it has completed; a non-zero code is then fetched and cleared with
+ * mg_device_status.  No counterpart in the reference. */
+int mg_device_status_async(mg_handle h, int32_t* host_words, void* stream);
+
 /* ---- sizes -------------------------------------------------------------- */
 
 /* Bytes of the packed weight buffer for the experts this rank owns (+ shared

@@ -192,6 +192,15 @@ int mg_device_status(mg_handle hh, int32_t* code, int32_t* detail) {
   return MG_OK;
 }
 
+int mg_device_status_async(mg_handle hh, int32_t* host_words, void* stream) {
+  Handle* h = check(hh);
+  if (!h) return MG_ERR_STATE;
+  MG_REQUIRE(host_words, MG_ERR_NULL, "null argument");
+  MG_CUDA(cudaMemcpyAsync(host_words, h->d_status, 2 * sizeof(int32_t), cudaMemcpyDeviceToHost,
+                          static_cast<cudaStream_t>(stream)));
+  return MG_OK;
+}
+
 int mg_packed_weight_bytes(mg_handle hh, size_t* bytes) {
   Handle* h = check(hh);
   if (!h) return MG_ERR_STATE;

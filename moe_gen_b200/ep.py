@@ -67,13 +67,17 @@ class EPMoELayer:
     PHASES = ["route_dispatch", "expert_ffn", "combine"]
 
     def __init__(self, layer: MoELayer, group: Optional[dist.ProcessGroup] = None, capacity_factor: float = 2.0,
-                 n_micro: int = 1, dedup: bool = True):
+                 n_micro: int = 1, dedup: bool = True, min_headroom: int = 4096):
         self.layer = layer
         self.group = group
         self.rank = dist.get_rank(group)
         self.world = dist.get_world_size(group)
         assert layer.desc.ep_size == self.world and layer.desc.ep_rank == self.rank
+        # a rank's receive buffers hold max(capacity_factor * mean rows, mean rows + min_headroom) rows
+        # (plus padding; min_headroom = 0 leaves the factor alone); more rows than that raise
+        # MG_DEV_CAPACITY, reported by check_status()
         self.capacity_factor = capacity_factor
+        self.min_headroom = min_headroom
         self.n_micro = max(1, n_micro)
         # one row per (token, destination rank) over NVLink; the owner copies the rows of a token's
         # further experts on that rank (pays off when top_k exceeds the number of ranks a token reaches)
@@ -90,6 +94,10 @@ class EPMoELayer:
         self._streams = [torch.cuda.Stream(device=self.dev) for _ in range(self.n_micro)]
         self.deq = None
         self._batch_tokens = 0             # local tokens of the batch forward_host is feeding in parts
+        # device status word mirrored into pinned host memory behind every forward (no synchronisation):
+        # a receive buffer that was too small drops picks, and the caller must hear about it
+        self._status_host = torch.zeros(2, dtype=torch.int32).pin_memory()
+        self._status_event: Optional[torch.cuda.Event] = None
 
     # ------------------------------------------------------------------ buffers
     def _setup(self, T: int):
@@ -106,7 +114,8 @@ class EPMoELayer:
                 mb.t0, mb.t1 = bounds[i], bounds[i + 1]
                 Tm = mb.t1 - mb.t0
                 avg_rows = Tm * k                              # rows a rank receives when load is even
-                cap = int(min(Tm * self.world * k, max(avg_rows * self.capacity_factor, avg_rows + 4096)))
+                floor = avg_rows + self.min_headroom if self.min_headroom > 0 else 0
+                cap = int(min(Tm * self.world * k, max(avg_rows * self.capacity_factor, floor)))
                 cap = (cap + TILE_M - 1) // TILE_M * TILE_M + El * TILE_M
                 assert cap < (1 << PEER_SHIFT)
                 mb.cap = cap
@@ -189,6 +198,38 @@ class EPMoELayer:
     def close(self):
         self._release()
 
+    def reconfigure(self, capacity_factor: Optional[float] = None):
+        """Changes the receive-buffer capacity (in multiples of the mean rows per rank); the shared
+        buffers are re-allocated by the next forward.  Collective: every rank must call it."""
+        if capacity_factor is not None:
+            self.capacity_factor = capacity_factor
+        self._release()
+
+    def check_status(self, wait: bool = False):
+        """Raises if a forward whose status has reached the host reported a device-side problem.
+        wait=False looks only at forwards that have already finished (no synchronisation); forward()
+        calls it on entry, forward_host() with wait=True before it returns.  MG_DEV_CAPACITY means a
+        rank's receive buffer was too small for the rows routed to its experts: the picks sent to that
+        rank were dropped from dispatch and combine, so that forward's output lacks their contributions."""
+        ev = self._status_event
+        if ev is None:
+            return
+        if wait:
+            ev.synchronize()
+        elif not ev.query():
+            return
+        self._status_event = None
+        code, detail = int(self._status_host[0]), int(self._status_host[1])
+        if code == L.DEV_OK:
+            return
+        self.layer.device_status()                      # fetch and clear on the device
+        if code == L.DEV_CAPACITY:
+            raise RuntimeError(
+                f"expert-parallel receive buffer of rank {detail} overflowed (capacity_factor="
+                f"{self.capacity_factor}): the picks routed to that rank were dropped and the output of that "
+                "forward is incomplete; raise capacity_factor (reconfigure) and run the batch again")
+        raise RuntimeError(f"device status {code} (detail {detail}) reported by an expert-parallel forward")
+
     @staticmethod
     def _barrier(mb):
         # a stream-ordered collective: kernels launched after it on this rank start only after
@@ -254,6 +295,7 @@ class EPMoELayer:
                     ev_out[b].record(s_out)
             self._batch_tokens = 0
             s_out.synchronize()
+        self.check_status(wait=True)
         return y_host
 
     def forward(self, x: torch.Tensor, out: Optional[torch.Tensor] = None, _first: bool = True,
@@ -261,6 +303,7 @@ class EPMoELayer:
         """_first / _last: set by forward_host for the parts of one batch; the FP8 weights are
         de-quantised in the first part and the copy is released after the last."""
         lay, lib = self.layer, self.lib
+        self.check_status()
         x2 = x.reshape(-1, lay.H)
         T = x2.shape[0]
         if T != self._tokens:
@@ -343,6 +386,10 @@ class EPMoELayer:
                 L.check(lib.mg_set_option(h, L.OPT_KEEP_DEQUANT, 0))
             for mb in self._mbs:
                 cur.wait_stream(mb.stream)
+            # the status word follows the result to the host; the next call (or check_status) reads it
+            L.check(lib.mg_device_status_async(h, self._status_host.data_ptr(), cur.cuda_stream))
+            self._status_event = torch.cuda.Event()
+            self._status_event.record(cur)
         if evs is not None:
             self._events.append(evs)
         return y.view(x.shape)

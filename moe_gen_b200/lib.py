@@ -15,7 +15,7 @@ LIB_PATH = os.path.join(_PKG, "libmoegen_b200.so")
 GATE_SOFTMAX_GREEDY, GATE_SOFTMAX_GROUP_MAX, GATE_SIGMOID_NOAUX_TC, GATE_SOFTMAX_TOPK_RENORM = 0, 1, 2, 3
 COMBINE_FP32, COMBINE_BF16_PROD, COMBINE_BF16_SEQ = 0, 1, 2
 WEIGHT_BF16, WEIGHT_FP8_BLOCK128 = 0, 1
-DEV_OK, DEV_WAIT_TIMEOUT = 0, 1
+DEV_OK, DEV_WAIT_TIMEOUT, DEV_CAPACITY = 0, 1, 2
 OPT_FP8_MODE = 1
 OPT_PAIR_GEMM = 2
 OPT_KEEP_DEQUANT = 3
@@ -42,6 +42,7 @@ SIGNATURES = {
     "mg_create": [_P(LayerDesc), _P(_vp)],
     "mg_destroy": [_vp],
     "mg_device_status": [_vp, _P(_i32), _P(_i32)],
+    "mg_device_status_async": [_vp, _vp, _vp],
     "mg_packed_weight_bytes": [_vp, _P(_sz)],
     "mg_workspace_bytes": [_vp, _i64, _i64, _P(_sz)],
     "mg_padded_rows": [_vp, _i64, _P(_i64)],

@@ -211,7 +211,7 @@ def permute_plan(topk_idx: torch.Tensor, n_experts: int):
     flat = topk_idx.reshape(-1)
     counts = torch.bincount(flat, minlength=n_experts)
     offsets = torch.zeros(n_experts + 1, dtype=torch.int64)
-    offsets[1:] = counts.cumsum(0)
+    offsets[1:] = counts.cumsum(0).cpu()          # read on the host (the reference's .cpu() at v3:673)
     order = flat.argsort(stable=True)
     return counts, offsets, order, order // k
 
@@ -262,11 +262,12 @@ def combine(spec: LayerSpec, rows_by_slot: torch.Tensor, topk_idx: torch.Tensor,
         T, k, H = rows_by_slot.shape
         w = topk_w.to(rows_by_slot.dtype)
         order = topk_idx.argsort(dim=-1, stable=True)                       # experts ascending
-        y = torch.zeros(T, H, dtype=rows_by_slot.dtype)
+        y = torch.zeros(T, H, dtype=rows_by_slot.dtype, device=rows_by_slot.device)
+        ar = torch.arange(T, device=rows_by_slot.device)
         for j in range(k):
             sel = order[:, j]
-            r = rows_by_slot[torch.arange(T), sel]
-            y = y + r * w[torch.arange(T), sel].unsqueeze(-1)
+            r = rows_by_slot[ar, sel]
+            y = y + r * w[ar, sel].unsqueeze(-1)
         return y
     raise ValueError(spec.combine_mode)
 
@@ -331,23 +332,33 @@ def make_inputs(spec: LayerSpec, T: int, seed: int, zipf_alpha: float = 0.0):
     return x, W
 
 
-def layer_forward(spec: LayerSpec, x: torch.Tensor, W: LayerWeights, gold_fp32: bool = False
-                  ) -> Dict[str, torch.Tensor]:
+def layer_forward(spec: LayerSpec, x: torch.Tensor, W: LayerWeights, gold_fp32: bool = False,
+                  dequant_per_call: bool = False) -> Dict[str, torch.Tensor]:
     """Whole layer on CPU.  gold_fp32=False follows the reference module as
     shipped (bf16 experts); gold_fp32=True is the same module with fp32
     parameters and input, i.e. the fp32-accumulated output the tolerance is
-    measured against.  Routing is fp32 in both."""
+    measured against.  Routing is fp32 in both.
+
+    dequant_per_call=True (FP8 layers): every expert call first de-quantises its three
+    matrices from W.q_* as the reference's Expert_Wrapper does on each forward
+    (moe_gen/models/Wrapper.py:481-491) instead of reading the bf16 copies in W.w_*;
+    the values are the same, only the work is."""
     T, H = x.shape
     logits = gate_logits(x, W.gate_w, bf16_out=(spec.gating == GATE_SOFTMAX_TOPK_RENORM))
     idx, w = route(spec, logits, W.bias)
     counts, offsets, order, src = permute_plan(idx, spec.n_experts)
     cd = torch.float32 if gold_fp32 else torch.bfloat16
     xs = x.to(cd)[src]                                                      # sorted_tokens
-    outs = torch.empty(xs.shape[0], H, dtype=cd)
+    outs = torch.empty(xs.shape[0], H, dtype=cd, device=x.device)
     for e in range(spec.n_experts):                                         # v3:675-691
         a, b = int(offsets[e]), int(offsets[e + 1])
         if b > a:
-            outs[a:b] = swiglu_mlp(xs[a:b], W.w_gate[e].to(cd), W.w_up[e].to(cd), W.w_down[e].to(cd))
+            if dequant_per_call and W.q_gate is not None:
+                wg, wu, wd = (dequantize_fp8_block128(*W.q_gate[e]), dequantize_fp8_block128(*W.q_up[e]),
+                              dequantize_fp8_block128(*W.q_down[e]))
+            else:
+                wg, wu, wd = W.w_gate[e], W.w_up[e], W.w_down[e]
+            outs[a:b] = swiglu_mlp(xs[a:b], wg.to(cd), wu.to(cd), wd.to(cd))
     back = torch.empty_like(outs)
     back[order] = outs                                                      # new_x[idxs] = outs
     rows = back.view(T, spec.top_k, H)

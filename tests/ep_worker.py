@@ -14,9 +14,26 @@ from oracle import moe_oracle as O  # noqa: E402
 
 
 def _init(rank, world, port, backend):
+    import datetime
     os.environ["MASTER_ADDR"] = "127.0.0.1"
     os.environ["MASTER_PORT"] = str(port)
-    dist.init_process_group(backend, rank=rank, world_size=world)
+    # finite: a rank that never joins or a stalled collective raises in the others instead of waiting forever
+    dist.init_process_group(backend, rank=rank, world_size=world, timeout=datetime.timedelta(seconds=120))
+
+
+def join_all(procs, timeout):
+    """Joins the spawned ranks; whatever is still alive after the timeout is ended (terminate, then
+    kill) so that no rank keeps a GPU, an IPC mapping or a communicator.  Returns the exit codes."""
+    for p in procs:
+        p.join(timeout=timeout)
+    for p in procs:
+        if p.is_alive():
+            p.terminate()
+            p.join(timeout=10)
+            if p.is_alive():
+                p.kill()
+                p.join(timeout=10)
+    return [p.exitcode for p in procs]
 
 
 def cpu_ep_worker(rank, world, port, spec, T_global, seed, result):
@@ -119,16 +136,36 @@ def gpu_ep_worker(rank, world, port, spec, T_global, seed, result):
     torch.cuda.synchronize()
     same = same and bool(torch.equal(y_m.cpu().view(torch.int16), ys[0].view(torch.int16)))
     status = layer.device_status()
+    # a receive buffer that is too small must be reported, not silently produce a partial result
+    overflow_reported = None
+    if spec.n_experts <= 8:
+        ep_s = EPMoELayer(layer, capacity_factor=0.3, min_headroom=0)
+        ep_s.forward(x)
+        try:
+            ep_s.check_status(wait=True)
+            overflow_reported = False
+        except RuntimeError as e:
+            overflow_reported = "overflowed" in str(e)
+        ep_s.close()
+        assert layer.device_status() == (0, 0)            # reading it cleared the word
+    idx_l, w_l = layer.route_topk(layer.gate_logits(x))
     gath = [None] * world
-    dist.all_gather_object(gath, (ys[0], ys[1], status, same))
+    dist.all_gather_object(gath, (ys[0], ys[1], status, same, idx_l.cpu(), w_l.cpu(), overflow_reported))
     if rank == 0:
         gold = O.layer_forward(spec, x_all, W, gold_fp32=True)
         y0 = torch.cat([g[0] for g in gath]).float()
         y1 = torch.cat([g[1] for g in gath]).float()
-        result["rel_l2"] = O.rel_l2(y0, gold["y"])
+        # tokens whose routing agrees with the oracle's (a router logit that rounds differently can flip
+        # a near-tie, above all with the Mixtral block's bf16 logits): the output bound applies to those
+        idx_all = torch.cat([g[4] for g in gath]).long()
+        w_all = torch.cat([g[5] for g in gath])
+        agree = (O.canonical_sets(idx_all, w_all)[0] == O.canonical_sets(gold["topk_idx"], gold["topk_w"])[0]).all(1)
+        result["routing_agree"] = float(agree.float().mean())
+        result["rel_l2"] = O.rel_l2(y0[agree], gold["y"][agree])
         result["repeat_equal"] = bool(torch.equal(y0, y1))
         result["status"] = [g[2] for g in gath]
         result["dedup_equal"] = all(g[3] for g in gath)
+        result["overflow_reported"] = [g[6] for g in gath]
     dist.barrier()
     ep_m.close()
     ep.close()

@@ -81,6 +81,13 @@ CASES = {
                                         O.WEIGHT_BF16, O.COMBINE_FP32), 96, 14),
 }
 
+# whole-layer cases at the full size of a named configuration: the full routing and histogram are
+# stored, of the outputs only SAMPLE_ROWS evenly spaced token rows (the fixture stays small)
+FULL_CASES = {
+    "v2lite_full": ("v2lite", 2048, 0),      # DeepSeek-V2-Lite layer exactly as the benchmark names it
+}
+SAMPLE_ROWS = 128
+
 GATE_CASES = {
     # full-size gate shapes of the named configs, T=512
     "gate_v2lite": ("v2lite", 512, 0),
@@ -114,13 +121,55 @@ def build_ref_module(spec: O.LayerSpec, W: O.LayerWeights, v2, v3, C2, C3):
     return m
 
 
+def write_full_cases(v2, v3, C2, C3):
+    for name, (cfg, T, seed) in FULL_CASES.items():
+        spec = O.named_spec(cfg)
+        x, W = O.make_inputs(spec, T, seed)
+        m = build_ref_module(spec, W, v2, v3, C2, C3)
+        with torch.no_grad():
+            xin = x.view(1, T, spec.hidden)
+            gout = m.gate(xin)
+            ridx, rw = gout[0], gout[1]
+            y_ref = m(xin).view(T, spec.hidden)
+            m32 = build_ref_module(spec, W, v2, v3, C2, C3).float()
+            if W.bias is not None:
+                m32.gate.e_score_correction_bias.data = W.bias.clone()
+            y_gold = m32(xin.float()).view(T, spec.hidden)
+        out = O.layer_forward(spec, x, W)
+        gold = O.layer_forward(spec, x, W, gold_fp32=True)
+        ri, rwc = O.canonical_sets(ridx, rw)
+        oi, owc = O.canonical_sets(out["topk_idx"], out["topk_w"])
+        assert torch.equal(ri, oi), f"{name}: routing sets differ"
+        assert (rwc - owc).abs().max() <= 2e-7 * max(1.0, spec.routed_scale), f"{name}: weights differ"
+        cnt = torch.bincount(ridx.view(-1), minlength=spec.n_experts)
+        assert torch.equal(cnt, out["counts"])
+        r_bf = O.rel_l2(out["y"].float(), y_ref.float())
+        r_gd = O.rel_l2(gold["y"], y_gold)
+        assert r_bf < 2e-3 and r_gd < 1e-5, (name, r_bf, r_gd)
+        rows = torch.linspace(0, T - 1, SAMPLE_ROWS).round().long()
+        np.savez_compressed(
+            os.path.join(HERE, name + ".npz"),
+            T=T, seed=seed, input_digest=digest(x, W.gate_w, W.w_gate[0], W.w_down[-1]),
+            topk_idx=ri.numpy().astype(np.int16), topk_w=rwc.numpy(), counts=cnt.numpy().astype(np.int32),
+            rows=rows.numpy().astype(np.int32), y_ref_bf16_rows=bits(y_ref[rows]),
+            y_gold_fp32_rows=y_gold[rows].numpy().astype(np.float32),
+            ref_bf16_vs_gold=np.float64(O.rel_l2(y_ref.float(), y_gold)))
+        print(f"{name}: ok  rel(oracle,ref)={r_bf:.2e} rel(oracle_gold,ref_gold)={r_gd:.2e} "
+              f"ref_bf16_vs_gold={O.rel_l2(y_ref.float(), y_gold):.2e}")
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--reference", default=os.environ.get("MOEGEN_REFERENCE"), required="MOEGEN_REFERENCE" not in os.environ)
-    ap.add_argument("--only", default="", help="'block': write only the decoder-layer-glue fixture")
+    ap.add_argument("--only", default="", help="'block': write only the decoder-layer-glue fixture; "
+                    "'full': only the full-size whole-layer fixtures")
     args = ap.parse_args()
     v2, v3, C2, C3, ref_dequant = load_reference(args.reference)
     torch.set_num_threads(max(1, os.cpu_count() or 1))
+
+    if args.only == "full":
+        write_full_cases(v2, v3, C2, C3)
+        return
 
     # ---- decoder-layer glue: the reference's RMSNorm in front of its V3 block, residual added after
     #      (modeling_deepseek_v3.py:1361-1365), on the inputs of the small bf16 V3 case
@@ -210,6 +259,8 @@ def main():
             ref_bf16_vs_gold=np.float64(O.rel_l2(y_ref.float(), y_gold)))
         print(f"{name}: ok  rel(oracle,ref)={r_bf:.2e} rel(oracle_gold,ref_gold)={r_gd:.2e} "
               f"ref_bf16_vs_gold={O.rel_l2(y_ref.float(), y_gold):.2e}")
+
+    write_full_cases(v2, v3, C2, C3)
 
     # ---- gate-only cases at full gate shapes ---------------------------------
     for name, (cfg, T, seed) in GATE_CASES.items():

@@ -61,8 +61,7 @@ def test_expert_parallel_two_gloo_ranks_match_single_process_oracle(spec, T):
         procs = [ctx.Process(target=ep_worker.cpu_ep_worker, args=(r, 2, port, spec, T, 7, result)) for r in range(2)]
         for p in procs:
             p.start()
-        for p in procs:
-            p.join(timeout=240)
-        assert all(p.exitcode == 0 for p in procs), [p.exitcode for p in procs]
+        codes = ep_worker.join_all(procs, 240)
+        assert all(c == 0 for c in codes), codes
         assert result["counts_ok"]
         assert result["rel_l2"] < 1e-5

@@ -7,7 +7,7 @@ import pytest
 import torch
 
 from oracle import moe_oracle as O
-from tests.golden.make_golden import CASES, GATE_CASES
+from tests.golden.make_golden import CASES, FULL_CASES, GATE_CASES
 from tests.util import bf16_from_bits, load_golden
 
 
@@ -34,6 +34,28 @@ def test_layer_matches_reference_fixture(name):
     gold = O.layer_forward(spec, x, W, gold_fp32=True)
     assert O.rel_l2(gold["y"], torch.from_numpy(g["y_gold_fp32"])) < 1e-5
     # the reference's own bf16 run sits well inside the 1e-2 bound against its fp32 run
+    assert float(g["ref_bf16_vs_gold"]) < 1e-2
+
+
+@pytest.mark.parametrize("name", sorted(FULL_CASES))
+def test_full_size_layer_matches_reference_fixture(name):
+    """A named configuration at its full size (DeepSeek-V2-Lite, which the reference runs on CPU):
+    routing and histogram of all tokens exact, the stored sample of output rows as close as the
+    small cases."""
+    cfg, T, seed = FULL_CASES[name]
+    spec = O.named_spec(cfg)
+    g = load_golden(name)
+    x, W = O.make_inputs(spec, T, seed)
+    assert _digest(x, W.gate_w, W.w_gate[0], W.w_down[-1]) == str(g["input_digest"]), "seeded inputs drifted"
+    out = O.layer_forward(spec, x, W)
+    idx, w = O.canonical_sets(out["topk_idx"], out["topk_w"])
+    assert np.array_equal(idx.numpy().astype(np.int16), g["topk_idx"])
+    assert np.abs(w.numpy() - g["topk_w"]).max() <= 2e-7 * max(1.0, spec.routed_scale)
+    assert np.array_equal(out["counts"].numpy().astype(np.int32), g["counts"])
+    rows = torch.from_numpy(g["rows"].astype(np.int64))
+    assert O.rel_l2(out["y"][rows].float(), bf16_from_bits(g["y_ref_bf16_rows"]).float()) < 2e-3
+    gold = O.layer_forward(spec, x, W, gold_fp32=True)
+    assert O.rel_l2(gold["y"][rows], torch.from_numpy(g["y_gold_fp32_rows"])) < 1e-5
     assert float(g["ref_bf16_vs_gold"]) < 1e-2
 
 
