@@ -119,6 +119,12 @@ int mg_device_status(mg_handle h, int32_t* code, int32_t* detail);
  * mg_device_status.  No counterpart in the reference. */
 int mg_device_status_async(mg_handle h, int32_t* host_words, void* stream);
 
+/* Sets aside `bytes` of the current device's L2 for accesses with the "evict last" policy
+ * (cudaLimitPersistingL2CacheSize: a limit of this process's context, gone when the process ends);
+ * *granted receives what the device allows.  The set-aside serves normal accesses too while no such
+ * lines occupy it.  No counterpart in the reference. */
+int mg_l2_set_aside(size_t bytes, size_t* granted);
+
 /* ---- sizes -------------------------------------------------------------- */
 
 /* Bytes of the packed weight buffer for the experts this rank owns (+ shared
@@ -221,8 +227,9 @@ int mg_permute_rows(mg_handle h, const void* d_x, const int32_t* d_dst_row, int6
  *   out_rows[r,:] = h_buf[r] . Wd_e^T                                  (bf16)
  * for r in [pad_offsets[e], pad_offsets[e]+counts[e]).  n_rows_padded bounds the
  * buffers (rows of perm_x / h_buf / out_rows).  For FP8 layers d_dequant_ws may be NULL
- * (the kernels convert weight tiles on the fly) or a bf16 scratch of mg_dequant_ws_bytes()
- * bytes (weights are de-quantised into it first); results are identical.
+ * (the kernels convert weight tiles on the fly in shared memory) or a scratch of
+ * mg_dequant_ws_bytes() bytes, whose size and use follow MG_OPT_FP8_MODE (a bf16 copy of all
+ * expert weights, or the ring of MG_FP8_RING); results are identical.
  * Replaces the expert loop (modeling_deepseek_v3.py:675-691) and
  * DeepseekV3MLP.forward (modeling_deepseek_v3.py:463-467). */
 int mg_dequant_ws_bytes(mg_handle h, size_t* bytes);
@@ -372,18 +379,31 @@ int mg_selftest_wait_timeout(mg_handle h, int32_t limit_ms, void* stream);
 int mg_last_launch_count(mg_handle h, int32_t* launches);
 
 /* Options (no counterpart in the reference).
- * MG_OPT_FP8_MODE, for MG_WEIGHT_FP8_BLOCK128 layers in mg_moe_forward:
- *   MG_FP8_PREDEQUANT  de-quantise the expert weights into workspace scratch, one chunk of
- *                      experts ahead of the bf16 grouped GEMMs, on a side stream (the reference
- *                      de-quantises per expert call, moe_gen/models/Wrapper.py:481-491);
- *   MG_FP8_IN_KERNEL   the grouped GEMMs convert FP8 weight tiles to bf16 in shared memory;
+ * MG_OPT_FP8_MODE, for MG_WEIGHT_FP8_BLOCK128 layers: where the grouped GEMMs get their bf16 operands
+ * (the reference de-quantises every expert's matrices on every expert call, moe_gen/models/Wrapper.py:481-491):
+ *   MG_FP8_IN_KERNEL   every CTA converts the FP8 weight tiles of its own row tiles in shared memory; no
+ *                      scratch; a weight is converted once per 128 or 256 rows that use it;
+ *   MG_FP8_PREDEQUANT  a bf16 copy of all local expert weights in scratch (2 bytes per weight), written by
+ *                      a separate pass on a side stream one chunk of experts ahead of the bf16 GEMMs;
+ *   MG_FP8_RING        the GEMM kernel's CTAs convert every weight once per expert into a bf16 ring of
+ *                      MG_OPT_RING_BYTES and fetch their B tiles from it by TMA: no bf16 copy of the weights,
+ *                      58 MB of scratch; measured 5 % slower than MG_FP8_PREDEQUANT at 65536 tokens of the
+ *                      DeepSeek-V3 layer (the ring does not stay in L2), so only on request;
  *   MG_FP8_AUTO        (default) in-kernel while an expert sees fewer than 1024 rows on average
  *                      (measured cross-over on the DeepSeek-V3 shape), else pre-dequantise.
- * All give bit-identical results.  Set before asking mg_workspace_bytes. */
+ * All give bit-identical results.  Set before asking mg_workspace_bytes / mg_dequant_ws_bytes. */
 #define MG_OPT_FP8_MODE    1
 #define MG_FP8_AUTO        0
 #define MG_FP8_PREDEQUANT  1
 #define MG_FP8_IN_KERNEL   2
+#define MG_FP8_RING        3
+/* MG_OPT_RING_BYTES: size of the ring of MG_FP8_RING in MiB (default 56: it has to fit in the 126 MB L2
+ * next to the activations in flight).  Set before asking mg_workspace_bytes / mg_dequant_ws_bytes. */
+#define MG_OPT_RING_BYTES  7
+/* MG_OPT_RING_PERSIST: 1 = the ring's stores and loads carry the L2 "evict last" policy, so that the ring
+ * outlives the streaming traffic beside it; it takes effect inside the part of L2 that the process has
+ * set aside for such accesses (mg_l2_set_aside).  0 (default) = ordinary accesses. */
+#define MG_OPT_RING_PERSIST 8
 /* MG_OPT_PAIR_GEMM: 1 = the bf16 expert GEMMs run on SM pairs (clusters of two CTAs,
  * tcgen05 cta_group::2, 256x256 tiles); 0 = one CTA per SM, 128x256 tiles. */
 #define MG_OPT_PAIR_GEMM   2

@@ -44,17 +44,52 @@ static size_t dequant_ws(const Handle* h) {
   return static_cast<size_t>(h->e_local) * 3 * h->d.inter * h->d.hidden * 2;
 }
 
-// FP8 layers: de-quantise ahead of the GEMMs (true) or convert tiles inside them (false).
-// Converting in the kernel re-does the work for every row tile of an expert; de-quantising first
-// moves every weight through HBM three more times.  On the DeepSeek-V3 shape the two cost the
-// same near 1024 rows per expert (256-row tiles), measured; below that converting wins by up
-// to 2.7x, above it de-quantising first by up to 12 %.
+// How an FP8 layer's grouped GEMMs get bf16 operands (MG_OPT_FP8_MODE):
+//   in-kernel   every CTA converts the weight tiles of its own row tiles in shared memory: no scratch, but
+//               a weight is converted once per 128 or 256 rows that use it;
+//   pre-dequant a bf16 copy of all expert weights in scratch, written by a separate pass on a side stream;
+//   ring        the GEMM kernel's own CTAs convert every weight once per expert and share the bf16 copy
+//               through a ring of a few tens of MB (gemm.cu: grouped_gemm_ring_kernel): 58 MB of scratch
+//               instead of 2 bytes per weight.
+// AUTO: converting in the kernel re-does the work for every row tile of an expert; de-quantising first
+// moves every weight through HBM three more times.  On the DeepSeek-V3 shape the two cost the same near
+// 1024 rows per expert (256-row tiles), measured; below that converting wins by up to 2.7x, above it
+// de-quantising first by up to 12 %.  The ring was built to take the large batches without the HBM round
+// trip of the bf16 copy, but L2 does not hold it (measured at the benchmark size: 21.6 GB written to and
+// 35.2 GB read from DRAM by the gate/up launch, i.e. the ring goes through HBM like the separate pass's
+// copy does), and it ends 5 % behind pre-dequantise there; it is chosen only on request.
+constexpr int64_t kRingMaxRows = 1ll << 24;          // rows the ring's counters are sized for
+static int fp8_mode_for(const Handle* h, int64_t rows) {
+  if (h->d.weight_format != MG_WEIGHT_FP8_BLOCK128) return MG_FP8_IN_KERNEL;
+  if (h->opt_fp8_mode != MG_FP8_AUTO) return h->opt_fp8_mode;
+  if (h->opt_batch_tokens * h->d.top_k > rows) rows = h->opt_batch_tokens * h->d.top_k;
+  return rows >= static_cast<int64_t>(1024) * h->d.n_experts ? MG_FP8_PREDEQUANT : MG_FP8_IN_KERNEL;
+}
+
+struct RingWs { size_t ring_bytes; int64_t counter_ints; size_t total; };
+static RingWs ring_ws(const Handle* h) {
+  const mg_layer_desc& d = h->d;
+  const RingPlan a = ring_plan(2 * d.inter, d.hidden, kRingMaxRows, h->e_local, h->opt_ring_bytes);
+  const RingPlan b = ring_plan(d.hidden, d.inter, kRingMaxRows, h->e_local, h->opt_ring_bytes);
+  RingWs w;
+  w.ring_bytes = (a.ring_bytes > b.ring_bytes ? a.ring_bytes : b.ring_bytes);
+  w.ring_bytes = (w.ring_bytes + 255) / 256 * 256;
+  w.counter_ints = 2 * (a.max_granules > b.max_granules ? a.max_granules : b.max_granules);
+  w.total = w.ring_bytes + static_cast<size_t>(w.counter_ints) * 4;
+  return w;
+}
+
+// scratch the FP8 mode of a call over `rows` routed rows needs
+static size_t fp8_scratch_bytes(const Handle* h, int64_t rows) {
+  switch (fp8_mode_for(h, rows)) {
+    case MG_FP8_PREDEQUANT: return dequant_ws(h);
+    case MG_FP8_RING: return ring_ws(h).total;
+    default: return 0;
+  }
+}
+
 static bool fp8_predequant(const Handle* h, int64_t T) {
-  if (h->d.weight_format != MG_WEIGHT_FP8_BLOCK128) return false;
-  if (h->opt_fp8_mode == MG_FP8_PREDEQUANT) return true;
-  if (h->opt_fp8_mode == MG_FP8_IN_KERNEL) return false;
-  if (h->opt_batch_tokens > T) T = h->opt_batch_tokens;
-  return T * h->d.top_k >= static_cast<int64_t>(1024) * h->d.n_experts;
+  return fp8_mode_for(h, T * h->d.top_k) == MG_FP8_PREDEQUANT;
 }
 
 static WsLayout ws_layout(const Handle* h, int64_t T, int64_t R) {
@@ -66,7 +101,7 @@ static WsLayout ws_layout(const Handle* h, int64_t T, int64_t R) {
   auto take = [&](int which, size_t bytes) { L.off[which] = off; off += (bytes + 255) / 256 * 256; };
   // first, so that its address does not depend on T: calls with different token counts on one
   // workspace can then share the de-quantised copy (MG_OPT_KEEP_DEQUANT)
-  take(WS_DEQ, fp8_predequant(h, T) ? dequant_ws(h) : 0);
+  take(WS_DEQ, fp8_scratch_bytes(h, T * d.top_k));
   take(WS_LOGITS, static_cast<size_t>(T) * d.n_experts * 4);
   take(WS_IDX, static_cast<size_t>(T) * d.top_k * 4);
   take(WS_W, static_cast<size_t>(T) * d.top_k * 4);
@@ -133,6 +168,8 @@ int mg_create(const mg_layer_desc* desc, mg_handle* out) {
   h->opt_shared_early = 2;
   h->opt_batch_tokens = 0;
   h->opt_keep_dequant = false;
+  h->opt_ring_bytes = static_cast<size_t>(56) << 20;
+  h->opt_ring_persist = 0;
   h->deq_valid = false;
   h->deq_inflight = false;
   h->deq_scratch = nullptr;
@@ -198,6 +235,14 @@ int mg_device_status_async(mg_handle hh, int32_t* host_words, void* stream) {
   MG_REQUIRE(host_words, MG_ERR_NULL, "null argument");
   MG_CUDA(cudaMemcpyAsync(host_words, h->d_status, 2 * sizeof(int32_t), cudaMemcpyDeviceToHost,
                           static_cast<cudaStream_t>(stream)));
+  return MG_OK;
+}
+
+int mg_l2_set_aside(size_t bytes, size_t* granted) {
+  MG_CUDA(cudaDeviceSetLimit(cudaLimitPersistingL2CacheSize, bytes));
+  size_t got = 0;
+  MG_CUDA(cudaDeviceGetLimit(&got, cudaLimitPersistingL2CacheSize));
+  if (granted) *granted = got;
   return MG_OK;
 }
 
@@ -311,7 +356,9 @@ int mg_dequant_ws_bytes(mg_handle hh, size_t* bytes) {
   Handle* h = check(hh);
   if (!h) return MG_ERR_STATE;
   MG_REQUIRE(bytes, MG_ERR_NULL, "null argument");
-  *bytes = dequant_ws(h);
+  // what mg_expert_ffn may use of d_dequant_ws under the current MG_OPT_FP8_MODE (AUTO: the bf16 copy)
+  *bytes = h->d.weight_format != MG_WEIGHT_FP8_BLOCK128 || h->opt_fp8_mode == MG_FP8_IN_KERNEL ? 0
+           : h->opt_fp8_mode == MG_FP8_RING ? ring_ws(h).total : dequant_ws(h);
   return MG_OK;
 }
 
@@ -368,8 +415,21 @@ static int expert_ffn(Handle* h, const void* perm_x, const int32_t* pad, const i
   const int E = h->e_local;
   GemmProblem p{};
   p.a_rows = rows_padded;
-  if (!fp8 || deq == nullptr) {
-    // bf16 weights, or FP8 tiles converted inside the GEMM kernels: two launches over all experts
+  // a caller that hands in scratch has chosen a scratch mode: the ring if that is the option, else the bf16 copy
+  const int mode = !fp8 || deq == nullptr ? MG_FP8_IN_KERNEL
+                   : h->opt_fp8_mode == MG_FP8_RING ? MG_FP8_RING : MG_FP8_PREDEQUANT;
+  if (mode != MG_FP8_PREDEQUANT) {
+    // bf16 weights, FP8 tiles converted inside the GEMM kernels, or FP8 weights converted once into the
+    // L2-resident ring by the GEMM kernel itself: two launches over all experts
+    if (mode == MG_FP8_RING) {
+      MG_REQUIRE(rows_padded <= kRingMaxRows, MG_ERR_LIMIT, "ring mode handles up to %lld rows per call",
+                 static_cast<long long>(kRingMaxRows));
+      const RingWs rw = ring_ws(h);
+      p.ring = deq;
+      p.ring_bytes = rw.ring_bytes;
+      p.ring_counters = reinterpret_cast<int32_t*>(static_cast<uint8_t*>(deq) + rw.ring_bytes);
+      p.ring_counter_ints = rw.counter_ints;
+    }
     if (timed) mark(h, MG_STAGE_DEQUANT, st);
     p.a = perm_x; p.b = base + L.w13; p.n_groups = E; p.n_per_group = 2 * d.inter; p.K = d.hidden;
     p.pad_offsets = pad; p.counts = counts; p.out = h_buf; p.ldo = d.inter; p.epilogue = EPI_SWIGLU_BF16;
@@ -383,7 +443,7 @@ static int expert_ffn(Handle* h, const void* perm_x, const int32_t* pad, const i
     p.scales = fp8 ? reinterpret_cast<const float*>(base + L.s2) : nullptr;
     rc = launch_grouped_gemm(h, p, st);
     if (timed) mark(h, MG_STAGE_EXPERT_GEMM2, st);
-    if (launches) *launches += 2;
+    if (launches) *launches += mode == MG_FP8_RING ? 4 : 2;      // ring: a counter reset in front of each GEMM
     return rc;
   }
   // FP8 weights de-quantised into `deq` one chunk of experts ahead of the bf16 GEMMs: the
@@ -438,6 +498,7 @@ int mg_dequant_start(mg_handle hh, const void* d_packed, void* d_dequant_ws, voi
   if (!h) return MG_ERR_STATE;
   MG_REQUIRE(d_packed && d_dequant_ws, MG_ERR_NULL, "mg_dequant_start: null pointer");
   MG_REQUIRE(h->d.weight_format == MG_WEIGHT_FP8_BLOCK128, MG_ERR_CONFIG, "layer has no FP8 weights");
+  if (h->opt_fp8_mode == MG_FP8_RING || h->opt_fp8_mode == MG_FP8_IN_KERNEL) return MG_OK;   // converted inside mg_expert_ffn
   return start_dequant(h, d_packed, d_dequant_ws, static_cast<cudaStream_t>(stream), nullptr);
 }
 
@@ -532,11 +593,11 @@ static int moe_forward_impl(mg_handle hh, const void* d_x, int64_t T, const void
   void* plan = ws + L.off[WS_PLAN];
   void* hs = ws + L.off[WS_HS];
   void* sh = d.inter_shared ? ws + L.off[WS_SHARED] : nullptr;
-  void* deq = fp8_predequant(h, T) ? ws + L.off[WS_DEQ] : nullptr;
+  void* deq = fp8_scratch_bytes(h, T * d.top_k) > 0 ? ws + L.off[WS_DEQ] : nullptr;
   int launches = 0;
   if (h->stage_timing) MG_CUDA(cudaEventRecord(h->stage_ev[h->stage_calls % kStageSlots][0], st));
   int rc;
-  if (deq != nullptr && !(h->opt_keep_dequant && h->deq_valid && h->deq_scratch == deq && h->deq_packed == d_packed &&
+  if (deq != nullptr && fp8_predequant(h, T) && !(h->opt_keep_dequant && h->deq_valid && h->deq_scratch == deq && h->deq_packed == d_packed &&
                           h->deq_stream == st)) {
     // the weights do not depend on the routing: their de-quantisation starts now, beside the
     // router, plan and scatter kernels
@@ -646,7 +707,7 @@ int mg_set_option(mg_handle hh, int32_t option, int32_t value) {
   if (!h) return MG_ERR_STATE;
   switch (option) {
     case MG_OPT_FP8_MODE:
-      MG_REQUIRE(value >= MG_FP8_AUTO && value <= MG_FP8_IN_KERNEL, MG_ERR_CONFIG, "bad FP8 mode %d", value);
+      MG_REQUIRE(value >= MG_FP8_AUTO && value <= MG_FP8_RING, MG_ERR_CONFIG, "bad FP8 mode %d", value);
       h->opt_fp8_mode = value;
       return MG_OK;
     case MG_OPT_PAIR_GEMM: h->opt_pair_gemm = value != 0; return MG_OK;
@@ -661,6 +722,11 @@ int mg_set_option(mg_handle hh, int32_t option, int32_t value) {
     case MG_OPT_FP8_M256:
       MG_REQUIRE(value >= 0 && value <= 2, MG_ERR_CONFIG, "bad value %d", value);
       h->opt_fp8_m256 = value;
+      return MG_OK;
+    case MG_OPT_RING_PERSIST: h->opt_ring_persist = value != 0; return MG_OK;
+    case MG_OPT_RING_BYTES:
+      MG_REQUIRE(value >= 1, MG_ERR_CONFIG, "bad ring size %d MiB", value);
+      h->opt_ring_bytes = static_cast<size_t>(value) << 20;
       return MG_OK;
     case MG_OPT_KEEP_DEQUANT:
       MG_REQUIRE(value >= 0 && value <= 2, MG_ERR_CONFIG, "bad keep-dequant level %d", value);

@@ -65,7 +65,9 @@ struct Handle {
   int64_t opt_batch_tokens;  // total tokens of a batch fed in chunks (0 = unknown), for the AUTO rule
   int opt_fp8_m256;       // in-kernel FP8: 0 = 128-row tiles, 1 = 256-row tiles when experts are big, 2 = always
   bool opt_pair_gemm;     // bf16 expert GEMMs on SM pairs (tcgen05 cta_group::2)
-  int opt_fp8_mode;       // MG_FP8_AUTO / MG_FP8_PREDEQUANT / MG_FP8_IN_KERNEL
+  int opt_fp8_mode;       // MG_FP8_AUTO / MG_FP8_PREDEQUANT / MG_FP8_IN_KERNEL / MG_FP8_RING
+  size_t opt_ring_bytes;  // budget of the bf16 ring of MG_FP8_RING (it should stay resident in L2)
+  int opt_ring_persist;   // ring accesses carry the L2 evict_last policy (needs an L2 set-aside, mg_l2_set_aside)
   cudaStream_t side;      // de-quantisation runs here, one chunk of experts ahead of the GEMMs
   cudaEvent_t ev_entry, ev_w13[kDequantChunks], ev_w2[kDequantChunks];
   cudaStream_t side2;     // the shared expert's GEMMs run here beside the routing and scatter kernels
@@ -147,7 +149,21 @@ struct GemmProblem {
   void* out;              // bf16 or fp32
   int64_t ldo;            // elements between output rows
   int epilogue;
+  // W8A16 through the L2-resident ring (grouped FP8 weights only): scratch for the bf16 ring and its
+  // 2 x max_granules counters, sized with ring_plan(); nullptr = not this path
+  void* ring;
+  size_t ring_bytes;
+  int32_t* ring_counters;
+  int64_t ring_counter_ints;
 };
+// how a grouped FP8 GEMM of this shape uses a ring of at most budget_bytes
+struct RingPlan {
+  int pg;                 // N tiles per granule
+  int slots;              // granules in the ring
+  size_t granule_bytes, ring_bytes;
+  int64_t max_granules;   // upper bound of granules for a_rows padded rows in n_groups experts
+};
+RingPlan ring_plan(int n_per_group, int K, int64_t a_rows, int n_groups, size_t budget_bytes);
 int launch_grouped_gemm(const Handle* h, const GemmProblem& p, cudaStream_t st);
 int launch_wait_probe(const Handle* h, int limit_ms, cudaStream_t st);
 

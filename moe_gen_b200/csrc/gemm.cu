@@ -94,10 +94,25 @@ __device__ __forceinline__ uint32_t mbar_try_wait(uint32_t bar, uint32_t parity)
       : "memory");
   return ok;
 }
+// nanoseconds; the two halves are read separately and the high half checked, so that a carry of the low
+// half between the reads cannot produce a value that is off by 2^32 ns
 __device__ __forceinline__ unsigned long long global_timer() {
-  unsigned long long t;
-  asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
-  return t;
+  uint32_t hi, lo, hi2;
+  do {
+    asm volatile("mov.u32 %0, %%globaltimer_hi;" : "=r"(hi));
+    asm volatile("mov.u32 %0, %%globaltimer_lo;" : "=r"(lo));
+    asm volatile("mov.u32 %0, %%globaltimer_hi;" : "=r"(hi2));
+  } while (hi != hi2);
+  return (static_cast<unsigned long long>(hi) << 32) | lo;
+}
+// The limit of a bounded wait has run out.  The 64-bit timer is read as two halves; a read that straddles
+// a carry of the low half can come out far too small or too large, so the difference is taken as a
+// signed number (a reading below t0 never counts) and an expiry must be seen by two readings in a row.
+__device__ __forceinline__ bool timed_out(unsigned long long t0, unsigned long long limit_ns) {
+  const long long d1 = static_cast<long long>(global_timer() - t0);
+  if (d1 <= static_cast<long long>(limit_ns)) return false;
+  const long long d2 = static_cast<long long>(global_timer() - t0);
+  return d2 > static_cast<long long>(limit_ns) && d2 >= d1;
 }
 // Bounded wait.  Returns false if the wait ran out or another role already gave up.
 __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile int* abort_flag,
@@ -110,7 +125,7 @@ __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatil
     if (mbar_try_wait(bar, parity)) return true;
     if ((++spins & 63u) == 0u) {
       if (*abort_flag) return false;
-      if (global_timer() - t0 > limit_ns) {
+      if (timed_out(t0, limit_ns)) {
         *abort_flag = 1;
         if (atomicCAS(status, MG_DEV_OK, MG_DEV_WAIT_TIMEOUT) == MG_DEV_OK) status[1] = where;
         return false;
@@ -124,6 +139,24 @@ __device__ __forceinline__ void tma_load_2d(uint32_t dst, const CUtensorMap* map
       "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];"
       ::"r"(dst), "l"(map), "r"(bar), "r"(c0), "r"(c1)
       : "memory");
+}
+// L2 residency hints for data that is written once and read many times before it is overwritten
+__device__ __forceinline__ uint64_t policy_evict_last() {
+  uint64_t pol;
+  asm volatile("createpolicy.fractional.L2::evict_last.b64 %0, 1.0;" : "=l"(pol));
+  return pol;
+}
+__device__ __forceinline__ void tma_load_2d_hint(uint32_t dst, const CUtensorMap* map, int c0, int c1, uint32_t bar,
+                                                 uint64_t pol) {
+  asm volatile(
+      "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes.L2::cache_hint [%0], [%1, {%3, %4}], [%2], %5;"
+      ::"r"(dst), "l"(map), "r"(bar), "r"(c0), "r"(c1), "l"(pol)
+      : "memory");
+}
+__device__ __forceinline__ void st_global_hint16(void* ptr, const uint4& v, uint64_t pol) {
+  asm volatile("st.global.L2::cache_hint.v4.b32 [%0], {%1, %2, %3, %4}, %5;" ::"l"(ptr), "r"(v.x), "r"(v.y), "r"(v.z),
+               "r"(v.w), "l"(pol)
+               : "memory");
 }
 __device__ __forceinline__ void tc_fence_before() {
   asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
@@ -1123,6 +1156,365 @@ grouped_gemm_w8_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_con
   }
 }
 
+// =======================================================================================
+// W8A16 through an L2-resident ring ("convert once, share through L2").
+//
+// The kernels above convert a weight tile again for every row tile that uses it (8 to 16 times per
+// weight at large batch), or read a bf16 copy that a separate pass wrote to HBM.  Here every FP8
+// weight is read from HBM and converted ONCE per group of row tiles: the eight converter warps of all
+// CTAs together turn one "granule" of weights (a few MB: one or more 256-row panels of B, whole K)
+// into bf16 in a small ring in global memory, sized to stay in the 126 MB L2; the CTAs whose tiles use
+// that panel fetch their B tiles from the ring by TMA exactly as the bf16 kernel fetches them from a
+// weight buffer.  A ring slot is written again only after every tile that reads it has finished, so
+// the bf16 copy lives in L2 between its one write and its ~16 reads and, at best, never reaches HBM.
+//
+//   granule g      PG consecutive N tiles of one (expert, group of <= 16 row tiles), in tile order
+//   ready[g]       += 1 by every CTA when its share of granule g is in the ring (release);
+//                  a producer warp waits for ready[g] == gridDim.x before its first B load of a tile
+//   done[g]        += 1 by a CTA's MMA thread when the last operand block of one of its tiles of
+//                  granule g has landed in shared memory; the converters wait for
+//                  done[g - slots] == tiles of that granule before they overwrite its slot
+// All CTAs convert a part of every granule, so all of them must be resident: the kernel is launched
+// cooperatively with at most one CTA per SM.  Every wait is bounded (status MG_DEV_WAIT_TIMEOUT).
+// Results are bit-identical to de-quantising first: same bf16(float(q) * scale), same MMA order.
+// =======================================================================================
+struct RingArgs {
+  const uint8_t* b8;     // FP8 weights, [n_groups * n_per_group][K] row-major
+  uint8_t* ring;         // bf16 ring, [slots * pg * 256][K] row-major
+  int32_t* ready;        // [granules]
+  int32_t* done;         // [granules]
+  int slots;             // granules the ring holds
+  int pg;                // N tiles (256 weight rows each) per granule; divides n_tiles
+  int keep_in_l2;        // ring stores and loads carry the L2 evict_last policy
+};
+constexpr int RING_MAX_SLOTS = 64;
+constexpr int RING_GROUP_M = 16;
+constexpr size_t SMEM_RING_CTRL_BYTES = 8 * NUM_BARS + 32 + 4 * (3 * kMaxExperts + 3) + 4 * RING_MAX_SLOTS;
+constexpr size_t SMEM_RING_BYTES = 1024 + Cfg<false>::RING_BYTES + SMEM_RING_CTRL_BYTES + 1024 + 4 * 2 * EPI_PIECE_BYTES;
+static_assert(SMEM_RING_BYTES <= 232448, "shared memory of the ring kernel exceeds the 227 KiB a CTA may have");
+constexpr int RING_THREADS = GEMM_THREADS + CONVERT_THREADS;
+
+__device__ __forceinline__ int ld_acquire_gpu(const int32_t* p) {
+  int v;
+  asm volatile("ld.acquire.gpu.global.s32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
+  return v;
+}
+__device__ __forceinline__ void red_release_gpu_add(int32_t* p, int v) {
+  asm volatile("red.release.gpu.global.add.s32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
+}
+// bounded poll of a global counter; false when the wait ran out or another role gave up
+__device__ __forceinline__ bool wait_counter(const int32_t* p, int target, volatile int* abort_flag, int32_t* status,
+                                             int where) {
+  if (ld_acquire_gpu(p) >= target) return true;
+  const unsigned long long t0 = global_timer();
+  uint32_t spins = 0;
+  while (true) {
+    if (ld_acquire_gpu(p) >= target) return true;
+    __nanosleep(64);
+    if ((++spins & 15u) == 0u) {
+      if (*abort_flag) return false;
+      if (timed_out(t0, WAIT_LIMIT_NS)) {
+        *abort_flag = 1;
+        if (atomicCAS(status, MG_DEV_OK, MG_DEV_WAIT_TIMEOUT) == MG_DEV_OK) status[1] = where;
+        return false;
+      }
+    }
+  }
+}
+
+struct RingTile {
+  int row0, valid_rows, b_row, n_idx;
+  int granule;      // index of the tile's granule in conversion order
+  int ring_row;     // first row of the tile's B panel inside the ring
+};
+
+// s_gb[e] = granules of the experts before e.  Tile order as locate_tile: expert-major, groups of 16 row
+// tiles, N-major inside a group, row tiles fastest.
+__device__ __forceinline__ RingTile locate_ring(int tile, const int* s_pad, const int* s_cnt, const int* s_gb,
+                                                const GemmArgs& g, const RingArgs& r) {
+  const int base0 = s_pad[0];
+  int lo = 0, hi = g.n_groups;
+  while (hi - lo > 1) {
+    int mid = (lo + hi) >> 1;
+    if (((s_pad[mid] - base0) / BM) * g.n_tiles <= tile) lo = mid; else hi = mid;
+  }
+  const int e = lo;
+  const int local = tile - ((s_pad[e] - base0) / BM) * g.n_tiles;
+  const int m_e = (s_pad[e + 1] - s_pad[e]) / BM;
+  const int per_group = RING_GROUP_M * g.n_tiles;
+  const int grp = local / per_group;
+  const int rem = local - grp * per_group;
+  const int gm = min(RING_GROUP_M, m_e - grp * RING_GROUP_M);
+  const int n = rem / gm;
+  const int m = grp * RING_GROUP_M + (rem - n * gm);
+  RingTile t;
+  t.row0 = s_pad[e] + m * BM;
+  t.valid_rows = min(BM, s_cnt[e] - m * BM);
+  t.b_row = e * g.n_per_group + n * BN_MAX;
+  t.n_idx = n;
+  const int per_exp = g.n_tiles / r.pg;
+  t.granule = s_gb[e] + grp * per_exp + n / r.pg;
+  t.ring_row = ((t.granule % r.slots) * r.pg + n % r.pg) * BN_MAX;
+  return t;
+}
+
+template <int EPI>
+__global__ void __launch_bounds__(RING_THREADS, 1)
+grouped_gemm_ring_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
+                         const __grid_constant__ CUtensorMap tmC, const GemmArgs g, const RingArgs r) {
+  constexpr int STAGE_BYTES = Cfg<false>::STAGE_BYTES;
+  constexpr int NS = STAGES;
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  uint64_t* bars = reinterpret_cast<uint64_t*>(smem + Cfg<false>::RING_BYTES);
+  uint64_t* full = bars;
+  uint64_t* empty = bars + STAGES;
+  uint64_t* tfull = bars + 2 * STAGES;
+  uint64_t* tempty = bars + 2 * STAGES + 2;
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + NUM_BARS);
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
+  volatile int* conv_ok = reinterpret_cast<volatile int*>(tmem_slot + 2);
+  int* s_pad = reinterpret_cast<int*>(tmem_slot + 8);
+  int* s_cnt = s_pad + kMaxExperts + 1;
+  int* s_gb = s_cnt + kMaxExperts + 1;
+  int* s_uses = s_gb + kMaxExperts + 1;                  // tiles of the granule that last used each slot
+  uint8_t* epi_stage = reinterpret_cast<uint8_t*>(
+      (reinterpret_cast<uintptr_t>(smem + Cfg<false>::RING_BYTES + SMEM_RING_CTRL_BYTES) + 1023) & ~uintptr_t(1023));
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < NS; ++s) { mbar_init(smem_u32(&full[s]), 1); mbar_init(smem_u32(&empty[s]), 1); }
+    for (int a = 0; a < 2; ++a) { mbar_init(smem_u32(&tfull[a]), 1); mbar_init(smem_u32(&tempty[a]), 4); }
+    *abort_flag = 0;
+    conv_ok[0] = 1;
+    conv_ok[1] = 1;
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+  }
+  for (int i = threadIdx.x; i <= g.n_groups; i += blockDim.x) s_pad[i] = g.pad_offsets[i];
+  for (int i = threadIdx.x; i < g.n_groups; i += blockDim.x) s_cnt[i] = g.counts[i];
+  __syncthreads();
+  const int per_exp = g.n_tiles / r.pg;                  // granules per (expert, group of row tiles)
+  if (threadIdx.x == 0) {
+    int acc = 0;
+    for (int e = 0; e < g.n_groups; ++e) {
+      s_gb[e] = acc;
+      const int m_e = (s_pad[e + 1] - s_pad[e]) / BM;
+      acc += ((m_e + RING_GROUP_M - 1) / RING_GROUP_M) * per_exp;
+    }
+    s_gb[g.n_groups] = acc;
+  }
+  if (warp == 1) {
+    __syncwarp();
+    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(tmem_slot)),
+                 "r"(TMEM_COLS)
+                 : "memory");
+    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = *tmem_slot;
+  const int total_tiles = ((s_pad[g.n_groups] - s_pad[0]) / BM) * g.n_tiles;
+  const uint32_t smem_base = smem_u32(smem);
+  const int n_ctas = static_cast<int>(gridDim.x);
+
+  if (warp == 0) {
+    // ---------------- TMA producer: A from the rows, B from the ring ----------------
+    if (lane == 0) {
+      uint32_t it = 0;
+      int have = -1;                                    // granule already known to be in the ring
+      const uint64_t keep = policy_evict_last();
+      const uint32_t tx_bytes = A_BYTES + B_BYTES;
+      for (int tile = blockIdx.x; tile < total_tiles && !*abort_flag; tile += gridDim.x) {
+        const RingTile t = locate_ring(tile, s_pad, s_cnt, s_gb, g, r);
+        if (t.granule != have) {
+          if (!wait_counter(r.ready + t.granule, n_ctas, abort_flag, g.status, 41)) break;
+          // the bf16 bytes were written with ordinary stores by other SMs: order them before the TMA reads
+          asm volatile("fence.proxy.async.global;" ::: "memory");
+          have = t.granule;
+        }
+        for (int kb = 0; kb < g.k_blocks; ++kb, ++it) {
+          const uint32_t s = it % NS, ph = (it / NS) & 1u;
+          if (!mbar_wait(smem_u32(&empty[s]), ph ^ 1u, abort_flag, g.status, 42)) break;
+          const uint32_t fb = smem_u32(&full[s]);
+          mbar_expect_tx(fb, tx_bytes);
+          const uint32_t sa = smem_base + s * STAGE_BYTES;
+          tma_load_2d(sa, &tmA, kb * BK, t.row0, fb);
+          if (r.keep_in_l2) tma_load_2d_hint(sa + A_BYTES, &tmB, kb * BK, t.ring_row, fb, keep);
+          else tma_load_2d(sa + A_BYTES, &tmB, kb * BK, t.ring_row, fb);
+        }
+      }
+    }
+  } else if (warp == 1) {
+    // ---------------- MMA issuer ----------------
+    if (lane == 0) {
+      uint32_t it = 0, tcount = 0;
+      for (int tile = blockIdx.x; tile < total_tiles && !*abort_flag; tile += gridDim.x, ++tcount) {
+        const RingTile t = locate_ring(tile, s_pad, s_cnt, s_gb, g, r);
+        const uint32_t acc = tcount & 1u, acc_ph = (tcount >> 1) & 1u;
+        if (!mbar_wait(smem_u32(&tempty[acc]), acc_ph ^ 1u, abort_flag, g.status, 43)) break;
+        tc_fence_after();
+        const uint32_t d_tmem = tmem_base + acc * ACC_COLS;
+        bool ok = true;
+        for (int kb = 0; kb < g.k_blocks; ++kb, ++it) {
+          const uint32_t s = it % NS, ph = (it / NS) & 1u;
+          if (!mbar_wait(smem_u32(&full[s]), ph, abort_flag, g.status, 44)) { ok = false; break; }
+          tc_fence_after();
+          const uint32_t sa = smem_base + s * STAGE_BYTES;
+          const uint64_t da = make_smem_desc(sa);
+          const uint64_t db = make_smem_desc(sa + A_BYTES);
+#pragma unroll
+          for (int k = 0; k < BK / 16; ++k)
+            tc_mma_bf16(d_tmem, da + 2 * k, db + 2 * k, g.idesc, (kb | k) != 0 ? 1u : 0u);
+          tc_commit(smem_u32(&empty[s]));
+        }
+        if (!ok) break;
+        // every B block of this tile has left the ring (its loads completed on the barriers above)
+        red_release_gpu_add(r.done + t.granule, 1);
+        tc_commit(smem_u32(&tfull[acc]));
+      }
+    }
+  } else if (warp >= 6) {
+    // ---------------- converters: FP8 panel -> bf16 ring slot, this CTA's share of every granule ----------
+    // Two groups of four warps take alternate granules, so that one group's hand-off latencies (the poll
+    // for a free slot, the drain of its stores, the barriers) overlap the other group's conversion.  The
+    // FP8 bytes of a group's next granule are fetched into registers before it waits for the current
+    // slot, which keeps the HBM latency of the weights off the hand-off path.
+    constexpr int GT = CONVERT_THREADS / 2;              // threads per group
+    const int ct = (threadIdx.x - GEMM_THREADS) & (GT - 1);
+    const int grp_id = (threadIdx.x - GEMM_THREADS) / GT;
+    const int units_per_row = g.k_blocks * (BK / 16);    // 16-byte FP8 units per weight row
+    const int units = r.pg * BN_MAX * units_per_row;      // per granule; the host keeps it below 2^31
+    const long long row_bytes = static_cast<long long>(g.k_blocks) * BK;
+    const int stride = n_ctas * GT;
+    const int u_first = static_cast<int>(blockIdx.x) * GT + ct;
+    constexpr int PF = 8;                                // units of a granule a thread keeps in registers
+    volatile int* my_ok = conv_ok + grp_id;
+    const uint64_t keep = policy_evict_last();
+
+    struct Cursor { int e, grp, nb, m_e; };
+    auto settle = [&](Cursor& c) {                       // skip experts without rows; false at the end
+      while (c.e < g.n_groups) {
+        c.m_e = (s_pad[c.e + 1] - s_pad[c.e]) / BM;
+        if (c.grp * RING_GROUP_M < c.m_e) return true;
+        ++c.e; c.grp = 0; c.nb = 0;
+      }
+      return false;
+    };
+    auto advance = [&](Cursor& c) {
+      if (++c.nb == per_exp) { c.nb = 0; ++c.grp; }
+      return settle(c);
+    };
+    auto fetch = [&](const Cursor& c, uint4 (&q)[PF], float (&sc)[PF]) {
+      const int b_row0 = c.e * g.n_per_group + c.nb * r.pg * BN_MAX;
+      const uint8_t* src = r.b8 + static_cast<long long>(b_row0) * row_bytes;
+#pragma unroll
+      for (int i = 0; i < PF; ++i) {
+        const int u = u_first + i * stride;
+        if (u < units) {
+          const int row = u / units_per_row;
+          const int cu = u - row * units_per_row;
+          q[i] = __ldcs(reinterpret_cast<const uint4*>(src + static_cast<long long>(u) * 16));
+          sc[i] = __ldg(g.scales + static_cast<long long>((b_row0 + row) >> 7) * g.scale_cols + (cu >> 3));
+        }
+      }
+    };
+
+    Cursor cur{0, 0, 0, 0};
+    bool more = settle(cur);
+    if (more && grp_id == 1) more = advance(cur);        // group 1 starts at granule 1
+    uint4 qn[PF];
+    float sn[PF];
+    if (more) fetch(cur, qn, sn);
+    for (int gi = grp_id; more; gi += 2) {
+      uint4 q[PF];
+      float sc[PF];
+#pragma unroll
+      for (int i = 0; i < PF; ++i) { q[i] = qn[i]; sc[i] = sn[i]; }
+      const Cursor me = cur;
+      more = advance(cur);
+      if (more) more = advance(cur);
+      if (more) fetch(cur, qn, sn);
+      const int slot = gi % r.slots;
+      if (ct == 0) {
+        // one thread decides for its group (the others meet it at the barrier below, so the decision
+        // must be uniform): another role gave up, or the tiles that read this slot's previous granule
+        // have not all fetched their last block within the limit
+        if (*abort_flag) *my_ok = 0;
+        else if (gi >= r.slots && !wait_counter(r.done + (gi - r.slots), s_uses[slot], abort_flag, g.status, 45))
+          *my_ok = 0;
+      }
+      asm volatile("bar.sync %0, %1;" ::"r"(1 + grp_id), "n"(GT) : "memory");
+      if (!*my_ok) break;
+      const int gm = min(RING_GROUP_M, me.m_e - me.grp * RING_GROUP_M);
+      if (ct == 0) s_uses[slot] = r.pg * gm;
+      uint8_t* dst = r.ring + static_cast<long long>(slot) * r.pg * BN_MAX * row_bytes * 2;
+#pragma unroll
+      for (int i = 0; i < PF; ++i) {
+        const int u = u_first + i * stride;
+        if (u < units) {
+          uint4 lo, hi;
+          convert16(q[i], sc[i], lo, hi);
+          uint4* o = reinterpret_cast<uint4*>(dst + static_cast<long long>(u) * 32);
+          if (r.keep_in_l2) { st_global_hint16(o, lo, keep); st_global_hint16(o + 1, hi, keep); }
+          else { o[0] = lo; o[1] = hi; }
+        }
+      }
+      // a grid smaller than the one PF was sized for leaves units beyond the prefetched ones
+      if (u_first + PF * stride < units) {
+        const int b_row0 = me.e * g.n_per_group + me.nb * r.pg * BN_MAX;
+        const uint8_t* src = r.b8 + static_cast<long long>(b_row0) * row_bytes;
+        for (int u = u_first + PF * stride; u < units; u += stride) {
+          const int row = u / units_per_row;
+          const int cu = u - row * units_per_row;
+          const float s1 = __ldg(g.scales + static_cast<long long>((b_row0 + row) >> 7) * g.scale_cols + (cu >> 3));
+          const uint4 q1 = __ldcs(reinterpret_cast<const uint4*>(src + static_cast<long long>(u) * 16));
+          uint4 lo, hi;
+          convert16(q1, s1, lo, hi);
+          uint4* o = reinterpret_cast<uint4*>(dst + static_cast<long long>(u) * 32);
+          if (r.keep_in_l2) { st_global_hint16(o, lo, keep); st_global_hint16(o + 1, hi, keep); }
+          else { o[0] = lo; o[1] = hi; }
+        }
+      }
+      // ordinary stores -> ordered before the TMA (async proxy) reads of other SMs; the barrier orders the
+      // group's stores before thread 0's release, which publishes them at GPU scope
+      asm volatile("fence.proxy.async.global;" ::: "memory");
+      asm volatile("bar.sync %0, %1;" ::"r"(1 + grp_id), "n"(GT) : "memory");
+      if (ct == 0) red_release_gpu_add(r.ready + gi, 1);
+    }
+  } else {
+    // ---------------- epilogue ----------------
+    const int quarter = warp & 3;
+    const int row_in_tile = quarter * 32 + lane;
+    EpiWarp ew{epi_stage + quarter * 2 * EPI_PIECE_BYTES, 0u, lane, 2};
+    uint32_t tcount = 0;
+    for (int tile = blockIdx.x; tile < total_tiles && !*abort_flag; tile += gridDim.x, ++tcount) {
+      const RingTile t = locate_ring(tile, s_pad, s_cnt, s_gb, g, r);
+      const uint32_t acc = tcount & 1u, acc_ph = (tcount >> 1) & 1u;
+      if (!mbar_wait(smem_u32(&tfull[acc]), acc_ph, abort_flag, g.status, 46)) break;
+      tc_fence_after();
+      const uint32_t taddr = tmem_base + acc * ACC_COLS + (static_cast<uint32_t>(quarter * 32) << 16);
+      const bool live = row_in_tile < t.valid_rows;
+      const long long row = static_cast<long long>(t.row0) + row_in_tile;
+      epilogue_rows<EPI>(taddr, g, &tmC, ew, row, t.row0 + quarter * 32, t.n_idx, live, quarter * 32 < t.valid_rows);
+      tc_fence_before();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(smem_u32(&tempty[acc]));
+    }
+    epilogue_drain(ew);
+  }
+
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 1) {
+    __syncwarp();
+    tc_fence_after();
+    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(TMEM_COLS)
+                 : "memory");
+  }
+}
+
+
 // Self-test of the bounded wait: one thread waits on a barrier that nothing will ever complete,
 // with a short limit; the wait must give up, record MG_DEV_WAIT_TIMEOUT and let the kernel end.
 __global__ void wait_probe_kernel(unsigned long long limit_ns, int32_t* status) {
@@ -1233,6 +1625,35 @@ static int launch_pair(const Handle* h, const CUtensorMap& ta, const CUtensorMap
   return MG_OK;
 }
 
+RingPlan ring_plan(int n_per_group, int K, int64_t a_rows, int n_groups, size_t budget_bytes) {
+  RingPlan r;
+  const int n_tiles = n_per_group / BN_MAX;
+  const size_t panel = static_cast<size_t>(BN_MAX) * K * 2;
+  r.pg = 1;
+  for (int d = 1; d <= n_tiles; ++d)
+    if (n_tiles % d == 0 && d * panel <= (static_cast<size_t>(9) << 19)) r.pg = d;       // granules of up to 4.5 MiB
+  r.granule_bytes = r.pg * panel;
+  long long slots = static_cast<long long>(budget_bytes / r.granule_bytes);
+  r.slots = static_cast<int>(slots < 2 ? 2 : slots > RING_MAX_SLOTS ? RING_MAX_SLOTS : slots);
+  r.ring_bytes = r.slots * r.granule_bytes;
+  r.max_granules = ((a_rows / BM + RING_GROUP_M - 1) / RING_GROUP_M + n_groups) * (n_tiles / r.pg);
+  return r;
+}
+
+template <int EPI>
+static int launch_ring(const Handle* h, const CUtensorMap& ta, const CUtensorMap& tb, const CUtensorMap& tc,
+                       const GemmArgs& args, const RingArgs& ring, int grid, cudaStream_t st) {
+  static bool done[64];
+  int rc = allow_smem(grouped_gemm_ring_kernel<EPI>, SMEM_RING_BYTES, h->device, done);
+  if (rc != MG_OK) return rc;
+  // every CTA converts a share of every granule and waits for the others': all must be resident at once
+  void* params[] = {const_cast<CUtensorMap*>(&ta), const_cast<CUtensorMap*>(&tb), const_cast<CUtensorMap*>(&tc),
+                    const_cast<GemmArgs*>(&args), const_cast<RingArgs*>(&ring)};
+  MG_CUDA(cudaLaunchCooperativeKernel(reinterpret_cast<const void*>(grouped_gemm_ring_kernel<EPI>), dim3(grid),
+                                      dim3(RING_THREADS), params, SMEM_RING_BYTES, st));
+  return MG_OK;
+}
+
 template <int EPI, int TM>
 static int launch_w8(const Handle* h, const CUtensorMap& ta, const CUtensorMap& tc, const void* b8,
                      const GemmArgs& args, int grid, cudaStream_t st) {
@@ -1244,6 +1665,60 @@ static int launch_w8(const Handle* h, const CUtensorMap& ta, const CUtensorMap& 
   grouped_gemm_w8_kernel<EPI, TM><<<grid, W8_THREADS, smem, st>>>(ta, tc, static_cast<const uint8_t*>(b8), args);
   MG_CUDA(cudaGetLastError());
   return MG_OK;
+}
+
+// W8A16 through the L2-resident ring: p.ring / p.ring_counters are the caller's scratch (ring_plan)
+static int launch_ring_gemm(const Handle* h, const GemmProblem& p, cudaStream_t st) {
+  MG_REQUIRE(p.b_fp8 && p.scales != nullptr && p.pad_offsets != nullptr, MG_ERR_CONFIG, "ring GEMM needs grouped FP8 weights");
+  MG_REQUIRE(p.K % 128 == 0 && p.n_per_group % BN_MAX == 0, MG_ERR_SHAPE, "ring GEMM: K %% 128 and N %% 256 required");
+  MG_REQUIRE(p.epilogue == EPI_SWIGLU_BF16 || p.epilogue == EPI_PLAIN_BF16, MG_ERR_CONFIG, "ring GEMM: bf16 epilogues only");
+  const RingPlan rp = ring_plan(p.n_per_group, p.K, p.a_rows, p.n_groups, p.ring_bytes);
+  MG_REQUIRE(rp.ring_bytes <= p.ring_bytes && 2 * rp.max_granules <= p.ring_counter_ints, MG_ERR_WORKSPACE,
+             "ring scratch too small: %zu bytes / %lld counters given, %zu / %lld needed", p.ring_bytes,
+             static_cast<long long>(p.ring_counter_ints), rp.ring_bytes, static_cast<long long>(2 * rp.max_granules));
+  MG_REQUIRE(static_cast<long long>(rp.pg) * BN_MAX * (p.K / 16) < (1ll << 31), MG_ERR_LIMIT, "granule too large");
+  CUtensorMap ta, tb, tc;
+  int rc = encode_2d(h, &ta, p.a, static_cast<uint64_t>(p.a_rows), static_cast<uint64_t>(p.K), BM);
+  if (rc != MG_OK) return rc;
+  rc = encode_2d(h, &tb, p.ring, static_cast<uint64_t>(rp.slots) * rp.pg * BN_MAX, static_cast<uint64_t>(p.K), BN_MAX);
+  if (rc != MG_OK) return rc;
+  MG_REQUIRE(p.ldo % 8 == 0, MG_ERR_SHAPE, "output row length %lld must be a multiple of 8", static_cast<long long>(p.ldo));
+  rc = encode_2d(h, &tc, p.out, static_cast<uint64_t>(p.a_rows), static_cast<uint64_t>(p.ldo), 32, false, true);
+  if (rc != MG_OK) return rc;
+  GemmArgs a;
+  a.pad_offsets = p.pad_offsets;
+  a.counts = p.counts;
+  a.n_groups = p.n_groups;
+  a.dense_rows = 0;
+  a.n_tiles = p.n_per_group / BN_MAX;
+  a.bn = BN_MAX;
+  a.n_per_group = p.n_per_group;
+  a.k_blocks = p.K / BK;
+  a.group_m = RING_GROUP_M;
+  a.idesc = (1u << 4) | (1u << 7) | (1u << 10) | (static_cast<uint32_t>(BN_MAX >> 3) << 17) |
+            (static_cast<uint32_t>(BM >> 4) << 24);
+  a.scales = p.scales;
+  a.scale_cols = p.K / 128;
+  a.out = p.out;
+  a.ldo = p.ldo;
+  a.status = h->d_status;
+  RingArgs r;
+  r.b8 = static_cast<const uint8_t*>(p.b);
+  r.ring = static_cast<uint8_t*>(p.ring);
+  r.ready = p.ring_counters;
+  r.done = p.ring_counters + rp.max_granules;
+  r.slots = rp.slots;
+  r.pg = rp.pg;
+  r.keep_in_l2 = h->opt_ring_persist ? 1 : 0;
+  MG_CUDA(cudaMemsetAsync(p.ring_counters, 0, sizeof(int32_t) * 2 * rp.max_granules, st));
+  int grid = h->sm_count;
+  const long long max_tiles = (p.a_rows / BM) * a.n_tiles;
+  if (max_tiles < grid) grid = static_cast<int>(max_tiles);
+  if (grid < 1) return MG_OK;
+  switch (p.epilogue) {
+    case EPI_SWIGLU_BF16: return launch_ring<EPI_SWIGLU_BF16>(h, ta, tb, tc, a, r, grid, st);
+    default: return launch_ring<EPI_PLAIN_BF16>(h, ta, tb, tc, a, r, grid, st);
+  }
 }
 
 int launch_grouped_gemm(const Handle* h, const GemmProblem& p, cudaStream_t st) {
@@ -1270,6 +1745,7 @@ int launch_grouped_gemm(const Handle* h, const GemmProblem& p, cudaStream_t st) 
   // kernel, whose FP8 bytes arrive by TMA, streams them faster than register loads do
   const bool m256 = p.b_fp8 && !pair && !f32_out && !dense && h->opt_fp8_m256 &&
                     p.a_rows >= static_cast<int64_t>(p.n_groups) * (h->opt_fp8_m256 == 2 ? 0 : 120 + 127);
+  if (p.ring != nullptr) return launch_ring_gemm(h, p, st);
   CUtensorMap ta, tb;
   int rc = encode_2d(h, &ta, p.a, static_cast<uint64_t>(p.a_rows), static_cast<uint64_t>(p.K), m256 ? 2 * BM : BM);
   if (rc != MG_OK) return rc;

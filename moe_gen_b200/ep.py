@@ -166,10 +166,12 @@ class EPMoELayer:
             self.shared_out = torch.empty(T, lay.H, dtype=torch.bfloat16, device=self.dev) if lay.Is else None
             nd = C.c_size_t()
             L.check(self.lib.mg_dequant_ws_bytes(lay._h, C.byref(nd)))
-            # FP8: pre-dequantise when an expert sees many rows (same rule as the single-GPU path)
+            # FP8: scratch for the library's FP8 mode (the L2-resident ring from 1024 rows per expert on, or
+            # the bf16 copy of pre-dequantise mode); below that the GEMMs convert in shared memory
             mode = lay.options.get(L.OPT_FP8_MODE, 0)
             Tb = max(T, self._batch_tokens)    # parts of one batch share the de-quantised copy
-            use_deq = nd.value > 0 and (mode == 1 or (mode == 0 and Tb * self.world * k >= 1024 * E))
+            use_deq = nd.value > 0 and (mode in (L.FP8_PREDEQUANT, L.FP8_RING) or
+                                        (mode == L.FP8_AUTO and Tb * self.world * k >= 1024 * E))
             self.deq = torch.empty(nd.value, dtype=torch.uint8, device=self.dev) if use_deq else None
             if nd.value > 0 and L.OPT_FP8_M256 not in lay.options:
                 # the library picks the tile height of its convert-in-the-GEMM kernels from the rows of

@@ -22,7 +22,9 @@ OPT_KEEP_DEQUANT = 3
 OPT_FP8_M256 = 4
 OPT_BATCH_TOKENS = 5
 OPT_SHARED_EARLY = 6
-FP8_AUTO, FP8_PREDEQUANT, FP8_IN_KERNEL = 0, 1, 2
+OPT_RING_BYTES = 7
+OPT_RING_PERSIST = 8
+FP8_AUTO, FP8_PREDEQUANT, FP8_IN_KERNEL, FP8_RING = 0, 1, 2, 3
 
 
 class LayerDesc(C.Structure):
@@ -43,6 +45,7 @@ SIGNATURES = {
     "mg_destroy": [_vp],
     "mg_device_status": [_vp, _P(_i32), _P(_i32)],
     "mg_device_status_async": [_vp, _vp, _vp],
+    "mg_l2_set_aside": [_sz, _P(_sz)],
     "mg_packed_weight_bytes": [_vp, _P(_sz)],
     "mg_workspace_bytes": [_vp, _i64, _i64, _P(_sz)],
     "mg_padded_rows": [_vp, _i64, _P(_i64)],

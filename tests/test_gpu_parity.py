@@ -219,10 +219,13 @@ def test_all_tokens_to_one_expert(built_lib):
     assert worst < 5e-3
 
 
-def test_fp8_weights_converted_in_the_gemm_equal_dequantise_first(built_lib):
+@pytest.mark.parametrize("H,I", [(512, 256), (1024, 512)])
+def test_fp8_weights_converted_in_the_gemm_equal_dequantise_first(built_lib, H, I):
     """W8A16: converting FP8 tiles inside the grouped GEMM gives the same bits as de-quantising
-    the matrices first (the reference's order, Wrapper.py:481-491) and running the bf16 kernel."""
-    spec = O.LayerSpec(512, 256, 16, 4, 256, 4, 2, O.GATE_SIGMOID_NOAUX_TC, True, 2.5, O.WEIGHT_FP8_BLOCK128,
+    the matrices first (the reference's order, Wrapper.py:481-491) and running the bf16 kernel.
+    The two shapes take the two de-quantisation kernels of the packed stacks (rows of a multiple of
+    512 bytes stream through the row kernel, others through the generic one)."""
+    spec = O.LayerSpec(H, I, 16, 4, 256, 4, 2, O.GATE_SIGMOID_NOAUX_TC, True, 2.5, O.WEIGHT_FP8_BLOCK128,
                        O.COMBINE_FP32)
     x, W = O.make_inputs(spec, 900, 51)
     layer = make_layer(spec, W, DEV)
@@ -231,12 +234,20 @@ def test_fp8_weights_converted_in_the_gemm_equal_dequantise_first(built_lib):
     counts, offsets, pad, dst = layer.permute_plan(idx)
     perm = layer.permute_rows(xd, dst, layer.padded_rows(900 * 4))
     h1, o1 = layer.expert_ffn(perm, pad, counts, predequant=False)
-    h2, o2 = layer.expert_ffn(perm, pad, counts, predequant=True)
-    _status_ok(layer)
     live = torch.zeros(perm.shape[0], dtype=torch.bool)
     live[dst.cpu().long().view(-1)] = True
-    assert torch.equal(h1.cpu()[live].view(torch.int16), h2.cpu()[live].view(torch.int16))
-    assert torch.equal(o1.cpu()[live].view(torch.int16), o2.cpu()[live].view(torch.int16))
+    # scratch-based modes: the bf16 copy written by a separate pass (1), the L2-resident ring filled by
+    # the GEMM kernel itself (3), the latter also with a ring of two slots that every expert reuses
+    for mode, ring_mib in ((1, 56), (3, 56), (3, 1)):
+        layer.set_option(1, mode)
+        layer.set_option(7, ring_mib)
+        for _ in range(2):
+            h2, o2 = layer.expert_ffn(perm, pad, counts, predequant=True)
+            _status_ok(layer)
+            assert torch.equal(h1.cpu()[live].view(torch.int16), h2.cpu()[live].view(torch.int16)), (mode, ring_mib)
+            assert torch.equal(o1.cpu()[live].view(torch.int16), o2.cpu()[live].view(torch.int16)), (mode, ring_mib)
+    layer.set_option(7, 56)
+    layer.set_option(1, 0)
     for tall in (0, 2, 1):                             # 128-row tiles, 256-row tiles, by expert size
         layer.set_option(4, tall)
         h4, o4 = layer.expert_ffn(perm, pad, counts, predequant=False)
@@ -248,7 +259,7 @@ def test_fp8_weights_converted_in_the_gemm_equal_dequantise_first(built_lib):
     ys = []
     for pair in (0, 1):                                # one CTA per SM / SM pairs
         layer.set_option(2, pair)
-        for mode in (0, 1, 2, 1):                      # auto, pre-dequantise, in-kernel, again
+        for mode in (0, 1, 2, 3, 1):                   # auto, pre-dequantise, in-kernel, ring, again
             layer.set_option(1, mode)
             ys.append(layer.forward(xd).cpu())
             _status_ok(layer)
