@@ -447,6 +447,10 @@ def main():
                     help="expert parallel, host-buffer path: parts each rank's tokens are fed in")
     ap.add_argument("--ep-dedup", type=int, default=1,
                     help="expert parallel: 1 sends one row per (token, destination GPU), 0 one per (token, expert)")
+    ap.add_argument("--ep-push", type=int, default=-1,
+                    help="expert parallel: 1 owners push results home part by part beside the down projection, "
+                         "0 the combine gathers them after the experts, -1 by the number of GPUs")
+    ap.add_argument("--ep-parts", type=int, default=4, help="expert parallel: parts of the pushed return")
     ap.add_argument("--shared-early", type=int, default=-1,
                     help="1/0 shared expert beside the routing kernels / after the routed experts")
     ap.add_argument("--pair-gemm", type=int, default=-1, help="1/0 force the SM-pair expert GEMM on/off")
@@ -505,7 +509,7 @@ def main():
         # skewed routing can send most rows to one GPU: size the receive buffers for it
         cap = args.capacity_factor if args.capacity_factor > 0 else (float(world) if args.zipf > 0 else 2.0)
         layer = EPMoELayer(build_layer(name, device, rank, world, args.zipf), capacity_factor=cap, n_micro=args.micro,
-                           dedup=bool(args.ep_dedup))
+                           dedup=bool(args.ep_dedup), push_return=None if args.ep_push < 0 else bool(args.ep_push), return_parts=args.ep_parts)
         x = make_tokens(name, T // world, device, rank, args.zipf)
         step = lambda: layer.forward(x)                                   # noqa: E731
         T_total = T
@@ -569,7 +573,12 @@ def main():
         # router product, top-k, count + scan, layout + place, dispatch (+ duplicate table clear and fill),
         # [shared 2], experts (2, or 2 GEMMs + 2 de-quantisations per chunk of experts when FP8 weights are
         # pre-dequantised), combine; NCCL kernels not counted
-        launches = 7 + (2 if layer.dedup else 0) + (2 if Is else 0) + (32 if layer.deq is not None else 2) + 1
+        parts = min(layer.return_parts, base.e_local, 8)
+        if layer.deq is not None:
+            experts = 16 + 16 + (8 if layer.push_return else 0)
+        else:
+            experts = 1 + (2 * parts if layer.push_return else 1)
+        launches = 7 + (1 if layer.dedup else 0) + (2 if Is else 0) + experts + 1
     code, detail = base.device_status()
     if code != 0:
         raise SystemExit(f"device status {code} (detail {detail}) in the timed region")

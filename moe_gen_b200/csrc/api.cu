@@ -206,6 +206,11 @@ int mg_destroy(mg_handle hh) {
       if (h->stage_ev[s][i]) cudaEventDestroy(h->stage_ev[s][i]);
   if (h->side) cudaStreamDestroy(h->side);
   if (h->side2) cudaStreamDestroy(h->side2);
+  if (h->side3) {
+    cudaStreamDestroy(h->side3);
+    for (int i = 0; i < kDequantChunks; ++i) cudaEventDestroy(h->ev_part[i]);
+    cudaEventDestroy(h->ev_ret);
+  }
   if (h->ev_shared_in) cudaEventDestroy(h->ev_shared_in);
   if (h->ev_shared_out) cudaEventDestroy(h->ev_shared_out);
   if (h->ev_entry) cudaEventDestroy(h->ev_entry);
@@ -405,9 +410,36 @@ static int start_dequant(Handle* h, const void* packed, void* deq, cudaStream_t 
   return MG_OK;
 }
 
+static int ensure_return_stream(Handle* h) {
+  if (h->side3) return MG_OK;
+  MG_CUDA(cudaStreamCreateWithFlags(&h->side3, cudaStreamNonBlocking));
+  for (int i = 0; i < kDequantChunks; ++i) MG_CUDA(cudaEventCreateWithFlags(&h->ev_part[i], cudaEventDisableTiming));
+  MG_CUDA(cudaEventCreateWithFlags(&h->ev_ret, cudaEventDisableTiming));
+  return MG_OK;
+}
+
+// the output rows of local experts [lo, lo + n) are complete on `st`: send them home on the return stream
+static int push_part(Handle* h, const ReturnHook* hook, const void* out_rows, const int32_t* pad, int lo, int n,
+                     int part, cudaStream_t st) {
+  cudaEvent_t ev = h->ev_part[part % kDequantChunks];
+  MG_CUDA(cudaEventRecord(ev, st));
+  MG_CUDA(cudaStreamWaitEvent(h->side3, ev, 0));
+  return launch_return_rows(h, out_rows, hook->back, pad, lo, n, hook->rets, h->side3);
+}
+
+static int join_return(Handle* h, cudaStream_t st) {
+  MG_CUDA(cudaEventRecord(h->ev_ret, h->side3));
+  MG_CUDA(cudaStreamWaitEvent(st, h->ev_ret, 0));
+  return MG_OK;
+}
+
 static int expert_ffn(Handle* h, const void* perm_x, const int32_t* pad, const int32_t* counts, int64_t rows_padded,
                       const void* packed, void* h_buf, void* out_rows, void* deq, cudaStream_t st, int* launches,
-                      bool timed = false) {
+                      bool timed = false, const ReturnHook* hook = nullptr) {
+  if (hook != nullptr) {
+    int rc0 = ensure_return_stream(h);
+    if (rc0 != MG_OK) return rc0;
+  }
   const mg_layer_desc& d = h->d;
   const PackedLayout L = packed_layout(h);
   const uint8_t* base = static_cast<const uint8_t*>(packed);
@@ -441,7 +473,31 @@ static int expert_ffn(Handle* h, const void* perm_x, const int32_t* pad, const i
     p.a = h_buf; p.b = base + L.w2; p.n_per_group = d.hidden; p.K = d.inter; p.out = out_rows; p.ldo = d.hidden;
     p.epilogue = EPI_PLAIN_BF16;
     p.scales = fp8 ? reinterpret_cast<const float*>(base + L.s2) : nullptr;
-    rc = launch_grouped_gemm(h, p, st);
+    if (hook != nullptr && mode != MG_FP8_RING) {
+      // the down projection in parts of experts, each part's rows sent home while the next part computes
+      const int parts = hook->n_parts < 1 ? 1 : hook->n_parts > E ? E : hook->n_parts > kDequantChunks ? kDequantChunks : hook->n_parts;
+      const int per = (E + parts - 1) / parts;
+      const size_t w2_expert = static_cast<size_t>(d.hidden) * d.inter * L.w_elem;
+      const size_t s2_expert = static_cast<size_t>(d.hidden / 128) * (d.inter / 128);
+      for (int c = 0, lo = 0; lo < E; ++c, lo += per) {
+        const int n = lo + per <= E ? per : E - lo;
+        p.n_groups = n; p.pad_offsets = pad + lo; p.counts = counts + lo;
+        p.b = base + L.w2 + lo * w2_expert;
+        p.scales = fp8 ? reinterpret_cast<const float*>(base + L.s2) + lo * s2_expert : nullptr;
+        rc = launch_grouped_gemm(h, p, st);
+        if (rc != MG_OK) return rc;
+        rc = push_part(h, hook, out_rows, pad, lo, n, c, st);
+        if (rc != MG_OK) return rc;
+        if (launches) *launches += 2;
+      }
+      rc = join_return(h, st);
+    } else {
+      rc = launch_grouped_gemm(h, p, st);
+      if (rc == MG_OK && hook != nullptr) {
+        rc = push_part(h, hook, out_rows, pad, 0, E, 0, st);
+        if (rc == MG_OK) rc = join_return(h, st);
+      }
+    }
     if (timed) mark(h, MG_STAGE_EXPERT_GEMM2, st);
     if (launches) *launches += mode == MG_FP8_RING ? 4 : 2;      // ring: a counter reset in front of each GEMM
     return rc;
@@ -482,6 +538,14 @@ static int expert_ffn(Handle* h, const void* perm_x, const int32_t* pad, const i
       }
       rc = launch_grouped_gemm(h, p, st);
       if (rc != MG_OK) return rc;
+      if (which == 1 && hook != nullptr) {
+        rc = push_part(h, hook, out_rows, pad, lo, n, c, st);
+        if (rc != MG_OK) return rc;
+      }
+    }
+    if (which == 1 && hook != nullptr) {
+      rc = join_return(h, st);
+      if (rc != MG_OK) return rc;
     }
     if (timed) mark(h, which == 0 ? MG_STAGE_EXPERT_GEMM1 : MG_STAGE_EXPERT_GEMM2, st);
   }
@@ -492,6 +556,16 @@ static int expert_ffn(Handle* h, const void* perm_x, const int32_t* pad, const i
   h->deq_stream = st;
   return MG_OK;
 }
+
+}  // extern "C"
+namespace mg {
+int expert_ffn_return(Handle* h, const void* perm_x, const int32_t* pad, const int32_t* counts, int64_t rows_padded,
+                      const void* packed, void* h_buf, void* out_rows, void* deq, const ReturnHook& hook,
+                      cudaStream_t st) {
+  return expert_ffn(h, perm_x, pad, counts, rows_padded, packed, h_buf, out_rows, deq, st, nullptr, false, &hook);
+}
+}  // namespace mg
+extern "C" {
 
 int mg_dequant_start(mg_handle hh, const void* d_packed, void* d_dequant_ws, void* stream) {
   Handle* h = check(hh);

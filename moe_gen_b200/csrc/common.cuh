@@ -70,6 +70,8 @@ struct Handle {
   int opt_ring_persist;   // ring accesses carry the L2 evict_last policy (needs an L2 set-aside, mg_l2_set_aside)
   cudaStream_t side;      // de-quantisation runs here, one chunk of experts ahead of the GEMMs
   cudaEvent_t ev_entry, ev_w13[kDequantChunks], ev_w2[kDequantChunks];
+  cudaStream_t side3;     // expert-parallel return: pushes of finished expert parts run here beside the GEMMs
+  cudaEvent_t ev_part[kDequantChunks], ev_ret;
   cudaStream_t side2;     // the shared expert's GEMMs run here beside the routing and scatter kernels
   cudaEvent_t ev_shared_in, ev_shared_out;
   int opt_shared_early;
@@ -108,8 +110,19 @@ int launch_rmsnorm(const Handle* h, const void* x, const void* weight, float eps
                    cudaStream_t st);
 
 struct PeerPtrs { void* p[kMaxPeers]; };
+// expert-parallel return pushed from inside the expert FFN: after the down projection of each part of the
+// local experts, their output rows travel to the token owners' return buffers on a side stream
+struct ReturnHook {
+  const int32_t* back;    // this rank's return table [cap_rows]
+  PeerPtrs rets;          // every rank's return buffer as mapped here
+  int n_parts;            // parts the down projection is cut into (when it is not chunked already)
+};
 int launch_dispatch_rows(const Handle* h, const void* x, const int32_t* dst, int64_t T,
-                         const PeerPtrs& peers, const PeerPtrs* dups, cudaStream_t st);
+                         const PeerPtrs& peers, const PeerPtrs* dups, const PeerPtrs* backs, cudaStream_t st);
+int launch_return_rows(const Handle* h, const void* out_rows, const int32_t* back, const int32_t* pad, int e_lo,
+                       int e_n, const PeerPtrs& rets, cudaStream_t st);
+int launch_combine_slots(const Handle* h, const void* ret_rows, const int32_t* dst, const int32_t* idx, const float* w,
+                         const void* shared, int64_t T, void* y, cudaStream_t st);
 int launch_fill_duplicates(const Handle* h, void* rows, const int32_t* dup, int64_t n_rows, cudaStream_t st);
 int launch_combine_peers(const Handle* h, const PeerPtrs& peers, const int32_t* dst,
                          const int32_t* idx, const float* w, const void* shared, int64_t T, void* y,
@@ -166,5 +179,10 @@ struct RingPlan {
 RingPlan ring_plan(int n_per_group, int K, int64_t a_rows, int n_groups, size_t budget_bytes);
 int launch_grouped_gemm(const Handle* h, const GemmProblem& p, cudaStream_t st);
 int launch_wait_probe(const Handle* h, int limit_ms, cudaStream_t st);
+
+// the expert FFN with the expert-parallel return pushed from inside it (api.cu)
+int expert_ffn_return(Handle* h, const void* perm_x, const int32_t* pad, const int32_t* counts, int64_t rows_padded,
+                      const void* packed, void* h_buf, void* out_rows, void* deq, const ReturnHook& hook,
+                      cudaStream_t st);
 
 }  // namespace mg

@@ -91,7 +91,7 @@ int mg_ep_dispatch(mg_handle hh, const void* d_x, const int32_t* d_dst, int64_t 
   PeerPtrs peers;
   int rc = gather_peers(h, peer_recv, &peers);
   if (rc != MG_OK) return rc;
-  return launch_dispatch_rows(h, d_x, d_dst, T, peers, nullptr, static_cast<cudaStream_t>(stream));
+  return launch_dispatch_rows(h, d_x, d_dst, T, peers, nullptr, nullptr, static_cast<cudaStream_t>(stream));
 }
 
 int mg_ep_dispatch_dedup(mg_handle hh, const void* d_x, const int32_t* d_dst, int64_t T, void* const* peer_recv,
@@ -106,7 +106,57 @@ int mg_ep_dispatch_dedup(mg_handle hh, const void* d_x, const int32_t* d_dst, in
   if (rc != MG_OK) return rc;
   rc = gather_peers(h, peer_dup, &dups);
   if (rc != MG_OK) return rc;
-  return launch_dispatch_rows(h, d_x, d_dst, T, peers, &dups, static_cast<cudaStream_t>(stream));
+  return launch_dispatch_rows(h, d_x, d_dst, T, peers, &dups, nullptr, static_cast<cudaStream_t>(stream));
+}
+
+int mg_ep_dispatch_back(mg_handle hh, const void* d_x, const int32_t* d_dst, int64_t T, void* const* peer_recv,
+                        void* const* peer_dup, void* const* peer_back, void* stream) {
+  Handle* h = check_handle(hh);
+  if (!h) return MG_ERR_STATE;
+  MG_REQUIRE(T >= 0, MG_ERR_SHAPE, "negative token count");
+  if (T == 0) return MG_OK;
+  MG_REQUIRE(d_x && d_dst && peer_back, MG_ERR_NULL, "mg_ep_dispatch_back: null pointer");
+  MG_REQUIRE(T * h->d.top_k <= kPeerRowMask, MG_ERR_LIMIT, "tokens * top_k exceeds 2^%d picks per rank", kPeerShift);
+  PeerPtrs peers, dups, backs;
+  int rc = gather_peers(h, peer_recv, &peers);
+  if (rc != MG_OK) return rc;
+  rc = gather_peers(h, peer_back, &backs);
+  if (rc != MG_OK) return rc;
+  if (peer_dup != nullptr) {
+    rc = gather_peers(h, peer_dup, &dups);
+    if (rc != MG_OK) return rc;
+  }
+  return launch_dispatch_rows(h, d_x, d_dst, T, peers, peer_dup ? &dups : nullptr, &backs,
+                              static_cast<cudaStream_t>(stream));
+}
+
+int mg_ep_expert_ffn_return(mg_handle hh, const void* d_recv_x, const int32_t* d_recv_pad, const int32_t* d_recv_counts,
+                            int64_t cap_rows, const void* d_packed, void* d_h_buf, void* d_out_rows, void* d_dequant_ws,
+                            const int32_t* d_back, void* const* peer_ret, int32_t n_parts, void* stream) {
+  Handle* h = check_handle(hh);
+  if (!h) return MG_ERR_STATE;
+  MG_REQUIRE(d_recv_x && d_recv_pad && d_recv_counts && d_packed && d_h_buf && d_out_rows && d_back, MG_ERR_NULL,
+             "mg_ep_expert_ffn_return: null pointer");
+  MG_REQUIRE(cap_rows >= 0 && cap_rows % kTileM == 0, MG_ERR_SHAPE, "cap_rows=%lld must be a multiple of %d",
+             static_cast<long long>(cap_rows), kTileM);
+  ReturnHook hook;
+  hook.back = d_back;
+  hook.n_parts = n_parts;
+  int rc = gather_peers(h, peer_ret, &hook.rets);
+  if (rc != MG_OK) return rc;
+  return expert_ffn_return(h, d_recv_x, d_recv_pad, d_recv_counts, cap_rows, d_packed, d_h_buf, d_out_rows, d_dequant_ws,
+                           hook, static_cast<cudaStream_t>(stream));
+}
+
+int mg_ep_combine_slots(mg_handle hh, const void* d_ret, const int32_t* d_dst, const int32_t* d_topk_idx,
+                        const float* d_topk_w, const void* d_shared_out, int64_t T, void* d_y, void* stream) {
+  Handle* h = check_handle(hh);
+  if (!h) return MG_ERR_STATE;
+  MG_REQUIRE(T >= 0, MG_ERR_SHAPE, "negative token count");
+  if (T == 0) return MG_OK;
+  MG_REQUIRE(d_ret && d_dst && d_topk_idx && d_topk_w && d_y, MG_ERR_NULL, "mg_ep_combine_slots: null pointer");
+  return launch_combine_slots(h, d_ret, d_dst, d_topk_idx, d_topk_w, d_shared_out, T, d_y,
+                              static_cast<cudaStream_t>(stream));
 }
 
 int mg_ep_clear_duplicates(mg_handle hh, void* d_dup, int64_t cap_rows, void* stream) {

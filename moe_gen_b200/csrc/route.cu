@@ -426,15 +426,20 @@ int launch_permute_plan_static(const Handle* h, const int32_t* idx, int64_t T, i
 // DEDUP: when several picks of a token go to the same rank, only the first one's row travels; for
 // the others the kernel writes, into the destination rank's duplicate table at the pick's row, the
 // row of that first pick, and the owner copies the row locally (fill_duplicate_rows_kernel).
-template <bool PEER, bool DEDUP>
+// BACK: every pick also leaves, in the destination rank's return table at the pick's row, where the
+// expert's output for that row has to go: source rank << kPeerShift | (token * k + slot).
+template <bool PEER, bool DEDUP, bool BACK>
 __global__ void __launch_bounds__(256) permute_rows_kernel(const uint4* __restrict__ x,
                                                            const int32_t* __restrict__ dst_row,
                                                            int64_t T, int k, int vec_per_row,
-                                                           PeerPtrs bufs, PeerPtrs dups) {
+                                                           PeerPtrs bufs, PeerPtrs dups, PeerPtrs backs, int my_rank) {
   const int lane = threadIdx.x & 31;
   const int64_t t = static_cast<int64_t>(blockIdx.x) * (blockDim.x >> 5) + (threadIdx.x >> 5);
   if (t >= T) return;
   int32_t my_dst = lane < k ? dst_row[t * k + lane] : -1;
+  if (BACK && my_dst >= 0)
+    static_cast<int32_t*>(backs.p[my_dst >> kPeerShift])[my_dst & kPeerRowMask] =
+        (my_rank << kPeerShift) | static_cast<int32_t>(t * k + lane);
   uint32_t skip = 0;                           // bit j: pick j's row is copied on its owner
   if (DEDUP) {
     int my_first = -1;                         // earliest pick of this token with my destination rank
@@ -505,23 +510,70 @@ int launch_permute_rows(const Handle* h, const void* x, const int32_t* dst_row, 
   dim3 grid(static_cast<unsigned>((T + warps - 1) / warps)), block(warps * 32);
   PeerPtrs bufs{};
   bufs.p[0] = perm_x;
-  permute_rows_kernel<false, false><<<grid, block, 0, st>>>(static_cast<const uint4*>(x), dst_row, T,
-                                                            h->d.top_k, h->d.hidden / 8, bufs, bufs);
+  permute_rows_kernel<false, false, false><<<grid, block, 0, st>>>(static_cast<const uint4*>(x), dst_row, T,
+                                                                   h->d.top_k, h->d.hidden / 8, bufs, bufs, bufs, 0);
   MG_CUDA(cudaGetLastError());
   return MG_OK;
 }
 
 int launch_dispatch_rows(const Handle* h, const void* x, const int32_t* dst, int64_t T,
-                         const PeerPtrs& peers, const PeerPtrs* dups, cudaStream_t st) {
+                         const PeerPtrs& peers, const PeerPtrs* dups, const PeerPtrs* backs, cudaStream_t st) {
   if (T == 0) return MG_OK;
   const int warps = 8;
   dim3 grid(static_cast<unsigned>((T + warps - 1) / warps)), block(warps * 32);
-  if (dups != nullptr)
-    permute_rows_kernel<true, true><<<grid, block, 0, st>>>(static_cast<const uint4*>(x), dst, T,
-                                                            h->d.top_k, h->d.hidden / 8, peers, *dups);
+  const uint4* xs = static_cast<const uint4*>(x);
+  const int k = h->d.top_k, vpr = h->d.hidden / 8, me = h->d.ep_rank;
+  const PeerPtrs& d = dups ? *dups : peers;
+  const PeerPtrs& b = backs ? *backs : peers;
+  if (dups != nullptr && backs != nullptr)
+    permute_rows_kernel<true, true, true><<<grid, block, 0, st>>>(xs, dst, T, k, vpr, peers, d, b, me);
+  else if (dups != nullptr)
+    permute_rows_kernel<true, true, false><<<grid, block, 0, st>>>(xs, dst, T, k, vpr, peers, d, b, me);
+  else if (backs != nullptr)
+    permute_rows_kernel<true, false, true><<<grid, block, 0, st>>>(xs, dst, T, k, vpr, peers, d, b, me);
   else
-    permute_rows_kernel<true, false><<<grid, block, 0, st>>>(static_cast<const uint4*>(x), dst, T,
-                                                             h->d.top_k, h->d.hidden / 8, peers, peers);
+    permute_rows_kernel<true, false, false><<<grid, block, 0, st>>>(xs, dst, T, k, vpr, peers, d, b, me);
+  MG_CUDA(cudaGetLastError());
+  return MG_OK;
+}
+
+// Owner side of the return: the output rows of local experts [e_lo, e_lo + e_n) go to the ranks their
+// tokens came from, each into row (token * k + slot) of that rank's return buffer, as the return table
+// says (rows without an entry are padding).  Plain 128-bit stores through the peer mappings; a warp per
+// row, rows taken in a grid-stride loop because their number is only known on the device.
+__global__ void __launch_bounds__(256) return_rows_kernel(const uint4* __restrict__ out_rows,
+                                                          const int32_t* __restrict__ back,
+                                                          const int32_t* __restrict__ pad, int e_lo, int e_n,
+                                                          int vec_per_row, PeerPtrs rets) {
+  const int lane = threadIdx.x & 31;
+  const int64_t row0 = pad[e_lo], row1 = pad[e_lo + e_n];
+  const int64_t warps = static_cast<int64_t>(gridDim.x) * (blockDim.x >> 5);
+  for (int64_t r = row0 + static_cast<int64_t>(blockIdx.x) * (blockDim.x >> 5) + (threadIdx.x >> 5); r < row1; r += warps) {
+    const int32_t b = back[r];
+    if (b < 0) continue;
+    const uint4* src = out_rows + r * vec_per_row;
+    uint4* dst = static_cast<uint4*>(rets.p[b >> kPeerShift]) + static_cast<int64_t>(b & kPeerRowMask) * vec_per_row;
+    for (int v0 = 0; v0 < vec_per_row; v0 += 128) {
+      uint4 val[4];
+#pragma unroll
+      for (int u = 0; u < 4; ++u) {
+        int v = v0 + u * 32 + lane;
+        if (v < vec_per_row) val[u] = src[v];
+      }
+#pragma unroll
+      for (int u = 0; u < 4; ++u) {
+        int v = v0 + u * 32 + lane;
+        if (v < vec_per_row) dst[v] = val[u];
+      }
+    }
+  }
+}
+
+int launch_return_rows(const Handle* h, const void* out_rows, const int32_t* back, const int32_t* pad, int e_lo,
+                       int e_n, const PeerPtrs& rets, cudaStream_t st) {
+  if (e_n <= 0) return MG_OK;
+  return_rows_kernel<<<h->sm_count * 2, 256, 0, st>>>(static_cast<const uint4*>(out_rows), back, pad, e_lo, e_n,
+                                                      h->d.hidden / 8, rets);
   MG_CUDA(cudaGetLastError());
   return MG_OK;
 }
@@ -558,6 +610,8 @@ __device__ __forceinline__ float round_bf16(float f) {
   return __bfloat162float(__float2bfloat16_rn(f));
 }
 
+// by_slot: the rows lie at (token * k + slot) (the return buffer of the expert-parallel push); dst_row
+// then only says which picks exist (negative = dropped).
 template <int MODE, bool PEER>
 __global__ void __launch_bounds__(256) combine_kernel(PeerPtrs bufs,
                                                       const int32_t* __restrict__ dst_row,
@@ -566,7 +620,7 @@ __global__ void __launch_bounds__(256) combine_kernel(PeerPtrs bufs,
                                                       const uint4* __restrict__ shared,
                                                       const uint4* residual,
                                                       int64_t T, int k, int vec_per_row, int v_chunk,
-                                                      uint4* y) {
+                                                      uint4* y, int by_slot) {
   const int lane = threadIdx.x & 31;
   const int64_t t = static_cast<int64_t>(blockIdx.x) * (blockDim.x >> 5) + (threadIdx.x >> 5);
   if (t >= T) return;
@@ -574,6 +628,7 @@ __global__ void __launch_bounds__(256) combine_kernel(PeerPtrs bufs,
   float my_w = 0.f;
   if (lane < k) {
     my_dst = dst_row[t * k + lane];
+    if (by_slot && my_dst >= 0) my_dst = static_cast<int32_t>(t * k + lane);
     my_w = topk_w[t * k + lane];
     if (MODE == MG_COMBINE_BF16_SEQ) my_e = topk_idx[t * k + lane];
     if (MODE != MG_COMBINE_FP32) my_w = round_bf16(my_w);
@@ -661,7 +716,7 @@ __global__ void __launch_bounds__(256) combine_kernel(PeerPtrs bufs,
 template <bool PEER>
 static int launch_combine_impl(const Handle* h, const PeerPtrs& bufs, const int32_t* dst_row,
                                const int32_t* idx, const float* w, const void* shared, const void* residual,
-                               int64_t T, void* y, cudaStream_t st) {
+                               int64_t T, void* y, cudaStream_t st, int by_slot = 0) {
   if (T == 0) return MG_OK;
   const int warps = 8;
   const int k = h->d.top_k, vpr = h->d.hidden / 8;
@@ -677,7 +732,7 @@ static int launch_combine_impl(const Handle* h, const PeerPtrs& bufs, const int3
   combine_kernel<M, PEER><<<grid, block, 0, st>>>(bufs, dst_row, idx, w,                          \
                                                   static_cast<const uint4*>(shared),              \
                                                   static_cast<const uint4*>(residual), T, k, vpr, \
-                                                  v_chunk, static_cast<uint4*>(y))
+                                                  v_chunk, static_cast<uint4*>(y), by_slot)
   switch (h->d.combine_mode) {
     case MG_COMBINE_FP32: MG_COMBINE_CASE(MG_COMBINE_FP32); break;
     case MG_COMBINE_BF16_PROD: MG_COMBINE_CASE(MG_COMBINE_BF16_PROD); break;
@@ -695,6 +750,13 @@ int launch_combine(const Handle* h, const void* out_rows, const int32_t* dst_row
   PeerPtrs bufs{};
   bufs.p[0] = const_cast<void*>(out_rows);
   return launch_combine_impl<false>(h, bufs, dst_row, idx, w, shared, residual, T, y, st);
+}
+
+int launch_combine_slots(const Handle* h, const void* ret_rows, const int32_t* dst, const int32_t* idx, const float* w,
+                         const void* shared, int64_t T, void* y, cudaStream_t st) {
+  PeerPtrs bufs{};
+  bufs.p[0] = const_cast<void*>(ret_rows);
+  return launch_combine_impl<false>(h, bufs, dst, idx, w, shared, nullptr, T, y, st, 1);
 }
 
 int launch_combine_peers(const Handle* h, const PeerPtrs& peers, const int32_t* dst,

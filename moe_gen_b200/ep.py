@@ -67,7 +67,8 @@ class EPMoELayer:
     PHASES = ["route_dispatch", "expert_ffn", "combine"]
 
     def __init__(self, layer: MoELayer, group: Optional[dist.ProcessGroup] = None, capacity_factor: float = 2.0,
-                 n_micro: int = 1, dedup: bool = True, min_headroom: int = 4096):
+                 n_micro: int = 1, dedup: bool = True, min_headroom: int = 4096, push_return: Optional[bool] = None,
+                 return_parts: int = 4):
         self.layer = layer
         self.group = group
         self.rank = dist.get_rank(group)
@@ -82,6 +83,13 @@ class EPMoELayer:
         # one row per (token, destination rank) over NVLink; the owner copies the rows of a token's
         # further experts on that rank (pays off when top_k exceeds the number of ranks a token reaches)
         self.dedup = dedup
+        # the owners push their experts' outputs into the token owners' return buffers part by part while the
+        # next part's down projection runs, and the combine is local; False = the combine gathers the rows
+        # from the owners' buffers after the experts have finished
+        # None: by the group size (measured at 2 GPUs: every rank returns half of all rows, the extra copy of
+        # the push costs the experts more than the local combine saves, 30.5 against 29.6 ms per step)
+        self.push_return = (self.world >= 4) if push_return is None else push_return
+        self.return_parts = return_parts
         self.lib = layer.lib
         self.dev = layer.device
         self._mbs: List[_MicroBatch] = []
@@ -120,7 +128,8 @@ class EPMoELayer:
                 assert cap < (1 << PEER_SHIFT)
                 mb.cap = cap
                 mb.own = []
-                for nbytes in (cap * lay.H * 2, cap * lay.H * 2, cap * 4):   # recv_x, out_rows, duplicate table
+                # recv_x, out_rows, duplicate table, return table, return buffer
+                for nbytes in (cap * lay.H * 2, cap * lay.H * 2, cap * 4, cap * 4, max(Tm * k, 1) * lay.H * 2):
                     p = C.c_void_p()
                     L.check(self.lib.mg_ep_alloc(nbytes, C.byref(p)))
                     hd = (C.c_ubyte * 64)()
@@ -148,20 +157,19 @@ class EPMoELayer:
             gathered: List[Optional[list]] = [None] * self.world
             dist.all_gather_object(gathered, handles, group=self.group)
             for i, mb in enumerate(self._mbs):
-                recv = (C.c_void_p * self.world)()
-                out = (C.c_void_p * self.world)()
-                dup = (C.c_void_p * self.world)()
+                tables = [(C.c_void_p * self.world)() for _ in range(5)]
                 for r in range(self.world):
                     if r == self.rank:
-                        recv[r], out[r], dup[r] = mb.own[0], mb.own[1], mb.own[2]
+                        for which, table in enumerate(tables):
+                            table[r] = mb.own[which]
                         continue
-                    for which, table in ((0, recv), (1, out), (2, dup)):
+                    for which, table in enumerate(tables):
                         p = C.c_void_p()
-                        buf = (C.c_ubyte * 64).from_buffer_copy(gathered[r][3 * i + which])
+                        buf = (C.c_ubyte * 64).from_buffer_copy(gathered[r][5 * i + which])
                         L.check(self.lib.mg_ep_import(buf, C.byref(p)))
                         table[r] = p.value
                         mb.imported.append(p.value)
-                mb.peer_recv, mb.peer_out, mb.peer_dup = recv, out, dup
+                mb.peer_recv, mb.peer_out, mb.peer_dup, mb.peer_back, mb.peer_ret = tables
             self.hs = torch.empty(T, max(lay.Is, 1), dtype=torch.bfloat16, device=self.dev)
             self.shared_out = torch.empty(T, lay.H, dtype=torch.bfloat16, device=self.dev) if lay.Is else None
             nd = C.c_size_t()
@@ -333,9 +341,12 @@ class EPMoELayer:
                 Tm = mb.t1 - mb.t0
                 xp = x2.data_ptr() + mb.t0 * H2
                 with torch.cuda.stream(mb.stream):
+                    # tables other ranks write during the dispatch: reset before this rank joins the count
+                    # exchange, i.e. before any rank can dispatch
                     if self.dedup:
-                        # before this rank joins the count exchange, i.e. before any rank can dispatch
                         L.check(lib.mg_ep_clear_duplicates(h, mb.own[2], mb.cap, st))
+                    if self.push_return:
+                        L.check(lib.mg_ep_clear_duplicates(h, mb.own[3], mb.cap, st))
                     L.check(lib.mg_gate_logits(h, xp, lay.gate_w.data_ptr(), Tm, mb.logits.data_ptr(), st))
                     L.check(lib.mg_route_topk(h, mb.logits.data_ptr(), _ptr(lay.bias), Tm, mb.idx.data_ptr(),
                                               mb.w.data_ptr(), st))
@@ -352,7 +363,10 @@ class EPMoELayer:
                                                   self.shared_out.data_ptr(), self._side.cuda_stream))
                     if sent is not None:
                         mb.stream.wait_event(sent)
-                    if self.dedup:
+                    if self.push_return:
+                        L.check(lib.mg_ep_dispatch_back(h, xp, mb.dst.data_ptr(), Tm, mb.peer_recv,
+                                                        mb.peer_dup if self.dedup else None, mb.peer_back, st))
+                    elif self.dedup:
                         L.check(lib.mg_ep_dispatch_dedup(h, xp, mb.dst.data_ptr(), Tm, mb.peer_recv, mb.peer_dup, st))
                     else:
                         L.check(lib.mg_ep_dispatch(h, xp, mb.dst.data_ptr(), Tm, mb.peer_recv, st))
@@ -368,9 +382,15 @@ class EPMoELayer:
                 with torch.cuda.stream(mb.stream):
                     if prev is not None:
                         mb.stream.wait_event(prev)   # also orders the reuse of the de-quantised weights
-                    L.check(lib.mg_expert_ffn(h, mb.own[0], mb.recv_pad.data_ptr(), mb.recv_counts.data_ptr(),
-                                              mb.cap, lay.packed.data_ptr(), mb.h_buf.data_ptr(), mb.own[1],
-                                              _ptr(self.deq), mb.stream.cuda_stream))
+                    if self.push_return:
+                        L.check(lib.mg_ep_expert_ffn_return(h, mb.own[0], mb.recv_pad.data_ptr(),
+                                                            mb.recv_counts.data_ptr(), mb.cap, lay.packed.data_ptr(),
+                                                            mb.h_buf.data_ptr(), mb.own[1], _ptr(self.deq), mb.own[3],
+                                                            mb.peer_ret, self.return_parts, mb.stream.cuda_stream))
+                    else:
+                        L.check(lib.mg_expert_ffn(h, mb.own[0], mb.recv_pad.data_ptr(), mb.recv_counts.data_ptr(),
+                                                  mb.cap, lay.packed.data_ptr(), mb.h_buf.data_ptr(), mb.own[1],
+                                                  _ptr(self.deq), mb.stream.cuda_stream))
                     prev = torch.cuda.Event()
                     prev.record(mb.stream)
                     self._barrier(mb)                # all owners' out_rows of this micro-batch are complete
@@ -381,8 +401,13 @@ class EPMoELayer:
                     if lay.Is:
                         mb.stream.wait_stream(self._side)
                     sh = self.shared_out.data_ptr() + mb.t0 * H2 if lay.Is else None
-                    L.check(lib.mg_ep_combine(h, mb.peer_out, mb.dst.data_ptr(), mb.idx.data_ptr(), mb.w.data_ptr(),
-                                              sh, mb.t1 - mb.t0, y.data_ptr() + mb.t0 * H2, mb.stream.cuda_stream))
+                    if self.push_return:
+                        L.check(lib.mg_ep_combine_slots(h, mb.own[4], mb.dst.data_ptr(), mb.idx.data_ptr(),
+                                                        mb.w.data_ptr(), sh, mb.t1 - mb.t0, y.data_ptr() + mb.t0 * H2,
+                                                        mb.stream.cuda_stream))
+                    else:
+                        L.check(lib.mg_ep_combine(h, mb.peer_out, mb.dst.data_ptr(), mb.idx.data_ptr(), mb.w.data_ptr(),
+                                                  sh, mb.t1 - mb.t0, y.data_ptr() + mb.t0 * H2, mb.stream.cuda_stream))
             self._mark(evs, s0)
             if self.deq is not None and _last:
                 L.check(lib.mg_set_option(h, L.OPT_KEEP_DEQUANT, 0))

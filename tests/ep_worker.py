@@ -126,6 +126,13 @@ def gpu_ep_worker(rank, world, port, spec, T_global, seed, result):
     y_plain = ep.forward(x)
     torch.cuda.synchronize()
     same = bool(torch.equal(y_plain.cpu().view(torch.int16), ys[0].view(torch.int16)))
+    ep.push_return = False                               # the combine gathers from the owners (no pushed return)
+    for dd in (False, True):
+        ep.dedup = dd
+        y_pull = ep.forward(x)
+        torch.cuda.synchronize()
+        same = same and bool(torch.equal(y_pull.cpu().view(torch.int16), ys[0].view(torch.int16)))
+    ep.push_return = True
     # host buffers in two parts per rank (last: it re-allocates the shared buffers for the part size)
     ep.dedup = True
     yh = ep.forward_host(x.cpu().pin_memory(), n_chunks=2)

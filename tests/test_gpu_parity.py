@@ -568,9 +568,10 @@ def test_bounded_wait_gives_up_and_reports(built_lib):
     assert O.rel_l2(y.cpu().float(), O.layer_forward(spec, x, W, gold_fp32=True)["y"]) <= TOL_LAYER
 
 
+@pytest.mark.parametrize("push", [False, True])
 @pytest.mark.parametrize("dedup", [False, True])
 @pytest.mark.parametrize("n_ranks", [2, 4])
-def test_expert_parallel_ranks_emulated_on_one_gpu(built_lib, n_ranks, dedup):
+def test_expert_parallel_ranks_emulated_on_one_gpu(built_lib, n_ranks, dedup, push):
     """The expert-parallel kernels (layout, peer scatter, peer gather) run for every rank in turn in
     one process, the 'peer' buffers being ordinary allocations of this GPU.  The result must equal
     the single-GPU forward bit for bit, and the layout must equal its host restatement."""
@@ -596,6 +597,11 @@ def test_expert_parallel_ranks_emulated_on_one_gpu(built_lib, n_ranks, dedup):
     i32 = dict(dtype=torch.int32, device=DEV)
     dupt = [torch.zeros(cap, **i32) for _ in range(n_ranks)]
     peer_dup = (C.c_void_p * n_ranks)(*[t.data_ptr() for t in dupt])
+    # pushed return: a return table per owner and a return buffer per token owner
+    backt = [torch.full((cap,), -1, **i32) for _ in range(n_ranks)]
+    rett = [torch.zeros(Tl * k, H, dtype=torch.bfloat16, device=DEV) for _ in range(n_ranks)]
+    peer_back = (C.c_void_p * n_ranks)(*[t.data_ptr() for t in backt])
+    peer_ret = (C.c_void_p * n_ranks)(*[t.data_ptr() for t in rett])
     for r, lay in enumerate(ranks):
         L.check(lib.mg_ep_clear_duplicates(lay._h, dupt[r].data_ptr(), cap, st))
     idx, w, counts, plan_ws = [], [], [], []
@@ -614,7 +620,10 @@ def test_expert_parallel_ranks_emulated_on_one_gpu(built_lib, n_ranks, dedup):
         d = torch.empty(Tl, k, **i32); c = torch.empty(El, **i32); p = torch.empty(El + 1, **i32)
         L.check(lib.mg_ep_place(lay._h, idx[r].data_ptr(), Tl, counts_all.data_ptr(), cap, plan_ws[r].data_ptr(),
                                 c.data_ptr(), p.data_ptr(), d.data_ptr(), st))
-        if dedup:
+        if push:
+            L.check(lib.mg_ep_dispatch_back(lay._h, xd[r * Tl:(r + 1) * Tl].data_ptr(), d.data_ptr(), Tl, peer_recv,
+                                            peer_dup if dedup else None, peer_back, st))
+        elif dedup:
             L.check(lib.mg_ep_dispatch_dedup(lay._h, xd[r * Tl:(r + 1) * Tl].data_ptr(), d.data_ptr(), Tl, peer_recv,
                                              peer_dup, st))
         else:
@@ -643,15 +652,25 @@ def test_expert_parallel_ranks_emulated_on_one_gpu(built_lib, n_ranks, dedup):
                 assert torch.equal(got[rows].view(torch.int16), x[toks].view(torch.int16))
     for r, lay in enumerate(ranks):
         hb = torch.zeros(cap, spec.inter, dtype=torch.bfloat16, device=DEV)
-        L.check(lib.mg_expert_ffn(lay._h, recv[r].data_ptr(), rp[r].data_ptr(), rc[r].data_ptr(), cap,
-                                  lay.packed.data_ptr(), hb.data_ptr(), outb[r].data_ptr(), None, st))
+        if push:
+            L.check(lib.mg_ep_expert_ffn_return(lay._h, recv[r].data_ptr(), rp[r].data_ptr(), rc[r].data_ptr(), cap,
+                                                lay.packed.data_ptr(), hb.data_ptr(), outb[r].data_ptr(), None,
+                                                backt[r].data_ptr(), peer_ret, 3, st))
+        else:
+            L.check(lib.mg_expert_ffn(lay._h, recv[r].data_ptr(), rp[r].data_ptr(), rc[r].data_ptr(), cap,
+                                      lay.packed.data_ptr(), hb.data_ptr(), outb[r].data_ptr(), None, st))
     ys = []
     for r, lay in enumerate(ranks):
         xs = xd[r * Tl:(r + 1) * Tl]
         sh = lay.shared_ffn(xs)
         y = torch.empty(Tl, H, dtype=torch.bfloat16, device=DEV)
-        L.check(lib.mg_ep_combine(lay._h, peer_out, dst[r].data_ptr(), idx[r].data_ptr(), w[r].data_ptr(),
-                                  sh.data_ptr(), Tl, y.data_ptr(), st))
+        if push:
+            torch.cuda.synchronize()            # every owner's pushes (on their return streams) have landed
+            L.check(lib.mg_ep_combine_slots(lay._h, rett[r].data_ptr(), dst[r].data_ptr(), idx[r].data_ptr(),
+                                            w[r].data_ptr(), sh.data_ptr(), Tl, y.data_ptr(), st))
+        else:
+            L.check(lib.mg_ep_combine(lay._h, peer_out, dst[r].data_ptr(), idx[r].data_ptr(), w[r].data_ptr(),
+                                      sh.data_ptr(), Tl, y.data_ptr(), st))
         ys.append(y)
     torch.cuda.synchronize()
     for lay in ranks:
