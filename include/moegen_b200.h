@@ -266,6 +266,22 @@ int mg_moe_forward(mg_handle h, const void* d_x, int64_t n_tokens,
                    const void* d_gate_w, const float* d_bias, const void* d_packed,
                    void* d_workspace, size_t workspace_bytes, void* d_y, void* stream);
 
+/* The layer on HOST buffers: x_host / y_host are [n_tokens, H] bf16 in host memory (pinned, for the copies
+ * to overlap).  Tokens are independent, so the batch goes through in chunks: chunk c+1 is copied in and
+ * chunk c-1 copied out on the library's copy streams while chunk c computes on `stream`; the first and
+ * last chunk are half of chunk_tokens (their copies are exposed), the ones between one and a half.  FP8
+ * layers in pre-dequantise mode de-quantise once for all chunks.  d_workspace holds the staging buffers
+ * and the forward's workspace: mg_host_workspace_bytes(h, n_tokens, chunk_tokens).  The call returns once
+ * everything is enqueued; `stream` is ordered after the last copy, so y_host is complete when the caller
+ * has synchronised it.  mg_host_chunk_plan gives the chunk sizes (no device needed).
+ * Replaces the host side the reference reaches through its engine: hidden states staged to the device,
+ * DeepseekV3MoE.forward, results staged back (moe_gen/engine.py:708-763 around modeling_deepseek_v3.py:614-626). */
+int mg_host_chunk_plan(int64_t n_tokens, int64_t chunk_tokens, int64_t* sizes, int32_t max_chunks, int32_t* n_chunks);
+int mg_host_workspace_bytes(mg_handle h, int64_t n_tokens, int64_t chunk_tokens, size_t* bytes);
+int mg_moe_forward_host(mg_handle h, const void* x_host, int64_t n_tokens, const void* d_gate_w, const float* d_bias,
+                        const void* d_packed, void* d_workspace, size_t workspace_bytes, void* y_host,
+                        int64_t chunk_tokens, void* stream);
+
 /* The same layer on router logits the caller computed: logits[T,E] fp32 replace the library's
  * router product, everything after it is mg_moe_forward.  The reference computes its logits with an
  * fp32 matrix product (F.linear(x.float(), W.float()), modeling_deepseek_v3.py:503-508); the

@@ -7,3 +7,4 @@ from .lib import (COMBINE_BF16_PROD, COMBINE_BF16_SEQ, COMBINE_FP32, GATE_SIGMOI
                   WEIGHT_FP8_BLOCK128, MoeGenError, load)
 from .layer import MoELayer  # noqa: F401
 from .patch import layer_from_deepseek, layer_from_mixtral, patch_decoder_layer, patch_moe_module  # noqa: F401
+from .batching import ModuleBatchingConfig, MoEBatcher  # noqa: F401

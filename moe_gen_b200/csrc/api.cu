@@ -205,6 +205,12 @@ int mg_destroy(mg_handle hh) {
     for (int i = 0; i <= MG_STAGE_COUNT; ++i)
       if (h->stage_ev[s][i]) cudaEventDestroy(h->stage_ev[s][i]);
   if (h->side) cudaStreamDestroy(h->side);
+  if (h->copy_in) {
+    cudaStreamDestroy(h->copy_in);
+    cudaStreamDestroy(h->copy_out);
+    for (int i = 0; i < 2; ++i) { cudaEventDestroy(h->ev_in[i]); cudaEventDestroy(h->ev_done[i]); cudaEventDestroy(h->ev_out[i]); }
+    cudaEventDestroy(h->ev_host);
+  }
   if (h->side2) cudaStreamDestroy(h->side2);
   if (h->side3) {
     cudaStreamDestroy(h->side3);
@@ -671,8 +677,9 @@ static int moe_forward_impl(mg_handle hh, const void* d_x, int64_t T, const void
   int launches = 0;
   if (h->stage_timing) MG_CUDA(cudaEventRecord(h->stage_ev[h->stage_calls % kStageSlots][0], st));
   int rc;
-  if (deq != nullptr && fp8_predequant(h, T) && !(h->opt_keep_dequant && h->deq_valid && h->deq_scratch == deq && h->deq_packed == d_packed &&
-                          h->deq_stream == st)) {
+  const bool deq_same = h->deq_scratch == deq && h->deq_packed == d_packed && h->deq_stream == st;
+  if (deq != nullptr && fp8_predequant(h, T) && !(h->opt_keep_dequant && h->deq_valid && deq_same) &&
+      !(h->deq_inflight && deq_same)) {
     // the weights do not depend on the routing: their de-quantisation starts now, beside the
     // router, plan and scatter kernels
     rc = start_dequant(h, d_packed, deq, st, &launches);
@@ -746,6 +753,154 @@ int mg_moe_forward_from_logits(mg_handle hh, const void* d_x, int64_t T, const f
                                const void* d_packed, void* d_ws, size_t ws_bytes, void* d_y, void* stream) {
   MG_REQUIRE(d_logits != nullptr || T == 0, MG_ERR_NULL, "mg_moe_forward_from_logits: null logits");
   return moe_forward_impl(hh, d_x, T, nullptr, d_bias, d_packed, d_ws, ws_bytes, nullptr, d_y, stream, d_logits);
+}
+
+// ---- host-buffer forward: chunk pipeline behind the C ABI ------------------------------------------
+// Chunk sizes: the copy-in of the first chunk and the copy-out of the last one cannot overlap with
+// compute, so those two are half a chunk; the ones between them are one and a half, because every
+// chunk streams all expert weights once.
+static int host_chunk_plan(int64_t T, int64_t chunk, int64_t* sizes, int max_n) {
+  int n = 0;
+  if (T <= 0) return 0;
+  const int64_t c = chunk < 1 ? 1 : chunk;
+  auto put = [&](int64_t v) { if (n < max_n) sizes[n] = v; ++n; };
+  if (T <= 2 * c) {
+    for (int64_t t0 = 0; t0 < T; t0 += c) put(T - t0 < c ? T - t0 : c);
+    return n;
+  }
+  const int64_t edge = c / 2 > 128 ? c / 2 : 128;
+  int64_t rest = T - 2 * edge;
+  const int64_t mid = c + c / 2;
+  const int64_t n_mid = (rest + mid - 1) / mid > 1 ? (rest + mid - 1) / mid : 1;
+  int64_t base = (rest + n_mid - 1) / n_mid;
+  base = (base + 127) / 128 * 128;
+  put(edge);
+  while (rest > 0) {
+    const int64_t v = base < rest ? base : rest;
+    put(v);
+    rest -= v;
+  }
+  put(edge);
+  return n;
+}
+constexpr int kMaxHostChunks = 1024;
+
+struct HostWs { size_t stage_bytes, fwd_off, fwd_bytes, total; int64_t cs; };
+static HostWs host_ws(Handle* h, int64_t T, int64_t chunk) {
+  int64_t sizes[kMaxHostChunks];
+  const int n = host_chunk_plan(T, chunk, sizes, kMaxHostChunks);
+  int64_t cs = 1;
+  for (int i = 0; i < n && i < kMaxHostChunks; ++i) cs = sizes[i] > cs ? sizes[i] : cs;
+  HostWs w;
+  w.cs = cs;
+  w.stage_bytes = (static_cast<size_t>(cs) * h->d.hidden * 2 + 255) / 256 * 256;     // one of 4: x in [2], y out [2]
+  w.fwd_off = 4 * w.stage_bytes;
+  // the FP8 mode is chosen for the whole batch, not per chunk
+  const int64_t keep = h->opt_batch_tokens;
+  if (h->d.weight_format == MG_WEIGHT_FP8_BLOCK128 && T > cs) h->opt_batch_tokens = T;
+  w.fwd_bytes = ws_layout(h, cs, 0).total;
+  h->opt_batch_tokens = keep;
+  w.total = w.fwd_off + w.fwd_bytes;
+  return w;
+}
+
+static int ensure_host_streams(Handle* h) {
+  if (h->copy_in) return MG_OK;
+  MG_CUDA(cudaStreamCreateWithFlags(&h->copy_in, cudaStreamNonBlocking));
+  MG_CUDA(cudaStreamCreateWithFlags(&h->copy_out, cudaStreamNonBlocking));
+  for (int i = 0; i < 2; ++i) {
+    MG_CUDA(cudaEventCreateWithFlags(&h->ev_in[i], cudaEventDisableTiming));
+    MG_CUDA(cudaEventCreateWithFlags(&h->ev_done[i], cudaEventDisableTiming));
+    MG_CUDA(cudaEventCreateWithFlags(&h->ev_out[i], cudaEventDisableTiming));
+  }
+  MG_CUDA(cudaEventCreateWithFlags(&h->ev_host, cudaEventDisableTiming));
+  return MG_OK;
+}
+
+int mg_host_chunk_plan(int64_t n_tokens, int64_t chunk_tokens, int64_t* sizes, int32_t max_chunks, int32_t* n_chunks) {
+  MG_REQUIRE(n_chunks && (sizes || max_chunks == 0), MG_ERR_NULL, "mg_host_chunk_plan: null argument");
+  MG_REQUIRE(n_tokens >= 0 && chunk_tokens >= 1 && max_chunks >= 0, MG_ERR_SHAPE, "mg_host_chunk_plan: bad size");
+  *n_chunks = host_chunk_plan(n_tokens, chunk_tokens, sizes, max_chunks);
+  return MG_OK;
+}
+
+int mg_host_workspace_bytes(mg_handle hh, int64_t n_tokens, int64_t chunk_tokens, size_t* bytes) {
+  Handle* h = check(hh);
+  if (!h) return MG_ERR_STATE;
+  MG_REQUIRE(bytes, MG_ERR_NULL, "null argument");
+  MG_REQUIRE(n_tokens >= 0 && chunk_tokens >= 1, MG_ERR_SHAPE, "mg_host_workspace_bytes: bad size");
+  *bytes = host_ws(h, n_tokens, chunk_tokens).total;
+  return MG_OK;
+}
+
+int mg_moe_forward_host(mg_handle hh, const void* x_host, int64_t T, const void* d_gate_w, const float* d_bias,
+                        const void* d_packed, void* d_ws, size_t ws_bytes, void* y_host, int64_t chunk_tokens,
+                        void* stream) {
+  Handle* h = check(hh);
+  if (!h) return MG_ERR_STATE;
+  MG_REQUIRE(T >= 0 && chunk_tokens >= 1, MG_ERR_SHAPE, "mg_moe_forward_host: bad size");
+  if (T == 0) { h->last_launches = 0; return MG_OK; }
+  MG_REQUIRE(x_host && y_host && d_gate_w && d_packed && d_ws, MG_ERR_NULL, "mg_moe_forward_host: null pointer");
+  int64_t sizes[kMaxHostChunks];
+  const int n = host_chunk_plan(T, chunk_tokens, sizes, kMaxHostChunks);
+  MG_REQUIRE(n <= kMaxHostChunks, MG_ERR_LIMIT, "more than %d chunks: raise chunk_tokens", kMaxHostChunks);
+  const HostWs W = host_ws(h, T, chunk_tokens);
+  MG_REQUIRE(ws_bytes >= W.total, MG_ERR_WORKSPACE, "workspace %zu bytes < %zu needed (mg_host_workspace_bytes)", ws_bytes,
+             W.total);
+  int rc = ensure_host_streams(h);
+  if (rc != MG_OK) return rc;
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  uint8_t* ws = static_cast<uint8_t*>(d_ws);
+  uint8_t* xin[2] = {ws, ws + W.stage_bytes};
+  uint8_t* yout[2] = {ws + 2 * W.stage_bytes, ws + 3 * W.stage_bytes};
+  const size_t row = static_cast<size_t>(h->d.hidden) * 2;
+  // the copy streams start after whatever the caller's stream holds
+  MG_CUDA(cudaEventRecord(h->ev_host, st));
+  MG_CUDA(cudaStreamWaitEvent(h->copy_in, h->ev_host, 0));
+  MG_CUDA(cudaStreamWaitEvent(h->copy_out, h->ev_host, 0));
+  // one de-quantisation (pre-dequantise mode) serves every chunk of this batch
+  const int64_t keep_batch = h->opt_batch_tokens;
+  const int keep_deq = h->opt_keep_dequant;
+  if (h->d.weight_format == MG_WEIGHT_FP8_BLOCK128 && T > W.cs) h->opt_batch_tokens = T;
+  h->opt_keep_dequant = 1;
+  h->deq_valid = false;
+  h->deq_inflight = false;
+  int launches = 0;
+  if (fp8_predequant(h, W.cs)) {
+    // the weights do not depend on the input: their de-quantisation starts now, beside the first copy-in
+    const WsLayout L = ws_layout(h, W.cs, 0);
+    rc = start_dequant(h, d_packed, ws + W.fwd_off + L.off[WS_DEQ], st, &launches);
+    if (rc != MG_OK) return rc;
+  }
+  int64_t t0 = 0;
+  for (int c = 0; c < n && rc == MG_OK; ++c) {
+    const int b = c & 1;
+    const int64_t m = sizes[c];
+    if (c >= 2) MG_CUDA(cudaStreamWaitEvent(h->copy_in, h->ev_done[b], 0));      // chunk c-2 has consumed this buffer
+    MG_CUDA(cudaMemcpyAsync(xin[b], static_cast<const uint8_t*>(x_host) + t0 * row, m * row, cudaMemcpyHostToDevice,
+                            h->copy_in));
+    MG_CUDA(cudaEventRecord(h->ev_in[b], h->copy_in));
+    MG_CUDA(cudaStreamWaitEvent(st, h->ev_in[b], 0));
+    if (c >= 2) MG_CUDA(cudaStreamWaitEvent(st, h->ev_out[b], 0));               // chunk c-2's result has left
+    rc = moe_forward_impl(hh, xin[b], m, d_gate_w, d_bias, d_packed, ws + W.fwd_off, W.fwd_bytes, nullptr, yout[b], stream);
+    launches += h->last_launches;
+    if (rc != MG_OK) break;
+    MG_CUDA(cudaEventRecord(h->ev_done[b], st));
+    MG_CUDA(cudaStreamWaitEvent(h->copy_out, h->ev_done[b], 0));
+    MG_CUDA(cudaMemcpyAsync(static_cast<uint8_t*>(y_host) + t0 * row, yout[b], m * row, cudaMemcpyDeviceToHost,
+                            h->copy_out));
+    MG_CUDA(cudaEventRecord(h->ev_out[b], h->copy_out));
+    t0 += m;
+  }
+  h->opt_batch_tokens = keep_batch;
+  h->opt_keep_dequant = keep_deq;
+  h->deq_valid = false;
+  if (rc != MG_OK) return rc;
+  // the caller's stream ends after the last copies: synchronising it means y_host is complete
+  MG_CUDA(cudaStreamWaitEvent(st, h->ev_out[(n - 1) & 1], 0));
+  if (n >= 2) MG_CUDA(cudaStreamWaitEvent(st, h->ev_out[(n - 2) & 1], 0));
+  h->last_launches = launches;
+  return MG_OK;
 }
 
 int mg_rmsnorm(mg_handle hh, const void* d_x, const void* d_weight, float eps, int64_t T, void* d_out,

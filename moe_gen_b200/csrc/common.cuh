@@ -70,6 +70,8 @@ struct Handle {
   int opt_ring_persist;   // ring accesses carry the L2 evict_last policy (needs an L2 set-aside, mg_l2_set_aside)
   cudaStream_t side;      // de-quantisation runs here, one chunk of experts ahead of the GEMMs
   cudaEvent_t ev_entry, ev_w13[kDequantChunks], ev_w2[kDequantChunks];
+  cudaStream_t copy_in, copy_out;   // host-buffer forward: copies of the chunks either side of the compute
+  cudaEvent_t ev_in[2], ev_done[2], ev_out[2], ev_host;
   cudaStream_t side3;     // expert-parallel return: pushes of finished expert parts run here beside the GEMMs
   cudaEvent_t ev_part[kDequantChunks], ev_ret;
   cudaStream_t side2;     // the shared expert's GEMMs run here beside the routing and scatter kernels

@@ -132,6 +132,7 @@ class MoELayer:
         self.options[option] = value
         if option != L.OPT_KEEP_DEQUANT:
             self._ws, self._ws_tokens = None, -1    # workspace layout may depend on options
+            self._hws = None
 
     def set_stage_timing(self, enable: bool):
         L.check(self.lib.mg_set_stage_timing(self._h, int(enable)))
@@ -224,74 +225,39 @@ class MoELayer:
 
     @staticmethod
     def host_chunks(T: int, chunk_tokens: int) -> list:
-        """Token counts of the chunks forward_host uses.  The copy-in of the first chunk and the
-        copy-out of the last one cannot overlap with compute, so those two are half a chunk; the ones
-        between them are one and a half, because every chunk streams all expert weights once."""
-        c = max(1, chunk_tokens)
-        if T <= 2 * c:
-            return [min(c, T - t0) for t0 in range(0, max(T, 1), c)] if T > 0 else []
-        edge = max(128, c // 2)
-        rest = T - 2 * edge
-        n_mid = max(1, -(-rest // (c + c // 2)))
-        base = -(-rest // n_mid)
-        base = -(-base // 128) * 128
-        mids = []
-        while rest > 0:
-            mids.append(min(base, rest))
-            rest -= mids[-1]
-        return [edge] + mids + [edge]
+        """Token counts of the chunks the host-buffer forward uses (mg_host_chunk_plan): the copy-in of
+        the first chunk and the copy-out of the last one cannot overlap with compute, so those two are
+        half a chunk; the ones between them are one and a half, because every chunk streams all expert
+        weights once."""
+        lib = L.load()
+        n = C.c_int32()
+        L.check(lib.mg_host_chunk_plan(T, max(1, chunk_tokens), None, 0, C.byref(n)))
+        sizes = (C.c_int64 * max(n.value, 1))()
+        L.check(lib.mg_host_chunk_plan(T, max(1, chunk_tokens), sizes, n.value, C.byref(n)))
+        return [int(v) for v in sizes[:n.value]]
 
     def forward_host(self, x_host: torch.Tensor, y_host: Optional[torch.Tensor] = None,
                      chunk_tokens: int = 8192) -> torch.Tensor:
-        """Host-buffer entry: x_host [T,H] bf16 in (preferably pinned) host memory -> y_host.
-        Tokens are independent, so chunks (host_chunks) are copied in, computed and copied out on
-        three streams; returns after the last copy has finished."""
+        """Host-buffer entry (mg_moe_forward_host): x_host [T,H] bf16 in (preferably pinned) host memory
+        -> y_host.  The library copies chunks in, computes and copies out on three streams; returns
+        after the last copy has finished."""
         T = x_host.shape[0]
+        if x_host.dtype != torch.bfloat16 or not x_host.is_contiguous() or x_host.is_cuda:
+            raise ValueError("x_host: expected a contiguous bfloat16 tensor in host memory")
         if y_host is None:
             y_host = torch.empty_like(x_host, pin_memory=x_host.is_pinned())
-        sizes = self.host_chunks(T, chunk_tokens)
-        cs = max(sizes) if sizes else 1
+        if T == 0:
+            return y_host
         with torch.cuda.device(self.device):
-            if getattr(self, "_hb", None) is None or self._hb[0].shape[0] < cs:
-                self._hb = [torch.empty(cs, self.H, dtype=torch.bfloat16, device=self.device) for _ in range(4)]
-                self._hs = [torch.cuda.Stream(), torch.cuda.Stream()]
-            xin, yout = self._hb[:2], self._hb[2:]
-            s_in, s_out = self._hs
-            comp = torch.cuda.current_stream()
-            ev_in = [torch.cuda.Event() for _ in range(2)]
-            ev_done = [torch.cuda.Event() for _ in range(2)]
-            ev_out = [torch.cuda.Event() for _ in range(2)]
-            s_in.wait_stream(comp)
-            s_out.wait_stream(comp)
-            # the FP8 mode is chosen for the whole batch, not per chunk
-            hint = self.desc.weight_format == L.WEIGHT_FP8_BLOCK128 and T > cs
-            if hint:
-                self.set_option(L.OPT_BATCH_TOKENS, T)
-            self._workspace(cs)
-            # FP8 layers in pre-dequantise mode: de-quantise once for all chunks of this forward
-            self.set_option(L.OPT_KEEP_DEQUANT, 1)
-            t0 = 0
-            for c, n in enumerate(sizes):
-                b = c & 1
-                if c >= 2:
-                    s_in.wait_event(ev_done[b])
-                with torch.cuda.stream(s_in):
-                    xin[b][:n].copy_(x_host[t0:t0 + n], non_blocking=True)
-                    ev_in[b].record(s_in)
-                comp.wait_event(ev_in[b])
-                if c >= 2:
-                    comp.wait_event(ev_out[b])
-                self.forward(xin[b][:n], out=yout[b][:n])
-                ev_done[b].record(comp)
-                s_out.wait_event(ev_done[b])
-                with torch.cuda.stream(s_out):
-                    y_host[t0:t0 + n].copy_(yout[b][:n], non_blocking=True)
-                    ev_out[b].record(s_out)
-                t0 += n
-            self.set_option(L.OPT_KEEP_DEQUANT, 0)
-            s_out.synchronize()
-            if hint:
-                self.set_option(L.OPT_BATCH_TOKENS, 0)
+            n = C.c_size_t()
+            L.check(self.lib.mg_host_workspace_bytes(self._h, T, chunk_tokens, C.byref(n)))
+            if getattr(self, "_hws", None) is None or self._hws.numel() < n.value:
+                self._hws = None
+                self._hws = torch.empty(n.value, dtype=torch.uint8, device=self.device)
+            L.check(self.lib.mg_moe_forward_host(self._h, x_host.data_ptr(), T, self.gate_w.data_ptr(), _ptr(self.bias),
+                                                 self.packed.data_ptr(), self._hws.data_ptr(), self._hws.numel(),
+                                                 y_host.data_ptr(), chunk_tokens, self._stream()))
+            torch.cuda.current_stream().synchronize()
         return y_host
 
     # ------------------------------------------------------------------ stages

@@ -63,6 +63,9 @@ SIGNATURES = {
     "mg_shared_ffn": [_vp, _vp, _i64, _vp, _vp, _vp, _vp],
     "mg_combine": [_vp, _vp, _vp, _vp, _vp, _vp, _i64, _vp, _vp],
     "mg_moe_forward": [_vp, _vp, _i64, _vp, _vp, _vp, _vp, _sz, _vp, _vp],
+    "mg_host_chunk_plan": [_i64, _i64, _P(_i64), _i32, _P(_i32)],
+    "mg_host_workspace_bytes": [_vp, _i64, _i64, _P(_sz)],
+    "mg_moe_forward_host": [_vp, _vp, _i64, _vp, _vp, _vp, _vp, _sz, _vp, _i64, _vp],
     "mg_moe_forward_from_logits": [_vp, _vp, _i64, _vp, _vp, _vp, _vp, _sz, _vp, _vp],
     "mg_workspace_ptr": [_vp, _vp, _i64, _i64, _i32, _P(_vp)],
     "mg_selftest_wait_timeout": [_vp, _i32, _vp],

@@ -115,7 +115,7 @@ def gpu_ep_worker(rank, world, port, spec, T_global, seed, result):
     Tl = T_global // world
     dev = f"cuda:{rank}"
     layer = make_layer(spec, W, dev, rank, world)
-    ep = EPMoELayer(layer)
+    ep = EPMoELayer(layer, push_return=True)             # owners push results home; the pulled return follows below
     x = x_all[rank * Tl:(rank + 1) * Tl].to(dev)
     ys = []
     for _ in range(2):                                   # twice: buffers are reused across forwards
