@@ -13,7 +13,7 @@ CSRC = os.path.join(PKG, "csrc")
 LIB = os.path.join(PKG, "libmoegen_b200.so")
 SOURCES = ["api.cu", "route.cu", "pack.cu", "gemm.cu", "ep.cu"]
 NVCC_FLAGS = ["-std=c++17", "-O3", "-lineinfo", "-gencode", "arch=compute_100a,code=sm_100a",
-              "-Xcompiler", "-fPIC", "-shared", "-cudart", "static"]
+              "-Xcompiler", "-fPIC", "-shared", "-cudart", "static", "-ldl"]
 
 
 def _stale(target: str, deps) -> bool:

@@ -4,11 +4,24 @@
 
 #include <new>
 
+#include <nvtx3/nvToolsExt.h>
+#include <stdlib.h>
+
 #include "common.cuh"
 
 namespace mg {
 
 static thread_local char g_err[512] = "";
+
+static bool log_calls() {
+  static const bool on = [] { const char* v = getenv("MG_LOG"); return v != nullptr && v[0] == '1'; }();
+  return on;
+}
+CallTrace::CallTrace(const char* name, long long n) {
+  nvtxRangePushA(name);
+  if (log_calls()) fprintf(stderr, "[moegen_b200] %s n=%lld\n", name, n);
+}
+CallTrace::~CallTrace() { nvtxRangePop(); }
 
 void set_error(const char* fmt, ...) {
   va_list ap;
@@ -285,6 +298,7 @@ int mg_padded_rows(mg_handle hh, int64_t n_rows, int64_t* padded) {
 
 int mg_pack_expert(mg_handle hh, int32_t local_expert, const void* d_gate, const void* d_up, const void* d_down,
                    const float* gs, const float* us, const float* ds, void* d_packed, void* stream) {
+  MG_TRACE("mg_pack_expert", local_expert);
   Handle* h = check(hh);
   if (!h) return MG_ERR_STATE;
   MG_REQUIRE(d_gate && d_up && d_down && d_packed, MG_ERR_NULL, "mg_pack_expert: null pointer");
@@ -296,12 +310,14 @@ int mg_pack_expert(mg_handle hh, int32_t local_expert, const void* d_gate, const
 
 int mg_dequant_fp8_block128(const void* d_q, const float* d_scale_inv, int64_t rows, int64_t cols, void* d_out,
                             void* stream) {
+  MG_TRACE("mg_dequant_fp8_block128", rows);
   MG_REQUIRE(d_q && d_scale_inv && d_out, MG_ERR_NULL, "mg_dequant_fp8_block128: null pointer");
   MG_REQUIRE(rows >= 0 && cols >= 0, MG_ERR_SHAPE, "negative size");
   return launch_dequant(d_q, d_scale_inv, rows, cols, d_out, static_cast<cudaStream_t>(stream));
 }
 
 int mg_gate_logits(mg_handle hh, const void* d_x, const void* d_gate_w, int64_t T, float* d_logits, void* stream) {
+  MG_TRACE("mg_gate_logits", T);
   Handle* h = check(hh);
   if (!h) return MG_ERR_STATE;
   MG_REQUIRE(d_x && d_gate_w && d_logits, MG_ERR_NULL, "mg_gate_logits: null pointer");
@@ -316,6 +332,7 @@ int mg_gate_logits(mg_handle hh, const void* d_x, const void* d_gate_w, int64_t 
 
 int mg_route_topk(mg_handle hh, const float* d_logits, const float* d_bias, int64_t T, int32_t* d_idx, float* d_w,
                   void* stream) {
+  MG_TRACE("mg_route_topk", T);
   Handle* h = check(hh);
   if (!h) return MG_ERR_STATE;
   MG_REQUIRE(d_logits && d_idx && d_w, MG_ERR_NULL, "mg_route_topk: null pointer");
@@ -335,6 +352,7 @@ int mg_plan_ws_bytes(mg_handle hh, int64_t T, size_t* bytes) {
 
 int mg_permute_plan(mg_handle hh, const int32_t* d_idx, int64_t T, int32_t expert_lo, int32_t n_plan,
                     int32_t* d_counts, int32_t* d_offsets, int32_t* d_pad, int32_t* d_dst, void* d_ws, void* stream) {
+  MG_TRACE("mg_permute_plan", T);
   Handle* h = check(hh);
   if (!h) return MG_ERR_STATE;
   MG_REQUIRE(d_idx && d_counts && d_offsets && d_pad && d_dst && d_ws, MG_ERR_NULL, "mg_permute_plan: null pointer");
@@ -346,6 +364,7 @@ int mg_permute_plan(mg_handle hh, const int32_t* d_idx, int64_t T, int32_t exper
 
 int mg_permute_plan_static(mg_handle hh, const int32_t* d_idx, int64_t T, int32_t expert_lo, int32_t n_plan,
                            int32_t* d_counts, int32_t* d_offsets, int32_t* d_pad, int32_t* d_dst, void* stream) {
+  MG_TRACE("mg_permute_plan_static", T);
   Handle* h = check(hh);
   if (!h) return MG_ERR_STATE;
   MG_REQUIRE(d_idx && d_counts && d_offsets && d_pad && d_dst, MG_ERR_NULL, "mg_permute_plan_static: null pointer");
@@ -356,6 +375,7 @@ int mg_permute_plan_static(mg_handle hh, const int32_t* d_idx, int64_t T, int32_
 }
 
 int mg_permute_rows(mg_handle hh, const void* d_x, const int32_t* d_dst, int64_t T, void* d_perm, void* stream) {
+  MG_TRACE("mg_permute_rows", T);
   Handle* h = check(hh);
   if (!h) return MG_ERR_STATE;
   MG_REQUIRE(d_x && d_dst && d_perm, MG_ERR_NULL, "mg_permute_rows: null pointer");
@@ -574,6 +594,7 @@ int expert_ffn_return(Handle* h, const void* perm_x, const int32_t* pad, const i
 extern "C" {
 
 int mg_dequant_start(mg_handle hh, const void* d_packed, void* d_dequant_ws, void* stream) {
+  MG_TRACE("mg_dequant_start", 0);
   Handle* h = check(hh);
   if (!h) return MG_ERR_STATE;
   MG_REQUIRE(d_packed && d_dequant_ws, MG_ERR_NULL, "mg_dequant_start: null pointer");
@@ -585,6 +606,7 @@ int mg_dequant_start(mg_handle hh, const void* d_packed, void* d_dequant_ws, voi
 int mg_expert_ffn(mg_handle hh, const void* d_perm_x, const int32_t* d_pad, const int32_t* d_counts,
                   int64_t n_rows_padded, const void* d_packed, void* d_h_buf, void* d_out_rows, void* d_deq,
                   void* stream) {
+  MG_TRACE("mg_expert_ffn", n_rows_padded);
   Handle* h = check(hh);
   if (!h) return MG_ERR_STATE;
   MG_REQUIRE(d_perm_x && d_pad && d_counts && d_packed && d_h_buf && d_out_rows, MG_ERR_NULL,
@@ -614,6 +636,7 @@ static int shared_ffn(Handle* h, const void* x, int64_t T, const void* packed, v
 
 int mg_shared_ffn(mg_handle hh, const void* d_x, int64_t T, const void* d_packed, void* d_hs, void* d_out,
                   void* stream) {
+  MG_TRACE("mg_shared_ffn", T);
   Handle* h = check(hh);
   if (!h) return MG_ERR_STATE;
   MG_REQUIRE(d_x && d_packed && d_hs && d_out, MG_ERR_NULL, "mg_shared_ffn: null pointer");
@@ -623,6 +646,7 @@ int mg_shared_ffn(mg_handle hh, const void* d_x, int64_t T, const void* d_packed
 
 int mg_combine(mg_handle hh, const void* d_out_rows, const int32_t* d_dst, const int32_t* d_idx, const float* d_w,
                const void* d_shared, int64_t T, void* d_y, void* stream) {
+  MG_TRACE("mg_combine", T);
   Handle* h = check(hh);
   if (!h) return MG_ERR_STATE;
   MG_REQUIRE(d_out_rows && d_dst && d_idx && d_w && d_y, MG_ERR_NULL, "mg_combine: null pointer");
@@ -746,11 +770,13 @@ static int moe_forward_impl(mg_handle hh, const void* d_x, int64_t T, const void
 
 int mg_moe_forward(mg_handle hh, const void* d_x, int64_t T, const void* d_gate_w, const float* d_bias,
                    const void* d_packed, void* d_ws, size_t ws_bytes, void* d_y, void* stream) {
+  MG_TRACE("mg_moe_forward", T);
   return moe_forward_impl(hh, d_x, T, d_gate_w, d_bias, d_packed, d_ws, ws_bytes, nullptr, d_y, stream);
 }
 
 int mg_moe_forward_from_logits(mg_handle hh, const void* d_x, int64_t T, const float* d_logits, const float* d_bias,
                                const void* d_packed, void* d_ws, size_t ws_bytes, void* d_y, void* stream) {
+  MG_TRACE("mg_moe_forward_from_logits", T);
   MG_REQUIRE(d_logits != nullptr || T == 0, MG_ERR_NULL, "mg_moe_forward_from_logits: null logits");
   return moe_forward_impl(hh, d_x, T, nullptr, d_bias, d_packed, d_ws, ws_bytes, nullptr, d_y, stream, d_logits);
 }
@@ -836,6 +862,7 @@ int mg_host_workspace_bytes(mg_handle hh, int64_t n_tokens, int64_t chunk_tokens
 int mg_moe_forward_host(mg_handle hh, const void* x_host, int64_t T, const void* d_gate_w, const float* d_bias,
                         const void* d_packed, void* d_ws, size_t ws_bytes, void* y_host, int64_t chunk_tokens,
                         void* stream) {
+  MG_TRACE("mg_moe_forward_host", T);
   Handle* h = check(hh);
   if (!h) return MG_ERR_STATE;
   MG_REQUIRE(T >= 0 && chunk_tokens >= 1, MG_ERR_SHAPE, "mg_moe_forward_host: bad size");
@@ -905,6 +932,7 @@ int mg_moe_forward_host(mg_handle hh, const void* x_host, int64_t T, const void*
 
 int mg_rmsnorm(mg_handle hh, const void* d_x, const void* d_weight, float eps, int64_t T, void* d_out,
                void* stream) {
+  MG_TRACE("mg_rmsnorm", T);
   Handle* h = check(hh);
   if (!h) return MG_ERR_STATE;
   MG_REQUIRE(T >= 0, MG_ERR_SHAPE, "negative token count");
@@ -917,6 +945,7 @@ int mg_rmsnorm(mg_handle hh, const void* d_x, const void* d_weight, float eps, i
 int mg_moe_block_forward(mg_handle hh, const void* d_hidden, const void* d_norm_weight, float eps, int64_t T,
                          const void* d_gate_w, const float* d_bias, const void* d_packed, void* d_xnorm,
                          void* d_ws, size_t ws_bytes, void* d_out, void* stream) {
+  MG_TRACE("mg_moe_block_forward", T);
   Handle* h = check(hh);
   if (!h) return MG_ERR_STATE;
   MG_REQUIRE(T >= 0, MG_ERR_SHAPE, "negative token count");

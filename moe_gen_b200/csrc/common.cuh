@@ -48,6 +48,15 @@ struct TensorMapCache {
   int used = 0, next = 0;
 };
 
+// Call tracing: an NVTX range around every entry point that does device work (visible to a profiler
+// that attaches; without one the calls cost a branch), and, when the environment variable MG_LOG is 1,
+// one line per call on stderr: name and the call's leading size.
+struct CallTrace {
+  CallTrace(const char* name, long long n);
+  ~CallTrace();
+};
+#define MG_TRACE(name, n) ::mg::CallTrace _mg_trace(name, static_cast<long long>(n))
+
 struct Handle {
   uint32_t magic;
   mg_layer_desc d;

@@ -48,6 +48,7 @@ int mg_ep_unimport(void* d_ptr) {
 
 int mg_ep_count(mg_handle hh, const int32_t* d_topk_idx, int64_t T, int32_t* d_counts, void* d_plan_ws,
                 void* stream) {
+  MG_TRACE("mg_ep_count", T);
   Handle* h = check_handle(hh);
   if (!h) return MG_ERR_STATE;
   MG_REQUIRE(d_counts && d_plan_ws && (T == 0 || d_topk_idx), MG_ERR_NULL, "mg_ep_count: null pointer");
@@ -57,6 +58,7 @@ int mg_ep_count(mg_handle hh, const int32_t* d_topk_idx, int64_t T, int32_t* d_c
 
 int mg_ep_place(mg_handle hh, const int32_t* d_topk_idx, int64_t T, const int32_t* d_counts_all, int64_t cap_rows,
                 void* d_plan_ws, int32_t* d_recv_counts, int32_t* d_recv_pad, int32_t* d_dst, void* stream) {
+  MG_TRACE("mg_ep_place", T);
   Handle* h = check_handle(hh);
   if (!h) return MG_ERR_STATE;
   MG_REQUIRE(d_counts_all && d_plan_ws && d_recv_counts && d_recv_pad && (T == 0 || (d_topk_idx && d_dst)),
@@ -83,6 +85,7 @@ static int gather_peers(const Handle* h, void* const* ptrs, PeerPtrs* out) {
 
 int mg_ep_dispatch(mg_handle hh, const void* d_x, const int32_t* d_dst, int64_t T, void* const* peer_recv,
                    void* stream) {
+  MG_TRACE("mg_ep_dispatch", T);
   Handle* h = check_handle(hh);
   if (!h) return MG_ERR_STATE;
   MG_REQUIRE(T >= 0, MG_ERR_SHAPE, "negative token count");
@@ -96,6 +99,7 @@ int mg_ep_dispatch(mg_handle hh, const void* d_x, const int32_t* d_dst, int64_t 
 
 int mg_ep_dispatch_dedup(mg_handle hh, const void* d_x, const int32_t* d_dst, int64_t T, void* const* peer_recv,
                          void* const* peer_dup, void* stream) {
+  MG_TRACE("mg_ep_dispatch_dedup", T);
   Handle* h = check_handle(hh);
   if (!h) return MG_ERR_STATE;
   MG_REQUIRE(T >= 0, MG_ERR_SHAPE, "negative token count");
@@ -111,6 +115,7 @@ int mg_ep_dispatch_dedup(mg_handle hh, const void* d_x, const int32_t* d_dst, in
 
 int mg_ep_dispatch_back(mg_handle hh, const void* d_x, const int32_t* d_dst, int64_t T, void* const* peer_recv,
                         void* const* peer_dup, void* const* peer_back, void* stream) {
+  MG_TRACE("mg_ep_dispatch_back", T);
   Handle* h = check_handle(hh);
   if (!h) return MG_ERR_STATE;
   MG_REQUIRE(T >= 0, MG_ERR_SHAPE, "negative token count");
@@ -133,6 +138,7 @@ int mg_ep_dispatch_back(mg_handle hh, const void* d_x, const int32_t* d_dst, int
 int mg_ep_expert_ffn_return(mg_handle hh, const void* d_recv_x, const int32_t* d_recv_pad, const int32_t* d_recv_counts,
                             int64_t cap_rows, const void* d_packed, void* d_h_buf, void* d_out_rows, void* d_dequant_ws,
                             const int32_t* d_back, void* const* peer_ret, int32_t n_parts, void* stream) {
+  MG_TRACE("mg_ep_expert_ffn_return", cap_rows);
   Handle* h = check_handle(hh);
   if (!h) return MG_ERR_STATE;
   MG_REQUIRE(d_recv_x && d_recv_pad && d_recv_counts && d_packed && d_h_buf && d_out_rows && d_back, MG_ERR_NULL,
@@ -150,6 +156,7 @@ int mg_ep_expert_ffn_return(mg_handle hh, const void* d_recv_x, const int32_t* d
 
 int mg_ep_combine_slots(mg_handle hh, const void* d_ret, const int32_t* d_dst, const int32_t* d_topk_idx,
                         const float* d_topk_w, const void* d_shared_out, int64_t T, void* d_y, void* stream) {
+  MG_TRACE("mg_ep_combine_slots", T);
   Handle* h = check_handle(hh);
   if (!h) return MG_ERR_STATE;
   MG_REQUIRE(T >= 0, MG_ERR_SHAPE, "negative token count");
@@ -168,6 +175,7 @@ int mg_ep_clear_duplicates(mg_handle hh, void* d_dup, int64_t cap_rows, void* st
 }
 
 int mg_ep_fill_duplicates(mg_handle hh, void* d_recv_x, const void* d_dup, int64_t cap_rows, void* stream) {
+  MG_TRACE("mg_ep_fill_duplicates", cap_rows);
   Handle* h = check_handle(hh);
   if (!h) return MG_ERR_STATE;
   MG_REQUIRE(d_recv_x && d_dup && cap_rows >= 0, MG_ERR_NULL, "mg_ep_fill_duplicates: bad argument");
@@ -177,6 +185,7 @@ int mg_ep_fill_duplicates(mg_handle hh, void* d_recv_x, const void* d_dup, int64
 
 int mg_ep_combine(mg_handle hh, void* const* peer_out, const int32_t* d_dst, const int32_t* d_topk_idx,
                   const float* d_topk_w, const void* d_shared_out, int64_t T, void* d_y, void* stream) {
+  MG_TRACE("mg_ep_combine", T);
   Handle* h = check_handle(hh);
   if (!h) return MG_ERR_STATE;
   MG_REQUIRE(T >= 0, MG_ERR_SHAPE, "negative token count");

@@ -54,6 +54,9 @@ class StreamedMoELayer:
         self._deq: Optional[torch.Tensor] = None
         self._shared_loaded = False
         self.last_groups_moved = 0
+        self.last_group_order: List[int] = []
+        self._counts_host = None
+        self._counts_event = None
 
     # ------------------------------------------------------------------ weights
     def set_router(self, gate_weight, bias=None):
@@ -90,19 +93,36 @@ class StreamedMoELayer:
             counts, offsets, pad, dst = lay.permute_plan(idx, 0, E)
             rows = (-(-T * k // 128) + E) * 128
             perm = torch.empty(rows, lay.H, dtype=torch.bfloat16, device=dev)
-            L.check(lib.mg_permute_rows(lay._h, x2.data_ptr(), dst.data_ptr(), T, perm.data_ptr(), st))
             hbuf = torch.empty(rows, lay.I, dtype=torch.bfloat16, device=dev)
             outr = torch.empty(rows, lay.H, dtype=torch.bfloat16, device=dev)
             shared = None
-            if lay.Is:
-                # before the slots start to rotate: slot 0 still holds whatever group was last there,
-                # its shared section is never overwritten by a group copy (see _copy_group)
-                shared = lay.shared_ffn(x2)
+            if not self.routing_aware:
+                L.check(lib.mg_permute_rows(lay._h, x2.data_ptr(), dst.data_ptr(), T, perm.data_ptr(), st))
+                if lay.Is:
+                    # before the slots start to rotate: slot 0 still holds whatever group was last there,
+                    # its shared section is never overwritten by a group copy (see _copy_group)
+                    shared = lay.shared_ffn(x2)
             todo = list(range(self.groups))
             if self.routing_aware:
-                per_group = counts.view(self.groups, n).sum(1).cpu()        # one small read-back
-                todo = [g for g in todo if int(per_group[g]) > 0]
+                # The order of the copies follows the routing: the rows per group travel to pinned host
+                # memory behind the plan kernels (a few hundred bytes, asynchronous); the host waits for that
+                # one event only, while the scatter and the shared expert's GEMMs keep the GPU busy.  Groups
+                # without rows are neither copied nor computed; the others go by falling row count, so that
+                # the long GEMMs run first and hide the copies of the groups behind them.
+                per_group = counts.view(self.groups, n).sum(1, dtype=torch.int32)
+                if self._counts_host is None:
+                    self._counts_host = torch.empty(self.groups, dtype=torch.int32).pin_memory()
+                    self._counts_event = torch.cuda.Event()
+                self._counts_host.copy_(per_group, non_blocking=True)
+                self._counts_event.record(comp)
+                L.check(lib.mg_permute_rows(lay._h, x2.data_ptr(), dst.data_ptr(), T, perm.data_ptr(), st))
+                if lay.Is:
+                    shared = lay.shared_ffn(x2)
+                self._counts_event.synchronize()
+                rows_of = self._counts_host.tolist()
+                todo = sorted((g for g in todo if rows_of[g] > 0), key=lambda g: (-rows_of[g], g))
             self.last_groups_moved = len(todo)
+            self.last_group_order = list(todo)
             # FP8: de-quantise a group ahead of its GEMMs when it sees many rows, else convert in the GEMM
             use_deq = self._deq_bytes > 0 and T * k >= 1024 * E
             if use_deq and self._deq is None:

@@ -43,6 +43,8 @@ def test_streamed_layer_equals_resident_layer(built_lib, fp8, group, slots):
     for _ in range(2):                                   # twice: the slots are reused across forwards
         y1 = got.forward(xd)
         assert torch.equal(y0.view(torch.int16), y1.view(torch.int16))
+    # and against the CPU oracle, not only against the resident layer
+    assert O.rel_l2(y1.cpu().float(), O.layer_forward(spec, x, W, gold_fp32=True)["y"]) <= 1e-2
     assert got.layer.device_status() == (0, 0)
     assert got.last_groups_moved == spec.n_experts // group
     assert got.forward(xd[:0]).shape == (0, spec.hidden)
@@ -58,3 +60,25 @@ def test_routing_aware_streaming_skips_groups_without_rows(built_lib):
     idx, _ = want.route_topk(want.gate_logits(xd))
     groups_hit = len(set((idx.cpu().view(-1) // 2).tolist()))
     assert got.last_groups_moved == groups_hit < 8
+
+
+def test_routing_aware_streaming_orders_the_copies_by_routed_rows(built_lib):
+    """The groups travel in the order of their routed row counts (largest first, ties by group id), as read
+    from the device-side plan; the result still equals the resident layer and the oracle."""
+    spec = O.LayerSpec(256, 128, 16, 4, 128, 4, 2, O.GATE_SIGMOID_NOAUX_TC, True, 2.5, O.WEIGHT_FP8_BLOCK128,
+                       O.COMBINE_FP32)
+    x, W = O.make_inputs(spec, 500, 31, zipf_alpha=1.2)  # skewed routing: the groups differ in size
+    want = make_layer(spec, W, DEV)
+    got = _streamed(spec, W, 4, 2, routing_aware=True)
+    xd = x.to(DEV)
+    y0 = want.forward(xd)
+    for _ in range(2):
+        y1 = got.forward(xd)
+        assert torch.equal(y0.view(torch.int16), y1.view(torch.int16))
+    assert O.rel_l2(y1.cpu().float(), O.layer_forward(spec, x, W, gold_fp32=True)["y"]) <= 1e-2
+    idx, _ = want.route_topk(want.gate_logits(xd))
+    per_group = torch.bincount(idx.cpu().view(-1).long() // 4, minlength=4).tolist()
+    expect = sorted((g for g in range(4) if per_group[g] > 0), key=lambda g: (-per_group[g], g))
+    assert got.last_group_order == expect
+    assert len(set(per_group)) > 1
+    assert got.layer.device_status() == (0, 0)
