@@ -361,18 +361,21 @@ int mg_ep_fill_duplicates(mg_handle h, void* d_recv_x, const void* d_dup, int64_
  *      writes, into the owner's return table at every pick's row, rank << 24 | (token * k + slot);
  *   2. mg_ep_expert_ffn_return is mg_expert_ffn whose down projection runs in n_parts parts of experts
  *      (the chunks of pre-dequantise mode when that is on): as soon as a part is done, its output rows are
- *      stored into the token owners' return buffers on a side stream while the next part computes;
- *      the call returns with `stream` ordered after the last store;
+ *      stored into the token owners' return buffers on a side stream while the next part computes
+ *      (rows of this rank's own tokens stay in d_out_rows); the call returns with `stream` ordered
+ *      after the last store;
  *   3. after a barrier among the ranks, mg_ep_combine_slots sums a token's k rows from its own rank's
- *      return buffer (d_dst only tells which picks were dropped): local, HBM-speed. */
+ *      return buffer, or from this rank's d_out_rows for picks of its own experts (d_dst tells which
+ *      is which and which picks were dropped): local, HBM-speed. */
 int mg_ep_dispatch_back(mg_handle h, const void* d_x, const int32_t* d_dst, int64_t n_tokens,
                         void* const* peer_recv, void* const* peer_dup, void* const* peer_back, void* stream);
 int mg_ep_expert_ffn_return(mg_handle h, const void* d_recv_x, const int32_t* d_recv_pad,
                             const int32_t* d_recv_counts, int64_t cap_rows, const void* d_packed, void* d_h_buf,
                             void* d_out_rows, void* d_dequant_ws, const int32_t* d_back, void* const* peer_ret,
                             int32_t n_parts, void* stream);
-int mg_ep_combine_slots(mg_handle h, const void* d_ret, const int32_t* d_dst, const int32_t* d_topk_idx,
-                        const float* d_topk_w, const void* d_shared_out, int64_t n_tokens, void* d_y, void* stream);
+int mg_ep_combine_slots(mg_handle h, const void* d_ret, const void* d_out_rows, const int32_t* d_dst,
+                        const int32_t* d_topk_idx, const float* d_topk_w, const void* d_shared_out, int64_t n_tokens,
+                        void* d_y, void* stream);
 
 /* peer_out[ep_size]: every rank's out_rows.  Replaces the return all_to_all and the
  * weighted sum (modeling_deepseek_v3.py:692-710). */

@@ -132,8 +132,8 @@ int launch_dispatch_rows(const Handle* h, const void* x, const int32_t* dst, int
                          const PeerPtrs& peers, const PeerPtrs* dups, const PeerPtrs* backs, cudaStream_t st);
 int launch_return_rows(const Handle* h, const void* out_rows, const int32_t* back, const int32_t* pad, int e_lo,
                        int e_n, const PeerPtrs& rets, cudaStream_t st);
-int launch_combine_slots(const Handle* h, const void* ret_rows, const int32_t* dst, const int32_t* idx, const float* w,
-                         const void* shared, int64_t T, void* y, cudaStream_t st);
+int launch_combine_slots(const Handle* h, const void* ret_rows, const void* own_out_rows, const int32_t* dst,
+                         const int32_t* idx, const float* w, const void* shared, int64_t T, void* y, cudaStream_t st);
 int launch_fill_duplicates(const Handle* h, void* rows, const int32_t* dup, int64_t n_rows, cudaStream_t st);
 int launch_combine_peers(const Handle* h, const PeerPtrs& peers, const int32_t* dst,
                          const int32_t* idx, const float* w, const void* shared, int64_t T, void* y,

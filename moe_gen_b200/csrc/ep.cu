@@ -154,15 +154,17 @@ int mg_ep_expert_ffn_return(mg_handle hh, const void* d_recv_x, const int32_t* d
                            hook, static_cast<cudaStream_t>(stream));
 }
 
-int mg_ep_combine_slots(mg_handle hh, const void* d_ret, const int32_t* d_dst, const int32_t* d_topk_idx,
-                        const float* d_topk_w, const void* d_shared_out, int64_t T, void* d_y, void* stream) {
+int mg_ep_combine_slots(mg_handle hh, const void* d_ret, const void* d_out_rows, const int32_t* d_dst,
+                        const int32_t* d_topk_idx, const float* d_topk_w, const void* d_shared_out, int64_t T, void* d_y,
+                        void* stream) {
   MG_TRACE("mg_ep_combine_slots", T);
   Handle* h = check_handle(hh);
   if (!h) return MG_ERR_STATE;
   MG_REQUIRE(T >= 0, MG_ERR_SHAPE, "negative token count");
   if (T == 0) return MG_OK;
-  MG_REQUIRE(d_ret && d_dst && d_topk_idx && d_topk_w && d_y, MG_ERR_NULL, "mg_ep_combine_slots: null pointer");
-  return launch_combine_slots(h, d_ret, d_dst, d_topk_idx, d_topk_w, d_shared_out, T, d_y,
+  MG_REQUIRE(d_ret && d_out_rows && d_dst && d_topk_idx && d_topk_w && d_y, MG_ERR_NULL, "mg_ep_combine_slots: null pointer");
+  MG_REQUIRE(h->d.ep_size <= kMaxPeers, MG_ERR_LIMIT, "ep_size %d > %d", h->d.ep_size, kMaxPeers);
+  return launch_combine_slots(h, d_ret, d_out_rows, d_dst, d_topk_idx, d_topk_w, d_shared_out, T, d_y,
                               static_cast<cudaStream_t>(stream));
 }
 

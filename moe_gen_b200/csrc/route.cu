@@ -539,18 +539,18 @@ int launch_dispatch_rows(const Handle* h, const void* x, const int32_t* dst, int
 
 // Owner side of the return: the output rows of local experts [e_lo, e_lo + e_n) go to the ranks their
 // tokens came from, each into row (token * k + slot) of that rank's return buffer, as the return table
-// says (rows without an entry are padding).  Plain 128-bit stores through the peer mappings; a warp per
+// says (rows without an entry are padding; rows of this rank's own tokens stay where they are).  Plain 128-bit stores through the peer mappings; a warp per
 // row, rows taken in a grid-stride loop because their number is only known on the device.
 __global__ void __launch_bounds__(256) return_rows_kernel(const uint4* __restrict__ out_rows,
                                                           const int32_t* __restrict__ back,
                                                           const int32_t* __restrict__ pad, int e_lo, int e_n,
-                                                          int vec_per_row, PeerPtrs rets) {
+                                                          int vec_per_row, PeerPtrs rets, int my_rank) {
   const int lane = threadIdx.x & 31;
   const int64_t row0 = pad[e_lo], row1 = pad[e_lo + e_n];
   const int64_t warps = static_cast<int64_t>(gridDim.x) * (blockDim.x >> 5);
   for (int64_t r = row0 + static_cast<int64_t>(blockIdx.x) * (blockDim.x >> 5) + (threadIdx.x >> 5); r < row1; r += warps) {
     const int32_t b = back[r];
-    if (b < 0) continue;
+    if (b < 0 || (b >> kPeerShift) == my_rank) continue;     // padding, or a token of this rank: it reads the row in place
     const uint4* src = out_rows + r * vec_per_row;
     uint4* dst = static_cast<uint4*>(rets.p[b >> kPeerShift]) + static_cast<int64_t>(b & kPeerRowMask) * vec_per_row;
     for (int v0 = 0; v0 < vec_per_row; v0 += 128) {
@@ -573,7 +573,7 @@ int launch_return_rows(const Handle* h, const void* out_rows, const int32_t* bac
                        int e_n, const PeerPtrs& rets, cudaStream_t st) {
   if (e_n <= 0) return MG_OK;
   return_rows_kernel<<<h->sm_count * 2, 256, 0, st>>>(static_cast<const uint4*>(out_rows), back, pad, e_lo, e_n,
-                                                      h->d.hidden / 8, rets);
+                                                      h->d.hidden / 8, rets, h->d.ep_rank);
   MG_CUDA(cudaGetLastError());
   return MG_OK;
 }
@@ -610,8 +610,9 @@ __device__ __forceinline__ float round_bf16(float f) {
   return __bfloat162float(__float2bfloat16_rn(f));
 }
 
-// by_slot: the rows lie at (token * k + slot) (the return buffer of the expert-parallel push); dst_row
-// then only says which picks exist (negative = dropped).
+// by_slot = rank + 1 (expert-parallel pushed return): a pick whose owner is another rank lies at row
+// (token * k + slot) of this rank's return buffer (bufs.p[owner] all point at it), a pick of this rank's own
+// experts is read in place from its out_rows (bufs.p[rank]); 0 = rows as dst_row says.
 template <int MODE, bool PEER>
 __global__ void __launch_bounds__(256) combine_kernel(PeerPtrs bufs,
                                                       const int32_t* __restrict__ dst_row,
@@ -628,7 +629,8 @@ __global__ void __launch_bounds__(256) combine_kernel(PeerPtrs bufs,
   float my_w = 0.f;
   if (lane < k) {
     my_dst = dst_row[t * k + lane];
-    if (by_slot && my_dst >= 0) my_dst = static_cast<int32_t>(t * k + lane);
+    if (by_slot > 0 && my_dst >= 0 && (my_dst >> kPeerShift) != by_slot - 1)
+      my_dst = (my_dst & ~kPeerRowMask) | static_cast<int32_t>(t * k + lane);
     my_w = topk_w[t * k + lane];
     if (MODE == MG_COMBINE_BF16_SEQ) my_e = topk_idx[t * k + lane];
     if (MODE != MG_COMBINE_FP32) my_w = round_bf16(my_w);
@@ -752,11 +754,12 @@ int launch_combine(const Handle* h, const void* out_rows, const int32_t* dst_row
   return launch_combine_impl<false>(h, bufs, dst_row, idx, w, shared, residual, T, y, st);
 }
 
-int launch_combine_slots(const Handle* h, const void* ret_rows, const int32_t* dst, const int32_t* idx, const float* w,
-                         const void* shared, int64_t T, void* y, cudaStream_t st) {
+int launch_combine_slots(const Handle* h, const void* ret_rows, const void* own_out_rows, const int32_t* dst,
+                         const int32_t* idx, const float* w, const void* shared, int64_t T, void* y, cudaStream_t st) {
   PeerPtrs bufs{};
-  bufs.p[0] = const_cast<void*>(ret_rows);
-  return launch_combine_impl<false>(h, bufs, dst, idx, w, shared, nullptr, T, y, st, 1);
+  for (int r = 0; r < h->d.ep_size && r < kMaxPeers; ++r) bufs.p[r] = const_cast<void*>(ret_rows);
+  bufs.p[h->d.ep_rank] = const_cast<void*>(own_out_rows);
+  return launch_combine_impl<true>(h, bufs, dst, idx, w, shared, nullptr, T, y, st, h->d.ep_rank + 1);
 }
 
 int launch_combine_peers(const Handle* h, const PeerPtrs& peers, const int32_t* dst,

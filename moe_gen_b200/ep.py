@@ -402,7 +402,7 @@ class EPMoELayer:
                         mb.stream.wait_stream(self._side)
                     sh = self.shared_out.data_ptr() + mb.t0 * H2 if lay.Is else None
                     if self.push_return:
-                        L.check(lib.mg_ep_combine_slots(h, mb.own[4], mb.dst.data_ptr(), mb.idx.data_ptr(),
+                        L.check(lib.mg_ep_combine_slots(h, mb.own[4], mb.own[1], mb.dst.data_ptr(), mb.idx.data_ptr(),
                                                         mb.w.data_ptr(), sh, mb.t1 - mb.t0, y.data_ptr() + mb.t0 * H2,
                                                         mb.stream.cuda_stream))
                     else:

@@ -666,7 +666,7 @@ def test_expert_parallel_ranks_emulated_on_one_gpu(built_lib, n_ranks, dedup, pu
         y = torch.empty(Tl, H, dtype=torch.bfloat16, device=DEV)
         if push:
             torch.cuda.synchronize()            # every owner's pushes (on their return streams) have landed
-            L.check(lib.mg_ep_combine_slots(lay._h, rett[r].data_ptr(), dst[r].data_ptr(), idx[r].data_ptr(),
+            L.check(lib.mg_ep_combine_slots(lay._h, rett[r].data_ptr(), outb[r].data_ptr(), dst[r].data_ptr(), idx[r].data_ptr(),
                                             w[r].data_ptr(), sh.data_ptr(), Tl, y.data_ptr(), st))
         else:
             L.check(lib.mg_ep_combine(lay._h, peer_out, dst[r].data_ptr(), idx[r].data_ptr(), w[r].data_ptr(),
