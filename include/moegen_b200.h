@@ -63,6 +63,9 @@ extern "C" {
 #define MG_DEV_OK             0
 #define MG_DEV_WAIT_TIMEOUT   1  /* a bounded mbarrier wait ran out; results invalid */
 #define MG_DEV_CAPACITY       2  /* expert-parallel receive buffer too small; detail = rank */
+#define MG_DEV_BOUNDS         3  /* checked build (-DMG_BOUNDS_CHECK) only: a row index read from a table lay outside
+                                    its buffer; the access was skipped; detail = 103 scatter, 104 combine,
+                                    105 duplicate fill, 106 pushed return */
 
 /* stages of mg_moe_forward, in launch order (mg_stage_times) */
 #define MG_STAGE_GATE_LOGITS   0
@@ -444,6 +447,12 @@ int mg_last_launch_count(mg_handle h, int32_t* launches);
  * outlives the streaming traffic beside it; it takes effect inside the part of L2 that the process has
  * set aside for such accesses (mg_l2_set_aside).  0 (default) = ordinary accesses. */
 #define MG_OPT_RING_PERSIST 8
+/* MG_OPT_ROWS_BOUND: rows of the expert-sorted buffers the caller hands to the stage-level entry points
+ * (mg_permute_rows, mg_combine, the expert-parallel dispatch and combine calls); 0 = not declared.  Only a
+ * library built with -DMG_BOUNDS_CHECK looks at it: its row-moving kernels then compare every row index they
+ * read from a table with this bound and report MG_DEV_BOUNDS instead of touching memory outside the buffer.
+ * mg_moe_forward sets its own bound. */
+#define MG_OPT_ROWS_BOUND 9
 /* MG_OPT_PAIR_GEMM: 1 = the bf16 expert GEMMs run on SM pairs (clusters of two CTAs,
  * tcgen05 cta_group::2, 256x256 tiles); 0 = one CTA per SM, 128x256 tiles. */
 #define MG_OPT_PAIR_GEMM   2

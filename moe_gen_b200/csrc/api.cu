@@ -183,6 +183,7 @@ int mg_create(const mg_layer_desc* desc, mg_handle* out) {
   h->opt_keep_dequant = false;
   h->opt_ring_bytes = static_cast<size_t>(56) << 20;
   h->opt_ring_persist = 0;
+  h->guard_rows = 0x7fffffffffffffffll;
   h->deq_valid = false;
   h->deq_inflight = false;
   h->deq_scratch = nullptr;
@@ -699,6 +700,9 @@ static int moe_forward_impl(mg_handle hh, const void* d_x, int64_t T, const void
   void* sh = d.inter_shared ? ws + L.off[WS_SHARED] : nullptr;
   void* deq = fp8_scratch_bytes(h, T * d.top_k) > 0 ? ws + L.off[WS_DEQ] : nullptr;
   int launches = 0;
+  const long long guard_keep = h->guard_rows;
+  h->guard_rows = padded_rows(h, T * d.top_k);     // what this call's dst_row entries may address
+  struct RestoreGuard { Handle* h; long long v; ~RestoreGuard() { h->guard_rows = v; } } restore_guard{h, guard_keep};
   if (h->stage_timing) MG_CUDA(cudaEventRecord(h->stage_ev[h->stage_calls % kStageSlots][0], st));
   int rc;
   const bool deq_same = h->deq_scratch == deq && h->deq_packed == d_packed && h->deq_stream == st;
@@ -980,6 +984,10 @@ int mg_set_option(mg_handle hh, int32_t option, int32_t value) {
     case MG_OPT_FP8_M256:
       MG_REQUIRE(value >= 0 && value <= 2, MG_ERR_CONFIG, "bad value %d", value);
       h->opt_fp8_m256 = value;
+      return MG_OK;
+    case MG_OPT_ROWS_BOUND:
+      MG_REQUIRE(value >= 0, MG_ERR_CONFIG, "bad value %d", value);
+      h->guard_rows = value > 0 ? value : 0x7fffffffffffffffll;
       return MG_OK;
     case MG_OPT_RING_PERSIST: h->opt_ring_persist = value != 0; return MG_OK;
     case MG_OPT_RING_BYTES:

@@ -75,6 +75,7 @@ struct Handle {
   int opt_fp8_m256;       // in-kernel FP8: 0 = 128-row tiles, 1 = 256-row tiles when experts are big, 2 = always
   bool opt_pair_gemm;     // bf16 expert GEMMs on SM pairs (tcgen05 cta_group::2)
   int opt_fp8_mode;       // MG_FP8_AUTO / MG_FP8_PREDEQUANT / MG_FP8_IN_KERNEL / MG_FP8_RING
+  long long guard_rows;   // bound the row-moving kernels check table entries against in a -DMG_BOUNDS_CHECK build
   size_t opt_ring_bytes;  // budget of the bf16 ring of MG_FP8_RING (it should stay resident in L2)
   int opt_ring_persist;   // ring accesses carry the L2 evict_last policy (needs an L2 set-aside, mg_l2_set_aside)
   cudaStream_t side;      // de-quantisation runs here, one chunk of experts ahead of the GEMMs
@@ -121,6 +122,22 @@ int launch_rmsnorm(const Handle* h, const void* x, const void* weight, float eps
                    cudaStream_t st);
 
 struct PeerPtrs { void* p[kMaxPeers]; };
+
+// Index guard of the row-moving kernels.  In a build with -DMG_BOUNDS_CHECK (the stand-in for a memory
+// checker on machines where none can run) every row index taken from a table is compared with the
+// bound the host knows; the first violation is recorded in the status word (MG_DEV_BOUNDS, detail =
+// which kernel) and the access is skipped, never trapped.  Other builds carry the struct and ignore it.
+struct Guard {
+  int32_t* status;
+  long long rows_bound;   // rows of the buffer the indices point into (LLONG_MAX = not declared)
+  int n_peers;
+};
+#ifdef MG_BOUNDS_CHECK
+#define MG_GUARD(ok, g, where) \
+  ((ok) ? true : ((atomicCAS((g).status, MG_DEV_OK, MG_DEV_BOUNDS) == MG_DEV_OK ? ((g).status[1] = (where)) : 0), false))
+#else
+#define MG_GUARD(ok, g, where) (true)
+#endif
 // expert-parallel return pushed from inside the expert FFN: after the down projection of each part of the
 // local experts, their output rows travel to the token owners' return buffers on a side stream
 struct ReturnHook {

@@ -432,11 +432,15 @@ template <bool PEER, bool DEDUP, bool BACK>
 __global__ void __launch_bounds__(256) permute_rows_kernel(const uint4* __restrict__ x,
                                                            const int32_t* __restrict__ dst_row,
                                                            int64_t T, int k, int vec_per_row,
-                                                           PeerPtrs bufs, PeerPtrs dups, PeerPtrs backs, int my_rank) {
+                                                           PeerPtrs bufs, PeerPtrs dups, PeerPtrs backs, int my_rank,
+                                                           Guard guard) {
   const int lane = threadIdx.x & 31;
   const int64_t t = static_cast<int64_t>(blockIdx.x) * (blockDim.x >> 5) + (threadIdx.x >> 5);
   if (t >= T) return;
   int32_t my_dst = lane < k ? dst_row[t * k + lane] : -1;
+  if (my_dst >= 0 && !MG_GUARD((PEER ? (my_dst & kPeerRowMask) : my_dst) < guard.rows_bound &&
+                               (!PEER || (my_dst >> kPeerShift) < guard.n_peers), guard, 103))
+    my_dst = -1;
   if (BACK && my_dst >= 0)
     static_cast<int32_t*>(backs.p[my_dst >> kPeerShift])[my_dst & kPeerRowMask] =
         (my_rank << kPeerShift) | static_cast<int32_t>(t * k + lane);
@@ -480,12 +484,13 @@ __global__ void __launch_bounds__(256) permute_rows_kernel(const uint4* __restri
 // the dispatch.
 __global__ void __launch_bounds__(256) fill_duplicate_rows_kernel(uint4* __restrict__ rows,
                                                                   const int32_t* __restrict__ dup,
-                                                                  int64_t n_rows, int vec_per_row) {
+                                                                  int64_t n_rows, int vec_per_row, Guard guard) {
   const int lane = threadIdx.x & 31;
   const int64_t r = static_cast<int64_t>(blockIdx.x) * (blockDim.x >> 5) + (threadIdx.x >> 5);
   if (r >= n_rows) return;
   const int32_t s = dup[r];
   if (s < 0) return;
+  if (!MG_GUARD(s < n_rows, guard, 105)) return;
   const uint4* src = rows + static_cast<int64_t>(s) * vec_per_row;
   uint4* dst = rows + r * vec_per_row;
   for (int v0 = 0; v0 < vec_per_row; v0 += 128) {
@@ -511,7 +516,8 @@ int launch_permute_rows(const Handle* h, const void* x, const int32_t* dst_row, 
   PeerPtrs bufs{};
   bufs.p[0] = perm_x;
   permute_rows_kernel<false, false, false><<<grid, block, 0, st>>>(static_cast<const uint4*>(x), dst_row, T,
-                                                                   h->d.top_k, h->d.hidden / 8, bufs, bufs, bufs, 0);
+                                                                   h->d.top_k, h->d.hidden / 8, bufs, bufs, bufs, 0,
+                                                                   Guard{h->d_status, h->guard_rows, 1});
   MG_CUDA(cudaGetLastError());
   return MG_OK;
 }
@@ -525,14 +531,15 @@ int launch_dispatch_rows(const Handle* h, const void* x, const int32_t* dst, int
   const int k = h->d.top_k, vpr = h->d.hidden / 8, me = h->d.ep_rank;
   const PeerPtrs& d = dups ? *dups : peers;
   const PeerPtrs& b = backs ? *backs : peers;
+  const Guard guard{h->d_status, h->guard_rows, h->d.ep_size};
   if (dups != nullptr && backs != nullptr)
-    permute_rows_kernel<true, true, true><<<grid, block, 0, st>>>(xs, dst, T, k, vpr, peers, d, b, me);
+    permute_rows_kernel<true, true, true><<<grid, block, 0, st>>>(xs, dst, T, k, vpr, peers, d, b, me, guard);
   else if (dups != nullptr)
-    permute_rows_kernel<true, true, false><<<grid, block, 0, st>>>(xs, dst, T, k, vpr, peers, d, b, me);
+    permute_rows_kernel<true, true, false><<<grid, block, 0, st>>>(xs, dst, T, k, vpr, peers, d, b, me, guard);
   else if (backs != nullptr)
-    permute_rows_kernel<true, false, true><<<grid, block, 0, st>>>(xs, dst, T, k, vpr, peers, d, b, me);
+    permute_rows_kernel<true, false, true><<<grid, block, 0, st>>>(xs, dst, T, k, vpr, peers, d, b, me, guard);
   else
-    permute_rows_kernel<true, false, false><<<grid, block, 0, st>>>(xs, dst, T, k, vpr, peers, d, b, me);
+    permute_rows_kernel<true, false, false><<<grid, block, 0, st>>>(xs, dst, T, k, vpr, peers, d, b, me, guard);
   MG_CUDA(cudaGetLastError());
   return MG_OK;
 }
@@ -544,13 +551,14 @@ int launch_dispatch_rows(const Handle* h, const void* x, const int32_t* dst, int
 __global__ void __launch_bounds__(256) return_rows_kernel(const uint4* __restrict__ out_rows,
                                                           const int32_t* __restrict__ back,
                                                           const int32_t* __restrict__ pad, int e_lo, int e_n,
-                                                          int vec_per_row, PeerPtrs rets, int my_rank) {
+                                                          int vec_per_row, PeerPtrs rets, int my_rank, Guard guard) {
   const int lane = threadIdx.x & 31;
   const int64_t row0 = pad[e_lo], row1 = pad[e_lo + e_n];
   const int64_t warps = static_cast<int64_t>(gridDim.x) * (blockDim.x >> 5);
   for (int64_t r = row0 + static_cast<int64_t>(blockIdx.x) * (blockDim.x >> 5) + (threadIdx.x >> 5); r < row1; r += warps) {
     const int32_t b = back[r];
     if (b < 0 || (b >> kPeerShift) == my_rank) continue;     // padding, or a token of this rank: it reads the row in place
+    if (!MG_GUARD((b >> kPeerShift) < guard.n_peers, guard, 106)) continue;
     const uint4* src = out_rows + r * vec_per_row;
     uint4* dst = static_cast<uint4*>(rets.p[b >> kPeerShift]) + static_cast<int64_t>(b & kPeerRowMask) * vec_per_row;
     for (int v0 = 0; v0 < vec_per_row; v0 += 128) {
@@ -573,7 +581,8 @@ int launch_return_rows(const Handle* h, const void* out_rows, const int32_t* bac
                        int e_n, const PeerPtrs& rets, cudaStream_t st) {
   if (e_n <= 0) return MG_OK;
   return_rows_kernel<<<h->sm_count * 2, 256, 0, st>>>(static_cast<const uint4*>(out_rows), back, pad, e_lo, e_n,
-                                                      h->d.hidden / 8, rets, h->d.ep_rank);
+                                                      h->d.hidden / 8, rets, h->d.ep_rank,
+                                                      Guard{h->d_status, h->guard_rows, h->d.ep_size});
   MG_CUDA(cudaGetLastError());
   return MG_OK;
 }
@@ -582,7 +591,8 @@ int launch_fill_duplicates(const Handle* h, void* rows, const int32_t* dup, int6
   if (n_rows == 0) return MG_OK;
   const int warps = 8;
   dim3 grid(static_cast<unsigned>((n_rows + warps - 1) / warps)), block(warps * 32);
-  fill_duplicate_rows_kernel<<<grid, block, 0, st>>>(static_cast<uint4*>(rows), dup, n_rows, h->d.hidden / 8);
+  fill_duplicate_rows_kernel<<<grid, block, 0, st>>>(static_cast<uint4*>(rows), dup, n_rows, h->d.hidden / 8,
+                                                     Guard{h->d_status, n_rows, h->d.ep_size});
   MG_CUDA(cudaGetLastError());
   return MG_OK;
 }
@@ -621,7 +631,7 @@ __global__ void __launch_bounds__(256) combine_kernel(PeerPtrs bufs,
                                                       const uint4* __restrict__ shared,
                                                       const uint4* residual,
                                                       int64_t T, int k, int vec_per_row, int v_chunk,
-                                                      uint4* y, int by_slot) {
+                                                      uint4* y, int by_slot, Guard guard) {
   const int lane = threadIdx.x & 31;
   const int64_t t = static_cast<int64_t>(blockIdx.x) * (blockDim.x >> 5) + (threadIdx.x >> 5);
   if (t >= T) return;
@@ -629,6 +639,9 @@ __global__ void __launch_bounds__(256) combine_kernel(PeerPtrs bufs,
   float my_w = 0.f;
   if (lane < k) {
     my_dst = dst_row[t * k + lane];
+    if (my_dst >= 0 && !MG_GUARD((PEER ? (my_dst & kPeerRowMask) : my_dst) < guard.rows_bound &&
+                                 (!PEER || (my_dst >> kPeerShift) < guard.n_peers), guard, 104))
+      my_dst = -1;
     if (by_slot > 0 && my_dst >= 0 && (my_dst >> kPeerShift) != by_slot - 1)
       my_dst = (my_dst & ~kPeerRowMask) | static_cast<int32_t>(t * k + lane);
     my_w = topk_w[t * k + lane];
@@ -734,7 +747,8 @@ static int launch_combine_impl(const Handle* h, const PeerPtrs& bufs, const int3
   combine_kernel<M, PEER><<<grid, block, 0, st>>>(bufs, dst_row, idx, w,                          \
                                                   static_cast<const uint4*>(shared),              \
                                                   static_cast<const uint4*>(residual), T, k, vpr, \
-                                                  v_chunk, static_cast<uint4*>(y), by_slot)
+                                                  v_chunk, static_cast<uint4*>(y), by_slot,                     \
+                                                  Guard{h->d_status, h->guard_rows, PEER ? h->d.ep_size : 1})
   switch (h->d.combine_mode) {
     case MG_COMBINE_FP32: MG_COMBINE_CASE(MG_COMBINE_FP32); break;
     case MG_COMBINE_BF16_PROD: MG_COMBINE_CASE(MG_COMBINE_BF16_PROD); break;

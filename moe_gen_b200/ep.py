@@ -185,6 +185,9 @@ class EPMoELayer:
                 # the library picks the tile height of its convert-in-the-GEMM kernels from the rows of
                 # the buffer it is given; here that is the receive capacity, so decide from the batch
                 L.check(self.lib.mg_set_option(lay._h, L.OPT_FP8_M256, 2 if T * self.world * k >= 120 * E else 0))
+            # rows the dispatch, duplicate-fill and combine kernels may address in a rank's buffers (looked at by
+            # a -DMG_BOUNDS_CHECK build of the library only)
+            L.check(self.lib.mg_set_option(lay._h, L.OPT_ROWS_BOUND, max(mb.cap for mb in self._mbs)))
         self._tokens = T
         dist.barrier(group=self.group)
 

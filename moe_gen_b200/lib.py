@@ -10,12 +10,13 @@ import ctypes as C
 import os
 
 _PKG = os.path.dirname(os.path.abspath(__file__))
-LIB_PATH = os.path.join(_PKG, "libmoegen_b200.so")
+# MOEGEN_B200_LIB selects another build of the same library (the -DMG_BOUNDS_CHECK one, for test runs)
+LIB_PATH = os.environ.get("MOEGEN_B200_LIB") or os.path.join(_PKG, "libmoegen_b200.so")
 
 GATE_SOFTMAX_GREEDY, GATE_SOFTMAX_GROUP_MAX, GATE_SIGMOID_NOAUX_TC, GATE_SOFTMAX_TOPK_RENORM = 0, 1, 2, 3
 COMBINE_FP32, COMBINE_BF16_PROD, COMBINE_BF16_SEQ = 0, 1, 2
 WEIGHT_BF16, WEIGHT_FP8_BLOCK128 = 0, 1
-DEV_OK, DEV_WAIT_TIMEOUT, DEV_CAPACITY = 0, 1, 2
+DEV_OK, DEV_WAIT_TIMEOUT, DEV_CAPACITY, DEV_BOUNDS = 0, 1, 2, 3
 OPT_FP8_MODE = 1
 OPT_PAIR_GEMM = 2
 OPT_KEEP_DEQUANT = 3
@@ -24,6 +25,7 @@ OPT_BATCH_TOKENS = 5
 OPT_SHARED_EARLY = 6
 OPT_RING_BYTES = 7
 OPT_RING_PERSIST = 8
+OPT_ROWS_BOUND = 9
 FP8_AUTO, FP8_PREDEQUANT, FP8_IN_KERNEL, FP8_RING = 0, 1, 2, 3
 
 
