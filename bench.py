@@ -449,7 +449,7 @@ def main():
                     help="expert parallel: 1 sends one row per (token, destination GPU), 0 one per (token, expert)")
     ap.add_argument("--ep-push", type=int, default=-1,
                     help="expert parallel: 1 owners push results home part by part beside the down projection, "
-                         "0 the combine gathers them after the experts, -1 by the number of GPUs")
+                         "0 the combine gathers them after the experts (-1: the library's default, 0)")
     ap.add_argument("--ep-parts", type=int, default=4, help="expert parallel: parts of the pushed return")
     ap.add_argument("--shared-early", type=int, default=-1,
                     help="1/0 shared expert beside the routing kernels / after the routed experts")

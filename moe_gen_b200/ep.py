@@ -86,9 +86,9 @@ class EPMoELayer:
         # the owners push their experts' outputs into the token owners' return buffers part by part while the
         # next part's down projection runs, and the combine is local; False = the combine gathers the rows
         # from the owners' buffers after the experts have finished
-        # None: by the group size (measured at 2 GPUs: every rank returns half of all rows, the extra copy of
-        # the push costs the experts more than the local combine saves, 30.5 against 29.6 ms per step)
-        self.push_return = (self.world >= 4) if push_return is None else push_return
+        # None = off: measured at 2 GPUs the pushes slow the experts beside them by about their own duration
+        # (24.5 against 21.4 ms) while the combine gets 2.2 ms shorter: 30.2 against 29.4 ms per step
+        self.push_return = False if push_return is None else push_return
         self.return_parts = return_parts
         self.lib = layer.lib
         self.dev = layer.device
