@@ -320,7 +320,7 @@ def sample_check(name: str, layer, x: torch.Tensor, y: torch.Tensor, zipf: float
     H, I, E, k, Is, G, keep, gating, norm, scale, wfmt, comb, _, seed = WORKLOADS[name]
     dev = x.device
     T = x.shape[0]
-    idx, w = layer.route_topk(layer.gate_logits(x))
+    idx, w, _, fix = layer.gate_route(x)
     # routing from fp32 (CUDA-core) logits, as the reference computes them
     if gating == 3:
         lg = F.linear(x, layer.gate_w).float()
@@ -328,6 +328,15 @@ def sample_check(name: str, layer, x: torch.Tensor, y: torch.Tensor, zipf: float
         lg = F.linear(x.float(), layer.gate_w.float())
     idx2, _ = layer.route_topk(lg.contiguous())
     differ = int((idx.sort(1).values != idx2.sort(1).values).any(1).sum())
+    # ... and from the correctly rounded logits (fp64 product, rounded once), which the layer's routing
+    # has to equal token for token where the router works in fp32
+    differ_exact = None
+    if gating != 3:
+        lg = F.linear(x.double(), layer.gate_w.double()).float()
+        idx3, _ = layer.route_topk(lg.contiguous())
+        differ_exact = int((idx.sort(1).values != idx3.sort(1).values).any(1).sum())
+        del idx3
+    del lg
 
     def fp32_mats(e):
         ws = expert_tensors(name, dev, e)
@@ -347,7 +356,9 @@ def sample_check(name: str, layer, x: torch.Tensor, y: torch.Tensor, zipf: float
         ref.index_add_(0, rows, mlp(xs[rows], *fp32_mats(e)) * pw[rows, slots].unsqueeze(1))
     err = (y[tokens].float() - ref).norm(dim=1) / ref.norm(dim=1).clamp_min(1e-30)
     return {"sampled_tokens": int(len(tokens)), "worst_rel_l2_vs_torch_fp32": float(err.max()), "tolerance": 1e-2,
-            "tokens_routed_differently_from_fp32_logits": differ, "tokens": T}
+            "tokens_routed_differently_from_fp32_logits": differ,
+            "tokens_routed_differently_from_exact_logits": differ_exact, "tokens_rerouted_by_fixup": int(fix[0]),
+            "tokens": T}
 
 
 def quick_config(name: str, T: int, zipf: float, world: int, rank: int, device, steps: int = 5, reuse=None):
@@ -386,9 +397,12 @@ def quick_config(name: str, T: int, zipf: float, world: int, rank: int, device, 
     code, detail = base.device_status()
     chk = sample_check(name, base, x, y, zipf, n_tokens=8)
     if world > 1:
-        t = torch.tensor([ms, chk["worst_rel_l2_vs_torch_fp32"], float(code)], device=device)
+        t = torch.tensor([ms, chk["worst_rel_l2_vs_torch_fp32"], float(code),
+                          float(chk["tokens_routed_differently_from_exact_logits"] or 0)], device=device)
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
         ms, chk["worst_rel_l2_vs_torch_fp32"], code = float(t[0]), float(t[1]), int(t[2])
+        if chk["tokens_routed_differently_from_exact_logits"] is not None:
+            chk["tokens_routed_differently_from_exact_logits"] = int(t[3])
         chk["sampled_tokens"] *= world
     if reuse is None:
         if world > 1:
@@ -398,8 +412,9 @@ def quick_config(name: str, T: int, zipf: float, world: int, rank: int, device, 
            "tokens_per_s": round(T / (ms * 1e-3), 1), "device_status": code,
            "check": {"sampled_tokens": chk["sampled_tokens"],
                      "worst_rel_l2_vs_torch_fp32": round(chk["worst_rel_l2_vs_torch_fp32"], 6),
-                     "tokens_routed_differently_from_fp32_logits": chk["tokens_routed_differently_from_fp32_logits"]}}
-    if code != 0 or chk["worst_rel_l2_vs_torch_fp32"] > 1e-2:
+                     "tokens_routed_differently_from_fp32_logits": chk["tokens_routed_differently_from_fp32_logits"],
+                     "tokens_routed_differently_from_exact_logits": chk["tokens_routed_differently_from_exact_logits"]}}
+    if code != 0 or chk["worst_rel_l2_vs_torch_fp32"] > 1e-2 or chk["tokens_routed_differently_from_exact_logits"]:
         raise SystemExit(f"correctness gate failed for {out}")
     return out
 
@@ -454,6 +469,8 @@ def main():
     ap.add_argument("--shared-early", type=int, default=-1,
                     help="1/0 shared expert beside the routing kernels / after the routed experts")
     ap.add_argument("--pair-gemm", type=int, default=-1, help="1/0 force the SM-pair expert GEMM on/off")
+    ap.add_argument("--route-fixup", type=int, default=-1,
+                    help="0 = route every token from the tensor-core router product as it is (no near-tie fix-up)")
     ap.add_argument("--fp8-mode", type=int, default=-1, help="0 auto, 1 pre-dequantise, 2 convert in the GEMM")
     ap.add_argument("--fp8-tall", type=int, default=-1, help="convert-in-GEMM tile height: 0 128 rows, 1 auto, 2 256 rows")
     args = ap.parse_args()
@@ -523,6 +540,8 @@ def main():
     base = layer.layer if world > 1 else layer
     if args.pair_gemm >= 0:
         base.set_option(2, args.pair_gemm)
+    if args.route_fixup >= 0:
+        base.set_option(10, args.route_fixup)
     if args.fp8_mode >= 0:
         base.set_option(1, args.fp8_mode)
     if args.fp8_tall >= 0:
@@ -633,7 +652,7 @@ def main():
     # rows each GPU's experts receive (all ranks' picks), for the load-balance figures
     ep_load = None
     if world > 1:
-        idx_l, _ = base.route_topk(base.gate_logits(x))
+        idx_l, _ = base.gate_route(x)[:2]
         hist = torch.bincount(idx_l.view(-1).long(), minlength=E).to(torch.int64)
         dist.all_reduce(hist)
         per_gpu = hist.view(world, E // world).sum(1).cpu().tolist()
@@ -647,17 +666,21 @@ def main():
     if not args.no_check:
         check = sample_check(name, base, x, y, args.zipf)
         if world > 1:
-            t = torch.tensor([check["worst_rel_l2_vs_torch_fp32"], float(check["tokens_routed_differently_from_fp32_logits"])],
-                             device=device)
+            t = torch.tensor([check["worst_rel_l2_vs_torch_fp32"], float(check["tokens_routed_differently_from_fp32_logits"]),
+                              float(check["tokens_routed_differently_from_exact_logits"] or 0),
+                              float(check["tokens_rerouted_by_fixup"])], device=device)
             worst = t.clone()
             dist.all_reduce(worst, op=dist.ReduceOp.MAX)
             dist.all_reduce(t, op=dist.ReduceOp.SUM)
             check["worst_rel_l2_vs_torch_fp32"] = float(worst[0])
             check["tokens_routed_differently_from_fp32_logits"] = int(t[1])
+            if check["tokens_routed_differently_from_exact_logits"] is not None:
+                check["tokens_routed_differently_from_exact_logits"] = int(t[2])
+            check["tokens_rerouted_by_fixup"] = int(t[3])
             check["sampled_tokens"] *= world
             check["tokens"] = T_total
             check["note"] = "every rank checks sampled tokens of its own shard against its own output; worst over ranks"
-        if check["worst_rel_l2_vs_torch_fp32"] > 1e-2:
+        if check["worst_rel_l2_vs_torch_fp32"] > 1e-2 or check["tokens_routed_differently_from_exact_logits"]:
             raise SystemExit(f"correctness gate failed: {check}")
     code, detail = base.device_status()
     if world > 1:

@@ -183,6 +183,23 @@ int mg_gate_logits(mg_handle h, const void* d_x, const void* d_gate_w, int64_t n
 int mg_route_topk(mg_handle h, const float* d_logits, const float* d_bias, int64_t n_tokens,
                   int32_t* d_topk_idx, float* d_topk_w, void* stream);
 
+/* Router product and top-k in one call, with the near-tie fix-up: mg_gate_logits, mg_route_topk, then
+ * every token whose pick the tensor-core product's rounding could have changed (its last kept expert or
+ * group leads the best rejected one by less than a logits error of (6e-9 * H + 4e-6) * max(1, max|logit|)
+ * allows, four times the error measured for the product) has the logits that can decide it recomputed as
+ * the rounded exact sum (bf16 products accumulated in fp64) and is routed again.  The selection is that
+ * of correctly rounded fp32 logits, the value F.linear(x.float(), W.float()) approximates
+ * (modeling_deepseek_v3.py:503-508); mg_moe_forward routes this way unless MG_OPT_ROUTE_FIXUP is 0.
+ * d_logits[T,E]: scratch, holds the logits afterwards (recomputed entries included).
+ * d_fix: scratch of mg_route_fix_bytes(T) bytes, int32; afterwards [0] = tokens routed again, [1] = of
+ * which with their whole row recomputed, [2] = single logits asked for; the tokens from [4], the
+ * row tokens from [4+T], the (token, expert) pairs from [4+2T] (8T+64 pairs at most; a token whose pairs
+ * do not fit has its row recomputed).  For MG_GATE_SOFTMAX_TOPK_RENORM (bf16-rounded logits, where
+ * near-ties are exact ties) the call is mg_gate_logits + mg_route_topk and the counts are 0. */
+int mg_gate_route_topk(mg_handle h, const void* d_x, const void* d_gate_w, const float* d_bias, int64_t n_tokens,
+                       float* d_logits, int32_t* d_topk_idx, float* d_topk_w, int32_t* d_fix, void* stream);
+int mg_route_fix_bytes(int64_t n_tokens, size_t* bytes);
+
 /* Histogram + prefix sums + stable placement over experts [expert_lo,
  * expert_lo + n_plan_experts): picks outside that range are skipped (dst_row=-1).
  *   counts[n]        rows per expert
@@ -453,6 +470,9 @@ int mg_last_launch_count(mg_handle h, int32_t* launches);
  * read from a table with this bound and report MG_DEV_BOUNDS instead of touching memory outside the buffer.
  * mg_moe_forward sets its own bound. */
 #define MG_OPT_ROWS_BOUND 9
+/* MG_OPT_ROUTE_FIXUP: 1 (default) = mg_moe_forward re-routes near-tie tokens from exactly recomputed logits
+ * (see mg_gate_route_topk); 0 = it routes every token from the tensor-core product as it is. */
+#define MG_OPT_ROUTE_FIXUP 10
 /* MG_OPT_PAIR_GEMM: 1 = the bf16 expert GEMMs run on SM pairs (clusters of two CTAs,
  * tcgen05 cta_group::2, 256x256 tiles); 0 = one CTA per SM, 128x256 tiles. */
 #define MG_OPT_PAIR_GEMM   2

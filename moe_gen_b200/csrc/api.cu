@@ -49,7 +49,7 @@ static int64_t padded_rows(const Handle* h, int64_t rows) {
 
 // workspace carving ---------------------------------------------------------------------
 enum { WS_LOGITS, WS_IDX, WS_W, WS_COUNTS, WS_OFFSETS, WS_PAD, WS_DST, WS_PERM, WS_H, WS_OUT, WS_PLAN,
-       WS_HS, WS_SHARED, WS_DEQ, WS_N };
+       WS_HS, WS_SHARED, WS_DEQ, WS_FIX, WS_N };
 struct WsLayout { size_t off[WS_N]; size_t total; };
 
 static size_t dequant_ws(const Handle* h) {
@@ -128,6 +128,7 @@ static WsLayout ws_layout(const Handle* h, int64_t T, int64_t R) {
   take(WS_PLAN, plan_ws_bytes(h, T));
   take(WS_HS, static_cast<size_t>(T) * d.inter_shared * 2);
   take(WS_SHARED, d.inter_shared ? static_cast<size_t>(T) * d.hidden * 2 : 0);
+  take(WS_FIX, route_fix_bytes(T));
   L.total = off;
   return L;
 }
@@ -329,6 +330,36 @@ int mg_gate_logits(mg_handle hh, const void* d_x, const void* d_gate_w, int64_t 
   p.pad_offsets = nullptr; p.counts = nullptr; p.dense_rows = T; p.out = d_logits; p.ldo = h->d.n_experts;
   p.epilogue = h->d.gating == MG_GATE_SOFTMAX_TOPK_RENORM ? EPI_ROUND_BF16_F32 : EPI_PLAIN_F32;
   return launch_grouped_gemm(h, p, static_cast<cudaStream_t>(stream));
+}
+
+// The fix-up recomputes fp32 logits; the bf16 router of MG_GATE_SOFTMAX_TOPK_RENORM rounds its logits to
+// bf16, where near-ties are exact ties that both sides break by the lower index.
+static bool route_fixup_applies(const Handle* h) {
+  return h->opt_route_fixup && h->d.gating != MG_GATE_SOFTMAX_TOPK_RENORM;
+}
+
+int mg_gate_route_topk(mg_handle hh, const void* d_x, const void* d_gate_w, const float* d_bias, int64_t T,
+                       float* d_logits, int32_t* d_idx, float* d_w, int32_t* d_fix, void* stream) {
+  MG_TRACE("mg_gate_route_topk", T);
+  Handle* h = check(hh);
+  if (!h) return MG_ERR_STATE;
+  MG_REQUIRE(d_x && d_gate_w && d_logits && d_idx && d_w && d_fix, MG_ERR_NULL, "mg_gate_route_topk: null pointer");
+  MG_REQUIRE(h->d.gating != MG_GATE_SIGMOID_NOAUX_TC || d_bias, MG_ERR_NULL, "noaux_tc gating needs the correction bias");
+  int rc = mg_gate_logits(hh, d_x, d_gate_w, T, d_logits, stream);
+  if (rc != MG_OK) return rc;
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  if (!route_fixup_applies(h)) {
+    if (T > 0) MG_CUDA(cudaMemsetAsync(d_fix, 0, 16, st));
+    return launch_route_topk(h, d_logits, d_bias, T, d_idx, d_w, st);
+  }
+  return launch_route_topk_fixup(h, d_x, d_gate_w, d_logits, d_bias, T, d_idx, d_w, d_fix, st, nullptr);
+}
+
+int mg_route_fix_bytes(int64_t T, size_t* bytes) {
+  MG_REQUIRE(bytes, MG_ERR_NULL, "mg_route_fix_bytes: null pointer");
+  MG_REQUIRE(T >= 0, MG_ERR_SHAPE, "negative token count");
+  *bytes = route_fix_bytes(T);
+  return MG_OK;
 }
 
 int mg_route_topk(mg_handle hh, const float* d_logits, const float* d_bias, int64_t T, int32_t* d_idx, float* d_w,
@@ -739,10 +770,17 @@ static int moe_forward_impl(mg_handle hh, const void* d_x, int64_t T, const void
     MG_CUDA(cudaEventRecord(h->ev_shared_out, h->side2));
     launches += 2;
   }
-  rc = launch_route_topk(h, logits, d_bias, T, idx, w, st);
+  if (d_logits_in == nullptr && route_fixup_applies(h)) {
+    // logits from the tensor-core product: tokens whose pick its rounding could have changed are re-routed
+    // from exactly recomputed logits, so the routing is that of correctly rounded fp32 logits
+    rc = launch_route_topk_fixup(h, d_x, d_gate_w, logits, d_bias, T, idx, w,
+                                 reinterpret_cast<int32_t*>(ws + L.off[WS_FIX]), st, &launches);
+  } else {
+    rc = launch_route_topk(h, logits, d_bias, T, idx, w, st);
+    launches += 1;
+  }
   if (rc != MG_OK) return rc;
   mark(h, MG_STAGE_ROUTE_TOPK, st);
-  launches += 1;
   rc = launch_permute_plan(h, idx, T, 0, d.n_experts, counts, offsets, pad, dst, plan, st, &launches);
   if (rc != MG_OK) return rc;
   mark(h, MG_STAGE_PERMUTE_PLAN, st);
@@ -990,6 +1028,7 @@ int mg_set_option(mg_handle hh, int32_t option, int32_t value) {
       h->guard_rows = value > 0 ? value : 0x7fffffffffffffffll;
       return MG_OK;
     case MG_OPT_RING_PERSIST: h->opt_ring_persist = value != 0; return MG_OK;
+    case MG_OPT_ROUTE_FIXUP: h->opt_route_fixup = value != 0; return MG_OK;
     case MG_OPT_RING_BYTES:
       MG_REQUIRE(value >= 1, MG_ERR_CONFIG, "bad ring size %d MiB", value);
       h->opt_ring_bytes = static_cast<size_t>(value) << 20;

@@ -77,7 +77,8 @@ struct Handle {
   int opt_fp8_mode;       // MG_FP8_AUTO / MG_FP8_PREDEQUANT / MG_FP8_IN_KERNEL / MG_FP8_RING
   long long guard_rows;   // bound the row-moving kernels check table entries against in a -DMG_BOUNDS_CHECK build
   size_t opt_ring_bytes;  // budget of the bf16 ring of MG_FP8_RING (it should stay resident in L2)
-  int opt_ring_persist;   // ring accesses carry the L2 evict_last policy (needs an L2 set-aside, mg_l2_set_aside)
+  bool opt_route_fixup = true;   // MG_OPT_ROUTE_FIXUP
+  int opt_ring_persist;          // ring accesses carry the L2 evict_last policy (needs an L2 set-aside, mg_l2_set_aside)
   cudaStream_t side;      // de-quantisation runs here, one chunk of experts ahead of the GEMMs
   cudaEvent_t ev_entry, ev_w13[kDequantChunks], ev_w2[kDequantChunks];
   cudaStream_t copy_in, copy_out;   // host-buffer forward: copies of the chunks either side of the compute
@@ -106,6 +107,9 @@ PackedLayout packed_layout(const Handle* h);
 // routing / permute / combine launchers (route.cu) -------------------------------------
 int launch_route_topk(const Handle* h, const float* logits, const float* bias, int64_t T,
                       int32_t* idx, float* w, cudaStream_t st);
+size_t route_fix_bytes(int64_t T);
+int launch_route_topk_fixup(const Handle* h, const void* x, const void* gate_w, float* logits, const float* bias,
+                            int64_t T, int32_t* idx, float* w, int32_t* fix, cudaStream_t st, int* launches);
 size_t plan_ws_bytes(const Handle* h, int64_t T);
 int launch_permute_plan(const Handle* h, const int32_t* idx, int64_t T, int expert_lo, int n_exp,
                         int32_t* counts, int32_t* offsets, int32_t* pad_offsets, int32_t* dst_row,

@@ -39,22 +39,77 @@ __device__ __forceinline__ float warp_sum_f(float v) {
   return v;
 }
 
+// Routing of one token by one warp, with the detection of near-ties for the fix-up (fix != nullptr).
+//
+// The tensor-core router product accumulates H/16 partial sums in fp32 with truncation: its error grows
+// with H and with the size of the sums.  Measured on random inputs: 1.2e-5 * max|logit| at H = 7168; the
+// bound assumed below is 4x that (the tests hold the measured error under half of it).  With a logit
+// error of at most dl, a sigmoid score moves by at most dl/4 (a group score, the sum of two, by dl/2) and a
+// softmax score p by at most 2*p*dl.  A token is "close" when its last kept group or expert leads the
+// best rejected one by less than twice that; only then can the pick differ from that of exact logits.
+// For a close token the experts that can change the outcome ("in play") are listed as (token, expert)
+// pairs, their logits are recomputed exactly, and the token is routed again:
+//   * group selection close: in-play groups are those within the error of the kept/rejected boundary;
+//     of each, the experts that can be among the values its score is made of;
+//   * top-k: with U_min / U_max the groups kept in every / in some admissible outcome and v_lo / v_hi
+//     the k-th best value over them, the experts of U_max between v_lo - 2*de and v_hi + 2*de (anything
+//     above is picked and anything below is not, whatever the errors do).
+// Every other logit keeps its tensor-core value: it cannot change a pick, and it moves a routing weight by
+// no more than it does for a token that is not close.
+// fix layout (int32): [0] tokens to route again, [1] of which with whole rows to recompute, [2] pairs
+// asked for (may exceed the capacity), [3] unused; tokens [4, 4+T); row tokens [4+T, 4+2T); pairs from
+// 4+2T, rp.pair_cap of them.  A token whose pairs do not fit, or whose groups are not runs of lanes,
+// has its whole row recomputed instead.
+__host__ __device__ inline float route_fix_err(int hidden) { return 6.0e-9f * hidden + 4.0e-6f; }
+__device__ __forceinline__ float from_ordered_bits(uint32_t key) {
+  return __uint_as_float((key & 0x80000000u) ? (key ^ 0x80000000u) : ~key);
+}
+
 struct RouteParams {
   int E, k, n_group, topk_group, gating, norm;
   float scale;
+  float fix_err;
+  int pair_cap;
+  int64_t T;
 };
 
+// k-th best selection value when only the groups in `groups` compete (others count as 0.0, as in the
+// selection itself); -inf when fewer than k experts exist.
 template <int P>
-__global__ void __launch_bounds__(256) route_topk_kernel(const float* __restrict__ logits,
-                                                         const float* __restrict__ bias,
-                                                         int64_t T, RouteParams rp,
-                                                         int32_t* __restrict__ out_idx,
-                                                         float* __restrict__ out_w) {
+__device__ __forceinline__ float kth_best_value(const float (&c0)[P], uint32_t groups, bool grouped, int gsz,
+                                                int E, int k, int lane) {
+  uint32_t taken = 0, best = 0;
+  for (int r = 0; r < k; ++r) {
+    uint32_t bkey = 0u;
+    int bslot = 0;
+#pragma unroll
+    for (int i = 0; i < P; ++i) {
+      const int e = lane * P + i;
+      const float v = (!grouped || ((groups >> (e / gsz)) & 1u)) ? c0[i] : 0.0f;
+      const uint32_t key = (e < E && !((taken >> i) & 1u)) ? ordered_bits(v) : 0u;
+      if (key > bkey) { bkey = key; bslot = i; }
+    }
+    best = __reduce_max_sync(0xFFFFFFFFu, bkey);
+    if (best == 0u) return __int_as_float(0xff800000);
+    const uint32_t e_win = __reduce_min_sync(0xFFFFFFFFu, bkey == best ? static_cast<uint32_t>(lane * P + bslot) : 0xFFFFFFFFu);
+    if (lane == static_cast<int>(e_win) / P) taken |= 1u << bslot;
+  }
+  return from_ordered_bits(best);
+}
+
+template <int P>
+__device__ __forceinline__ void route_token(const float* __restrict__ logits, const float* __restrict__ bias,
+                                            int64_t t, const RouteParams& rp, int32_t* __restrict__ out_idx,
+                                            float* __restrict__ out_w, int32_t* __restrict__ fix) {
   const int lane = threadIdx.x & 31;
-  const int64_t t = static_cast<int64_t>(blockIdx.x) * (blockDim.x >> 5) + (threadIdx.x >> 5);
-  if (t >= T) return;
   const int E = rp.E;
   const float NEG_INF = __int_as_float(0xff800000);
+  float group_margin = __int_as_float(0x7f800000), group_kept_min = 0.f, group_open_max = NEG_INF;
+  float grp_b1 = NEG_INF, grp_b2 = NEG_INF;      // the two best values of this lane's group (groups that are lane runs)
+  bool lane_groups = false;
+  uint32_t kept_groups = 0;
+  float lane_gs = NEG_INF;                       // score of the group this lane reports
+  int lane_g = -1;
 
   float lg[P];   // logits
   float s[P];    // scores (softmax or sigmoid)
@@ -91,6 +146,10 @@ __global__ void __launch_bounds__(256) route_topk_kernel(const float* __restrict
     }
   }
 
+  float c0[P];   // selection values before the group mask
+#pragma unroll
+  for (int i = 0; i < P; ++i) c0[i] = c[i];
+
   // group-limited selection: keep topk_group groups, others compete with value 0.0
   if (rp.gating == MG_GATE_SOFTMAX_GROUP_MAX || rp.gating == MG_GATE_SIGMOID_NOAUX_TC) {
     const int G = rp.n_group, gsz = E / G;
@@ -113,6 +172,8 @@ __global__ void __launch_bounds__(256) route_topk_kernel(const float* __restrict
         b2 = fmaxf(lo, fmaxf(b2, o2));
         b1 = hi;
       }
+      grp_b1 = b1; grp_b2 = b2;
+      lane_groups = true;
       const int g = (lane * P) / gsz;
       if (lane * P < E && (lane & (lanes_per_group - 1)) == 0) {
         my_g = g;
@@ -152,6 +213,15 @@ __global__ void __launch_bounds__(256) route_topk_kernel(const float* __restrict
       const uint32_t win = __reduce_min_sync(0xFFFFFFFFu, (open && gkey == best) ? static_cast<uint32_t>(my_g) : 0xFFFFFFFFu);
       gmask |= 1u << win;
     }
+    if (fix != nullptr) {
+      const bool kept = my_g >= 0 && ((gmask >> my_g) & 1u);
+      group_kept_min = -warp_max_f(kept ? -my_gs : NEG_INF);
+      group_open_max = warp_max_f(my_g >= 0 && !kept ? my_gs : NEG_INF);
+      group_margin = group_kept_min - group_open_max;
+      kept_groups = gmask;
+      lane_gs = my_gs;
+      lane_g = my_g;
+    }
 #pragma unroll
     for (int i = 0; i < P; ++i) {
       int e = lane * P + i;
@@ -161,8 +231,8 @@ __global__ void __launch_bounds__(256) route_topk_kernel(const float* __restrict
 
   // k rounds of warp arg-max: score descending, equal scores -> lower expert id
   uint32_t taken = 0;
-  int my_idx = 0;
-  float my_w = 0.f;
+  int my_idx = 0, last_owner = 0;
+  float my_w = 0.f, last_c = 0.f;
   for (int r = 0; r < rp.k; ++r) {
     uint32_t bkey = 0u;
     int bslot = 0;
@@ -179,10 +249,85 @@ __global__ void __launch_bounds__(256) route_topk_kernel(const float* __restrict
       taken |= 1u << bslot;
 #pragma unroll
       for (int i = 0; i < P; ++i)
-        if (i == bslot) wv = rp.gating == MG_GATE_SIGMOID_NOAUX_TC ? s[i] : c[i];
+        if (i == bslot) { wv = rp.gating == MG_GATE_SIGMOID_NOAUX_TC ? s[i] : c[i]; last_c = c[i]; }
     }
     wv = __shfl_sync(0xFFFFFFFFu, wv, owner);
+    last_owner = owner;
     if (lane == r) { my_idx = static_cast<int>(e_win); my_w = wv; }
+  }
+  if (fix != nullptr) {
+    last_c = __shfl_sync(0xFFFFFFFFu, last_c, last_owner);
+    float next_c = NEG_INF, amax = 0.f;
+#pragma unroll
+    for (int i = 0; i < P; ++i) {
+      if ((lane * P + i) < E) {
+        amax = fmaxf(amax, fabsf(lg[i]));
+        if (!((taken >> i) & 1u)) next_c = fmaxf(next_c, c[i]);
+      }
+    }
+    next_c = warp_max_f(next_c);
+    amax = warp_max_f(amax);
+    const float dl = rp.fix_err * fmaxf(1.0f, amax);
+    const bool sig = rp.gating == MG_GATE_SIGMOID_NOAUX_TC;
+    const bool grouped = sig || rp.gating == MG_GATE_SOFTMAX_GROUP_MAX;
+    const int gsz = grouped ? E / rp.n_group : E;
+    const float dg = sig ? 0.5f * dl : 2.0f * fabsf(group_kept_min) * dl;
+    const bool g_close = grouped && group_margin < 2.0f * dg;
+    const bool e_close = (last_c - next_c) < 2.0f * (sig ? 0.25f * dl : 2.0f * fabsf(last_c) * dl);
+    if (g_close || e_close) {                       // the same for the whole warp
+      bool whole_row = g_close && !lane_groups;
+      if (!whole_row) {
+        uint32_t in_play = 0;                        // bit i: this lane's expert i
+        if (!g_close) {
+          const float de = sig ? 0.25f * dl : 2.0f * fabsf(last_c) * dl;
+          const float lo = next_c - 2.0f * de, hi = last_c + 2.0f * de;
+#pragma unroll
+          for (int i = 0; i < P; ++i) {
+            const int e = lane * P + i;
+            const bool open = e < E && (!grouped || ((kept_groups >> (e / gsz)) & 1u));
+            if (open && c0[i] >= lo && c0[i] <= hi) in_play |= 1u << i;
+          }
+        } else {
+          const bool near = lane_g >= 0 && lane_gs >= group_open_max - 2.0f * dg && lane_gs <= group_kept_min + 2.0f * dg;
+          const uint32_t play_groups = __reduce_or_sync(0xFFFFFFFFu, near ? 1u << lane_g : 0u);
+          const uint32_t u_max = kept_groups | play_groups, u_min = kept_groups & ~play_groups;
+          const float v_hi = kth_best_value<P>(c0, u_max, true, gsz, E, rp.k, lane);
+          const float v_lo = kth_best_value<P>(c0, u_min, true, gsz, E, rp.k, lane);
+          const float de = sig ? 0.25f * dl : 2.0f * fmaxf(fabsf(v_hi), fabsf(last_c)) * dl;
+          const float de_g = sig ? 0.25f * dl : 2.0f * fabsf(grp_b1) * dl;
+          const float contender = (sig ? grp_b2 : grp_b1) - 2.0f * de_g;
+#pragma unroll
+          for (int i = 0; i < P; ++i) {
+            const int e = lane * P + i;
+            if (e >= E) continue;
+            const int g = e / gsz;
+            if (!((u_max >> g) & 1u)) continue;
+            const bool band = c0[i] >= v_lo - 2.0f * de && c0[i] <= v_hi + 2.0f * de;
+            const bool scores = ((play_groups >> g) & 1u) && c0[i] >= contender;
+            if (band || scores) in_play |= 1u << i;
+          }
+        }
+        bool full = false;
+        int32_t* pairs = fix + 4 + 2 * rp.T;
+#pragma unroll
+        for (int i = 0; i < P; ++i) {
+          if ((in_play >> i) & 1u) {
+            const int pos = atomicAdd(fix + 2, 1);
+            if (pos < rp.pair_cap) {
+              pairs[2 * pos] = static_cast<int32_t>(t);
+              pairs[2 * pos + 1] = lane * P + i;
+            } else {
+              full = true;
+            }
+          }
+        }
+        whole_row = __any_sync(0xFFFFFFFFu, full);
+      }
+      if (lane == 0) {
+        fix[4 + atomicAdd(fix, 1)] = static_cast<int32_t>(t);
+        if (whole_row) fix[4 + rp.T + atomicAdd(fix + 1, 1)] = static_cast<int32_t>(t);
+      }
+    }
   }
 
   // normalise / scale
@@ -203,17 +348,220 @@ __global__ void __launch_bounds__(256) route_topk_kernel(const float* __restrict
   }
 }
 
+template <int P>
+__global__ void __launch_bounds__(256) route_topk_kernel(const float* __restrict__ logits,
+                                                         const float* __restrict__ bias,
+                                                         int64_t T, RouteParams rp,
+                                                         int32_t* __restrict__ out_idx,
+                                                         float* __restrict__ out_w, int32_t* __restrict__ fix) {
+  const int64_t t = static_cast<int64_t>(blockIdx.x) * (blockDim.x >> 5) + (threadIdx.x >> 5);
+  if (t >= T) return;
+  route_token<P>(logits, bias, t, rp, out_idx, out_w, fix);
+}
+
+// The close tokens once more, now that their in-play logits are exact.
+template <int P>
+__global__ void __launch_bounds__(256) route_topk_list_kernel(const float* __restrict__ logits,
+                                                              const float* __restrict__ bias, RouteParams rp,
+                                                              int32_t* __restrict__ out_idx, float* __restrict__ out_w,
+                                                              const int32_t* __restrict__ fix) {
+  const int n = fix[0];
+  const int warps = gridDim.x * (blockDim.x >> 5);
+  for (int i = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5); i < n; i += warps)
+    route_token<P>(logits, bias, fix[4 + i], rp, out_idx, out_w, nullptr);
+}
+
+// Whole logits rows of the listed tokens, recomputed as the rounded exact sum: the products of two bf16
+// values are exact in fp64 and the 64-bit accumulation leaves an error far below half an fp32 ulp, so
+// the stored value is the correctly rounded logit whatever the summation order.  A block takes a batch
+// of kFixTokens tokens (their x rows in shared memory) and a slice of kFixSlice experts; each warp holds
+// a kFixWarpExperts x kFixTokens tile of fp64 sums, lanes across H, so that an operand is widened to
+// fp64 once per 4 or 8 multiply-adds.
+constexpr int kFixTokens = 4;
+constexpr int kFixWarpExperts = 8;
+constexpr int kFixSlice = 8 * kFixWarpExperts;     // 8 warps per block
+__device__ __forceinline__ double bf16_lo_f64(uint32_t pair) { return static_cast<double>(__uint_as_float(pair << 16)); }
+__device__ __forceinline__ double bf16_hi_f64(uint32_t pair) { return static_cast<double>(__uint_as_float(pair & 0xffff0000u)); }
+__global__ void __launch_bounds__(256) route_fix_logits_kernel(const __nv_bfloat16* __restrict__ x,
+                                                               const __nv_bfloat16* __restrict__ gate_w, int H, int E,
+                                                               const int32_t* __restrict__ fix, int64_t T,
+                                                               float* __restrict__ logits) {
+  extern __shared__ __align__(16) unsigned char fix_smem[];
+  uint4* xs = reinterpret_cast<uint4*>(fix_smem);            // [kFixTokens][H/8]
+  const int n = fix[1];
+  const int32_t* list = fix + 4 + T;
+  const int vecs = H >> 3;
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  const int n_slices = (E + kFixSlice - 1) / kFixSlice;
+  const int n_batches = (n + kFixTokens - 1) / kFixTokens;
+  int loaded = -1;
+  for (int item = blockIdx.x; item < n_batches * n_slices; item += gridDim.x) {
+    const int b = item / n_slices, slice = item - b * n_slices;
+    int tok[kFixTokens];
+#pragma unroll
+    for (int j = 0; j < kFixTokens; ++j) {
+      const int i = b * kFixTokens + j;
+      tok[j] = list[i < n ? i : n - 1];                      // a short batch repeats its last token
+    }
+    if (b != loaded) {
+      __syncthreads();
+#pragma unroll
+      for (int j = 0; j < kFixTokens; ++j) {
+        const uint4* row = reinterpret_cast<const uint4*>(x + static_cast<int64_t>(tok[j]) * H);
+        for (int v = threadIdx.x; v < vecs; v += blockDim.x) xs[j * vecs + v] = row[v];
+      }
+      __syncthreads();
+      loaded = b;
+    }
+    const int e0 = slice * kFixSlice + warp * kFixWarpExperts;
+    if (e0 >= E) continue;                                    // warp-uniform; no barrier below in this item
+    const uint4* wrow[kFixWarpExperts];
+#pragma unroll
+    for (int i = 0; i < kFixWarpExperts; ++i) {
+      const int e = e0 + i < E ? e0 + i : E - 1;
+      wrow[i] = reinterpret_cast<const uint4*>(gate_w + static_cast<int64_t>(e) * H);
+    }
+    double acc[kFixWarpExperts][kFixTokens];
+#pragma unroll
+    for (int i = 0; i < kFixWarpExperts; ++i)
+#pragma unroll
+      for (int j = 0; j < kFixTokens; ++j) acc[i][j] = 0.0;
+    for (int v = lane; v < vecs; v += 32) {
+      uint4 wv[kFixWarpExperts], xv[kFixTokens];
+#pragma unroll
+      for (int i = 0; i < kFixWarpExperts; ++i) wv[i] = wrow[i][v];
+#pragma unroll
+      for (int j = 0; j < kFixTokens; ++j) xv[j] = xs[j * vecs + v];
+#pragma unroll
+      for (int q = 0; q < 4; ++q) {
+        double xl[kFixTokens], xh[kFixTokens];
+#pragma unroll
+        for (int j = 0; j < kFixTokens; ++j) {
+          const uint32_t pair = q == 0 ? xv[j].x : q == 1 ? xv[j].y : q == 2 ? xv[j].z : xv[j].w;
+          xl[j] = bf16_lo_f64(pair);
+          xh[j] = bf16_hi_f64(pair);
+        }
+#pragma unroll
+        for (int i = 0; i < kFixWarpExperts; ++i) {
+          const uint32_t pair = q == 0 ? wv[i].x : q == 1 ? wv[i].y : q == 2 ? wv[i].z : wv[i].w;
+          const double wl = bf16_lo_f64(pair), wh = bf16_hi_f64(pair);
+#pragma unroll
+          for (int j = 0; j < kFixTokens; ++j) {
+            acc[i][j] = fma(xl[j], wl, acc[i][j]);
+            acc[i][j] = fma(xh[j], wh, acc[i][j]);
+          }
+        }
+      }
+    }
+#pragma unroll
+    for (int i = 0; i < kFixWarpExperts; ++i) {
+#pragma unroll
+      for (int j = 0; j < kFixTokens; ++j) {
+        double a = acc[i][j];
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) a += __shfl_xor_sync(0xFFFFFFFFu, a, o);
+        if (lane == 0 && e0 + i < E && b * kFixTokens + j < n)
+          logits[static_cast<int64_t>(tok[j]) * E + e0 + i] = static_cast<float>(a);
+      }
+    }
+  }
+}
+
+// Single logits, the same way: one warp per (token, expert) pair, lanes across H.
+__global__ void __launch_bounds__(256) route_fix_pairs_kernel(const __nv_bfloat16* __restrict__ x,
+                                                              const __nv_bfloat16* __restrict__ gate_w, int H, int E,
+                                                              const int32_t* __restrict__ fix, int64_t T, int pair_cap,
+                                                              float* __restrict__ logits) {
+  const int n = fix[2] < pair_cap ? fix[2] : pair_cap;
+  const int32_t* pairs = fix + 4 + 2 * T;
+  const int vecs = H >> 3;
+  const int lane = threadIdx.x & 31;
+  const int warps = gridDim.x * (blockDim.x >> 5);
+  for (int i = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5); i < n; i += warps) {
+    const int64_t t = pairs[2 * i];
+    const int e = pairs[2 * i + 1];
+    const uint4* xr = reinterpret_cast<const uint4*>(x + t * H);
+    const uint4* wr = reinterpret_cast<const uint4*>(gate_w + static_cast<int64_t>(e) * H);
+    double a0 = 0.0, a1 = 0.0, a2 = 0.0, a3 = 0.0;
+    for (int v = lane; v < vecs; v += 32) {
+      const uint4 xv = xr[v], wv = wr[v];
+      a0 = fma(bf16_lo_f64(xv.x), bf16_lo_f64(wv.x), a0);
+      a1 = fma(bf16_hi_f64(xv.x), bf16_hi_f64(wv.x), a1);
+      a2 = fma(bf16_lo_f64(xv.y), bf16_lo_f64(wv.y), a2);
+      a3 = fma(bf16_hi_f64(xv.y), bf16_hi_f64(wv.y), a3);
+      a0 = fma(bf16_lo_f64(xv.z), bf16_lo_f64(wv.z), a0);
+      a1 = fma(bf16_hi_f64(xv.z), bf16_hi_f64(wv.z), a1);
+      a2 = fma(bf16_lo_f64(xv.w), bf16_lo_f64(wv.w), a2);
+      a3 = fma(bf16_hi_f64(xv.w), bf16_hi_f64(wv.w), a3);
+    }
+    double a = (a0 + a1) + (a2 + a3);
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) a += __shfl_xor_sync(0xFFFFFFFFu, a, o);
+    if (lane == 0) logits[t * E + e] = static_cast<float>(a);
+  }
+}
+
+static int route_P(int n_experts) {
+  const int P = (n_experts + 31) / 32;
+  return P <= 1 ? 1 : P <= 2 ? 2 : P <= 4 ? 4 : P <= 5 ? 5 : P <= 8 ? 8 : P <= 16 ? 16 : 0;
+}
+
+static int64_t route_pair_cap(int64_t T) { return 8 * T + 64; }
+size_t route_fix_bytes(int64_t T) { return static_cast<size_t>(4 + 2 * T + 2 * route_pair_cap(T)) * 4; }
+
+// Routing from the tensor-core router product with the near-tie fix-up: routes every token, lists the
+// close tokens and the logits that decide them, recomputes those exactly (single logits, or whole rows
+// where the pairs could not be listed) and routes the close tokens again.  The selection equals that of
+// correctly rounded fp32 logits.  fix: route_fix_bytes(T) of scratch, laid out as described above.
+int launch_route_topk_fixup(const Handle* h, const void* x, const void* gate_w, float* logits, const float* bias,
+                            int64_t T, int32_t* idx, float* w, int32_t* fix, cudaStream_t st, int* launches) {
+  if (T == 0) return MG_OK;
+  const mg_layer_desc& d = h->d;
+  if (T > (0x7fffffff - 64) / 8) { set_error("token count beyond the fix-up list's index range"); return MG_ERR_SHAPE; }
+  RouteParams rp{d.n_experts, d.top_k, d.n_group, d.topk_group, d.gating, d.norm_topk_prob,
+                 d.routed_scale, route_fix_err(d.hidden), static_cast<int>(route_pair_cap(T)), T};
+  const int P = route_P(d.n_experts);
+  if (P == 0) { set_error("n_experts %d > 512 unsupported by the top-k kernel", d.n_experts); return MG_ERR_SHAPE; }
+  MG_CUDA(cudaMemsetAsync(fix, 0, 16, st));
+  const int warps = 8;
+  dim3 grid(static_cast<unsigned>((T + warps - 1) / warps)), block(warps * 32);
+  const int sms = h->sm_count > 0 ? h->sm_count : 148;
+  const size_t smem = static_cast<size_t>(kFixTokens) * d.hidden * 2;
+  static bool done[64];
+  if (smem > 48 * 1024 && !(h->device >= 0 && h->device < 64 && done[h->device])) {
+    MG_CUDA(cudaFuncSetAttribute(route_fix_logits_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                 static_cast<int>(smem)));
+    if (h->device >= 0 && h->device < 64) done[h->device] = true;
+  }
+  const __nv_bfloat16* xb = static_cast<const __nv_bfloat16*>(x);
+  const __nv_bfloat16* wb = static_cast<const __nv_bfloat16*>(gate_w);
+#define MG_ROUTE_CASE(PP)                                                                              \
+  case PP:                                                                                             \
+    route_topk_kernel<PP><<<grid, block, 0, st>>>(logits, bias, T, rp, idx, w, fix);                   \
+    route_fix_logits_kernel<<<sms, 256, smem, st>>>(xb, wb, d.hidden, d.n_experts, fix, T, logits);    \
+    route_fix_pairs_kernel<<<4 * sms, 256, 0, st>>>(xb, wb, d.hidden, d.n_experts, fix, T, rp.pair_cap, logits); \
+    route_topk_list_kernel<PP><<<sms, block, 0, st>>>(logits, bias, rp, idx, w, fix);                  \
+    break
+  switch (P) {
+    MG_ROUTE_CASE(1); MG_ROUTE_CASE(2); MG_ROUTE_CASE(4); MG_ROUTE_CASE(5); MG_ROUTE_CASE(8); MG_ROUTE_CASE(16);
+  }
+#undef MG_ROUTE_CASE
+  MG_CUDA(cudaGetLastError());
+  if (launches) *launches += 4;
+  return MG_OK;
+}
+
 int launch_route_topk(const Handle* h, const float* logits, const float* bias, int64_t T,
                       int32_t* idx, float* w, cudaStream_t st) {
   if (T == 0) return MG_OK;
   const mg_layer_desc& d = h->d;
   RouteParams rp{d.n_experts, d.top_k, d.n_group, d.topk_group, d.gating, d.norm_topk_prob,
-                 d.routed_scale};
+                 d.routed_scale, 0.f, 0, T};
   const int warps = 8;
   dim3 grid(static_cast<unsigned>((T + warps - 1) / warps)), block(warps * 32);
   const int P = (d.n_experts + 31) / 32;
 #define MG_ROUTE_CASE(PP)                                                             \
-  route_topk_kernel<PP><<<grid, block, 0, st>>>(logits, bias, T, rp, idx, w)
+  route_topk_kernel<PP><<<grid, block, 0, st>>>(logits, bias, T, rp, idx, w, nullptr)
   if (P <= 1) MG_ROUTE_CASE(1);
   else if (P <= 2) MG_ROUTE_CASE(2);
   else if (P <= 4) MG_ROUTE_CASE(4);

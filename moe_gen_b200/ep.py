@@ -145,6 +145,9 @@ class EPMoELayer:
                 mb.idx = torch.empty(Tm, k, **i32)
                 mb.w = torch.empty(Tm, k, dtype=torch.float32, device=self.dev)
                 mb.logits = torch.empty(Tm, E, dtype=torch.float32, device=self.dev)
+                nf = C.c_size_t()
+                L.check(self.lib.mg_route_fix_bytes(Tm, C.byref(nf)))
+                mb.fix = torch.zeros(nf.value // 4, **i32)
                 nb = C.c_size_t()
                 L.check(self.lib.mg_plan_ws_bytes(lay._h, Tm, C.byref(nb)))
                 mb.plan_ws = torch.empty(nb.value, dtype=torch.uint8, device=self.dev)
@@ -350,9 +353,9 @@ class EPMoELayer:
                         L.check(lib.mg_ep_clear_duplicates(h, mb.own[2], mb.cap, st))
                     if self.push_return:
                         L.check(lib.mg_ep_clear_duplicates(h, mb.own[3], mb.cap, st))
-                    L.check(lib.mg_gate_logits(h, xp, lay.gate_w.data_ptr(), Tm, mb.logits.data_ptr(), st))
-                    L.check(lib.mg_route_topk(h, mb.logits.data_ptr(), _ptr(lay.bias), Tm, mb.idx.data_ptr(),
-                                              mb.w.data_ptr(), st))
+                    L.check(lib.mg_gate_route_topk(h, xp, lay.gate_w.data_ptr(), _ptr(lay.bias), Tm,
+                                                   mb.logits.data_ptr(), mb.idx.data_ptr(), mb.w.data_ptr(),
+                                                   mb.fix.data_ptr(), st))
                     L.check(lib.mg_ep_count(h, mb.idx.data_ptr(), Tm, mb.counts.data_ptr(), mb.plan_ws.data_ptr(), st))
                     dist.all_gather_into_tensor(mb.counts_all, mb.counts, group=mb.group)
                     L.check(lib.mg_ep_place(h, mb.idx.data_ptr(), Tm, mb.counts_all.data_ptr(), mb.cap,

@@ -280,6 +280,25 @@ class MoELayer:
                                            w.data_ptr(), self._stream()))
         return idx, w
 
+    def gate_route(self, x: torch.Tensor) -> Tuple[torch.Tensor, torch.Tensor, torch.Tensor, torch.Tensor]:
+        """The routing mg_moe_forward uses: router product on the tensor cores, top-k, and near-tie tokens
+        re-routed from exactly recomputed logits.  -> topk_idx, topk_w, logits (recomputed entries included),
+        fix (int32: [0] tokens routed again, [1] of which with the whole row recomputed, [2] single logits
+        recomputed; tokens from [4], row tokens from [4+T], (token, expert) pairs from [4+2T])."""
+        self._check_in(x, torch.bfloat16, "hidden_states")
+        T = x.shape[0]
+        logits = torch.empty(T, self.E, dtype=torch.float32, device=self.device)
+        idx = torch.empty(T, self.k, dtype=torch.int32, device=self.device)
+        w = torch.empty(T, self.k, dtype=torch.float32, device=self.device)
+        n = C.c_size_t()
+        L.check(self.lib.mg_route_fix_bytes(T, C.byref(n)))
+        fix = torch.zeros(n.value // 4, dtype=torch.int32, device=self.device)
+        with torch.cuda.device(self.device):
+            L.check(self.lib.mg_gate_route_topk(self._h, x.data_ptr(), self.gate_w.data_ptr(), _ptr(self.bias), T,
+                                                logits.data_ptr(), idx.data_ptr(), w.data_ptr(), fix.data_ptr(),
+                                                self._stream()))
+        return idx, w, logits, fix
+
     def permute_plan(self, topk_idx: torch.Tensor, expert_lo: int = 0, n_plan: Optional[int] = None):
         """-> counts [n], offsets [n+1], pad_offsets [n+1], dst_row [T,k] (all int32)."""
         self._check_in(topk_idx, torch.int32, "topk_idx")

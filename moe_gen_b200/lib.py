@@ -26,6 +26,7 @@ OPT_SHARED_EARLY = 6
 OPT_RING_BYTES = 7
 OPT_RING_PERSIST = 8
 OPT_ROWS_BOUND = 9
+OPT_ROUTE_FIXUP = 10
 FP8_AUTO, FP8_PREDEQUANT, FP8_IN_KERNEL, FP8_RING = 0, 1, 2, 3
 
 
@@ -55,6 +56,8 @@ SIGNATURES = {
     "mg_dequant_fp8_block128": [_vp, _vp, _i64, _i64, _vp, _vp],
     "mg_gate_logits": [_vp, _vp, _vp, _i64, _vp, _vp],
     "mg_route_topk": [_vp, _vp, _vp, _i64, _vp, _vp, _vp],
+    "mg_gate_route_topk": [_vp, _vp, _vp, _vp, _i64, _vp, _vp, _vp, _vp, _vp],
+    "mg_route_fix_bytes": [_i64, _P(_sz)],
     "mg_plan_ws_bytes": [_vp, _i64, _P(_sz)],
     "mg_permute_plan": [_vp, _vp, _i64, _i32, _i32, _vp, _vp, _vp, _vp, _vp, _vp],
     "mg_permute_plan_static": [_vp, _vp, _i64, _i32, _i32, _vp, _vp, _vp, _vp, _vp],

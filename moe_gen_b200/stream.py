@@ -89,7 +89,7 @@ class StreamedMoELayer:
         with torch.cuda.device(dev):
             comp = torch.cuda.current_stream()
             st = comp.cuda_stream
-            idx, w = lay.route_topk(lay.gate_logits(x2))
+            idx, w = lay.gate_route(x2)[:2]
             counts, offsets, pad, dst = lay.permute_plan(idx, 0, E)
             rows = (-(-T * k // 128) + E) * 128
             perm = torch.empty(rows, lay.H, dtype=torch.bfloat16, device=dev)

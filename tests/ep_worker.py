@@ -155,7 +155,7 @@ def gpu_ep_worker(rank, world, port, spec, T_global, seed, result):
             overflow_reported = "overflowed" in str(e)
         ep_s.close()
         assert layer.device_status() == (0, 0)            # reading it cleared the word
-    idx_l, w_l = layer.route_topk(layer.gate_logits(x))
+    idx_l, w_l = layer.gate_route(x)[:2]
     gath = [None] * world
     dist.all_gather_object(gath, (ys[0], ys[1], status, same, idx_l.cpu(), w_l.cpu(), overflow_reported))
     if rank == 0:

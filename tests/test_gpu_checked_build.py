@@ -42,7 +42,7 @@ spec = O.LayerSpec(256, 128, 8, 2)
 x, W = O.make_inputs(spec, 64, 5)
 layer = make_layer(spec, W, DEV)
 xd = x.to(DEV)
-idx, w = layer.route_topk(layer.gate_logits(xd))
+idx, w = layer.gate_route(xd)[:2]
 counts, offsets, pad, dst = layer.permute_plan(idx)
 rows = layer.padded_rows(64 * 2)
 assert int(dst.max()) >= 256                       # the plan does address rows beyond the bound declared below

@@ -47,6 +47,34 @@ def _route_equal(spec, idx_gpu, w_gpu, idx_ref, w_ref, logits_ref, bias, exact_l
 
 
 # --------------------------------------------------------------------------- routing
+def test_fixup_recomputes_whole_rows_where_groups_are_not_runs_of_lanes(built_lib):
+    """96 experts in 4 groups of 24: a group is six lanes of four experts, not a power-of-two run, so a
+    token whose group selection is close gets its whole logits row recomputed; the selection still equals
+    that of the exactly rounded logits for every token."""
+    spec = O.LayerSpec(256, 128, 96, 4, 0, 4, 2, O.GATE_SIGMOID_NOAUX_TC, True, 2.5, O.WEIGHT_BF16, O.COMBINE_FP32)
+    T = 60000
+    gen = torch.Generator().manual_seed(77)
+    x = torch.randn(T, spec.hidden, generator=gen).to(torch.bfloat16)
+    gw = (torch.randn(spec.n_experts, spec.hidden, generator=gen) * 0.1).to(torch.bfloat16)
+    bias = torch.randn(spec.n_experts, generator=gen) * 0.01
+    layer = make_layer(spec, O.LayerWeights(gw, bias), DEV)
+    idx, w, logits, fix = layer.gate_route(x.to(DEV))
+    exact = (x.double() @ gw.double().t()).float()
+    eidx, ew = O.route(spec, exact, bias)
+    gi, _ = O.canonical_sets(idx.cpu().long(), w.cpu())
+    ei, _ = O.canonical_sets(eidx, ew)
+    assert torch.equal(gi, ei), f"{int((gi != ei).any(1).sum())} of {T} tokens differ from exact-logit routing"
+    n_fix, n_rows, n_pairs = (int(v) for v in fix[:3])
+    assert 0 < n_rows <= n_fix and n_pairs > 0
+    rows = fix[4 + T:4 + T + n_rows].cpu().long()
+    ulp = torch.finfo(torch.float32).eps * exact[rows].abs().clamp_min(2.0 ** -126)
+    assert bool(((logits.cpu()[rows] - exact[rows]).abs() <= ulp).all())
+    raw = layer.gate_logits(x.to(DEV)).cpu()
+    bound = (6.0e-9 * spec.hidden + 4.0e-6) * exact.abs().amax(1, keepdim=True).clamp_min(1.0)
+    assert float(((raw - exact).abs() / bound).max()) <= 0.5
+    _status_ok(layer)
+
+
 @pytest.mark.parametrize("name", sorted(GATE_CASES))
 def test_topk_on_identical_logits_is_exact_at_full_gate_shapes(built_lib, name):
     cfg, T, seed = GATE_CASES[name]
@@ -68,9 +96,30 @@ def test_topk_on_identical_logits_is_exact_at_full_gate_shapes(built_lib, name):
     gi, gwt = O.canonical_sets(idx.cpu().long(), w.cpu())
     assert np.array_equal(gi.numpy().astype(np.int16), g["topk_idx"])
     assert np.abs(gwt.numpy() - g["topk_w"]).max() <= 2e-6 * max(1.0, spec.routed_scale)
-    # fused path: logits from the tensor-core router GEMM
-    idx2, w2 = layer.route_topk(layer.gate_logits(x.to(DEV)))
+    # fused path: logits from the tensor-core router GEMM, near-tie tokens re-routed from recomputed logits
+    idx2, w2, logits2, fix = layer.gate_route(x.to(DEV))
     _route_equal(spec, idx2, w2, ridx, rw, logits, bias, exact_logits=False)
+    # ... which is the routing of the correctly rounded logits (fp64 product rounded once), token for token
+    exact = (x.double() @ gw.double().t()).float()
+    eidx, ew = O.route(spec, exact, bias)
+    gi, _ = O.canonical_sets(idx2.cpu().long(), w2.cpu())
+    ei, _ = O.canonical_sets(eidx, ew)
+    assert torch.equal(gi, ei), f"{int((gi != ei).any(1).sum())} of {T} tokens differ from exact-logit routing"
+    n_fix, n_rows, n_pairs = (int(v) for v in fix[:3])
+    again = fix[4:4 + n_fix].cpu().long()
+    assert 0 < n_fix <= T // 10 and again.unique().numel() == n_fix
+    assert n_rows == 0 and 0 < n_pairs <= 8 * T + 64                # groups are lane runs here, the pairs fit
+    pairs = fix[4 + 2 * T:4 + 2 * T + 2 * n_pairs].cpu().long().view(-1, 2)
+    assert set(pairs[:, 0].tolist()) == set(again.tolist())
+    raw = layer.gate_logits(x.to(DEV)).cpu()
+    bound = (6.0e-9 * spec.hidden + 4.0e-6) * exact.abs().amax(1, keepdim=True).clamp_min(1.0)
+    assert float(((raw - exact).abs() / bound).max()) <= 0.5       # the error the flagging assumes, with 2x to spare
+    # the recomputed entries are the exact product to the last bit or the one next to it
+    got, want = logits2.cpu()[pairs[:, 0], pairs[:, 1]], exact[pairs[:, 0], pairs[:, 1]]
+    assert bool(((got - want).abs() <= torch.finfo(torch.float32).eps * want.abs().clamp_min(2.0 ** -126)).all())
+    # without the fix-up the staged calls give the raw tensor-core routing
+    idx3, w3 = layer.route_topk(layer.gate_logits(x.to(DEV)))
+    _route_equal(spec, idx3, w3, ridx, rw, logits, bias, exact_logits=False)
     _status_ok(layer)
 
 
@@ -230,7 +279,7 @@ def test_fp8_weights_converted_in_the_gemm_equal_dequantise_first(built_lib, H, 
     x, W = O.make_inputs(spec, 900, 51)
     layer = make_layer(spec, W, DEV)
     xd = x.to(DEV)
-    idx, w = layer.route_topk(layer.gate_logits(xd))
+    idx, w = layer.gate_route(xd)[:2]
     counts, offsets, pad, dst = layer.permute_plan(idx)
     perm = layer.permute_rows(xd, dst, layer.padded_rows(900 * 4))
     h1, o1 = layer.expert_ffn(perm, pad, counts, predequant=False)
@@ -338,7 +387,7 @@ def test_layer_against_reference_fixture(built_lib, name):
     _status_ok(layer)
     # routing as the layer computed it (read back from its workspace through the staged calls)
     logits = O.gate_logits(x, W.gate_w)
-    idx, w = layer.route_topk(layer.gate_logits(xd))
+    idx, w = layer.gate_route(xd)[:2]
     ridx = torch.from_numpy(g["topk_idx"].astype(np.int64))
     rw = torch.from_numpy(g["topk_w"])
     flips = _route_equal(spec, idx, w, ridx, rw, logits, W.bias, exact_logits=False)
@@ -449,7 +498,7 @@ def test_mixtral_layer(built_lib):
     ref = O.layer_forward(spec, x, W)
     # the bf16 router output makes exact ties common; both sides resolve them to the lower id,
     # but a logit that rounds differently can still flip a token: compare only agreeing tokens
-    idx, w = layer.route_topk(layer.gate_logits(x.to(DEV)))
+    idx, w = layer.gate_route(x.to(DEV))[:2]
     same = (O.canonical_sets(idx.cpu().long(), w.cpu())[0] == O.canonical_sets(ref["topk_idx"], ref["topk_w"])[0]).all(1)
     assert float(same.float().mean()) > 0.995
     assert O.rel_l2(y.cpu().float()[same], gold["y"][same]) <= TOL_LAYER
@@ -607,7 +656,7 @@ def test_expert_parallel_ranks_emulated_on_one_gpu(built_lib, n_ranks, dedup, pu
     idx, w, counts, plan_ws = [], [], [], []
     for r, lay in enumerate(ranks):
         xs = xd[r * Tl:(r + 1) * Tl]
-        i_, w_ = lay.route_topk(lay.gate_logits(xs))
+        i_, w_ = lay.gate_route(xs)[:2]
         nb = C.c_size_t()
         L.check(lib.mg_plan_ws_bytes(lay._h, Tl, C.byref(nb)))
         ws = torch.empty(nb.value, dtype=torch.uint8, device=DEV)

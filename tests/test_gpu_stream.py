@@ -57,7 +57,7 @@ def test_routing_aware_streaming_skips_groups_without_rows(built_lib):
     got = _streamed(spec, W, 2, 2, routing_aware=True)
     xd = x.to(DEV)
     assert torch.equal(want.forward(xd).view(torch.int16), got.forward(xd).view(torch.int16))
-    idx, _ = want.route_topk(want.gate_logits(xd))
+    idx, _ = want.gate_route(xd)[:2]
     groups_hit = len(set((idx.cpu().view(-1) // 2).tolist()))
     assert got.last_groups_moved == groups_hit < 8
 
@@ -76,7 +76,7 @@ def test_routing_aware_streaming_orders_the_copies_by_routed_rows(built_lib):
         y1 = got.forward(xd)
         assert torch.equal(y0.view(torch.int16), y1.view(torch.int16))
     assert O.rel_l2(y1.cpu().float(), O.layer_forward(spec, x, W, gold_fp32=True)["y"]) <= 1e-2
-    idx, _ = want.route_topk(want.gate_logits(xd))
+    idx, _ = want.gate_route(xd)[:2]
     per_group = torch.bincount(idx.cpu().view(-1).long() // 4, minlength=4).tolist()
     expect = sorted((g for g in range(4) if per_group[g] > 0), key=lambda g: (-per_group[g], g))
     assert got.last_group_order == expect
