@@ -419,6 +419,50 @@ def quick_config(name: str, T: int, zipf: float, world: int, rank: int, device, 
     return out
 
 
+def host_copy_ceiling(xh: torch.Tensor, yh: torch.Tensor, device, world: int, reps: int = 5):
+    """Pinned-host <-> device copies of one step's input and output, all ranks at once, max over ranks."""
+    import torch.distributed as dist
+    xd = torch.empty_like(xh, device=device)
+    yd = torch.empty_like(yh, device=device)
+    s_in, s_out = torch.cuda.Stream(device), torch.cuda.Stream(device)
+
+    def timed(do_in: bool, do_out: bool) -> float:
+        torch.cuda.synchronize()
+        if world > 1:
+            dist.barrier()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        s_in.wait_stream(torch.cuda.current_stream())
+        s_out.wait_stream(torch.cuda.current_stream())
+        for _ in range(reps):
+            if do_in:
+                with torch.cuda.stream(s_in):
+                    xd.copy_(xh, non_blocking=True)
+            if do_out:
+                with torch.cuda.stream(s_out):
+                    yh.copy_(yd, non_blocking=True)
+        torch.cuda.current_stream().wait_stream(s_in)
+        torch.cuda.current_stream().wait_stream(s_out)
+        e1.record()
+        torch.cuda.synchronize()
+        ms = e0.elapsed_time(e1) / reps
+        if world > 1:
+            t = torch.tensor([ms], device=device)
+            dist.all_reduce(t, op=dist.ReduceOp.MAX)
+            ms = float(t.item())
+        return ms
+
+    yd.zero_()
+    timed(True, True)                                    # warm-up
+    h2d, d2h, both = timed(True, False), timed(False, True), timed(True, True)
+    nbytes = xh.numel() * 2
+    return {"bytes_per_rank_each_way": nbytes, "h2d_ms": round(h2d, 3), "d2h_ms": round(d2h, 3), "both_ms": round(both, 3),
+            "h2d_gbs_per_rank": round(nbytes / h2d / 1e6, 1), "d2h_gbs_per_rank": round(nbytes / d2h / 1e6, 1),
+            "both_gbs_per_rank_each_way": round(nbytes / both / 1e6, 1),
+            "note": "all ranks copy at once; slowest rank; the step's e2e time cannot be below both_ms, nor below "
+                    "the device step plus the first chunk in and the last chunk out"}
+
+
 def algorithmic(name: str, T: int):
     H, I, E, k, Is = WORKLOADS[name][:5]
     R = T * k
@@ -648,6 +692,11 @@ def main():
                "h2d_bytes_per_step": xh.numel() * 2 * world, "d2h_bytes_per_step": yh.numel() * 2 * world,
                "equals_device_path": bool(torch.equal(yh.view(torch.int16), y.cpu().view(torch.int16))),
                "chunks_per_rank": args.ep_chunks}
+
+    # what the host link delivers for this step's buffers with all ranks copying at once: H2D alone, D2H
+    # alone and both directions together (the e2e path's floor is the last of the three, fully overlapped)
+    if e2e is not None:
+        e2e["host_copy"] = host_copy_ceiling(xh, yh, device, world)
 
     # rows each GPU's experts receive (all ranks' picks), for the load-balance figures
     ep_load = None
