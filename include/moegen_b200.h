@@ -324,7 +324,7 @@ int mg_moe_forward_from_logits(mg_handle h, const void* d_x, int64_t n_tokens, c
  * with peer sources).  Between the steps the ranks need a barrier (any stream-ordered
  * collective, e.g. a one-element NCCL all-reduce): after dispatch before the experts run, and
  * after the experts before combine.  Sequence per forward on each rank:
- *   mg_gate_logits, mg_route_topk, mg_ep_count -> all-gather counts -> mg_ep_place,
+ *   mg_gate_route_topk (or mg_gate_logits + mg_route_topk), mg_ep_count -> all-gather counts -> mg_ep_place,
  *   mg_ep_dispatch, [mg_shared_ffn], barrier, mg_expert_ffn, barrier, mg_ep_combine. */
 
 /* Device memory that can be shared with the other ranks / its 64-byte IPC handle / mapping
