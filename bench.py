@@ -749,11 +749,20 @@ def main():
     others = None
     if not args.no_other_configs and name == "v3" and args.zipf == 0 and T == WORKLOADS["v3"][12]:
         others = []
+
+        def side_entry(oname, oT, ozipf, **kw):
+            # a side entry that fails its gate is reported as failed in its own line (the gate's verdict is
+            # all-reduced, so every rank takes the same branch); the headline's own gate above ends the run
+            try:
+                others.append(quick_config(oname, oT, ozipf, world, rank, device, **kw))
+            except SystemExit as e:
+                others.append({"workload": oname, "tokens": oT, "zipf_alpha": ozipf, "failed": str(e)[:400]})
+
         for oname, oT in (("v2lite", 2048), ("mixtral8x7b", 16384), ("v2_236b", 32768), ("v2_236b", 512)):
             if oT % world == 0 and WORKLOADS[oname][2] % world == 0:
-                others.append(quick_config(oname, oT, 0.0, world, rank, device))
+                side_entry(oname, oT, 0.0)
         for oT in (64, 256, 1024, 4096, 16384):
-            others.append(quick_config("v3", oT, 1.2, world, rank, device, reuse=layer))
+            side_entry("v3", oT, 1.2, reuse=layer)
         base.set_router(*router_tensors(name, device, args.zipf))
         if world > 1:
             layer.reconfigure(capacity_factor=cap)
