@@ -630,6 +630,7 @@ def main():
     else:
         layer.timing = False
         phases = layer.phase_times()
+        n_micro_batches = max(len(layer._mbs), 1)       # read now: later legs re-allocate the buffers
         all_phases = [None] * world
         dist.all_gather_object(all_phases, {k_: round(v, 3) for k_, v in phases.items()})
         stage_ms = {"expert_gemm1": 0.0}
@@ -777,7 +778,7 @@ def main():
         # expert phase of the first micro-batch = gate/up GEMM + down GEMM (+ FP8 conversion) of this
         # rank's experts over 1/n_micro of the rows
         t_g1 = phases["expert_ffn"] * 1e-3
-        n_mb = len(layer._mbs)
+        n_mb = n_micro_batches
         tf = (alg["gemm1_flops"] + alg["gemm2_flops"]) / world / n_mb / t_g1 / 1e12 if t_g1 > 0 else 0.0
     else:
         t_g1 = stage_ms["expert_gemm1"] * 1e-3
@@ -822,7 +823,7 @@ def main():
     if phases is not None:
         stages = {k_: {"ms": round(v, 4)} for k_, v in phases.items()}
         stages["by_rank_ms"] = all_phases
-        stages["note"] = (f"phases of the first of {len(layer._mbs)} pipelined micro-batches on its stream; "
+        stages["note"] = (f"phases of the first of {n_micro_batches} pipelined micro-batches on its stream; "
                           f"each rank fetches {Tl * k * H * 2 * (world - 1) / world / 1e6:.0f} MB over NVLink per step in the combine "
                           f"and sends at most that in the dispatch (one row per token and destination GPU)")
 
