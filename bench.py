@@ -510,6 +510,9 @@ def main():
                     help="expert parallel: 1 owners push results home part by part beside the down projection, "
                          "0 the combine gathers them after the experts (-1: the library's default, 0)")
     ap.add_argument("--ep-parts", type=int, default=4, help="expert parallel: parts of the pushed return")
+    ap.add_argument("--ep-copy", type=int, default=-1,
+                    help="expert parallel: 1 = the results travel home through the copy engines beside the down "
+                         "projection, 0 = the combine gathers them")
     ap.add_argument("--shared-early", type=int, default=-1,
                     help="1/0 shared expert beside the routing kernels / after the routed experts")
     ap.add_argument("--pair-gemm", type=int, default=-1, help="1/0 force the SM-pair expert GEMM on/off")
@@ -570,7 +573,8 @@ def main():
         # skewed routing can send most rows to one GPU: size the receive buffers for it
         cap = args.capacity_factor if args.capacity_factor > 0 else (float(world) if args.zipf > 0 else 2.0)
         layer = EPMoELayer(build_layer(name, device, rank, world, args.zipf), capacity_factor=cap, n_micro=args.micro,
-                           dedup=bool(args.ep_dedup), push_return=None if args.ep_push < 0 else bool(args.ep_push), return_parts=args.ep_parts)
+                           dedup=bool(args.ep_dedup), push_return=None if args.ep_push < 0 else bool(args.ep_push), return_parts=args.ep_parts,
+                           copy_return=args.ep_copy > 0)
         x = make_tokens(name, T // world, device, rank, args.zipf)
         step = lambda: layer.forward(x)                                   # noqa: E731
         T_total = T
@@ -634,15 +638,20 @@ def main():
         all_phases = [None] * world
         dist.all_gather_object(all_phases, {k_: round(v, 3) for k_, v in phases.items()})
         stage_ms = {"expert_gemm1": 0.0}
-        # router product, top-k, count + scan, layout + place, dispatch (+ duplicate table clear and fill),
-        # [shared 2], experts (2, or 2 GEMMs + 2 de-quantisations per chunk of experts when FP8 weights are
-        # pre-dequantised), combine; NCCL kernels not counted
+        # router product, top-k + the three fix-up kernels, count + scan, layout + place, dispatch (+ duplicate
+        # table fill), [shared 2], experts (2, or 2 GEMMs + 2 de-quantisations per chunk of experts when FP8
+        # weights are pre-dequantised; the down projection in parts, each followed by a return kernel, when the
+        # return is pushed; in parts and one offset kernel when the copy engines carry it), combine; NCCL
+        # kernels, memsets and copy-engine copies not counted
         parts = min(layer.return_parts, base.e_local, 8)
+        pushed = layer.push_return and not layer.copy_return
         if layer.deq is not None:
-            experts = 16 + 16 + (8 if layer.push_return else 0)
+            experts = 16 + 16 + (8 if pushed else 0)
         else:
-            experts = 1 + (2 * parts if layer.push_return else 1)
-        launches = 7 + (1 if layer.dedup else 0) + (2 if Is else 0) + experts + 1
+            experts = 1 + (2 * parts if pushed else parts if layer.copy_return else 1)
+        fixup = 3 if WORKLOADS[name][7] != 3 else 0
+        launches = (7 + fixup + (1 if layer.dedup else 0) + (2 if Is else 0) + experts + 1
+                    + (1 if layer.copy_return else 0))
     code, detail = base.device_status()
     if code != 0:
         raise SystemExit(f"device status {code} (detail {detail}) in the timed region")

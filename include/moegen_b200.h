@@ -397,6 +397,28 @@ int mg_ep_combine_slots(mg_handle h, const void* d_ret, const void* d_out_rows, 
                         const int32_t* d_topk_idx, const float* d_topk_w, const void* d_shared_out, int64_t n_tokens,
                         void* d_y, void* stream);
 
+/* The return through the copy engines (no counterpart in the reference either).  The rows this rank's
+ * experts computed for one source rank and one expert are contiguous in d_out_rows, and that source rank
+ * wants them contiguous too, at the place its own expert-sorted order gives expert e.  So the return is
+ * one device-to-device copy per (expert, source rank), issued on a side stream as soon as the part of the
+ * down projection that holds the expert is done, into the source rank's return buffer ret[T_local * k, H]
+ * (its own rank included): no SM stores a remote row.  The sizes are the gathered counts, which this call
+ * needs in HOST memory: h_counts_all[ep_size][n_experts], i.e. the caller reads them back after the
+ * all-gather (one synchronising 4 * ep_size * n_experts byte copy per forward).
+ *   mg_ep_mirror_delta   d_delta[e] = what turns a row number of the owner's layout (d_dst) into a row of
+ *                        this rank's return buffer, from the gathered counts on the device;
+ *   mg_ep_combine_mirror the combine over the return buffer alone (local, HBM speed), after the barrier
+ *                        that follows the experts.
+ * Bit-identical to the other two returns. */
+int mg_ep_expert_ffn_copy_return(mg_handle h, const void* d_recv_x, const int32_t* d_recv_pad,
+                                 const int32_t* d_recv_counts, int64_t cap_rows, const void* d_packed, void* d_h_buf,
+                                 void* d_out_rows, void* d_dequant_ws, const int32_t* h_counts_all,
+                                 void* const* peer_ret, int32_t n_parts, void* stream);
+int mg_ep_mirror_delta(mg_handle h, const int32_t* d_counts_all, int32_t* d_delta, void* stream);
+int mg_ep_combine_mirror(mg_handle h, const void* d_mirror, const int32_t* d_dst, const int32_t* d_delta,
+                         const int32_t* d_topk_idx, const float* d_topk_w, const void* d_shared_out,
+                         int64_t n_tokens, void* d_y, void* stream);
+
 /* peer_out[ep_size]: every rank's out_rows.  Replaces the return all_to_all and the
  * weighted sum (modeling_deepseek_v3.py:692-710). */
 int mg_ep_combine(mg_handle h, void* const* peer_out, const int32_t* d_dst, const int32_t* d_topk_idx,

@@ -191,6 +191,7 @@ int mg_create(const mg_layer_desc* desc, mg_handle* out) {
   h->deq_packed = nullptr;
   h->deq_stream = nullptr;
   h->side = nullptr;
+  h->ret_streams_used = false;
   h->ev_entry = nullptr;
   for (int i = 0; i < kDequantChunks; ++i) h->ev_w13[i] = h->ev_w2[i] = nullptr;
   h->stage_calls = 0;
@@ -231,6 +232,10 @@ int mg_destroy(mg_handle hh) {
     cudaStreamDestroy(h->side3);
     for (int i = 0; i < kDequantChunks; ++i) cudaEventDestroy(h->ev_part[i]);
     cudaEventDestroy(h->ev_ret);
+    for (int i = 0; i < kMaxPeers; ++i) {
+      cudaStreamDestroy(h->ret_streams[i]);
+      cudaEventDestroy(h->ev_rets[i]);
+    }
   }
   if (h->ev_shared_in) cudaEventDestroy(h->ev_shared_in);
   if (h->ev_shared_out) cudaEventDestroy(h->ev_shared_out);
@@ -473,19 +478,70 @@ static int ensure_return_stream(Handle* h) {
   MG_CUDA(cudaStreamCreateWithFlags(&h->side3, cudaStreamNonBlocking));
   for (int i = 0; i < kDequantChunks; ++i) MG_CUDA(cudaEventCreateWithFlags(&h->ev_part[i], cudaEventDisableTiming));
   MG_CUDA(cudaEventCreateWithFlags(&h->ev_ret, cudaEventDisableTiming));
+  for (int i = 0; i < kMaxPeers; ++i) {
+    MG_CUDA(cudaStreamCreateWithFlags(&h->ret_streams[i], cudaStreamNonBlocking));
+    MG_CUDA(cudaEventCreateWithFlags(&h->ev_rets[i], cudaEventDisableTiming));
+  }
   return MG_OK;
 }
 
 // the output rows of local experts [lo, lo + n) are complete on `st`: send them home on the return stream
+// Copy-engine return of the local experts [lo, lo + n): for every expert and source rank one copy of that
+// rank's rows (contiguous in out_rows: ep_layout_kernel's order) to where the source rank's own expert-sorted
+// order puts them in its buffer.  All sizes come from the gathered counts in host memory.
+static int copy_part(Handle* h, const ReturnHook* hook, const void* out_rows, int lo, int n, cudaEvent_t ready) {
+  const int N = h->d.ep_size, E = h->d.n_experts, El = h->e_local, me = h->d.ep_rank;
+  for (int s = 0; s < N; ++s) MG_CUDA(cudaStreamWaitEvent(h->ret_streams[s], ready, 0));
+  h->ret_streams_used = true;
+  const int32_t* cnt = hook->host_counts;
+  const size_t row_bytes = static_cast<size_t>(h->d.hidden) * 2;
+  // padded offsets of this rank's experts up to lo, and whether the layout kernel dropped this owner's rows
+  int64_t pad_e = 0, pad_all = 0;
+  for (int j = 0; j < El; ++j) {
+    int64_t tot = 0;
+    for (int s = 0; s < N; ++s) tot += cnt[static_cast<size_t>(s) * E + me * El + j];
+    if (j < lo) pad_e += (tot + kTileM - 1) / kTileM * kTileM;
+    pad_all += (tot + kTileM - 1) / kTileM * kTileM;
+  }
+  if (pad_all > hook->cap_rows) return MG_OK;              // overflow: nothing was dispatched here (status word set)
+  for (int j = lo; j < lo + n; ++j) {
+    const int e = me * El + j;
+    int64_t seg = pad_e, tot = 0;
+    for (int s = 0; s < N; ++s) {
+      const int64_t rows = cnt[static_cast<size_t>(s) * E + e];
+      if (rows > 0) {
+        int64_t own = 0;                                    // first row of expert e in rank s's own order
+        for (int e2 = 0; e2 < e; ++e2) own += cnt[static_cast<size_t>(s) * E + e2];
+        MG_CUDA(cudaMemcpyAsync(static_cast<uint8_t*>(hook->rets.p[s]) + own * row_bytes,
+                                static_cast<const uint8_t*>(out_rows) + seg * row_bytes, rows * row_bytes,
+                                cudaMemcpyDeviceToDevice, h->ret_streams[s]));
+      }
+      seg += rows;
+      tot += rows;
+    }
+    pad_e += (tot + kTileM - 1) / kTileM * kTileM;
+  }
+  return MG_OK;
+}
+
 static int push_part(Handle* h, const ReturnHook* hook, const void* out_rows, const int32_t* pad, int lo, int n,
                      int part, cudaStream_t st) {
   cudaEvent_t ev = h->ev_part[part % kDequantChunks];
   MG_CUDA(cudaEventRecord(ev, st));
+  if (hook->host_counts != nullptr) return copy_part(h, hook, out_rows, lo, n, ev);
   MG_CUDA(cudaStreamWaitEvent(h->side3, ev, 0));
   return launch_return_rows(h, out_rows, hook->back, pad, lo, n, hook->rets, h->side3);
 }
 
 static int join_return(Handle* h, cudaStream_t st) {
+  if (h->ret_streams_used) {
+    for (int s = 0; s < h->d.ep_size; ++s) {
+      MG_CUDA(cudaEventRecord(h->ev_rets[s], h->ret_streams[s]));
+      MG_CUDA(cudaStreamWaitEvent(st, h->ev_rets[s], 0));
+    }
+    h->ret_streams_used = false;
+    return MG_OK;
+  }
   MG_CUDA(cudaEventRecord(h->ev_ret, h->side3));
   MG_CUDA(cudaStreamWaitEvent(st, h->ev_ret, 0));
   return MG_OK;

@@ -85,6 +85,11 @@ struct Handle {
   cudaEvent_t ev_in[2], ev_done[2], ev_out[2], ev_host;
   cudaStream_t side3;     // expert-parallel return: pushes of finished expert parts run here beside the GEMMs
   cudaEvent_t ev_part[kDequantChunks], ev_ret;
+  // copy-engine return: one stream per destination rank, so that the copies to different peers run on
+  // different engines at once (one stream of 4 MB copies reaches about 300 GB/s)
+  cudaStream_t ret_streams[8];
+  cudaEvent_t ev_rets[8];
+  bool ret_streams_used;
   cudaStream_t side2;     // the shared expert's GEMMs run here beside the routing and scatter kernels
   cudaEvent_t ev_shared_in, ev_shared_out;
   int opt_shared_early;
@@ -145,9 +150,14 @@ struct Guard {
 // expert-parallel return pushed from inside the expert FFN: after the down projection of each part of the
 // local experts, their output rows travel to the token owners' return buffers on a side stream
 struct ReturnHook {
-  const int32_t* back;    // this rank's return table [cap_rows]
+  const int32_t* back;    // this rank's return table [cap_rows] (pushed by a kernel)
   PeerPtrs rets;          // every rank's return buffer as mapped here
   int n_parts;            // parts the down projection is cut into (when it is not chunked already)
+  // copied by the copy engines instead (back == nullptr): the gathered counts [ep_size][E] in HOST memory;
+  // every (expert, source rank) segment of out_rows goes to the source rank's buffer at the place the
+  // source rank's own expert-sorted order gives it
+  const int32_t* host_counts;
+  int64_t cap_rows;
 };
 int launch_dispatch_rows(const Handle* h, const void* x, const int32_t* dst, int64_t T,
                          const PeerPtrs& peers, const PeerPtrs* dups, const PeerPtrs* backs, cudaStream_t st);
@@ -155,6 +165,9 @@ int launch_return_rows(const Handle* h, const void* out_rows, const int32_t* bac
                        int e_n, const PeerPtrs& rets, cudaStream_t st);
 int launch_combine_slots(const Handle* h, const void* ret_rows, const void* own_out_rows, const int32_t* dst,
                          const int32_t* idx, const float* w, const void* shared, int64_t T, void* y, cudaStream_t st);
+int launch_mirror_delta(const Handle* h, const int32_t* counts_all, int32_t* delta, cudaStream_t st);
+int launch_combine_mirror(const Handle* h, const void* mirror, const int32_t* dst, const int32_t* delta,
+                          const int32_t* idx, const float* w, const void* shared, int64_t T, void* y, cudaStream_t st);
 int launch_fill_duplicates(const Handle* h, void* rows, const int32_t* dup, int64_t n_rows, cudaStream_t st);
 int launch_combine_peers(const Handle* h, const PeerPtrs& peers, const int32_t* dst,
                          const int32_t* idx, const float* w, const void* shared, int64_t T, void* y,

@@ -145,13 +145,59 @@ int mg_ep_expert_ffn_return(mg_handle hh, const void* d_recv_x, const int32_t* d
              "mg_ep_expert_ffn_return: null pointer");
   MG_REQUIRE(cap_rows >= 0 && cap_rows % kTileM == 0, MG_ERR_SHAPE, "cap_rows=%lld must be a multiple of %d",
              static_cast<long long>(cap_rows), kTileM);
-  ReturnHook hook;
+  ReturnHook hook{};
   hook.back = d_back;
   hook.n_parts = n_parts;
   int rc = gather_peers(h, peer_ret, &hook.rets);
   if (rc != MG_OK) return rc;
   return expert_ffn_return(h, d_recv_x, d_recv_pad, d_recv_counts, cap_rows, d_packed, d_h_buf, d_out_rows, d_dequant_ws,
                            hook, static_cast<cudaStream_t>(stream));
+}
+
+int mg_ep_expert_ffn_copy_return(mg_handle hh, const void* d_recv_x, const int32_t* d_recv_pad,
+                                 const int32_t* d_recv_counts, int64_t cap_rows, const void* d_packed, void* d_h_buf,
+                                 void* d_out_rows, void* d_dequant_ws, const int32_t* h_counts_all,
+                                 void* const* peer_ret, int32_t n_parts, void* stream) {
+  MG_TRACE("mg_ep_expert_ffn_copy_return", cap_rows);
+  Handle* h = check_handle(hh);
+  if (!h) return MG_ERR_STATE;
+  MG_REQUIRE(d_recv_x && d_recv_pad && d_recv_counts && d_packed && d_h_buf && d_out_rows && h_counts_all, MG_ERR_NULL,
+             "mg_ep_expert_ffn_copy_return: null pointer");
+  MG_REQUIRE(cap_rows >= 0 && cap_rows % kTileM == 0, MG_ERR_SHAPE, "cap_rows=%lld must be a multiple of %d",
+             static_cast<long long>(cap_rows), kTileM);
+  const int64_t n = static_cast<int64_t>(h->d.ep_size) * h->d.n_experts;
+  for (int64_t i = 0; i < n; ++i)
+    MG_REQUIRE(h_counts_all[i] >= 0 && h_counts_all[i] <= kPeerRowMask, MG_ERR_SHAPE,
+               "mg_ep_expert_ffn_copy_return: count %d at %lld is not a row count", h_counts_all[i], static_cast<long long>(i));
+  ReturnHook hook{};
+  hook.back = nullptr;
+  hook.n_parts = n_parts;
+  hook.host_counts = h_counts_all;
+  hook.cap_rows = cap_rows;
+  int rc = gather_peers(h, peer_ret, &hook.rets);
+  if (rc != MG_OK) return rc;
+  return expert_ffn_return(h, d_recv_x, d_recv_pad, d_recv_counts, cap_rows, d_packed, d_h_buf, d_out_rows, d_dequant_ws,
+                           hook, static_cast<cudaStream_t>(stream));
+}
+
+int mg_ep_mirror_delta(mg_handle hh, const int32_t* d_counts_all, int32_t* d_delta, void* stream) {
+  Handle* h = check_handle(hh);
+  if (!h) return MG_ERR_STATE;
+  MG_REQUIRE(d_counts_all && d_delta, MG_ERR_NULL, "mg_ep_mirror_delta: null pointer");
+  return launch_mirror_delta(h, d_counts_all, d_delta, static_cast<cudaStream_t>(stream));
+}
+
+int mg_ep_combine_mirror(mg_handle hh, const void* d_mirror, const int32_t* d_dst, const int32_t* d_delta,
+                         const int32_t* d_topk_idx, const float* d_topk_w, const void* d_shared_out, int64_t T,
+                         void* d_y, void* stream) {
+  MG_TRACE("mg_ep_combine_mirror", T);
+  Handle* h = check_handle(hh);
+  if (!h) return MG_ERR_STATE;
+  MG_REQUIRE(T >= 0, MG_ERR_SHAPE, "negative token count");
+  if (T == 0) return MG_OK;
+  MG_REQUIRE(d_mirror && d_dst && d_delta && d_topk_idx && d_topk_w && d_y, MG_ERR_NULL, "mg_ep_combine_mirror: null pointer");
+  return launch_combine_mirror(h, d_mirror, d_dst, d_delta, d_topk_idx, d_topk_w, d_shared_out, T, d_y,
+                               static_cast<cudaStream_t>(stream));
 }
 
 int mg_ep_combine_slots(mg_handle hh, const void* d_ret, const void* d_out_rows, const int32_t* d_dst,

@@ -979,7 +979,8 @@ __global__ void __launch_bounds__(256) combine_kernel(PeerPtrs bufs,
                                                       const uint4* __restrict__ shared,
                                                       const uint4* residual,
                                                       int64_t T, int k, int vec_per_row, int v_chunk,
-                                                      uint4* y, int by_slot, Guard guard) {
+                                                      uint4* y, int by_slot, const int32_t* __restrict__ delta,
+                                                      Guard guard) {
   const int lane = threadIdx.x & 31;
   const int64_t t = static_cast<int64_t>(blockIdx.x) * (blockDim.x >> 5) + (threadIdx.x >> 5);
   if (t >= T) return;
@@ -992,6 +993,9 @@ __global__ void __launch_bounds__(256) combine_kernel(PeerPtrs bufs,
       my_dst = -1;
     if (by_slot > 0 && my_dst >= 0 && (my_dst >> kPeerShift) != by_slot - 1)
       my_dst = (my_dst & ~kPeerRowMask) | static_cast<int32_t>(t * k + lane);
+    // mirror of the owners' rows in this rank's own expert-sorted order (bufs.p[0]): row in the owner's
+    // buffer + the expert's offset between the two layouts
+    if (delta != nullptr && my_dst >= 0) my_dst = (my_dst & kPeerRowMask) + delta[topk_idx[t * k + lane]];
     my_w = topk_w[t * k + lane];
     if (MODE == MG_COMBINE_BF16_SEQ) my_e = topk_idx[t * k + lane];
     if (MODE != MG_COMBINE_FP32) my_w = round_bf16(my_w);
@@ -1079,7 +1083,8 @@ __global__ void __launch_bounds__(256) combine_kernel(PeerPtrs bufs,
 template <bool PEER>
 static int launch_combine_impl(const Handle* h, const PeerPtrs& bufs, const int32_t* dst_row,
                                const int32_t* idx, const float* w, const void* shared, const void* residual,
-                               int64_t T, void* y, cudaStream_t st, int by_slot = 0) {
+                               int64_t T, void* y, cudaStream_t st, int by_slot = 0,
+                               const int32_t* delta = nullptr) {
   if (T == 0) return MG_OK;
   const int warps = 8;
   const int k = h->d.top_k, vpr = h->d.hidden / 8;
@@ -1095,7 +1100,7 @@ static int launch_combine_impl(const Handle* h, const PeerPtrs& bufs, const int3
   combine_kernel<M, PEER><<<grid, block, 0, st>>>(bufs, dst_row, idx, w,                          \
                                                   static_cast<const uint4*>(shared),              \
                                                   static_cast<const uint4*>(residual), T, k, vpr, \
-                                                  v_chunk, static_cast<uint4*>(y), by_slot,                     \
+                                                  v_chunk, static_cast<uint4*>(y), by_slot, delta,              \
                                                   Guard{h->d_status, h->guard_rows, PEER ? h->d.ep_size : 1})
   switch (h->d.combine_mode) {
     case MG_COMBINE_FP32: MG_COMBINE_CASE(MG_COMBINE_FP32); break;
@@ -1122,6 +1127,59 @@ int launch_combine_slots(const Handle* h, const void* ret_rows, const void* own_
   for (int r = 0; r < h->d.ep_size && r < kMaxPeers; ++r) bufs.p[r] = const_cast<void*>(ret_rows);
   bufs.p[h->d.ep_rank] = const_cast<void*>(own_out_rows);
   return launch_combine_impl<true>(h, bufs, dst, idx, w, shared, nullptr, T, y, st, h->d.ep_rank + 1);
+}
+
+int launch_combine_mirror(const Handle* h, const void* mirror, const int32_t* dst, const int32_t* delta,
+                          const int32_t* idx, const float* w, const void* shared, int64_t T, void* y, cudaStream_t st) {
+  PeerPtrs bufs{};
+  for (int r = 0; r < h->d.ep_size && r < kMaxPeers; ++r) bufs.p[r] = const_cast<void*>(mirror);
+  return launch_combine_impl<true>(h, bufs, dst, idx, w, shared, nullptr, T, y, st, 0, delta);
+}
+
+// delta[e] = (first row of expert e in this rank's own expert-sorted order, unpadded)
+//          - (first row of this rank's rows of expert e in the owner's buffer):
+// what turns a row number of the owner's layout (ep_layout_kernel) into a row of this rank's mirror.
+__global__ void __launch_bounds__(512) ep_mirror_delta_kernel(const int32_t* __restrict__ counts_all, int n_ranks,
+                                                              int rank, int E, int e_local,
+                                                              int32_t* __restrict__ delta) {
+  __shared__ int32_t tot[kMaxExperts];
+  __shared__ int32_t before[kMaxExperts];
+  __shared__ int32_t pad[kMaxExperts];
+  __shared__ int32_t own[kMaxExperts];
+  for (int e = threadIdx.x; e < E; e += blockDim.x) {
+    int32_t t = 0, b = 0;
+    for (int s = 0; s < n_ranks; ++s) {
+      const int32_t c = counts_all[s * E + e];
+      if (s < rank) b += c;
+      t += c;
+    }
+    tot[e] = t;
+    before[e] = b;
+  }
+  __syncthreads();
+  if (threadIdx.x < n_ranks) {
+    const int d = threadIdx.x;
+    int32_t p = 0;
+    for (int j = 0; j < e_local; ++j) {
+      pad[d * e_local + j] = p;
+      p += (tot[d * e_local + j] + kTileM - 1) / kTileM * kTileM;
+    }
+  }
+  if (threadIdx.x == 32) {
+    int32_t p = 0;
+    for (int e = 0; e < E; ++e) {
+      own[e] = p;
+      p += counts_all[rank * E + e];
+    }
+  }
+  __syncthreads();
+  for (int e = threadIdx.x; e < E; e += blockDim.x) delta[e] = own[e] - pad[e] - before[e];
+}
+
+int launch_mirror_delta(const Handle* h, const int32_t* counts_all, int32_t* delta, cudaStream_t st) {
+  ep_mirror_delta_kernel<<<1, 512, 0, st>>>(counts_all, h->d.ep_size, h->d.ep_rank, h->d.n_experts, h->e_local, delta);
+  MG_CUDA(cudaGetLastError());
+  return MG_OK;
 }
 
 int launch_combine_peers(const Handle* h, const PeerPtrs& peers, const int32_t* dst,

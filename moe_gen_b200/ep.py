@@ -68,7 +68,7 @@ class EPMoELayer:
 
     def __init__(self, layer: MoELayer, group: Optional[dist.ProcessGroup] = None, capacity_factor: float = 2.0,
                  n_micro: int = 1, dedup: bool = True, min_headroom: int = 4096, push_return: Optional[bool] = None,
-                 return_parts: int = 4):
+                 return_parts: int = 4, copy_return: bool = False):
         self.layer = layer
         self.group = group
         self.rank = dist.get_rank(group)
@@ -90,6 +90,11 @@ class EPMoELayer:
         # (24.5 against 21.4 ms) while the combine gets 2.2 ms shorter: 30.2 against 29.4 ms per step
         self.push_return = False if push_return is None else push_return
         self.return_parts = return_parts
+        # the owners' copy engines carry every (expert, source rank) segment of the results into the source
+        # rank's return buffer, in that rank's own expert-sorted order, part by part beside the down projection;
+        # the combine is local.  Needs the gathered counts on the host: one small synchronising read per
+        # forward, taken after the dispatch has been enqueued.  Wins over push_return when both are set.
+        self.copy_return = copy_return
         self.lib = layer.lib
         self.dev = layer.device
         self._mbs: List[_MicroBatch] = []
@@ -153,6 +158,9 @@ class EPMoELayer:
                 mb.plan_ws = torch.empty(nb.value, dtype=torch.uint8, device=self.dev)
                 mb.h_buf = torch.empty(cap, lay.I, dtype=torch.bfloat16, device=self.dev)
                 mb.flag = torch.zeros(1, dtype=torch.int32, device=self.dev)
+                mb.delta = torch.zeros(E, **i32)
+                mb.counts_host = torch.zeros(self.world, E, dtype=torch.int32).pin_memory()
+                mb.counts_event = torch.cuda.Event()
                 mb.stream = self._streams[i]
                 mb.group = self._groups[i]
                 mb.imported = []
@@ -351,13 +359,17 @@ class EPMoELayer:
                     # exchange, i.e. before any rank can dispatch
                     if self.dedup:
                         L.check(lib.mg_ep_clear_duplicates(h, mb.own[2], mb.cap, st))
-                    if self.push_return:
+                    if self.push_return and not self.copy_return:
                         L.check(lib.mg_ep_clear_duplicates(h, mb.own[3], mb.cap, st))
                     L.check(lib.mg_gate_route_topk(h, xp, lay.gate_w.data_ptr(), _ptr(lay.bias), Tm,
                                                    mb.logits.data_ptr(), mb.idx.data_ptr(), mb.w.data_ptr(),
                                                    mb.fix.data_ptr(), st))
                     L.check(lib.mg_ep_count(h, mb.idx.data_ptr(), Tm, mb.counts.data_ptr(), mb.plan_ws.data_ptr(), st))
                     dist.all_gather_into_tensor(mb.counts_all, mb.counts, group=mb.group)
+                    if self.copy_return:
+                        mb.counts_host.copy_(mb.counts_all, non_blocking=True)
+                        mb.counts_event.record(mb.stream)
+                        L.check(lib.mg_ep_mirror_delta(h, mb.counts_all.data_ptr(), mb.delta.data_ptr(), st))
                     L.check(lib.mg_ep_place(h, mb.idx.data_ptr(), Tm, mb.counts_all.data_ptr(), mb.cap,
                                             mb.plan_ws.data_ptr(), mb.recv_counts.data_ptr(), mb.recv_pad.data_ptr(),
                                             mb.dst.data_ptr(), st))
@@ -369,7 +381,7 @@ class EPMoELayer:
                                                   self.shared_out.data_ptr(), self._side.cuda_stream))
                     if sent is not None:
                         mb.stream.wait_event(sent)
-                    if self.push_return:
+                    if self.push_return and not self.copy_return:
                         L.check(lib.mg_ep_dispatch_back(h, xp, mb.dst.data_ptr(), Tm, mb.peer_recv,
                                                         mb.peer_dup if self.dedup else None, mb.peer_back, st))
                     elif self.dedup:
@@ -388,7 +400,14 @@ class EPMoELayer:
                 with torch.cuda.stream(mb.stream):
                     if prev is not None:
                         mb.stream.wait_event(prev)   # also orders the reuse of the de-quantised weights
-                    if self.push_return:
+                    if self.copy_return:
+                        mb.counts_event.synchronize()         # long done: the dispatch and a barrier were enqueued since
+                        L.check(lib.mg_ep_expert_ffn_copy_return(h, mb.own[0], mb.recv_pad.data_ptr(),
+                                                                 mb.recv_counts.data_ptr(), mb.cap, lay.packed.data_ptr(),
+                                                                 mb.h_buf.data_ptr(), mb.own[1], _ptr(self.deq),
+                                                                 mb.counts_host.data_ptr(), mb.peer_ret,
+                                                                 self.return_parts, mb.stream.cuda_stream))
+                    elif self.push_return:
                         L.check(lib.mg_ep_expert_ffn_return(h, mb.own[0], mb.recv_pad.data_ptr(),
                                                             mb.recv_counts.data_ptr(), mb.cap, lay.packed.data_ptr(),
                                                             mb.h_buf.data_ptr(), mb.own[1], _ptr(self.deq), mb.own[3],
@@ -407,7 +426,11 @@ class EPMoELayer:
                     if lay.Is:
                         mb.stream.wait_stream(self._side)
                     sh = self.shared_out.data_ptr() + mb.t0 * H2 if lay.Is else None
-                    if self.push_return:
+                    if self.copy_return:
+                        L.check(lib.mg_ep_combine_mirror(h, mb.own[4], mb.dst.data_ptr(), mb.delta.data_ptr(),
+                                                         mb.idx.data_ptr(), mb.w.data_ptr(), sh, mb.t1 - mb.t0,
+                                                         y.data_ptr() + mb.t0 * H2, mb.stream.cuda_stream))
+                    elif self.push_return:
                         L.check(lib.mg_ep_combine_slots(h, mb.own[4], mb.own[1], mb.dst.data_ptr(), mb.idx.data_ptr(),
                                                         mb.w.data_ptr(), sh, mb.t1 - mb.t0, y.data_ptr() + mb.t0 * H2,
                                                         mb.stream.cuda_stream))

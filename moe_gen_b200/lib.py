@@ -87,6 +87,9 @@ SIGNATURES = {
     "mg_ep_dispatch_back": [_vp, _vp, _vp, _i64, _P(_vp), _P(_vp), _P(_vp), _vp],
     "mg_ep_expert_ffn_return": [_vp, _vp, _vp, _vp, _i64, _vp, _vp, _vp, _vp, _vp, _P(_vp), _i32, _vp],
     "mg_ep_combine_slots": [_vp, _vp, _vp, _vp, _vp, _vp, _vp, _i64, _vp, _vp],
+    "mg_ep_expert_ffn_copy_return": [_vp, _vp, _vp, _vp, _i64, _vp, _vp, _vp, _vp, _vp, _vp, _i32, _vp],
+    "mg_ep_mirror_delta": [_vp, _vp, _vp, _vp],
+    "mg_ep_combine_mirror": [_vp, _vp, _vp, _vp, _vp, _vp, _vp, _i64, _vp, _vp],
     "mg_ep_clear_duplicates": [_vp, _vp, _i64, _vp],
     "mg_ep_fill_duplicates": [_vp, _vp, _vp, _i64, _vp],
     "mg_ep_combine": [_vp, _P(_vp), _vp, _vp, _vp, _vp, _i64, _vp, _vp],

@@ -132,6 +132,16 @@ def gpu_ep_worker(rank, world, port, spec, T_global, seed, result):
         y_pull = ep.forward(x)
         torch.cuda.synchronize()
         same = same and bool(torch.equal(y_pull.cpu().view(torch.int16), ys[0].view(torch.int16)))
+    ep.copy_return = True                                # the copy engines carry the results home
+    for dd in (False, True):
+        ep.dedup = dd
+        for _ in range(2):
+            y_copy = ep.forward(x)
+            torch.cuda.synchronize()
+            same = same and bool(torch.equal(y_copy.cpu().view(torch.int16), ys[0].view(torch.int16)))
+    yh_copy = ep.forward_host(x.cpu().pin_memory(), n_chunks=2)
+    same = same and bool(torch.equal(yh_copy.view(torch.int16), ys[0].view(torch.int16)))
+    ep.copy_return = False
     ep.push_return = True
     # host buffers in two parts per rank (last: it re-allocates the shared buffers for the part size)
     ep.dedup = True
@@ -139,6 +149,10 @@ def gpu_ep_worker(rank, world, port, spec, T_global, seed, result):
     same = same and bool(torch.equal(yh.view(torch.int16), ys[0].view(torch.int16)))
     # two pipelined micro-batches, each with its own stream, buffers and process group
     ep_m = EPMoELayer(layer, n_micro=2)
+    y_m = ep_m.forward(x)
+    torch.cuda.synchronize()
+    same = same and bool(torch.equal(y_m.cpu().view(torch.int16), ys[0].view(torch.int16)))
+    ep_m.copy_return = True
     y_m = ep_m.forward(x)
     torch.cuda.synchronize()
     same = same and bool(torch.equal(y_m.cpu().view(torch.int16), ys[0].view(torch.int16)))

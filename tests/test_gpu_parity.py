@@ -617,7 +617,7 @@ def test_bounded_wait_gives_up_and_reports(built_lib):
     assert O.rel_l2(y.cpu().float(), O.layer_forward(spec, x, W, gold_fp32=True)["y"]) <= TOL_LAYER
 
 
-@pytest.mark.parametrize("push", [False, True])
+@pytest.mark.parametrize("push", [False, True, "copy"])
 @pytest.mark.parametrize("dedup", [False, True])
 @pytest.mark.parametrize("n_ranks", [2, 4])
 def test_expert_parallel_ranks_emulated_on_one_gpu(built_lib, n_ranks, dedup, push):
@@ -669,7 +669,7 @@ def test_expert_parallel_ranks_emulated_on_one_gpu(built_lib, n_ranks, dedup, pu
         d = torch.empty(Tl, k, **i32); c = torch.empty(El, **i32); p = torch.empty(El + 1, **i32)
         L.check(lib.mg_ep_place(lay._h, idx[r].data_ptr(), Tl, counts_all.data_ptr(), cap, plan_ws[r].data_ptr(),
                                 c.data_ptr(), p.data_ptr(), d.data_ptr(), st))
-        if push:
+        if push is True:
             L.check(lib.mg_ep_dispatch_back(lay._h, xd[r * Tl:(r + 1) * Tl].data_ptr(), d.data_ptr(), Tl, peer_recv,
                                             peer_dup if dedup else None, peer_back, st))
         elif dedup:
@@ -701,7 +701,13 @@ def test_expert_parallel_ranks_emulated_on_one_gpu(built_lib, n_ranks, dedup, pu
                 assert torch.equal(got[rows].view(torch.int16), x[toks].view(torch.int16))
     for r, lay in enumerate(ranks):
         hb = torch.zeros(cap, spec.inter, dtype=torch.bfloat16, device=DEV)
-        if push:
+        if push == "copy":
+            # the copy engines carry every (expert, source rank) segment home; sizes from the counts on the host
+            counts_host = counts_all.cpu().contiguous()
+            L.check(lib.mg_ep_expert_ffn_copy_return(lay._h, recv[r].data_ptr(), rp[r].data_ptr(), rc[r].data_ptr(), cap,
+                                                     lay.packed.data_ptr(), hb.data_ptr(), outb[r].data_ptr(), None,
+                                                     counts_host.data_ptr(), peer_ret, 3, st))
+        elif push:
             L.check(lib.mg_ep_expert_ffn_return(lay._h, recv[r].data_ptr(), rp[r].data_ptr(), rc[r].data_ptr(), cap,
                                                 lay.packed.data_ptr(), hb.data_ptr(), outb[r].data_ptr(), None,
                                                 backt[r].data_ptr(), peer_ret, 3, st))
@@ -713,7 +719,17 @@ def test_expert_parallel_ranks_emulated_on_one_gpu(built_lib, n_ranks, dedup, pu
         xs = xd[r * Tl:(r + 1) * Tl]
         sh = lay.shared_ffn(xs)
         y = torch.empty(Tl, H, dtype=torch.bfloat16, device=DEV)
-        if push:
+        if push == "copy":
+            torch.cuda.synchronize()            # every owner's copies have landed
+            delta = torch.empty(E, **i32)
+            L.check(lib.mg_ep_mirror_delta(lay._h, counts_all.data_ptr(), delta.data_ptr(), st))
+            # the return buffer is this rank's rows in its own expert-sorted order: the single-GPU plan's offsets
+            own = torch.cumsum(counts_all[r].cpu().long(), 0) - counts_all[r].cpu().long()
+            base_r, *_ = ep_layout_reference(counts_all.cpu().numpy(), r, El, cap)
+            assert np.array_equal(delta.cpu().numpy(), own.numpy() - (base_r & 0xFFFFFF))
+            L.check(lib.mg_ep_combine_mirror(lay._h, rett[r].data_ptr(), dst[r].data_ptr(), delta.data_ptr(),
+                                             idx[r].data_ptr(), w[r].data_ptr(), sh.data_ptr(), Tl, y.data_ptr(), st))
+        elif push:
             torch.cuda.synchronize()            # every owner's pushes (on their return streams) have landed
             L.check(lib.mg_ep_combine_slots(lay._h, rett[r].data_ptr(), outb[r].data_ptr(), dst[r].data_ptr(), idx[r].data_ptr(),
                                             w[r].data_ptr(), sh.data_ptr(), Tl, y.data_ptr(), st))
