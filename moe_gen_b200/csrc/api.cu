@@ -485,7 +485,6 @@ static int ensure_return_stream(Handle* h) {
   return MG_OK;
 }
 
-// the output rows of local experts [lo, lo + n) are complete on `st`: send them home on the return stream
 // Copy-engine return of the local experts [lo, lo + n): for every expert and source rank one copy of that
 // rank's rows (contiguous in out_rows: ep_layout_kernel's order) to where the source rank's own expert-sorted
 // order puts them in its buffer.  All sizes come from the gathered counts in host memory.
@@ -524,6 +523,7 @@ static int copy_part(Handle* h, const ReturnHook* hook, const void* out_rows, in
   return MG_OK;
 }
 
+// the output rows of local experts [lo, lo + n) are complete on `st`: send them home beside what `st` does next
 static int push_part(Handle* h, const ReturnHook* hook, const void* out_rows, const int32_t* pad, int lo, int n,
                      int part, cudaStream_t st) {
   cudaEvent_t ev = h->ev_part[part % kDequantChunks];
