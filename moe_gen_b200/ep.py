@@ -51,6 +51,38 @@ def ep_layout_reference(counts_all: np.ndarray, rank: int, e_local: int, cap_row
     return send_base, recv_counts, recv_pad, over
 
 
+def ep_copy_plan_reference(counts_all: np.ndarray, rank: int, e_local: int, cap_rows: int):
+    """Host restatement of the copy-engine return as owner `rank` issues it (api.cu: copy_part), used by tests:
+    a list of (destination rank, first row in its return buffer, first row in this owner's out_rows, rows),
+    one entry per (local expert, source rank) that has rows.  The destination row is the first row of the
+    expert in the source rank's own expert-sorted, unpadded order."""
+    n, E = counts_all.shape
+    tot = counts_all.sum(axis=0)
+    seg = (tot[rank * e_local:(rank + 1) * e_local] + TILE_M - 1) // TILE_M * TILE_M
+    if seg.sum() > cap_rows:
+        return []
+    own = np.cumsum(counts_all, axis=1) - counts_all          # [s, e]: first row of expert e in rank s's order
+    plan, pad = [], 0
+    for j in range(e_local):
+        e = rank * e_local + j
+        row = pad
+        for s in range(n):
+            if counts_all[s, e] > 0:
+                plan.append((s, int(own[s, e]), int(row), int(counts_all[s, e])))
+            row += int(counts_all[s, e])
+        pad += int(seg[j])
+    return plan
+
+
+def ep_mirror_delta_reference(counts_all: np.ndarray, rank: int, e_local: int):
+    """Host restatement of ep_mirror_delta_kernel: per global expert, (first row of the expert in this rank's own
+    order) - (first row of this rank's rows of the expert in the owner's buffer)."""
+    n, E = counts_all.shape
+    own = np.cumsum(counts_all[rank]) - counts_all[rank]
+    base, *_ = ep_layout_reference(counts_all, rank, e_local, 1 << 40)
+    return own - (base & ((1 << PEER_SHIFT) - 1))
+
+
 class _MicroBatch:
     """Buffers, stream and process group of one token micro-batch of the expert-parallel forward."""
     pass

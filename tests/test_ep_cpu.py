@@ -6,7 +6,7 @@ import pytest
 import torch
 import torch.multiprocessing as mp
 
-from moe_gen_b200.ep import PEER_SHIFT, ep_layout_reference
+from moe_gen_b200.ep import PEER_SHIFT, ep_copy_plan_reference, ep_layout_reference, ep_mirror_delta_reference
 from oracle import moe_oracle as O
 from tests import ep_worker
 
@@ -39,6 +39,48 @@ def test_layout_tiles_every_owner_buffer_exactly(n, E):
                 assert (base & ((1 << PEER_SHIFT) - 1)) == pos
                 pos += counts[s, e]
             assert pos == recv_pad[j] + recv_counts[j] <= recv_pad[j + 1]
+
+
+@pytest.mark.parametrize("n,E,k", [(2, 8, 2), (4, 32, 4), (8, 64, 6)])
+def test_copy_return_rebuilds_every_rank_own_expert_sorted_order(n, E, k):
+    """The return through the copy engines, simulated on the host: every owner lays the picks it received out
+    as ep_layout says (expert-major, source ranks in order, tokens ascending), copies one segment per (expert,
+    source rank) as ep_copy_plan says, and every rank must end up with its own picks in stable expert-sorted
+    order; the per-expert offset turns a row of the owner's layout into that row."""
+    rng = np.random.default_rng(100 * n + E)
+    Tl, El, cap = 37, E // n, 1 << 20
+    idx = np.stack([np.stack([rng.choice(E, size=k, replace=False) for _ in range(Tl)]) for _ in range(n)])   # [n, Tl, k]
+    counts = np.stack([np.bincount(idx[s].ravel(), minlength=E) for s in range(n)]).astype(np.int64)
+    layouts = [ep_layout_reference(counts, s, El, cap) for s in range(n)]
+    mask = (1 << PEER_SHIFT) - 1
+    # dst[s][t, j]: owner << shift | row, ranks inside an expert's run in token order (the stable placement)
+    dst = np.zeros((n, Tl, k), dtype=np.int64)
+    out_rows = [dict() for _ in range(n)]                     # owner -> {row: (source rank, token, slot)}
+    for s in range(n):
+        seen = np.zeros(E, dtype=np.int64)
+        for t in range(Tl):
+            for j in range(k):
+                e = idx[s, t, j]
+                d = layouts[s][0][e] + seen[e]
+                seen[e] += 1
+                dst[s, t, j] = d
+                out_rows[d >> PEER_SHIFT][d & mask] = (s, t, j)
+    mirrors = [dict() for _ in range(n)]
+    for owner in range(n):
+        for dest, dest_row, src_row, rows in ep_copy_plan_reference(counts, owner, El, cap):
+            for i in range(rows):
+                assert dest_row + i not in mirrors[dest]
+                mirrors[dest][dest_row + i] = out_rows[owner][src_row + i]
+    for s in range(n):
+        assert sorted(mirrors[s]) == list(range(Tl * k))      # every row of the return buffer written once
+        order = sorted(((idx[s, t, j], t, j) for t in range(Tl) for j in range(k)))
+        assert [mirrors[s][r] for r in range(Tl * k)] == [(s, t, j) for _, t, j in order]
+        delta = ep_mirror_delta_reference(counts, s, El)
+        for t in range(Tl):
+            for j in range(k):
+                assert mirrors[s][(dst[s, t, j] & mask) + delta[idx[s, t, j]]] == (s, t, j)
+    # an owner whose buffer is too small copies nothing (its picks were dropped at the dispatch)
+    assert ep_copy_plan_reference(counts, 0, El, 128) == []
 
 
 def test_layout_flags_a_receive_buffer_that_is_too_small():
