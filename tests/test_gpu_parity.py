@@ -120,6 +120,12 @@ def test_topk_on_identical_logits_is_exact_at_full_gate_shapes(built_lib, name):
     # without the fix-up the staged calls give the raw tensor-core routing
     idx3, w3 = layer.route_topk(layer.gate_logits(x.to(DEV)))
     _route_equal(spec, idx3, w3, ridx, rw, logits, bias, exact_logits=False)
+    # ... and so does the fused call with the fix-up switched off
+    from moe_gen_b200 import lib as L
+    layer.set_option(L.OPT_ROUTE_FIXUP, 0)
+    idx4, w4, _, fix4 = layer.gate_route(x.to(DEV))
+    assert torch.equal(idx4, idx3) and torch.equal(w4, w3) and int(fix4[0]) == 0
+    layer.set_option(L.OPT_ROUTE_FIXUP, 1)
     _status_ok(layer)
 
 
