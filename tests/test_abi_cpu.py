@@ -30,6 +30,18 @@ def test_binding_covers_the_header(built_lib):
     assert declared == set(L.SIGNATURES), declared ^ set(L.SIGNATURES)
 
 
+def test_binding_argument_counts_match_the_header():
+    """Every prototype in the header has as many parameters as the ctypes table gives its function."""
+    src = open(os.path.join(ROOT, "include", "moegen_b200.h")).read()
+    src = re.sub(r"/\*.*?\*/", "", src, flags=re.S)
+    protos = dict(re.findall(r"\b(mg_[a-z0-9_]+)\s*\(([^;{]*?)\)\s*;", src, flags=re.S))
+    assert set(L.SIGNATURES) <= set(protos)
+    for name, argtypes in L.SIGNATURES.items():
+        params = protos[name].strip()
+        n = 0 if params in ("", "void") else params.count(",") + 1
+        assert n == len(argtypes), f"{name}: header declares {n} parameters, the binding passes {len(argtypes)}"
+
+
 def test_layer_desc_matches_header():
     src = open(os.path.join(ROOT, "include", "moegen_b200.h")).read()
     body = re.search(r"typedef struct mg_layer_desc \{(.*?)\} mg_layer_desc;", src, re.S).group(1)
